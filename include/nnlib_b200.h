@@ -1,0 +1,184 @@
+/*
+ * libnnlib_b200.so — C ABI of the B200 (sm_100a) multi-head attention path
+ * that stands behind NNlib.jl's
+ *     dot_product_attention / dot_product_attention_scores / make_causal_mask
+ * (NNlib.jl src/attention.jl:40-159).
+ *
+ * The boundary is plain C: pointers, sizes, strides, one params struct.  Every
+ * pointer in the struct is a DEVICE pointer of the CUDA context that is current
+ * on the calling thread; `stream` is a cudaStream_t / CUstream passed as
+ * void*.  All entry points enqueue work on that stream and return without
+ * synchronising; they never allocate device memory, never change the current
+ * device and never throw.  They are re-entrant: several host threads, one per
+ * device, may call them at once.
+ *
+ * Memory layout = the reference's column-major arrays:
+ *   q      (E , Lq , B)   element (e, i, b) at  q[e + q_stride_l*i + q_stride_b*b]
+ *   k      (E , Lkv, B)
+ *   v      (Ev, Lkv, B)
+ *   x      (Ev, Lq , B)   output
+ *   alpha  (Lkv, Lq, H, B) element (j, i, h, b) at alpha[j + Lkv*i + Lkv*Lq*h + alpha_stride_b*b]
+ *   lse    (Lq, H, B) float32, natural-log sum of exponentials of the scaled,
+ *          biased, masked logits of each query (−inf for a query with nothing
+ *          to attend to)
+ * with E = H*d, Ev = H*dv; head h owns features h*d .. h*d+d-1
+ * (split_heads is a pure reshape, src/attention.jl:158).
+ */
+#ifndef NNLIB_B200_H_
+#define NNLIB_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NNLIB_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+
+#if defined(__GNUC__)
+#define NNLIB_B200_API __attribute__((visibility("default")))
+#else
+#define NNLIB_B200_API
+#endif
+
+/* element types of q, k, v, x, alpha (one type for all five) and of bias */
+enum {
+  NNLIB_B200_F16 = 0,
+  NNLIB_B200_BF16 = 1,
+  NNLIB_B200_F32 = 2
+};
+
+/* return codes: 0 = enqueued, negative = nothing was enqueued */
+enum {
+  NNLIB_B200_OK = 0,
+  NNLIB_B200_INVALID_ARG = -1,       /* null pointer, bad size, bad stride, bad dtype, p outside [0,1) */
+  NNLIB_B200_UNSUPPORTED_SHAPE = -2, /* head dimension beyond what any kernel here handles */
+  NNLIB_B200_CUDA_ERROR = -3,        /* a CUDA runtime/driver call failed; see nnlib_b200_last_cuda_error */
+  NNLIB_B200_TIMEOUT = -4,           /* reported through *status by a kernel whose bounded wait ran out */
+  NNLIB_B200_WORKSPACE_TOO_SMALL = -5
+};
+
+/* which kernel family a call would use (nnlib_b200_attn_path) */
+enum {
+  NNLIB_B200_PATH_SIMT = 1,   /* CUDA-core kernel: any dtype, any d <= 1024, dv <= 512, any stride */
+  NNLIB_B200_PATH_UMMA = 2    /* tcgen05 + TMA kernel: f16/bf16, d = dv in {64,128}, 16-byte aligned rows */
+};
+
+typedef struct nnlib_b200_attn_params {
+  size_t struct_size;   /* = sizeof(nnlib_b200_attn_params); versions the struct */
+
+  int32_t dtype;        /* NNLIB_B200_F16 / BF16 / F32 */
+  int32_t bias_dtype;   /* element type of bias (ignored when bias == NULL) */
+
+  int64_t d;            /* qk features per head  (size(q,1) / nheads) */
+  int64_t dv;           /* v  features per head  (size(v,1) / nheads) */
+  int64_t H;            /* nheads */
+  int64_t Lq;           /* size(q,2) */
+  int64_t Lkv;          /* size(k,2) == size(v,2) */
+  int64_t B;            /* product of the batch dimensions */
+
+  const void* q;
+  const void* k;
+  const void* v;        /* unused by attn_stats / attn_scores */
+  void* x;              /* unused by attn_stats / attn_scores */
+
+  /* strides in ELEMENTS; the feature stride is 1.  0 means dense:
+     stride_l = H*d (or H*dv), stride_b = stride_l * L. */
+  int64_t q_stride_l, q_stride_b;
+  int64_t k_stride_l, k_stride_b;
+  int64_t v_stride_l, v_stride_b;
+  int64_t x_stride_l, x_stride_b;
+
+  /* bias added to the scaled logits before masking (apply_attn_bias,
+     src/attention.jl:129-131).  Element (j, i, h, b) at
+     bias[j*s[0] + i*s[1] + h*s[2] + b*s[3]]; a stride of 0 broadcasts. */
+  const void* bias;
+  int64_t bias_stride[4];
+
+  /* Bool mask, one byte per element, non-zero = attend (apply_attn_mask,
+     src/attention.jl:133-138).  Same indexing/broadcast rule as bias. */
+  const uint8_t* mask;
+  int64_t mask_stride[4];
+
+  int32_t causal;              /* 1: additionally keep only j <= i (make_causal_mask, src/attention.jl:149-153) */
+  int32_t nan_on_fully_masked; /* 1 (reference behaviour, src/softmax.jl:71-76): a query with nothing to
+                                  attend to yields NaN in x and alpha; 0: zeros */
+
+  float scale;                 /* multiplies q·k; 0 means 1/sqrt(d) (src/attention.jl:118) */
+
+  /* dropout on alpha (fdrop, src/attention.jl:126; keep-rule of src/dropout.jl:77-87):
+     element (j,i,h,b) is kept iff Philox4x32-10(key = seed, counter = position) > p*2^32,
+     kept entries are scaled by 1/(1-p).  p = 0 disables.  The position counter is
+     (j/4, r_lo, r_hi + offset_hi, offset_lo), word j%4, with
+     r = i + Lq*((h + rng_h0) + rng_H*(b + rng_b0)), so that a shard holding a sub-range of heads
+     or batches draws the same mask as the whole problem.  rng_H = 0 means H. */
+  float dropout_p;
+  uint64_t philox_seed;
+  uint64_t philox_offset;
+  int64_t rng_h0, rng_b0, rng_H;
+
+  float* lse;                  /* attn_fwd/attn_stats: written when non-NULL; attn_scores: read (required) */
+  int64_t lse_stride_b;        /* 0 = dense (Lq*H) */
+
+  void* alpha;                 /* attn_scores: written; attn_apply: read; attn_fwd: ignored */
+  int64_t alpha_stride_b;      /* 0 = dense (Lkv*Lq*H) */
+
+  int32_t* status;             /* optional device int32: set to NNLIB_B200_TIMEOUT by a kernel whose
+                                  bounded wait ran out (never happens in a correct run); else untouched */
+} nnlib_b200_attn_params;
+
+/* x = attention(q,k,v) and, when lse != NULL, lse.  Replaces the whole of
+   dot_product_attention's arithmetic (src/attention.jl:86-101,112-127 and the
+   softmax of src/softmax.jl:69-79) without materialising alpha. */
+NNLIB_B200_API int nnlib_b200_attn_fwd(const nnlib_b200_attn_params* p, void* stream);
+
+/* lse only: the first half of dot_product_attention_scores
+   (src/attention.jl:117-125) reduced to one float per query. */
+NNLIB_B200_API int nnlib_b200_attn_stats(const nnlib_b200_attn_params* p, void* stream);
+
+/* alpha (after dropout) from q, k, bias, mask and a previously computed lse:
+   the array dot_product_attention_scores returns (src/attention.jl:112-127). */
+NNLIB_B200_API int nnlib_b200_attn_scores(const nnlib_b200_attn_params* p, void* stream);
+
+/* x = V · alpha for an alpha the caller already holds, i.e. the second
+   batched_mul of _dot_product_attention (src/attention.jl:96-98).  Used when
+   fdrop is an arbitrary callable that was applied to alpha outside. */
+NNLIB_B200_API int nnlib_b200_attn_apply(const nnlib_b200_attn_params* p, void* stream);
+
+/* x AND alpha in one call: what dot_product_attention returns
+   (src/attention.jl:83).  lse goes to p->lse when non-NULL, else to
+   `workspace` (device memory, at least nnlib_b200_workspace_bytes(p)). */
+NNLIB_B200_API int nnlib_b200_attention(const nnlib_b200_attn_params* p, void* workspace,
+                         size_t workspace_bytes, void* stream);
+NNLIB_B200_API size_t nnlib_b200_workspace_bytes(const nnlib_b200_attn_params* p);
+
+/* make_causal_mask (src/attention.jl:149-153): fill an (L, L) byte matrix
+   with m[i + L*j] = (i <= j). */
+NNLIB_B200_API int nnlib_b200_causal_fill(uint8_t* mask, int64_t L, void* stream);
+
+/* *flag (device int32) := 1 if the (L, L) byte matrix equals make_causal_mask's
+   result, else 0.  Lets the caller swap a materialised causal mask for the
+   `causal` flag. */
+NNLIB_B200_API int nnlib_b200_causal_check(const uint8_t* mask, int64_t L, int32_t* flag, void* stream);
+
+/* NNLIB_B200_PATH_* that attn_fwd would take for p, or a negative error. */
+NNLIB_B200_API int nnlib_b200_attn_path(const nnlib_b200_attn_params* p);
+
+/* Synchronises `stream`, then returns NNLIB_B200_TIMEOUT if a kernel of this
+   library gave up on one of its bounded waits on the current device since the
+   previous call (the flag is cleared), else NNLIB_B200_OK.  Meant for tests
+   and for callers that want to turn a silent abort into an error. */
+NNLIB_B200_API int nnlib_b200_device_health(void* stream);
+
+NNLIB_B200_API const char* nnlib_b200_strerror(int code);
+NNLIB_B200_API int nnlib_b200_version(void);
+/* the cudaError_t of the last failed CUDA call on this thread (0 if none) */
+NNLIB_B200_API int nnlib_b200_last_cuda_error(void);
+/* number of kernels this library has launched since it was loaded */
+NNLIB_B200_API uint64_t nnlib_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNLIB_B200_H_ */

@@ -1,0 +1,18 @@
+"""B200-native multi-head attention behind NNlib.jl's API.
+
+``dot_product_attention``, ``dot_product_attention_scores`` and
+``make_causal_mask`` (NNlib.jl ``src/attention.jl``) for column-major CUDA
+tensors, computed by the hand-written sm_100a kernels of ``libnnlib_b200.so``
+(``csrc/``; C ABI in ``include/nnlib_b200.h``).  ``shard`` spreads the
+independent (batch, head) units of one call over the GPUs of a box.
+"""
+from .attention import (ArgumentError, CausalMask, LazyAttnScores, PhiloxDropout, device_health,
+                        dot_product_attention, dot_product_attention_scores, identity, make_causal_mask)
+from .layout import (as_column_major, is_column_major, jl_empty, jl_from_numpy, jl_reshape, jl_to_numpy,
+                     jl_zeros)
+
+__all__ = [
+    "ArgumentError", "CausalMask", "LazyAttnScores", "PhiloxDropout", "device_health",
+    "dot_product_attention", "dot_product_attention_scores", "identity", "make_causal_mask",
+    "as_column_major", "is_column_major", "jl_empty", "jl_from_numpy", "jl_reshape", "jl_to_numpy", "jl_zeros",
+]

@@ -1,0 +1,435 @@
+"""Host-side mirror of NNlib.jl's attention API for column-major CUDA tensors.
+
+Same names, argument meaning and error behaviour as the reference
+(``src/attention.jl``): ``dot_product_attention(q, k, v, [bias]; fdrop, mask,
+nheads)`` returns ``(x, α)``, ``dot_product_attention_scores(q, k, [bias];
+fdrop, mask)`` returns ``α``, ``make_causal_mask(x; dims)`` returns a Bool
+matrix.  This module is what the Julia ``CuArray`` methods in
+``julia/ext/NNlibCUDAExt/attention.jl`` do, statement for statement, with
+``ctypes`` in place of ``ccall``: validate, fill one params struct, call
+``libnnlib_b200.so`` on the current stream.  All arithmetic happens in that
+library; nothing here falls back to PyTorch ops or to the CPU.
+
+Tensors use the reference's shapes with column-major strides (see
+``layout.py``): ``q`` is ``(E, Lq, B...)``, ``α`` is ``(Lkv, Lq, H, B...)``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import weakref
+from typing import Callable, Optional
+
+import torch
+
+from . import _lib
+from .dropout import PhiloxDropout
+from .layout import is_column_major, jl_empty, jl_reshape
+
+__all__ = [
+    "ArgumentError",
+    "CausalMask",
+    "LazyAttnScores",
+    "PhiloxDropout",
+    "dot_product_attention",
+    "dot_product_attention_scores",
+    "make_causal_mask",
+    "identity",
+    "device_health",
+]
+
+
+class ArgumentError(ValueError):
+    """Julia's ``ArgumentError`` (thrown by ``src/attention.jl:42,55-78``)."""
+
+
+class CausalMask:
+    """Sentinel accepted as ``mask=``: the causal pattern ``kv <= query``
+    without materialising the ``(L, L)`` Bool matrix ``make_causal_mask``
+    returns (1 GiB at L = 32768)."""
+
+    def __repr__(self):
+        return "CausalMask()"
+
+
+def identity(x):
+    return x
+
+
+_DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+# data_ptr -> (version, L) of Bool matrices known to hold make_causal_mask's pattern
+_known_causal: dict = {}
+
+
+def _check(rc: int, where: str):
+    if rc == _lib.OK:
+        return
+    if rc == _lib.INVALID_ARG:
+        raise ArgumentError(f"{where}: {_lib.strerror(rc)}")
+    raise _lib.NNlibB200Error(rc, where)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_dense_cuda(name: str, t: torch.Tensor):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise TypeError(f"{name} lives on {t.device}: this method is defined for CUDA arrays only")
+    if t.dtype not in _DTYPES:
+        raise TypeError(f"{name} has eltype {t.dtype}; supported: Float16, BFloat16, Float32")
+    if not is_column_major(t):
+        raise TypeError(f"{name} is not a dense column-major array (strides {t.stride()} for size {tuple(t.shape)})")
+
+
+def _bcast_strides(name: str, t: torch.Tensor, full: tuple) -> list:
+    """Element strides of ``t`` against the ``(Lkv, Lq, H, B)`` scores, 0 where
+    ``t`` broadcasts.  Julia broadcasting: missing trailing dims count as 1."""
+    if t.ndim > 4:
+        raise ArgumentError(f"{name} has {t.ndim} dimensions; scores have 4")
+    out = []
+    for dim in range(4):
+        size = t.shape[dim] if dim < t.ndim else 1
+        if size == 1:
+            out.append(0)
+        elif size == full[dim]:
+            out.append(int(t.stride(dim)))
+        else:
+            raise ArgumentError(
+                f"{name} of size {tuple(t.shape)} does not broadcast to scores of size {full}")
+    return out
+
+
+class _Problem:
+    """Everything one call of the library needs, kept alive together."""
+
+    def __init__(self, q, k, v, bias, mask, nheads, dropout: Optional[PhiloxDropout], need_v: bool):
+        self.dev = q.device
+        self.dtype = q.dtype
+        E, Lq, B = q.shape
+        Lkv = k.shape[1]
+        H = nheads
+        self.E, self.Lq, self.B, self.Lkv, self.H = E, Lq, B, Lkv, H
+        self.d = E // H
+        self.q, self.k, self.v = q, k, v
+        self.Ev = v.shape[0] if need_v else E
+        self.dv = self.Ev // H
+        p = _lib.AttnParams()
+        p.dtype = _DTYPES[q.dtype]
+        p.d, p.dv, p.H, p.Lq, p.Lkv, p.B = self.d, self.dv, H, Lq, Lkv, B
+        p.q, p.k = q.data_ptr(), k.data_ptr()
+        if need_v:
+            p.v = v.data_ptr()
+        full = (Lkv, Lq, H, B)
+        self.keep = [q, k, v]
+        if bias is not None:
+            if not isinstance(bias, torch.Tensor) or not bias.is_cuda:
+                raise TypeError("bias must be a CUDA tensor")
+            if bias.dtype not in _DTYPES:
+                bias = bias.to(torch.float32)
+            st = _bcast_strides("bias", bias, full)
+            p.bias = bias.data_ptr()
+            p.bias_dtype = _DTYPES[bias.dtype]
+            p.bias_stride = (C.c_int64 * 4)(*st)
+            self.keep.append(bias)
+        causal = False
+        if isinstance(mask, CausalMask):
+            causal = True
+        elif mask is not None:
+            if not isinstance(mask, torch.Tensor) or not mask.is_cuda or mask.dtype != torch.bool:
+                raise TypeError("mask must be a Bool CUDA tensor, a CausalMask() or None")
+            if _is_causal_matrix(mask, Lq, Lkv):
+                causal = True
+            else:
+                st = _bcast_strides("mask", mask, full)
+                m8 = mask.view(torch.uint8)
+                p.mask = m8.data_ptr()
+                p.mask_stride = (C.c_int64 * 4)(*st)
+                self.keep.append(m8)
+        p.causal = 1 if causal else 0
+        p.nan_on_fully_masked = 1
+        p.scale = 0.0
+        if dropout is not None and dropout.p > 0.0:
+            p.dropout_p = dropout.p
+            p.philox_seed = dropout.seed & 0xFFFFFFFFFFFFFFFF
+            p.philox_offset = dropout.take_offset() & 0xFFFFFFFFFFFFFFFF
+        self.p = p
+
+    def alloc_lse(self):
+        self.lse = torch.empty((self.B, self.H, self.Lq), dtype=torch.float32, device=self.dev).permute(2, 1, 0)
+        self.p.lse = self.lse.data_ptr()
+        return self.lse
+
+    def alloc_x(self):
+        self.x = jl_empty((self.Ev, self.Lq, self.B), self.dtype, self.dev)
+        self.p.x = self.x.data_ptr()
+        return self.x
+
+    def alloc_alpha(self):
+        a = jl_empty((self.Lkv, self.Lq, self.H, self.B), self.dtype, self.dev)
+        self.p.alpha = a.data_ptr()
+        return a
+
+
+def _is_causal_matrix(mask: torch.Tensor, Lq: int, Lkv: int) -> bool:
+    """Is ``mask`` an ``(L, L)`` Bool matrix holding exactly ``kv <= query``?
+    Matrices made by :func:`make_causal_mask` are recognised by address; others
+    are checked once on the device and remembered until they are modified."""
+    if mask.ndim != 2 or Lq != Lkv or tuple(mask.shape) != (Lkv, Lq) or not is_column_major(mask):
+        return False
+    key = mask.data_ptr()
+    hit = _known_causal.get(key)
+    if hit is not None and hit[0] == mask._version and hit[1] == Lq:
+        return hit[2]
+    lib = _lib.load()
+    flag = torch.empty(1, dtype=torch.int32, device=mask.device)
+    with torch.cuda.device(mask.device):
+        _check(lib.nnlib_b200_causal_check(mask.view(torch.uint8).data_ptr(), Lq, flag.data_ptr(), _stream()),
+               "causal_check")
+    res = bool(flag.item())
+    _known_causal[key] = (mask._version, Lq, res)
+    if len(_known_causal) > 64:
+        _known_causal.pop(next(iter(_known_causal)))
+    return res
+
+
+class LazyAttnScores:
+    """The ``α`` of ``(x, α) = dot_product_attention(...)``, materialised on
+    first use.  The fused kernel keeps one log-sum-exp per query; the
+    ``(Lkv, Lq, H, B...)`` array is rebuilt from it (same dropout mask) by the
+    scores kernel only if somebody looks at it.  ``x, _ = ...`` never pays for
+    it."""
+
+    def __init__(self, problem: _Problem, shape: tuple):
+        self._problem = problem
+        self._shape = tuple(shape)
+        self._value: Optional[torch.Tensor] = None
+
+    # -- array-like surface ------------------------------------------------
+    @property
+    def shape(self):
+        return torch.Size(self._shape)
+
+    def size(self, dim=None):
+        return self.shape if dim is None else self._shape[dim]
+
+    @property
+    def ndim(self):
+        return len(self._shape)
+
+    @property
+    def dtype(self):
+        return self._problem.dtype
+
+    @property
+    def device(self):
+        return self._problem.dev
+
+    @property
+    def is_materialized(self) -> bool:
+        return self._value is not None
+
+    def reshape(self, *shape):
+        """Column-major reshape that stays lazy (the N-d wrapper of the
+        reference reshapes α, ``src/attention.jl:48``)."""
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+            shape = tuple(shape[0])
+        n = math.prod(self._shape)
+        if math.prod(shape) != n:
+            raise ValueError(f"cannot reshape scores of size {self._shape} to {shape}")
+        out = LazyAttnScores(self._problem, shape)
+        out._base = self
+        return out
+
+    def materialize(self) -> torch.Tensor:
+        base = getattr(self, "_base", None)
+        if base is not None:
+            return jl_reshape(base.materialize(), self._shape)
+        if self._value is None:
+            pr = self._problem
+            alpha = pr.alloc_alpha()
+            if pr.Lkv > 0 and pr.Lq > 0 and pr.B > 0:
+                with torch.cuda.device(pr.dev):
+                    _check(_lib.load().nnlib_b200_attn_scores(C.byref(pr.p), _stream()), "attn_scores")
+            self._value = jl_reshape(alpha, self._shape)
+        return self._value
+
+    def __array__(self, dtype=None):
+        t = self.materialize()
+        if t.dtype in (torch.bfloat16, torch.float16):
+            t = t.float()
+        a = t.cpu().numpy()
+        return a if dtype is None else a.astype(dtype)
+
+    def __getitem__(self, idx):
+        return self.materialize()[idx]
+
+    def __getattr__(self, name):
+        # anything else (sum, float, cpu, ...) acts on the materialised tensor
+        if name.startswith("_"):
+            raise AttributeError(name)
+        return getattr(self.materialize(), name)
+
+    def __repr__(self):
+        state = "materialized" if self.is_materialized else "lazy"
+        return f"LazyAttnScores(size={self._shape}, dtype={self.dtype}, {state})"
+
+
+def _validate_3d(q, k, v, nheads):
+    """The four checks of ``src/attention.jl:55-78``, same order and wording."""
+    if any(t.shape[0] % nheads != 0 for t in (q, k, v)):
+        raise ArgumentError(
+            "First dimension in query, key and value must be divisible by `nheads`.\n"
+            f"Instead:\n- size(q): {tuple(q.shape)}\n- size(k): {tuple(k.shape)}\n"
+            f"- size(v): {tuple(v.shape)}\n- nheads: {nheads}")
+    if not (q.shape[2] == k.shape[2] == v.shape[2]):
+        raise ArgumentError(
+            "Batch dimensions have to be the same. Instead:\n"
+            f"- size(q): {tuple(q.shape)}\n- size(k): {tuple(k.shape)}\n- size(v): {tuple(v.shape)}")
+    if q.shape[0] != k.shape[0]:
+        raise ArgumentError(
+            "First dimension in query and key has to be the same. Instead:\n"
+            f"- size(q): {tuple(q.shape)}\n- size(k): {tuple(k.shape)}")
+    if k.shape[1] != v.shape[1]:
+        raise ArgumentError(
+            "Second dimension in key and value has to be the same. Instead:\n"
+            f"- size(k): {tuple(k.shape)}\n- size(v): {tuple(v.shape)}")
+
+
+def dot_product_attention(q, k, v, bias=None, *, fdrop: Callable = identity, mask=None, nheads: int = 1):
+    """Multi-head dot-product attention (``src/attention.jl:40-84``).
+
+    ``q``: ``(qk_dim, q_len, batch...)``, ``k``: ``(qk_dim, kv_len, batch...)``,
+    ``v``: ``(v_dim, kv_len, batch...)``, column-major CUDA tensors of one
+    element type.  Returns ``(x, α)`` with ``x``: ``(v_dim, q_len, batch...)``
+    and ``α``: ``(kv_len, q_len, nheads, batch...)`` — the scores *after*
+    ``fdrop``, from which ``x`` was computed.
+
+    ``fdrop``: ``identity`` or a :class:`PhiloxDropout` run fused (α is then a
+    :class:`LazyAttnScores`); any other callable gets the materialised scores,
+    and ``x`` is computed from what it returns.  ``mask``: Bool tensor
+    broadcastable to the scores (true = attend), the result of
+    :func:`make_causal_mask`, or ``CausalMask()``.
+    """
+    for name, t in (("query", q), ("key", k), ("value", v)):
+        _require_dense_cuda(name, t)
+    if not (q.ndim == k.ndim == v.ndim):
+        raise TypeError("query, key and value must have the same number of dimensions")
+    if q.ndim < 2:
+        raise TypeError("query, key and value need at least (features, length) dimensions")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("query, key and value must share one element type")
+    batch_size = tuple(q.shape[2:])
+    if q.ndim != 3:
+        # N-d wrapper, src/attention.jl:40-50: flatten the batch dims, restore them on both outputs.
+        if not (batch_size == tuple(k.shape[2:]) == tuple(v.shape[2:])):
+            raise ArgumentError("Batch dimensions have to be the same.")
+        q, k, v = (jl_reshape(t, (t.shape[0], t.shape[1], -1)) for t in (q, k, v))
+    nheads = int(nheads)
+    _validate_3d(q, k, v, nheads)
+
+    if fdrop is None or fdrop is identity:
+        x, alpha = _fused(q, k, v, bias, mask, nheads, None)
+    elif isinstance(fdrop, PhiloxDropout):
+        x, alpha = _fused(q, k, v, bias, mask, nheads, fdrop)
+    else:
+        x, alpha = _unfused(q, k, v, bias, mask, nheads, fdrop)
+
+    if len(batch_size) != 1:
+        x = jl_reshape(x, tuple(x.shape[:2]) + batch_size)
+        alpha = alpha.reshape(tuple(alpha.shape[:3]) + batch_size) if isinstance(alpha, LazyAttnScores) \
+            else jl_reshape(alpha, tuple(alpha.shape[:3]) + batch_size)
+    return x, alpha
+
+
+def _fused(q, k, v, bias, mask, nheads, dropout):
+    pr = _Problem(q, k, v, bias, mask, nheads, dropout, need_v=True)
+    x = pr.alloc_x()
+    pr.alloc_lse()
+    if pr.Lq > 0 and pr.B > 0:
+        with torch.cuda.device(pr.dev):
+            _check(_lib.load().nnlib_b200_attn_fwd(C.byref(pr.p), _stream()), "attn_fwd")
+    return x, LazyAttnScores(pr, (pr.Lkv, pr.Lq, pr.H, pr.B))
+
+
+def _unfused(q, k, v, bias, mask, nheads, fdrop):
+    """``fdrop`` is an opaque callable: materialise α, let the caller's
+    function transform it, then x = V·α′ (``src/attention.jl:91-98``)."""
+    pr = _Problem(q, k, v, bias, mask, nheads, None, need_v=True)
+    lib = _lib.load()
+    x = pr.alloc_x()
+    pr.alloc_lse()
+    alpha = pr.alloc_alpha()
+    with torch.cuda.device(pr.dev):
+        if pr.Lq > 0 and pr.B > 0:
+            _check(lib.nnlib_b200_attn_stats(C.byref(pr.p), _stream()), "attn_stats")
+            _check(lib.nnlib_b200_attn_scores(C.byref(pr.p), _stream()), "attn_scores")
+        alpha2 = fdrop(alpha)
+        if not isinstance(alpha2, torch.Tensor) or tuple(alpha2.shape) != tuple(alpha.shape):
+            raise ArgumentError("fdrop must return an array of the scores' size")
+        if alpha2.dtype != pr.dtype or not is_column_major(alpha2) or alpha2.device != pr.dev:
+            fixed = jl_empty(alpha.shape, pr.dtype, pr.dev)
+            fixed.copy_(alpha2)
+            alpha2 = fixed
+        pr.p.alpha = alpha2.data_ptr()
+        if pr.Lq > 0 and pr.B > 0:
+            _check(lib.nnlib_b200_attn_apply(C.byref(pr.p), _stream()), "attn_apply")
+    return x, alpha2
+
+
+def dot_product_attention_scores(q, k, bias=None, *, fdrop: Callable = identity, mask=None):
+    """Attention scores only (``src/attention.jl:112-127``).  ``q``:
+    ``(d, nheads, q_len, batch)``, ``k``: ``(d, nheads, kv_len, batch)`` of one
+    element type → ``α``: ``(kv_len, q_len, nheads, batch)``."""
+    for name, t in (("query", q), ("key", k)):
+        _require_dense_cuda(name, t)
+    if q.ndim != 4 or k.ndim != 4:
+        raise TypeError("dot_product_attention_scores expects 4-d (d, nheads, len, batch) arrays")
+    if q.dtype != k.dtype:
+        raise TypeError("query and key must share one element type")
+    d, H, Lq, B = q.shape
+    if tuple(k.shape[:2]) != (d, H) or k.shape[3] != B:
+        raise ArgumentError(f"query of size {tuple(q.shape)} and key of size {tuple(k.shape)} do not match")
+    q3 = jl_reshape(q, (d * H, Lq, B))
+    k3 = jl_reshape(k, (d * H, k.shape[2], B))
+    dropout = fdrop if isinstance(fdrop, PhiloxDropout) else None
+    pr = _Problem(q3, k3, k3, bias, mask, H, dropout, need_v=False)
+    pr.alloc_lse()
+    alpha = pr.alloc_alpha()
+    if pr.Lq > 0 and pr.B > 0 and pr.Lkv > 0:
+        lib = _lib.load()
+        with torch.cuda.device(pr.dev):
+            _check(lib.nnlib_b200_attn_stats(C.byref(pr.p), _stream()), "attn_stats")
+            _check(lib.nnlib_b200_attn_scores(C.byref(pr.p), _stream()), "attn_scores")
+    if dropout is None and fdrop is not None and fdrop is not identity:
+        alpha = fdrop(alpha)
+    return alpha
+
+
+def make_causal_mask(x: torch.Tensor, dims: int = 2) -> torch.Tensor:
+    """Bool square matrix ``m`` of side ``size(x, dims)`` with ``m[i, j] = i <= j``
+    (``src/attention.jl:149-153``; ``dims`` is 1-based like the reference's),
+    on the device of ``x``.  Passing it as ``mask=`` selects the kernels' causal
+    mode; the matrix itself is never read by them."""
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        raise TypeError("make_causal_mask: this method is defined for CUDA arrays only")
+    n = int(x.shape[dims - 1])
+    m = jl_empty((n, n), torch.bool, x.device)
+    with torch.cuda.device(x.device):
+        _check(_lib.load().nnlib_b200_causal_fill(m.view(torch.uint8).data_ptr(), n, _stream()), "causal_fill")
+    _known_causal[m.data_ptr()] = (m._version, n, True)
+    weakref.finalize(m, _known_causal.pop, m.data_ptr(), None)
+    return m
+
+
+def device_health(device=None) -> None:
+    """Synchronise and raise if a kernel of the library gave up on a bounded
+    wait since the last call (``nnlib_b200_device_health``)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        rc = _lib.load().nnlib_b200_device_health(_stream())
+    if rc != _lib.OK:
+        raise _lib.NNlibB200Error(rc, "device_health")

@@ -1,0 +1,225 @@
+// The C ABI of libnnlib_b200.so (include/nnlib_b200.h): argument checking,
+// defaults, kernel selection.  No exceptions leave this file, no device memory
+// is allocated, nothing synchronises except nnlib_b200_device_health.
+#include <atomic>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+#include "launchers.h"
+
+namespace nb200 {
+
+static std::atomic<unsigned long long> g_launches{0};
+static thread_local int t_last_cuda_error = 0;
+
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+void set_last_cuda_error(cudaError_t e) { t_last_cuda_error = (int)e; }
+
+namespace {
+
+bool force_simt() {
+  static const bool v = [] {
+    const char* e = std::getenv("NNLIB_B200_FORCE_SIMT");
+    return e && e[0] && e[0] != '0';
+  }();
+  return v;
+}
+
+enum Need : unsigned {
+  NEED_V = 1u,      // v and x
+  NEED_LSE_IN = 2u, // lse must be given (read)
+  NEED_ALPHA = 4u,  // alpha must be given
+  NEED_QK = 8u      // q and k
+};
+
+int dtype_ok(int dt) { return dt == NNLIB_B200_F16 || dt == NNLIB_B200_BF16 || dt == NNLIB_B200_F32; }
+
+// Validate the caller's struct and turn it into the kernels' argument block.
+int resolve(const nnlib_b200_attn_params* p, unsigned need, AttnArgs* out) {
+  if (!p || p->struct_size != sizeof(nnlib_b200_attn_params)) return NNLIB_B200_INVALID_ARG;
+  if (!dtype_ok(p->dtype)) return NNLIB_B200_INVALID_ARG;
+  if (p->d < 1 || p->H < 1 || p->Lq < 0 || p->Lkv < 0 || p->B < 0) return NNLIB_B200_INVALID_ARG;
+  if ((need & NEED_V) && p->dv < 1) return NNLIB_B200_INVALID_ARG;
+  if (p->Lq > 0x7fffffffLL || p->Lkv > 0x7fffffffLL || p->H > 0x7fffffffLL || p->B > 0x7fffffffLL ||
+      p->d > 0x7fffffffLL || p->dv > 0x7fffffffLL)
+    return NNLIB_B200_INVALID_ARG;
+  const bool empty = (p->Lq == 0 || p->B == 0);
+  AttnArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.d = (int)p->d; a.dv = (int)p->dv; a.H = (int)p->H; a.Lq = (int)p->Lq; a.Lkv = (int)p->Lkv; a.B = (int)p->B;
+  const long long E = p->H * p->d, Ev = p->H * p->dv;
+  a.q = p->q; a.k = p->k; a.v = p->v; a.x = p->x;
+  a.q_sl = p->q_stride_l ? p->q_stride_l : E;   a.q_sb = p->q_stride_b ? p->q_stride_b : a.q_sl * p->Lq;
+  a.k_sl = p->k_stride_l ? p->k_stride_l : E;   a.k_sb = p->k_stride_b ? p->k_stride_b : a.k_sl * p->Lkv;
+  a.v_sl = p->v_stride_l ? p->v_stride_l : Ev;  a.v_sb = p->v_stride_b ? p->v_stride_b : a.v_sl * p->Lkv;
+  a.x_sl = p->x_stride_l ? p->x_stride_l : Ev;  a.x_sb = p->x_stride_b ? p->x_stride_b : a.x_sl * p->Lq;
+  if (a.q_sl < E || a.k_sl < E || a.q_sb < 0 || a.k_sb < 0) return NNLIB_B200_INVALID_ARG;
+  if ((need & NEED_V) && (a.v_sl < Ev || a.x_sl < Ev || a.v_sb < 0 || a.x_sb < 0)) return NNLIB_B200_INVALID_ARG;
+  if (!empty) {
+    if ((need & NEED_QK) && (!p->q || (p->Lkv > 0 && !p->k))) return NNLIB_B200_INVALID_ARG;
+    if ((need & NEED_V) && (!p->x || (p->Lkv > 0 && !p->v))) return NNLIB_B200_INVALID_ARG;
+    if ((need & NEED_LSE_IN) && !p->lse) return NNLIB_B200_INVALID_ARG;
+    if ((need & NEED_ALPHA) && p->Lkv > 0 && !p->alpha) return NNLIB_B200_INVALID_ARG;
+  }
+  a.bias = p->bias;
+  a.bias_dtype = p->bias_dtype;
+  if (p->bias && !dtype_ok(p->bias_dtype)) return NNLIB_B200_INVALID_ARG;
+  a.mask = p->mask;
+  for (int i = 0; i < 4; ++i) {
+    if (p->bias_stride[i] < 0 || p->mask_stride[i] < 0) return NNLIB_B200_INVALID_ARG;
+    a.bias_s[i] = p->bias_stride[i];
+    a.mask_s[i] = p->mask_stride[i];
+  }
+  a.causal = p->causal ? 1 : 0;
+  a.nan_fm = p->nan_on_fully_masked ? 1 : 0;
+  if (!(p->scale >= 0.f) || std::isinf(p->scale)) return NNLIB_B200_INVALID_ARG;
+  a.scale = (p->scale == 0.f) ? (float)(1.0 / std::sqrt((double)p->d)) : p->scale;
+  if (!(p->dropout_p >= 0.f && p->dropout_p < 1.f)) return NNLIB_B200_INVALID_ARG;
+  a.dropout_p = p->dropout_p;
+  a.inv_keep = (float)(1.0 / (1.0 - (double)p->dropout_p));
+  {
+    const double th = std::floor((double)p->dropout_p * 4294967296.0);
+    a.drop_thresh = (unsigned int)(th > 4294967295.0 ? 4294967295.0 : th);
+  }
+  a.key0 = (unsigned int)(p->philox_seed & 0xffffffffull);
+  a.key1 = (unsigned int)(p->philox_seed >> 32);
+  a.off_lo = (unsigned int)(p->philox_offset & 0xffffffffull);
+  a.off_hi = (unsigned int)(p->philox_offset >> 32);
+  if (p->rng_h0 < 0 || p->rng_b0 < 0 || p->rng_H < 0) return NNLIB_B200_INVALID_ARG;
+  a.rng_h0 = p->rng_h0; a.rng_b0 = p->rng_b0; a.rng_H = p->rng_H ? p->rng_H : p->H;
+  a.lse = p->lse;
+  a.lse_sb = p->lse_stride_b ? p->lse_stride_b : p->Lq * p->H;
+  a.alpha = p->alpha;
+  a.alpha_sb = p->alpha_stride_b ? p->alpha_stride_b : p->Lkv * p->Lq * p->H;
+  if (a.lse_sb < p->Lq * p->H || a.alpha_sb < p->Lkv * p->Lq * p->H) return NNLIB_B200_INVALID_ARG;
+  a.status = p->status;
+  *out = a;
+  return NNLIB_B200_OK;
+}
+
+int finish(cudaError_t e) {
+  if (e == cudaSuccess) return NNLIB_B200_OK;
+  set_last_cuda_error(e);
+  return NNLIB_B200_CUDA_ERROR;
+}
+
+bool use_umma(const AttnArgs& a, int dtype, bool need_v) {
+  return !force_simt() && umma_supports(a, dtype, need_v);
+}
+
+}  // namespace
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" {
+
+int nnlib_b200_attn_fwd(const nnlib_b200_attn_params* p, void* stream) {
+  AttnArgs a;
+  const int rc = resolve(p, NEED_QK | NEED_V, &a);
+  if (rc) return rc;
+  if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (use_umma(a, p->dtype, true)) return finish(umma_fwd(a, p->dtype, false, st));
+  if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  return finish(simt_fwd(a, p->dtype, st));
+}
+
+int nnlib_b200_attn_stats(const nnlib_b200_attn_params* p, void* stream) {
+  AttnArgs a;
+  const int rc = resolve(p, NEED_QK, &a);
+  if (rc) return rc;
+  if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
+  if (!a.lse) return NNLIB_B200_INVALID_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (use_umma(a, p->dtype, false)) return finish(umma_fwd(a, p->dtype, true, st));
+  if (!simt_supports(a.d, 1)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  return finish(simt_stats(a, p->dtype, st));
+}
+
+int nnlib_b200_attn_scores(const nnlib_b200_attn_params* p, void* stream) {
+  AttnArgs a;
+  const int rc = resolve(p, NEED_QK | NEED_LSE_IN | NEED_ALPHA, &a);
+  if (rc) return rc;
+  if (a.Lq == 0 || a.B == 0 || a.Lkv == 0) return NNLIB_B200_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (use_umma(a, p->dtype, false)) return finish(umma_scores(a, p->dtype, st));
+  if (!simt_supports(a.d, 1)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  return finish(simt_scores(a, p->dtype, st));
+}
+
+int nnlib_b200_attn_apply(const nnlib_b200_attn_params* p, void* stream) {
+  AttnArgs a;
+  const int rc = resolve(p, NEED_V | NEED_ALPHA, &a);
+  if (rc) return rc;
+  if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
+  if (!simt_supports(1, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  return finish(simt_apply(a, p->dtype, (cudaStream_t)stream));
+}
+
+size_t nnlib_b200_workspace_bytes(const nnlib_b200_attn_params* p) {
+  if (!p || p->struct_size != sizeof(nnlib_b200_attn_params)) return 0;
+  if (p->lse) return 0;
+  if (p->Lq < 0 || p->H < 0 || p->B < 0) return 0;
+  return (size_t)p->Lq * (size_t)p->H * (size_t)p->B * sizeof(float);
+}
+
+int nnlib_b200_attention(const nnlib_b200_attn_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!p || p->struct_size != sizeof(nnlib_b200_attn_params)) return NNLIB_B200_INVALID_ARG;
+  nnlib_b200_attn_params q = *p;
+  if (!q.lse) {
+    const size_t need = nnlib_b200_workspace_bytes(p);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return NNLIB_B200_WORKSPACE_TOO_SMALL;
+    q.lse = static_cast<float*>(workspace);
+    q.lse_stride_b = 0;
+  }
+  int rc = nnlib_b200_attn_fwd(&q, stream);
+  if (rc) return rc;
+  return nnlib_b200_attn_scores(&q, stream);
+}
+
+int nnlib_b200_causal_fill(uint8_t* mask, int64_t L, void* stream) {
+  if (L < 0 || (L > 0 && !mask)) return NNLIB_B200_INVALID_ARG;
+  return finish(causal_fill(mask, L, (cudaStream_t)stream));
+}
+
+int nnlib_b200_causal_check(const uint8_t* mask, int64_t L, int32_t* flag, void* stream) {
+  if (L < 0 || (L > 0 && !mask) || !flag) return NNLIB_B200_INVALID_ARG;
+  return finish(causal_check(mask, L, flag, (cudaStream_t)stream));
+}
+
+int nnlib_b200_attn_path(const nnlib_b200_attn_params* p) {
+  AttnArgs a;
+  const int rc = resolve(p, NEED_QK | NEED_V, &a);
+  if (rc) return rc;
+  if (use_umma(a, p->dtype, true)) return NNLIB_B200_PATH_UMMA;
+  if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  return NNLIB_B200_PATH_SIMT;
+}
+
+int nnlib_b200_device_health(void* stream) {
+  int v = 0;
+  const cudaError_t e = umma_take_abort(&v, (cudaStream_t)stream);
+  if (e != cudaSuccess) return finish(e);
+  return v ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
+}
+
+const char* nnlib_b200_strerror(int code) {
+  switch (code) {
+    case NNLIB_B200_OK: return "ok";
+    case NNLIB_B200_INVALID_ARG: return "invalid argument (null pointer, size, stride, dtype or dropout probability)";
+    case NNLIB_B200_UNSUPPORTED_SHAPE: return "head dimension not supported by any kernel of this library";
+    case NNLIB_B200_CUDA_ERROR: return "a CUDA call failed (see nnlib_b200_last_cuda_error)";
+    case NNLIB_B200_TIMEOUT: return "a kernel gave up on a bounded wait; results of that launch are invalid";
+    case NNLIB_B200_WORKSPACE_TOO_SMALL: return "workspace smaller than nnlib_b200_workspace_bytes";
+    default: return "unknown nnlib_b200 status";
+  }
+}
+
+int nnlib_b200_version(void) { return NNLIB_B200_VERSION; }
+int nnlib_b200_last_cuda_error(void) { return t_last_cuda_error; }
+uint64_t nnlib_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

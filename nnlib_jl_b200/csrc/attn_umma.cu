@@ -1,0 +1,825 @@
+// Fused attention forward on the sm_100a tensor cores.
+//
+// One CTA owns 256 consecutive queries (two 128-row tiles) of one (head,
+// batch) unit and walks over the keys/values in 128-row tiles:
+//
+//   warp 0      TMA producer: Q once, then a ring of K and V tiles
+//   warp 1      issues every tcgen05.mma:  S_t = Q_t K_j^T   (smem x smem -> TMEM)
+//                                          O_t += P_t V_j    (TMEM x smem -> TMEM)
+//   warp 2      allocates / frees the 512 TMEM columns
+//   warps 4-7   softmax of query tile 0 (thread r owns query row r: no shuffles)
+//   warps 8-11  softmax of query tile 1
+//
+// TMEM columns: S_0 [0,128) S_1 [128,256) O_0 [256,384) O_1 [384,512); the
+// half-precision probabilities P_t overwrite the first 64 columns of S_t.
+// The two query tiles ping-pong: while the softmax warps of one tile run
+// exponentials, the tensor core works on the other tile's products.
+//
+// Softmax is the online form of the reference's max-subtracted softmax
+// (NNlib.jl src/softmax.jl:69-79) in base 2: logits are scaled by
+// scale*log2(e), bias (src/attention.jl:129-131) and masks (:133-138) are
+// applied in registers, the running maximum is only raised when it grows by
+// more than 8 (so the O accumulator is rarely rescaled), dropout
+// (src/dropout.jl:77-87) multiplies P after the row sum was taken, and
+// x = O / l / (1-p) is written straight into the (Ev, Lq, B) array.
+// Per-query log-sum-exp is stored so that the scores can be rebuilt later.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "launchers.h"
+#include "umma.cuh"
+
+namespace nb200 {
+
+__device__ int g_umma_abort = 0;  // sticky: a bounded wait ran out somewhere
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;               // queries per tile
+constexpr int kBN = 128;               // keys per tile
+constexpr int kQT = 2;                 // query tiles per CTA
+constexpr int kThreads = 384;
+constexpr int kChunkBytes = 128 * 128; // 128 rows x 64 halves: one TMA box
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleGap = 8.0f;    // raise the running max only when it grew by > 2^8
+constexpr unsigned long long kDrainNs = 20ull * 1000 * 1000;  // 20 ms for in-flight copies on abort
+
+template <int D>
+struct Cfg {
+  static constexpr int kChunks = D / 64;
+  static constexpr int kTileBytes = kChunks * kChunkBytes;
+  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + kQT * kTileBytes;
+  static constexpr int kVOff = kKOff + kStages * kTileBytes;
+  static constexpr int kBarOff = kVOff + kStages * kTileBytes;
+  static constexpr int kSmemBytes = kBarOff + 512 + 1024;  // barrier block + alignment slack
+};
+
+struct Barriers {
+  uint64_t q_full[kQT];
+  uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
+  uint64_t s_full[kQT], p_full[kQT], o_full[kQT];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <int D, bool BF16, bool EXTRAS, bool STATS>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qblocks) {
+  using C = Cfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kBarOff);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // block -> (unit, query block); within a unit the longest causal rows come first
+  const int unit = blockIdx.x / n_qblocks;
+  const int qb = n_qblocks - 1 - (blockIdx.x % n_qblocks);
+  const int h = unit % a.H, b = unit / a.H;
+  const int q0 = qb * (kQT * kBM);
+
+  int n_t[kQT];
+#pragma unroll
+  for (int t = 0; t < kQT; ++t) {
+    const int qs = q0 + t * kBM;
+    int kv_end = a.Lkv;
+    if (a.causal) kv_end = min(kv_end, qs + kBM);
+    n_t[t] = (qs < a.Lq) ? (kv_end + kBN - 1) / kBN : 0;
+  }
+  const int n_kv = max(n_t[0], n_t[1]);
+
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < kQT; ++t) {
+      mbar_init(&bars->q_full[t], 1);
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 4);
+      mbar_init(&bars->o_full[t], 1);
+    }
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+    }
+    bars->abort_flag = *reinterpret_cast<volatile int*>(&g_umma_abort);
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const bool start_ok = (*abort_flag == 0);
+
+  const uint32_t q_smem = smem_u32(smem + C::kQOff);
+  const uint32_t k_smem = smem_u32(smem + C::kKOff);
+  const uint32_t v_smem = smem_u32(smem + C::kVOff);
+
+  // the softmax threads hold a whole 128-wide score row in registers: move the
+  // register budget from the copy / issue warps to them
+  if (warp < 4) {
+  setmaxnreg_dec<40>();
+  if (start_ok && warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
+      if (!STATS) prefetch_tensormap(&tm_v);
+      for (int t = 0; t < kQT; ++t) {
+        if (n_t[t] == 0) continue;
+        mbar_arrive_expect_tx(&bars->q_full[t], C::kTileBytes);
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_3d(smem + C::kQOff + t * C::kTileBytes + c * kChunkBytes, &tm_q, &bars->q_full[t],
+                      h * D + c * 64, q0 + t * kBM, b);
+      }
+      bool ok = true;
+      int j = 0;
+      for (; j < n_kv && ok; ++j) {
+        const int s = j % C::kStages;
+        if (j >= C::kStages) ok = mbar_wait(&bars->k_empty[s], ((j / C::kStages) - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars->k_full[s], C::kTileBytes);
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_3d(smem + C::kKOff + s * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->k_full[s],
+                      h * D + c * 64, j * kBN, b);
+        if (!STATS) {
+          if (j >= C::kStages) ok = mbar_wait(&bars->v_empty[s], ((j / C::kStages) - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars->v_full[s], C::kTileBytes);
+          for (int c = 0; c < C::kChunks; ++c)
+            tma_load_3d(smem + C::kVOff + s * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full[s],
+                        h * D + c * 64, j * kBN, b);
+        }
+      }
+      if (*abort_flag) {
+        // give copies still in flight a bounded chance to land before the CTA leaves
+        for (int jj = max(0, j - C::kStages); jj < j; ++jj) {
+          const int s = jj % C::kStages;
+          mbar_wait_drain(&bars->k_full[s], (jj / C::kStages) & 1, kDrainNs);
+          if (!STATS) mbar_wait_drain(&bars->v_full[s], (jj / C::kStages) & 1, kDrainNs);
+        }
+      }
+    }
+  } else if (start_ok && warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(BF16, kBM, kBN, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_f16(BF16, kBM, D, false, true);
+      bool ok = true;
+
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t qa = q_smem + t * C::kTileBytes, ka = k_smem + stage * C::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
+          umma_ss(tmem + t * kBN, make_smem_desc_sw128(qa + off, 16, 1024), make_smem_desc_sw128(ka + off, 16, 1024),
+                  idesc_qk, kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int t, int stage, bool first) {
+        const uint32_t va = v_smem + stage * C::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          umma_ts(tmem + kQT * kBN + t * D, tmem + t * kBN + kk * 8,
+                  make_smem_desc_sw128(va + kk * 2048, kChunkBytes, 1024), idesc_pv, (first && kk == 0) ? 0u : 1u);
+        }
+      };
+
+      for (int t = 0; t < kQT && ok; ++t)
+        if (n_t[t] > 0) ok = mbar_wait(&bars->q_full[t], 0, abort_flag);
+      // first score tiles
+      if (ok) ok = mbar_wait(&bars->k_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < kQT; ++t) {
+          if (n_t[t] == 0) continue;
+          issue_qk(t, 0);
+          umma_commit(&bars->s_full[t]);
+        }
+        umma_commit(&bars->k_empty[0]);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int sv = j % C::kStages;
+        const int sk = (j + 1) % C::kStages;
+        bool have_v = false, have_k = false;
+        for (int t = 0; t < kQT && ok; ++t) {
+          if (j >= n_t[t]) continue;
+          ok = mbar_wait(&bars->p_full[t], j & 1, abort_flag);  // P_t(j) stored (or S_t(j) consumed)
+          if (!ok) break;
+          if (!STATS) {
+            if (!have_v) { ok = mbar_wait(&bars->v_full[sv], (j / C::kStages) & 1, abort_flag); have_v = true; }
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, sv, j == 0);
+            if (j == n_t[t] - 1) umma_commit(&bars->o_full[t]);
+          }
+          if (j + 1 < n_t[t]) {
+            if (!have_k) { ok = mbar_wait(&bars->k_full[sk], ((j + 1) / C::kStages) & 1, abort_flag); have_k = true; }
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t, sk);
+            umma_commit(&bars->s_full[t]);
+          }
+        }
+        if (!ok) break;
+        if (!STATS) umma_commit(&bars->v_empty[sv]);
+        if (j + 1 < n_kv) umma_commit(&bars->k_empty[sk]);
+      }
+    }
+  }
+  } else {
+  setmaxnreg_inc<232>();
+  if (start_ok) {
+    // ------------------------------------------------------- softmax warps
+    const int t = (warp - 4) >> 2;        // query tile of this warpgroup
+    const int wq = warp & 3;              // TMEM lane quarter this warp may touch
+    const int r = wq * 32 + lane;         // row inside the tile
+    const int i = q0 + t * kBM + r;       // query index
+    const bool row_ok = i < a.Lq;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(wq * 32) << 16);
+    const uint32_t tS = lane_base + t * kBN;
+    const uint32_t tO = lane_base + kQT * kBN + t * D;
+    const float c2 = a.scale * kLog2e;
+    const int lim = a.causal ? min(i, a.Lkv - 1) : a.Lkv - 1;  // last kv index this row attends to
+    const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
+
+    float m_used = neg_inf();  // running maximum (scaled, base 2) the stored exponentials refer to
+    float l = 0.f;             // running sum of exponentials
+    bool ok = true;
+
+    for (int j = 0; j < n_t[t]; ++j) {
+      ok = mbar_wait(&bars->s_full[t], j & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
+      tmem_wait_ld();
+
+      const int j0 = j * kBN;
+      float mx = neg_inf();
+      if (EXTRAS) {
+        // logits in scaled base-2 units, bias added, masks applied
+        const long long bias_row = (long long)i * a.bias_s[1] + (long long)h * a.bias_s[2] + (long long)b * a.bias_s[3];
+        const long long mask_row = (long long)i * a.mask_s[1] + (long long)h * a.mask_s[2] + (long long)b * a.mask_s[3];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int jj = j0 + c * 32 + e;
+            float tv = __uint_as_float(sr[c][e]) * c2;
+            bool keep = (jj <= lim) && row_ok;
+            if (keep && a.bias) tv = fmaf(load_bias(a.bias, bias_row + jj * a.bias_s[0], a.bias_dtype), kLog2e, tv);
+            if (keep && a.mask) keep = a.mask[mask_row + jj * a.mask_s[0]] != 0;
+            tv = keep ? tv : neg_inf();
+            sr[c][e] = __float_as_uint(tv);
+            mx = fmaxf(mx, tv);
+          }
+        }
+      } else {
+        if (j0 + kBN - 1 > lim) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (j0 + c * 32 + e > lim) sr[c][e] = 0xff800000u;
+        }
+        float mx4[4] = {neg_inf(), neg_inf(), neg_inf(), neg_inf()};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sr[c][e]));
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c2;
+      }
+
+      // raise the reference maximum only when it is far behind (or not set yet)
+      const float m_new = fmaxf(m_used, mx);
+      const bool raise = m_new > m_used + kRescaleGap || (m_used == neg_inf() && m_new > neg_inf());
+      if (!STATS && j > 0 && __any_sync(0xffffffffu, raise)) {
+        const float f = raise ? ex2_approx(m_used - m_new) : 1.f;  // m_used = -inf gives 0: O is still 0 there
+        l *= f;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+          tmem_st32(tO + c * 32, o);
+        }
+      } else if (raise) {
+        l *= (m_used == neg_inf()) ? 0.f : ex2_approx(m_used - m_new);
+      }
+      if (raise) m_used = m_new;
+      const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
+
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (EXTRAS) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float p = ex2_approx(__uint_as_float(sr[c][e]) - m_sub);
+            sum4[e & 3] += p;
+            sr[c][e] = __float_as_uint(p);
+          }
+      } else {
+        const float nm = -m_sub;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float p = ex2_approx(fmaf(__uint_as_float(sr[c][e]), c2, nm));
+            sum4[e & 3] += p;
+            sr[c][e] = __float_as_uint(p);
+          }
+      }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+
+      if (!STATS) {
+        if (EXTRAS && a.dropout_p > 0.f) {
+          // one Philox call decides four neighbouring keys of this row
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              unsigned int w[4];
+              dropout_words(a, srow, (unsigned int)(j0 >> 2) + c * 8 + g, w);
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (!(w[u] > a.drop_thresh)) sr[c][g * 4 + u] = 0u;
+            }
+        }
+        uint32_t pk[2][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; e += 2)
+            pk[c >> 1][(c & 1) * 16 + (e >> 1)] =
+                pack2<BF16>(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
+        tmem_st32(tS, pk[0]);
+        tmem_st32(tS + 32, pk[1]);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full[t]);
+    }
+
+    // ------------------------------------------------------------ epilogue
+    if (ok && n_t[t] > 0) {
+      const bool dead = !(l > 0.f);
+      if (a.lse && row_ok) {
+        a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = dead ? neg_inf() : (m_used + log2f(l)) * kLn2;
+      }
+      if (!STATS) {
+        ok = mbar_wait(&bars->o_full[t], 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+          tc_fence_after();
+          float inv = dead ? (a.nan_fm ? __int_as_float(0x7fc00000) : 0.f) : a.inv_keep / l;
+          uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
+                          2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * D);
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + c * 32, o);
+            tmem_wait_ld();
+            if (row_ok) {
+#pragma unroll
+              for (int e = 0; e < 32; e += 8) {
+                uint4 v;
+                float f[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                  const float ov = __uint_as_float(o[e + u]);
+                  f[u] = dead ? (a.nan_fm ? inv : 0.f) : ov * inv;
+                }
+                v.x = pack2<BF16>(f[0], f[1]);
+                v.y = pack2<BF16>(f[2], f[3]);
+                v.z = pack2<BF16>(f[4], f[5]);
+                v.w = pack2<BF16>(f[6], f[7]);
+                *reinterpret_cast<uint4*>(xrow + (c * 32 + e) * 2) = v;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag) {
+    atomicExch(&g_umma_abort, 1);
+    if (a.status) atomicExch(a.status, NNLIB_B200_TIMEOUT);
+  }
+}
+
+
+// ===========================================================================
+// Scores kernel: alpha (after dropout) rebuilt from Q, K, bias, masks and the
+// saved log-sum-exp.  One CTA owns 128 queries of one unit and walks over all
+// key tiles; S = Q K^T is double-buffered in TMEM so the tensor core runs one
+// tile ahead of the four warps that turn logits into probabilities and write
+// them to the (Lkv, Lq, H, B) array (kv contiguous: each thread writes the
+// 128 consecutive scores of its own query).  Bound by the HBM writes.
+//   warps 0-3  epilogue (thread r owns query row r)
+//   warp 4     TMA producer, TMEM allocation
+//   warp 5     MMA issuer
+// ===========================================================================
+constexpr int kScThreads = 192;
+
+template <int D>
+struct ScCfg {
+  static constexpr int kChunks = D / 64;
+  static constexpr int kTileBytes = kChunks * kChunkBytes;
+  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kTileBytes;
+  static constexpr int kBarOff = kKOff + kStages * kTileBytes;
+  static constexpr int kSmemBytes = kBarOff + 256 + 1024;
+};
+
+struct ScBarriers {
+  uint64_t q_full;
+  uint64_t k_full[4], k_empty[4];
+  uint64_t s_full[2], s_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// write n (<= 128) scores of one query, given as 64 packed pairs
+template <typename T>
+__device__ __forceinline__ void store_score_row(T* dst, const uint32_t (&pk)[64], int n) {
+  if (n == 128 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+    for (int e = 0; e < 64; e += 4) {
+      uint4 v = make_uint4(pk[e], pk[e + 1], pk[e + 2], pk[e + 3]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(dst) + e * 4) = v;
+    }
+  } else {
+    unsigned short* d16 = reinterpret_cast<unsigned short*>(dst);
+#pragma unroll
+    for (int e = 0; e < 64; ++e) {
+      if (2 * e < n) d16[2 * e] = static_cast<unsigned short>(pk[e] & 0xffffu);
+      if (2 * e + 1 < n) d16[2 * e + 1] = static_cast<unsigned short>(pk[e] >> 16);
+    }
+  }
+}
+
+template <int D, bool BF16, bool EXTRAS>
+__global__ void __launch_bounds__(kScThreads)
+attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                        const AttnArgs a, const int n_qtiles) {
+  using C = ScCfg<D>;
+  using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  ScBarriers* bars = reinterpret_cast<ScBarriers*>(smem + C::kBarOff);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int unit = blockIdx.x / n_qtiles;
+  const int qt = n_qtiles - 1 - (blockIdx.x % n_qtiles);
+  const int h = unit % a.H, b = unit / a.H;
+  const int q0 = qt * kBM;
+  const int n_total = (a.Lkv + kBN - 1) / kBN;
+  const int n_live = a.causal ? min(n_total, (min(a.Lkv, q0 + kBM) + kBN - 1) / kBN) : n_total;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->s_empty[s], 4);
+    }
+    bars->abort_flag = *reinterpret_cast<volatile int*>(&g_umma_abort);
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&bars->tmem_base, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const bool start_ok = (*abort_flag == 0);
+
+  if (start_ok && warp == 4) {
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
+      mbar_arrive_expect_tx(&bars->q_full, C::kTileBytes);
+      for (int c = 0; c < C::kChunks; ++c)
+        tma_load_3d(smem + C::kQOff + c * kChunkBytes, &tm_q, &bars->q_full, h * D + c * 64, q0, b);
+      bool ok = true;
+      int j = 0;
+      for (; j < n_live; ++j) {
+        const int s = j % C::kStages;
+        if (j >= C::kStages) ok = mbar_wait(&bars->k_empty[s], ((j / C::kStages) - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars->k_full[s], C::kTileBytes);
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_3d(smem + C::kKOff + s * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->k_full[s],
+                      h * D + c * 64, j * kBN, b);
+      }
+      if (*abort_flag) {
+        mbar_wait_drain(&bars->q_full, 0, kDrainNs);
+        for (int jj = max(0, j - C::kStages); jj < j; ++jj)
+          mbar_wait_drain(&bars->k_full[jj % C::kStages], (jj / C::kStages) & 1, kDrainNs);
+      }
+    }
+  } else if (start_ok && warp == 5) {
+    if (lane == 0 && n_live > 0) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(BF16, kBM, kBN, false, false);
+      const uint32_t qa = smem_u32(smem + C::kQOff);
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      for (int j = 0; j < n_live && ok; ++j) {
+        const int s = j % C::kStages, sb = j & 1;
+        ok = mbar_wait(&bars->k_full[s], (j / C::kStages) & 1, abort_flag);
+        if (ok && j >= 2) ok = mbar_wait(&bars->s_empty[sb], ((j >> 1) - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ka = smem_u32(smem + C::kKOff + s * C::kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
+          umma_ss(tmem + sb * kBN, make_smem_desc_sw128(qa + off, 16, 1024), make_smem_desc_sw128(ka + off, 16, 1024),
+                  idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->s_full[sb]);
+        umma_commit(&bars->k_empty[s]);
+      }
+    }
+  } else if (start_ok && warp < 4) {
+    const int r = warp * 32 + lane;
+    const int i = q0 + r;
+    const bool row_ok = i < a.Lq;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const float c2 = a.scale * kLog2e;
+    const int lim = a.causal ? min(i, a.Lkv - 1) : a.Lkv - 1;
+    const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
+    const float lse_nat = row_ok ? a.lse[i + (long long)a.Lq * h + a.lse_sb * b] : 0.f;
+    const bool dead = (lse_nat == neg_inf());
+    const float lse2 = dead ? 0.f : lse_nat * kLog2e;
+    const float dead_val = a.nan_fm ? __int_as_float(0x7fc00000) : 0.f;
+    T* arow = reinterpret_cast<T*>(a.alpha) + ((long long)i + (long long)a.Lq * h) * a.Lkv + a.alpha_sb * b;
+    const long long bias_row = (long long)i * a.bias_s[1] + (long long)h * a.bias_s[2] + (long long)b * a.bias_s[3];
+    const long long mask_row = (long long)i * a.mask_s[1] + (long long)h * a.mask_s[2] + (long long)b * a.mask_s[3];
+
+    for (int j = 0; j < n_total; ++j) {
+      const int j0 = j * kBN;
+      const int nvalid = min(kBN, a.Lkv - j0);
+      uint32_t pk[64];
+      if (j < n_live) {
+        const int sb = j & 1;
+        bool ok = mbar_wait(&bars->s_full[sb], (j >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(lane_base + sb * kBN + c * 32, sr[c]);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_empty[sb]);
+
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int jj = j0 + c * 32 + e;
+            float tv = __uint_as_float(sr[c][e]) * c2;
+            bool keep = (jj <= lim) && row_ok;
+            if (EXTRAS) {
+              if (keep && a.bias) tv = fmaf(load_bias(a.bias, bias_row + jj * a.bias_s[0], a.bias_dtype), kLog2e, tv);
+              if (keep && a.mask) keep = a.mask[mask_row + jj * a.mask_s[0]] != 0;
+            }
+            float al = keep ? ex2_approx(tv - lse2) : 0.f;
+            if (dead) al = dead_val;
+            sr[c][e] = __float_as_uint(al);
+          }
+        }
+        if (EXTRAS && a.dropout_p > 0.f) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              unsigned int w[4];
+              dropout_words(a, srow, (unsigned int)(j0 >> 2) + c * 8 + g, w);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float al = __uint_as_float(sr[c][g * 4 + u]);
+                sr[c][g * 4 + u] = __float_as_uint((w[u] > a.drop_thresh) ? al * a.inv_keep : 0.f);
+              }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; e += 2)
+            pk[c * 16 + (e >> 1)] = pack2<BF16>(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
+      } else {
+        // tiles entirely above the causal diagonal
+        const uint32_t z = dead ? pack2<BF16>(dead_val, dead_val) : 0u;
+#pragma unroll
+        for (int e = 0; e < 64; ++e) pk[e] = z;
+      }
+      if (row_ok) store_score_row<T>(arow + j0, pk, nvalid);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+  if (threadIdx.x == 0 && *abort_flag) {
+    atomicExch(&g_umma_abort, 1);
+    if (a.status) atomicExch(a.status, NNLIB_B200_TIMEOUT);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// (features, positions, batch) array with 128-byte-swizzled boxes of 64 features x 128 positions
+bool make_map(CUtensorMap* m, const void* base, int dtype, long long feat, long long len, long long batch,
+              long long stride_l, long long stride_b) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)feat, (cuuint64_t)len, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)stride_l * 2, (cuuint64_t)stride_b * 2};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(m, dtype == NNLIB_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool stride_ok(long long s) { return s > 0 && (s % 8) == 0 && s * 2 < (1ll << 40); }
+
+template <int D, bool BF16, bool EXTRAS, bool STATS>
+cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
+                       cudaStream_t st) {
+  auto kern = attn_fwd_umma_kernel<D, BF16, EXTRAS, STATS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int n_qblocks = (a.Lq + kQT * kBM - 1) / (kQT * kBM);
+  const long long blocks = (long long)n_qblocks * a.H * a.B;
+  if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+  kern<<<(unsigned)blocks, kThreads, Cfg<D>::kSmemBytes, st>>>(mq, mk, mv, a, n_qblocks);
+  count_launch();
+  return cudaGetLastError();
+}
+
+template <int D, bool BF16, bool EXTRAS>
+cudaError_t launch_scores(const CUtensorMap& mq, const CUtensorMap& mk, const AttnArgs& a, cudaStream_t st) {
+  auto kern = attn_scores_umma_kernel<D, BF16, EXTRAS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ScCfg<D>::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int n_qtiles = (a.Lq + kBM - 1) / kBM;
+  const long long blocks = (long long)n_qtiles * a.H * a.B;
+  if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+  kern<<<(unsigned)blocks, kScThreads, ScCfg<D>::kSmemBytes, st>>>(mq, mk, a, n_qtiles);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool umma_supports(const AttnArgs& a, int dtype, bool need_v) {
+  if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
+  if (!(a.d == 64 || a.d == 128)) return false;
+  if (need_v && a.dv != a.d) return false;
+  if (!(a.scale > 0.f)) return false;
+  if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1) return false;
+  if (!aligned16(a.q) || !aligned16(a.k) || !stride_ok(a.q_sl) || !stride_ok(a.k_sl) || !stride_ok(a.q_sb) ||
+      !stride_ok(a.k_sb))
+    return false;
+  if (need_v) {
+    if (!aligned16(a.v) || !aligned16(a.x) || !stride_ok(a.v_sl) || !stride_ok(a.v_sb) || !stride_ok(a.x_sl) ||
+        !stride_ok(a.x_sb))
+      return false;
+  }
+  return encode_tiled_fn() != nullptr;
+}
+
+cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t st) {
+  CUtensorMap mq, mk, mv;
+  const long long E = (long long)a.H * a.d;
+  if (!make_map(&mq, a.q, dtype, E, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
+  if (!make_map(&mk, a.k, dtype, E, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
+  if (stats_only) {
+    mv = mk;
+  } else if (!make_map(&mv, a.v, dtype, (long long)a.H * a.dv, a.Lkv, a.B, a.v_sl, a.v_sb)) {
+    return cudaErrorInvalidValue;
+  }
+  const bool bf16 = dtype == NNLIB_B200_BF16;
+  const bool extras = a.bias != nullptr || a.mask != nullptr || a.dropout_p > 0.f;
+#define NB_FWD(DD, BF, EX, ST) return launch_fwd<DD, BF, EX, ST>(mq, mk, mv, a, st)
+#define NB_FWD_ST(DD, BF, EX) \
+  do { if (stats_only) NB_FWD(DD, BF, EX, true); else NB_FWD(DD, BF, EX, false); } while (0)
+#define NB_FWD_EX(DD, BF) \
+  do { if (extras) NB_FWD_ST(DD, BF, true); else NB_FWD_ST(DD, BF, false); } while (0)
+#define NB_FWD_BF(DD) \
+  do { if (bf16) NB_FWD_EX(DD, true); else NB_FWD_EX(DD, false); } while (0)
+  if (a.d == 128) NB_FWD_BF(128); else NB_FWD_BF(64);
+#undef NB_FWD_BF
+#undef NB_FWD_EX
+#undef NB_FWD_ST
+#undef NB_FWD
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st) {
+  CUtensorMap mq, mk;
+  const long long E = (long long)a.H * a.d;
+  if (!make_map(&mq, a.q, dtype, E, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
+  if (!make_map(&mk, a.k, dtype, E, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
+  const bool bf16 = dtype == NNLIB_B200_BF16;
+  const bool extras = a.bias != nullptr || a.mask != nullptr || a.dropout_p > 0.f;
+#define NB_SC(DD, BF, EX) return launch_scores<DD, BF, EX>(mq, mk, a, st)
+#define NB_SC_EX(DD, BF) \
+  do { if (extras) NB_SC(DD, BF, true); else NB_SC(DD, BF, false); } while (0)
+#define NB_SC_BF(DD) \
+  do { if (bf16) NB_SC_EX(DD, true); else NB_SC_EX(DD, false); } while (0)
+  if (a.d == 128) NB_SC_BF(128); else NB_SC_BF(64);
+#undef NB_SC_BF
+#undef NB_SC_EX
+#undef NB_SC
+  return cudaErrorInvalidValue;
+}
+
+// Reads and clears the sticky "a bounded wait ran out" flag of the current
+// device.  Synchronises the stream.
+cudaError_t umma_take_abort(int* out, cudaStream_t st) {
+  int v = 0;
+  cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpyFromSymbol(&v, g_umma_abort, sizeof(int));
+  if (e != cudaSuccess) return e;
+  if (v) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_umma_abort, &zero, sizeof(int));
+  }
+  *out = v;
+  return e;
+}
+
+}  // namespace nb200

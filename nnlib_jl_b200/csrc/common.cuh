@@ -1,0 +1,101 @@
+// Shared definitions of the attention kernels: the resolved argument block the
+// host hands to every kernel, element-type helpers and the Philox4x32-10
+// counter-based generator that decides which attention scores dropout keeps.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nnlib_b200.h"
+
+namespace nb200 {
+
+// Kernel-side view of nnlib_b200_attn_params with every default filled in
+// (dense strides, scale = 1/sqrt(d), rng_H = H) and dropout pre-digested.
+struct AttnArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* x;
+  long long q_sl, q_sb, k_sl, k_sb, v_sl, v_sb, x_sl, x_sb;
+  const void* bias;
+  long long bias_s[4];
+  const unsigned char* mask;
+  long long mask_s[4];
+  float* lse;
+  long long lse_sb;
+  void* alpha;
+  long long alpha_sb;
+  int* status;
+  long long rng_h0, rng_b0, rng_H;
+  unsigned int key0, key1, off_lo, off_hi;
+  unsigned int drop_thresh;  // keep iff philox word > drop_thresh
+  float inv_keep;            // 1/(1-p)
+  float dropout_p;
+  float scale;               // multiplies q·k (natural units)
+  int bias_dtype;
+  int causal, nan_fm;
+  int d, dv, H, Lq, Lkv, B;
+};
+
+// ---- element types --------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+
+// bias may have any of the three element types, chosen at run time
+__device__ __forceinline__ float load_bias(const void* p, long long idx, int dtype) {
+  if (dtype == NNLIB_B200_F16) return __half2float(reinterpret_cast<const __half*>(p)[idx]);
+  if (dtype == NNLIB_B200_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
+  return reinterpret_cast<const float*>(p)[idx];
+}
+
+// ---- Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11) ----
+__host__ __device__ __forceinline__ void philox4x32_10(unsigned int& c0, unsigned int& c1, unsigned int& c2,
+                                                       unsigned int& c3, unsigned int k0, unsigned int k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const unsigned long long p0 = 0xD2511F53ull * c0;
+    const unsigned long long p1 = 0xCD9E8D57ull * c2;
+    const unsigned int n0 = (unsigned int)(p1 >> 32) ^ c1 ^ k0;
+    const unsigned int n1 = (unsigned int)p1;
+    const unsigned int n2 = (unsigned int)(p0 >> 32) ^ c3 ^ k1;
+    const unsigned int n3 = (unsigned int)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+
+// The four random words that cover kv positions 4*j4 .. 4*j4+3 of score row r.
+__device__ __forceinline__ void dropout_words(const AttnArgs& a, unsigned long long r, unsigned int j4,
+                                              unsigned int w[4]) {
+  unsigned int c0 = j4, c1 = (unsigned int)r, c2 = (unsigned int)(r >> 32) + a.off_hi, c3 = a.off_lo;
+  philox4x32_10(c0, c1, c2, c3, a.key0, a.key1);
+  w[0] = c0; w[1] = c1; w[2] = c2; w[3] = c3;
+}
+
+// global score-row number of query i, head h, batch b (see nnlib_b200.h, dropout)
+__device__ __forceinline__ unsigned long long score_row(const AttnArgs& a, int i, int h, int b) {
+  return (unsigned long long)i +
+         (unsigned long long)a.Lq * ((unsigned long long)(h + a.rng_h0) +
+                                     (unsigned long long)a.rng_H * (unsigned long long)(b + a.rng_b0));
+}
+
+// launch bookkeeping shared by all translation units
+void count_launch(int n = 1);
+void set_last_cuda_error(cudaError_t e);
+
+}  // namespace nb200

@@ -1,0 +1,24 @@
+// Host-side launch functions of every kernel family, shared between the
+// translation units and the C ABI in api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include "common.cuh"
+
+namespace nb200 {
+
+// CUDA-core kernels (attn_simt.cu)
+bool simt_supports(int d, int dv);
+cudaError_t simt_fwd(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t simt_stats(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t simt_scores(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t simt_apply(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t causal_fill(unsigned char* m, long long L, cudaStream_t st);
+cudaError_t causal_check(const unsigned char* m, long long L, int* flag, cudaStream_t st);
+
+// tcgen05 + TMA kernels (attn_umma.cu)
+bool umma_supports(const AttnArgs& a, int dtype, bool need_v);
+cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t st);
+cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t umma_take_abort(int* out, cudaStream_t st);
+
+}  // namespace nb200
