@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path: one JSON line on stdout (rank 0).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c5|c2|c4]
+
+A "step" is one call of ``dot_product_attention`` over one batch of seeded
+synthetic inputs.  The default workload is the configuration the headline
+metric is quoted on: bf16 causal self-attention, E = 4096, nheads = 32
+(d = 128), L = 4096, batch = 8 per GPU, scores discarded (x-only).  With N > 1
+every rank runs the same per-GPU work on its own batch slice (weak scaling; the
+(batch, head) units are independent, so no collective is on the data path).
+
+* ``value``: whole-job TFLOP/s with inputs resident in HBM (CUDA events on the
+  launching stream, max over ranks); FLOPs are algorithmic:
+  2·(d+dv)·P·H·B with P = L(L+1)/2 for causal.
+* ``e2e``: the same metric through the public API from pinned HOST buffers,
+  H2D of q, k, v and D2H of x inside the timed region.
+* ``roofline``: algorithmic FLOP/s of the fused kernel against the measured
+  dense-bf16 peak of this pool (MEASURED_PEAKS.json).
+* ``cpu_baseline``: the CPU restatement of the reference's operation sequence
+  (the oracle), timed on this host's cores on a bounded sample.
+``--impl reference`` times only that CPU path (NNlib.jl itself is Julia, which
+is not installed here) with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "attention TFLOP/s per B200 (bf16 causal, L=4096, d=128); % of dense TC peak"
+
+WORKLOADS = {
+    # name: dtype, E, H, Lq, Lkv, B(per GPU), causal, extras
+    "c3": dict(desc="decoder causal self-attention (Llama-7B shape): bf16 E=4096 nheads=32 d=128 L=4096 batch=8, "
+                    "mask=make_causal_mask, x only",
+               dtype="bf16", E=4096, H=32, Lq=4096, Lkv=4096, B=8, causal=True),
+    "c5": dict(desc="long-context causal: bf16 E=2048 nheads=16 d=128 L=32768 batch=8 (128 units)",
+               dtype="bf16", E=2048, H=16, Lq=32768, Lkv=32768, B=8, causal=True),
+    "c2": dict(desc="encoder self-attention (BERT-base shape): bf16 E=768 nheads=12 d=64 L=512 batch=32, "
+                    "key-padding mask, scores returned",
+               dtype="bf16", E=768, H=12, Lq=512, Lkv=512, B=32, causal=False, padmask=True, alpha=True),
+    "c4": dict(desc="cross-attention with additive bias: fp16 q(1024,256,16) kv(1024,2048,16) nheads=16 d=64, "
+                    "bias f16 (Lkv,Lq,H,B), dropout 0.1",
+               dtype="f16", E=1024, H=16, Lq=256, Lkv=2048, B=16, causal=False, bias=True, dropout=0.1),
+}
+
+
+def algorithmic_flops(w) -> float:
+    d = w["E"] // w["H"]
+    P = w["Lq"] * (w["Lq"] + 1) // 2 if w["causal"] else w["Lq"] * w["Lkv"]
+    return 2.0 * (d + d) * P * w["H"] * w["B"]
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return dict(bf16=j["bf16_tflops"], bf16_sustained=j.get("bf16_tflops_sustained"), hbm=j["hbm_gbs"],
+                    source="measured (MEASURED_PEAKS.json)")
+    return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback (earlier measurement on this pool)")
+
+
+# --------------------------------------------------------------------------
+# clocks sampled during the timed region
+# --------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()   # the exact process this object started
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        busy = [s for s in sm if s >= 0.5 * max(sm)]
+        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+
+
+# --------------------------------------------------------------------------
+# CPU path (oracle) on a bounded sample
+# --------------------------------------------------------------------------
+def cpu_sample(w, budget_s: float = 20.0):
+    """Time the CPU restatement of the reference's op sequence on a slice of the
+    workload (whole heads of one batch element), sized from a one-head probe to
+    take roughly ``budget_s``.  Returns (TFLOP/s, cores, description)."""
+    import numpy as np
+    from oracle import attention_oracle as O
+    cores = os.cpu_count() or 1
+    d = w["E"] // w["H"]
+    rng = np.random.default_rng(1234)
+
+    def run(nh):
+        q = rng.standard_normal((d * nh, w["Lq"], 1), dtype=np.float32)
+        k = rng.standard_normal((d * nh, w["Lkv"], 1), dtype=np.float32)
+        v = rng.standard_normal((d * nh, w["Lkv"], 1), dtype=np.float32)
+        mask = O.make_causal_mask(q) if w["causal"] else None
+        t0 = time.perf_counter()
+        O.dot_product_attention(q, k, v, mask=mask, nheads=nh)
+        return time.perf_counter() - t0
+
+    t1 = run(1)
+    nh = int(max(1, min(w["H"], budget_s / max(t1, 1e-3))))
+    t = run(nh) if nh > 1 else t1
+    P = w["Lq"] * (w["Lq"] + 1) // 2 if w["causal"] else w["Lq"] * w["Lkv"]
+    flops = 2.0 * (d + d) * P * nh
+    return flops / t / 1e12, cores, (f"{nh} head(s) of one batch element of the workload "
+                                     f"({t:.2f} s, Float32, numpy/OpenBLAS, {cores} threads)")
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    desc = ""
+    cores = os.cpu_count() or 1
+    budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    for it in range(args.warmup + args.steps):
+        v, cores, desc = cpu_sample(w, budget_s=budget)
+        if it >= args.warmup:
+            vals.append(v)
+    value = statistics.mean(vals)
+    d = w["E"] // w["H"]
+    out = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["desc"], "note": "NNlib.jl is Julia (not installed here): the CPU restatement of "
+                   "its operation sequence (oracle/attention_oracle.py) is timed instead"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out), flush=True)
+
+
+# --------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------
+def run_ours(args, w):
+    import torch
+    import torch.distributed as dist
+
+    import nnlib_jl_b200 as nb
+    from nnlib_jl_b200 import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+
+    tdtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[w["dtype"]]
+    E, H, Lq, Lkv, B = w["E"], w["H"], w["Lq"], w["Lkv"], w["B"]
+    # seeded synthetic inputs; every rank owns its own batch slice of a global batch of B*world
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q = nb.jl_empty((E, Lq, B), tdtype, dev); q.normal_(generator=g)
+    k = nb.jl_empty((E, Lkv, B), tdtype, dev); k.normal_(generator=g)
+    v = nb.jl_empty((E, Lkv, B), tdtype, dev); v.normal_(generator=g)
+    kwargs = dict(nheads=H)
+    bias = None
+    if w.get("causal"):
+        kwargs["mask"] = nb.CausalMask()
+    if w.get("padmask"):
+        lens = torch.randint(Lkv // 2, Lkv + 1, (B,), generator=g, device=dev)
+        m = (torch.arange(Lkv, device=dev)[None, :] < lens[:, None])            # (B, Lkv) row-major
+        kwargs["mask"] = m.reshape(B, 1, 1, Lkv).permute(3, 2, 1, 0)            # (Lkv,1,1,B) column-major
+    if w.get("bias"):
+        bias = nb.jl_empty((Lkv, Lq, H, B), tdtype, dev); bias.normal_(0.0, 0.5, generator=g)
+    want_alpha = bool(w.get("alpha"))
+
+    def step():
+        if w.get("dropout"):
+            kwargs["fdrop"] = nb.PhiloxDropout(w["dropout"], seed=0xB200, offset=0)
+        y, a = nb.dot_product_attention(q, k, v, bias, **kwargs)
+        if want_alpha:
+            a.materialize()
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    nb.device_health(dev)
+
+    # ---- device-resident timing -------------------------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.nnlib_b200_launch_count()
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    launches = lib.nnlib_b200_launch_count() - launches0
+    ms_total = ev0.elapsed_time(ev1)
+    nb.device_health(dev)
+
+    # ---- end-to-end timing from pinned host buffers ------------------------
+    hq, hk, hv = (torch.empty(t.permute(2, 1, 0).shape, dtype=tdtype).pin_memory() for t in (q, k, v))
+    for h, t in ((hq, q), (hk, k), (hv, v)):
+        h.copy_(t.permute(2, 1, 0))
+    hx = torch.empty((B, Lq, E), dtype=tdtype).pin_memory()
+    dq, dk, dv = (nb.jl_empty(t.shape, tdtype, dev) for t in (q, k, v))
+
+    def e2e_step():
+        dq.permute(2, 1, 0).copy_(hq, non_blocking=True)
+        dk.permute(2, 1, 0).copy_(hk, non_blocking=True)
+        dv.permute(2, 1, 0).copy_(hv, non_blocking=True)
+        if w.get("dropout"):
+            kwargs["fdrop"] = nb.PhiloxDropout(w["dropout"], seed=0xB200, offset=0)
+        y, a = nb.dot_product_attention(dq, dk, dv, bias, **kwargs)
+        if want_alpha:
+            a.materialize()
+        hx.copy_(y.permute(2, 1, 0), non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- max over ranks -----------------------------------------------------
+    times = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = times.tolist()
+    ms_step = ms_total / args.steps
+    flops_gpu = algorithmic_flops(w)
+    value = flops_gpu * world / (ms_step * 1e-3) / 1e12
+    e2e_value = flops_gpu * world / (e2e_ms * 1e-3) / 1e12
+    esz = torch.empty(0, dtype=tdtype).element_size()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        per_gpu = value / world
+        path = "tcgen05"
+        out = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": args.workload + ": " + w["desc"], "per_gpu_batch": B, "global_batch": B * world,
+                       "l2": "inputs (q,k,v = %.0f MB per GPU) larger than the 126 MB L2" %
+                             ((q.numel() + k.numel() + v.numel()) * esz / 1e6),
+                       "kernel_path": path, "sharding": "batch slices per rank, no collective"},
+            "per_gpu_tflops": per_gpu,
+            "pct_of_dense_bf16_peak": 100.0 * per_gpu / peaks["bf16"],
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * esz,
+                    "d2h_bytes_per_step": Lq * E * B * esz},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                         "frac": per_gpu / peaks["bf16"], "peak_source": peaks["source"] + ", burst",
+                         "frac_of_sustained": (per_gpu / peaks["bf16_sustained"]) if peaks["bf16_sustained"] else None,
+                         "kernel": "attn_fwd_umma_kernel", "algorithmic_flops_per_launch": flops_gpu,
+                         "traffic": None},
+        }
+        if world == 1 and not args.no_cpu:
+            v_cpu, cores, desc = cpu_sample(w, budget_s=args.cpu_budget)
+            out["cpu_baseline"] = {"value": v_cpu, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

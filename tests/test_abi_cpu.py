@@ -1,0 +1,106 @@
+"""The C-ABI shared library without a GPU: it loads, exports every symbol the
+header declares, its params struct matches the ctypes mirror, and argument
+checking answers before any CUDA call is made."""
+import ctypes as C
+import re
+import subprocess
+from pathlib import Path
+
+import pytest
+
+from nnlib_jl_b200 import _lib
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "nnlib_b200.h"
+
+
+def test_every_declared_symbol_is_exported(lib):
+    declared = re.findall(r"NNLIB_B200_API\s+[\w\s\*]+?\b(nnlib_b200_\w+)\s*\(", HEADER.read_text())
+    assert len(declared) >= 14
+    assert set(declared) == set(_lib.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_nothing_else_is_exported(lib):
+    out = subprocess.run(["nm", "-D", "--defined-only", str(_lib.LIB_PATH)], capture_output=True, text=True).stdout
+    names = [ln.split()[-1] for ln in out.splitlines() if ln.strip()]
+    assert names and all(n.startswith("nnlib_b200_") for n in names), names
+
+
+def test_struct_layout_matches_header(tmp_path):
+    src = tmp_path / "sz.c"
+    src.write_text(
+        '#include "nnlib_b200.h"\n#include <stdio.h>\n#include <stddef.h>\n'
+        "int main(void){printf(\"%zu %zu %zu %zu %zu\\n\", sizeof(nnlib_b200_attn_params),"
+        "offsetof(nnlib_b200_attn_params, q), offsetof(nnlib_b200_attn_params, bias_stride),"
+        "offsetof(nnlib_b200_attn_params, scale), offsetof(nnlib_b200_attn_params, status));return 0;}\n")
+    exe = tmp_path / "sz"
+    subprocess.run(["gcc", "-std=c99", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    A = _lib.AttnParams
+    assert got == [C.sizeof(A), A.q.offset, A.bias_stride.offset, A.scale.offset, A.status.offset]
+
+
+def test_version_and_strerror(lib):
+    assert lib.nnlib_b200_version() == 100
+    assert _lib.strerror(0) == "ok"
+    for code in (-1, -2, -3, -4, -5, -99):
+        assert _lib.strerror(code)
+    assert lib.nnlib_b200_launch_count() >= 0
+
+
+def _params(**kw):
+    p = _lib.AttnParams()
+    p.dtype = _lib.BF16
+    p.d = p.dv = 64
+    p.H, p.Lq, p.Lkv, p.B = 2, 16, 16, 1
+    # fake non-null pointers: validation must reject the call before touching them
+    p.q = p.k = p.v = p.x = 0x1000
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("bad", [
+    dict(dtype=7), dict(d=0), dict(H=0), dict(Lq=-1), dict(dropout_p=1.0), dict(dropout_p=-0.1),
+    dict(scale=-1.0), dict(q=None), dict(x=None), dict(q_stride_l=64), dict(struct_size=8),
+    dict(bias=0x1000, bias_dtype=9), dict(rng_h0=-1), dict(lse_stride_b=1),
+])
+def test_invalid_arguments_are_rejected_without_a_gpu(lib, bad):
+    p = _params(**bad)
+    assert lib.nnlib_b200_attn_fwd(C.byref(p), None) == _lib.INVALID_ARG
+
+
+def test_null_params_and_missing_outputs(lib):
+    assert lib.nnlib_b200_attn_fwd(None, None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_scores(C.byref(_params()), None) == _lib.INVALID_ARG      # lse / alpha missing
+    assert lib.nnlib_b200_attn_apply(C.byref(_params()), None) == _lib.INVALID_ARG       # alpha missing
+    assert lib.nnlib_b200_attn_stats(C.byref(_params()), None) == _lib.INVALID_ARG       # lse missing
+    assert lib.nnlib_b200_causal_fill(None, 4, None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_causal_check(None, 4, None, None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attention(None, None, 0, None) == _lib.INVALID_ARG
+
+
+def test_empty_problems_enqueue_nothing(lib):
+    before = lib.nnlib_b200_launch_count()
+    assert lib.nnlib_b200_attn_fwd(C.byref(_params(Lq=0)), None) == _lib.OK
+    assert lib.nnlib_b200_attn_fwd(C.byref(_params(B=0)), None) == _lib.OK
+    assert lib.nnlib_b200_causal_fill(None, 0, None) == _lib.OK
+    assert lib.nnlib_b200_launch_count() == before
+
+
+def test_workspace_bytes(lib):
+    p = _params(Lq=100, H=3, B=5)
+    assert lib.nnlib_b200_workspace_bytes(C.byref(p)) == 100 * 3 * 5 * 4
+    p.lse = 0x2000
+    assert lib.nnlib_b200_workspace_bytes(C.byref(p)) == 0
+    assert lib.nnlib_b200_attention(C.byref(_params()), None, 0, None) == _lib.WORKSPACE_TOO_SMALL
+
+
+def test_path_selection_is_pure_host_logic(lib):
+    # f32 and odd head sizes go to the CUDA-core kernels; the selection needs no device
+    assert lib.nnlib_b200_attn_path(C.byref(_params(dtype=_lib.F32))) == _lib.PATH_SIMT
+    assert lib.nnlib_b200_attn_path(C.byref(_params(d=48, dv=48))) == _lib.PATH_SIMT
+    assert lib.nnlib_b200_attn_path(C.byref(_params(d=2048, dv=2048))) == _lib.UNSUPPORTED_SHAPE
+    assert lib.nnlib_b200_attn_path(C.byref(_params(q=0x1004))) == _lib.PATH_SIMT          # unaligned rows

@@ -1,0 +1,529 @@
+"""Parity of the CUDA path (through the C ABI of libnnlib_b200.so) with the CPU
+oracle, on the reference's own test cases (test/attention.jl,
+test/ext_amdgpu/attention.jl) and on the benchmark configurations.
+
+Tolerances (max-abs, mean-rel = mean|y-ŷ| / mean|ŷ|) against the Float32 oracle
+evaluated on the upcast inputs:
+    bf16 : 2e-2 , 5e-3        f16 : 3e-3 , 1e-3        f32 : 1e-5 (atol, like the reference's GPU tests)
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import nnlib_jl_b200 as nb
+from nnlib_jl_b200 import _lib
+from oracle import attention_oracle as O
+from oracle import philox_oracle as P
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.bfloat16: (2e-2, 5e-3), torch.float16: (3e-3, 1e-3), torch.float32: (1e-5, 1e-5)}
+DEV = "cuda:0"
+
+
+def _round_to(a: np.ndarray, dtype) -> np.ndarray:
+    """float32 values of `a` after rounding to the tensor dtype (what the device sees)."""
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dtype).float().numpy()
+
+
+def _dev(a: np.ndarray, dtype):
+    return nb.jl_from_numpy(a.astype(np.float32), dtype=dtype, device=DEV)
+
+
+def _close(got: np.ndarray, want: np.ndarray, dtype, what=""):
+    max_abs, mean_rel = TOL[dtype]
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert np.isfinite(got).all(), f"{what}: non-finite values"
+    assert err.max() <= max_abs, f"{what}: max-abs {err.max():.3e} > {max_abs}"
+    denom = np.abs(want).mean()
+    if denom > 0:
+        assert err.mean() / denom <= mean_rel, f"{what}: mean-rel {err.mean() / denom:.3e} > {mean_rel}"
+
+
+@pytest.fixture(autouse=True)
+def _health():
+    yield
+    nb.device_health(DEV)   # turns a silent bounded-wait abort into a test failure
+
+
+def _path(q, k, v, nheads):
+    """Which kernel family the library picks for these tensors."""
+    p = _lib.AttnParams()
+    p.dtype = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[q.dtype]
+    p.H = nheads
+    p.d, p.dv = q.shape[0] // nheads, v.shape[0] // nheads
+    p.Lq, p.Lkv, p.B = q.shape[1], k.shape[1], q.shape[2]
+    x = nb.jl_empty((v.shape[0], q.shape[1], q.shape[2]), q.dtype, q.device)
+    p.q, p.k, p.v, p.x = q.data_ptr(), k.data_ptr(), v.data_ptr(), x.data_ptr()
+    return _lib.load().nnlib_b200_attn_path(p)
+
+
+# --------------------------------------------------------------------------
+# the reference's own tests, run on the device
+# --------------------------------------------------------------------------
+
+def test_specific_results(golden):
+    # test/attention.jl:25-34 on the device (Float32 → CUDA-core kernel)
+    g = golden["attention_specific"]
+    qn = np.arange(1, 13, dtype=np.float32).reshape(g["q_shape"], order="F") / 12
+    q = _dev(qn, torch.float32)
+    y, a = nb.dot_product_attention(q, q, q, nheads=2)
+    ytrue = np.array(g["ytrue_colmajor"]).reshape(g["ytrue_shape"], order="F")
+    atrue = np.array(g["alphatrue_colmajor"]).reshape(g["alphatrue_shape"], order="F")
+    np.testing.assert_allclose(nb.jl_to_numpy(y), ytrue, atol=1e-5, rtol=0)
+    np.testing.assert_allclose(np.asarray(a), atrue, atol=1e-5, rtol=0)
+
+
+@pytest.mark.parametrize("batch_size", [(), (1,), (2,), (2, 1, 3)])
+@pytest.mark.parametrize("nheads", [1, 3, 5])
+def test_compare_cpu_gpu_small(batch_size, nheads):
+    # test/ext_amdgpu/attention.jl:1-23 (CPU vs device, atol 1f-5) and test/attention.jl:1-15
+    rng = np.random.default_rng(10)
+    n, lenq, lenkv = 15, 3, 4
+    qn = rng.random((n, lenq) + batch_size, dtype=np.float32)
+    kn = rng.random((n, lenkv) + batch_size, dtype=np.float32)
+    vn = rng.random((n, lenkv) + batch_size, dtype=np.float32)
+    y, a = nb.dot_product_attention(_dev(qn, torch.float32), _dev(kn, torch.float32), _dev(vn, torch.float32),
+                                    nheads=nheads)
+    assert y.is_cuda and y.dtype == torch.float32
+    assert tuple(y.shape) == (n, lenq) + batch_size
+    assert tuple(a.shape) == (lenkv, lenq, nheads) + batch_size
+    an = np.asarray(a)
+    np.testing.assert_allclose(an.sum(0), np.ones((lenq, nheads) + batch_size), rtol=1e-5)
+    yo, ao = O.dot_product_attention(qn, kn, vn, nheads=nheads)
+    np.testing.assert_allclose(nb.jl_to_numpy(y), yo, atol=1e-5, rtol=0)
+    np.testing.assert_allclose(an, ao, atol=1e-5, rtol=0)
+
+
+def test_scores_4d_matches_3d_entry():
+    # test/attention.jl:17-23
+    qn = np.arange(1, 25, dtype=np.float32).reshape((4, 2, 3, 1), order="F") / 24
+    q4 = _dev(qn, torch.float32)
+    a = nb.dot_product_attention_scores(q4, q4)
+    q3 = nb.jl_reshape(q4, (8, 3, 1))
+    _, a2 = nb.dot_product_attention(q3, q3, q3, nheads=2)
+    np.testing.assert_allclose(nb.jl_to_numpy(a), np.asarray(a2), atol=1e-6)
+    np.testing.assert_allclose(nb.jl_to_numpy(a), O.dot_product_attention_scores(qn, qn), atol=1e-5)
+
+
+def test_mask_and_causal_support():
+    # test/attention.jl:36-52 and test/ext_amdgpu/attention.jl:25-34
+    rng = np.random.default_rng(11)
+    qn = rng.random((4, 2, 3, 1), dtype=np.float32)
+    kn = rng.random((4, 2, 5, 1), dtype=np.float32)
+    mask = rng.random((5, 3)) > 0.5
+    mask[0] = True
+    a = nb.jl_to_numpy(nb.dot_product_attention_scores(
+        _dev(qn, torch.float32), _dev(kn, torch.float32), mask=nb.jl_from_numpy(mask, device=DEV)))
+    assert ((a[:, :, 0, 0] > 0) == mask).all() and ((a[:, :, 1, 0] > 0) == mask).all()
+    x = _dev(rng.random((4, 2, 3, 1), dtype=np.float32), torch.float32)
+    cm = nb.make_causal_mask(x, dims=3)
+    assert cm.is_cuda and cm.dtype == torch.bool and tuple(cm.shape) == (3, 3)
+    cmn = cm.cpu().numpy()
+    assert (cmn == O.make_causal_mask(np.zeros((4, 2, 3, 1)), dims=3)).all()
+    a = nb.jl_to_numpy(nb.dot_product_attention_scores(x, x, mask=cm))
+    assert ((a[:, :, 0, 0] > 0) == cmn).all() and ((a[:, :, 1, 0] > 0) == cmn).all()
+    # a hand-made copy of the causal matrix is detected by content, a different matrix is not
+    cm2 = nb.jl_from_numpy(cmn, device=DEV)
+    a2 = nb.jl_to_numpy(nb.dot_product_attention_scores(x, x, mask=cm2))
+    np.testing.assert_array_equal(a, a2)
+
+
+def test_dropout_with_opaque_fdrop():
+    # test/attention.jl:54-59: an arbitrary callable; returned α is post-dropout and x = V·α′
+    rng = np.random.default_rng(12)
+    qn = rng.random((10, 10, 10), dtype=np.float32)
+    q = _dev(qn, torch.float32)
+    fdrop = lambda a: (torch.rand_like(a) > 0.5) * a / (1 - 0.5)
+    y, a = nb.dot_product_attention(q, q, q, nheads=2, fdrop=fdrop)
+    an = nb.jl_to_numpy(a)
+    assert 0.4 < (an > 0).mean() < 0.6
+    v4 = O.split_heads(qn, 2)
+    x4 = O.batched_mul(np.transpose(v4, (0, 2, 1, 3)), an)
+    np.testing.assert_allclose(nb.jl_to_numpy(y), O.join_heads(np.transpose(x4, (0, 2, 1, 3))), atol=1e-5)
+
+
+def test_bias_shapes():
+    # test/attention.jl:61-68
+    rng = np.random.default_rng(13)
+    qn = rng.random((4, 5, 1), dtype=np.float32); kn = rng.random((4, 3, 1), dtype=np.float32)
+    bn = rng.standard_normal((3, 5)).astype(np.float32)
+    y, a = nb.dot_product_attention(_dev(qn, torch.float32), _dev(kn, torch.float32), _dev(kn, torch.float32),
+                                    _dev(bn, torch.float32), nheads=2)
+    assert tuple(a.shape) == (3, 5, 2, 1) and tuple(y.shape) == (4, 5, 1)
+    yo, ao = O.dot_product_attention(qn, kn, kn, bn, nheads=2)
+    np.testing.assert_allclose(nb.jl_to_numpy(y), yo, atol=1e-5)
+    np.testing.assert_allclose(np.asarray(a), ao, atol=1e-5)
+
+
+def test_argument_errors_on_device():
+    z = lambda *s: nb.jl_zeros(s, torch.float32, DEV)
+    with pytest.raises(nb.ArgumentError, match="divisible"):
+        nb.dot_product_attention(z(6, 2, 1), z(6, 2, 1), z(6, 2, 1), nheads=4)
+    with pytest.raises(nb.ArgumentError, match="Batch"):
+        nb.dot_product_attention(z(4, 2, 1), z(4, 2, 2), z(4, 2, 2))
+    with pytest.raises(nb.ArgumentError, match="query and key"):
+        nb.dot_product_attention(z(4, 2, 1), z(6, 2, 1), z(6, 2, 1))
+    with pytest.raises(nb.ArgumentError, match="key and value"):
+        nb.dot_product_attention(z(4, 2, 1), z(4, 3, 1), z(4, 2, 1))
+    with pytest.raises(TypeError):
+        nb.dot_product_attention(z(4, 2, 1).cpu(), z(4, 2, 1), z(4, 2, 1))
+
+
+def test_fully_masked_query_is_nan():
+    rng = np.random.default_rng(14)
+    for dtype, E, nheads in ((torch.float32, 8, 2), (torch.bfloat16, 128, 2)):
+        qn = rng.standard_normal((E, 130, 1)).astype(np.float32)
+        kn = rng.standard_normal((E, 140, 1)).astype(np.float32)
+        mask = np.ones((140, 130), dtype=bool); mask[:, 5] = False; mask[:, 129] = False
+        y, a = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(kn, dtype),
+                                        mask=nb.jl_from_numpy(mask, device=DEV), nheads=nheads)
+        yn, an = nb.jl_to_numpy(y), np.asarray(a)
+        assert np.isnan(yn[:, 5]).all() and np.isnan(yn[:, 129]).all() and np.isfinite(yn[:, 6]).all()
+        assert np.isnan(an[:, 5]).all() and np.isfinite(an[:, 4]).all()
+
+
+# --------------------------------------------------------------------------
+# tensor-core path vs oracle on ragged and benchmark shapes
+# --------------------------------------------------------------------------
+
+def _run_case(dtype, E, nheads, Lq, Lkv, B, *, causal=False, mask=None, bias=None, Ev=None, seed=0,
+              expect_umma=True, check_alpha=True):
+    rng = np.random.default_rng(seed)
+    Ev = Ev or E
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((Ev, Lkv, B)), dtype)
+    q, k, v = _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype)
+    if expect_umma is not None:
+        assert _path(q, k, v, nheads) == (_lib.PATH_UMMA if expect_umma else _lib.PATH_SIMT)
+    mask_np = None
+    mask_arg = None
+    if causal:
+        mask_np = O.make_causal_mask(np.zeros((1, Lq)), dims=2)
+        mask_arg = nb.make_causal_mask(q, dims=2)
+    elif mask is not None:
+        mask_np = mask
+        mask_arg = nb.jl_from_numpy(mask, device=DEV)
+    bias_np = None
+    bias_arg = None
+    if bias is not None:
+        bias_np = _round_to(bias, dtype)
+        bias_arg = _dev(bias_np, dtype)
+    y, a = nb.dot_product_attention(q, k, v, bias_arg, mask=mask_arg, nheads=nheads)
+    yo, ao = O.dot_product_attention(qn, kn, vn, bias_np, mask=mask_np, nheads=nheads)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x")
+    if check_alpha:
+        an = np.asarray(a)
+        _close(an, ao, dtype, "alpha")
+        if mask_np is not None:
+            keep = np.broadcast_to(O._bcast_to_scores(mask_np), ao.shape)
+            assert (an[~keep] == 0).all(), "masked scores must be exactly 0"
+        np.testing.assert_allclose(an.sum(0), 1.0, atol=1e-2)
+    return y, a
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [64, 128])
+def test_umma_plain_single_tile(dtype, d):
+    _run_case(dtype, d, 1, 128, 128, 1, seed=20)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d,H,Lq,Lkv,B", [
+    (64, 2, 256, 256, 2),      # two query tiles, two kv tiles
+    (128, 2, 384, 512, 1),     # second CTA has one live tile only
+    (128, 1, 100, 200, 2),     # ragged in both directions
+    (64, 3, 257, 129, 1),      # one row / one key past a tile boundary
+    (128, 2, 1, 1, 1),         # smallest
+    (64, 1, 700, 1500, 1),     # many kv tiles: pipeline wraps around
+])
+def test_umma_shapes(dtype, d, H, Lq, Lkv, B):
+    _run_case(dtype, d * H, H, Lq, Lkv, B, seed=21)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d,H,L,B", [(64, 2, 128, 1), (128, 2, 256, 2), (128, 1, 300, 1), (64, 1, 1000, 1)])
+def test_umma_causal(dtype, d, H, L, B):
+    _run_case(dtype, d * H, H, L, L, B, causal=True, seed=22)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_umma_key_padding_mask(dtype):
+    # BASELINE config 2 in small: (kv_len, 1, 1, B) Bool mask with per-sample valid lengths
+    rng = np.random.default_rng(23)
+    Lkv, B = 384, 3
+    lens = rng.integers(Lkv // 2, Lkv + 1, size=B)
+    mask = (np.arange(Lkv)[:, None, None, None] < lens[None, None, None, :])
+    _run_case(dtype, 128, 2, 300, Lkv, B, mask=mask, seed=23)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("bias_shape", [(200, 150, 2, 2), (200, 150), (200, 1, 2, 1), (1, 150, 1, 2)])
+def test_umma_bias_broadcast(dtype, bias_shape):
+    rng = np.random.default_rng(24)
+    bias = (0.5 * rng.standard_normal(bias_shape)).astype(np.float32)
+    _run_case(dtype, 128, 2, 150, 200, 2, bias=bias, seed=24)
+
+
+def test_umma_random_mask_and_bias():
+    rng = np.random.default_rng(25)
+    mask = rng.random((260, 130, 2, 2)) > 0.3
+    mask[0] = True
+    bias = rng.standard_normal((260, 130, 1, 1)).astype(np.float32)
+    _run_case(torch.bfloat16, 256, 2, 130, 260, 2, mask=mask, bias=bias, seed=25)
+
+
+def test_simt_matches_oracle_for_other_shapes():
+    # shapes the tensor-core kernels do not take run on the CUDA-core kernels
+    _run_case(torch.float32, 96, 3, 70, 90, 2, seed=26, expect_umma=False)
+    _run_case(torch.bfloat16, 96, 2, 70, 90, 2, seed=27, expect_umma=False)       # d = 48
+    _run_case(torch.float16, 64, 1, 33, 65, 1, Ev=32, seed=28, expect_umma=False)  # dv != d
+    _run_case(torch.float32, 64, 2, 50, 50, 1, causal=True, seed=29, expect_umma=False)
+
+
+def test_nd_batch_and_lazy_alpha():
+    rng = np.random.default_rng(30)
+    dtype = torch.bfloat16
+    qn = _round_to(rng.standard_normal((128, 130, 2, 1, 3)), dtype)
+    q = _dev(qn, dtype)
+    y, a = nb.dot_product_attention(q, q, q, nheads=2)
+    assert isinstance(a, nb.LazyAttnScores) and not a.is_materialized
+    assert tuple(y.shape) == (128, 130, 2, 1, 3) and tuple(a.shape) == (130, 130, 2, 2, 1, 3)
+    yo, ao = O.dot_product_attention(qn, qn, qn, nheads=2)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x")
+    _close(np.asarray(a), ao, dtype, "alpha")
+
+
+# --------------------------------------------------------------------------
+# fused Philox dropout
+# --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype,E,H", [(torch.float16, 128, 2), (torch.float32, 32, 2)])
+def test_philox_dropout_exact_mask_and_values(dtype, E, H):
+    rng = np.random.default_rng(31)
+    Lq, Lkv, B, p, seed = 140, 270, 2, 0.1, 0xB200
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    fd = nb.PhiloxDropout(p, seed=seed, offset=3)
+    y, a = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), nheads=H, fdrop=fd)
+    an = np.asarray(a)
+    keep = P.keep_mask((Lkv, Lq, H, B), p, seed, offset=3)
+    _, a0 = O.dot_product_attention(qn, kn, vn, nheads=H)
+    assert abs(keep.mean() - (1 - p)) < 0.01
+    # the device drew exactly the oracle's mask (scores are > 0 everywhere before dropout)
+    assert ((an > 0) == keep).all()
+    want_a = a0 * keep / np.float32(1 - p)
+    _close(an, want_a.astype(np.float32), dtype, "alpha'")
+    # x equals V·α′ for that mask
+    fdrop_o = lambda al: al * keep / np.float32(1 - p)
+    yo, _ = O.dot_product_attention(qn, kn, vn, nheads=H, fdrop=fdrop_o)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x")
+    # a second object with the same (p, seed, offset) reproduces the call; the next offset differs
+    y2, _ = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), nheads=H,
+                                     fdrop=nb.PhiloxDropout(p, seed=seed, offset=3))
+    assert torch.equal(y, y2)
+    y3, _ = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), nheads=H, fdrop=fd)
+    assert not torch.equal(y, y3)
+
+
+def test_philox_dropout_rate_like_reference():
+    # test/attention.jl:54-59 with the fused fdrop
+    rng = np.random.default_rng(32)
+    q = _dev(rng.random((128, 64, 10), dtype=np.float32), torch.bfloat16)
+    y, a = nb.dot_product_attention(q, q, q, nheads=2, fdrop=nb.PhiloxDropout(0.5, seed=1))
+    frac = (np.asarray(a) > 0).mean()
+    assert 0.4 < frac < 0.6
+
+
+# --------------------------------------------------------------------------
+# raw C-ABI: strides, separate entry points, status word
+# --------------------------------------------------------------------------
+
+def test_abi_strided_head_slice_and_entry_points():
+    """A shard that owns heads 1..2 of 4 addresses the parent arrays through
+    pointer offsets and the parent's strides (no copy), and the four entry
+    points agree with each other."""
+    import ctypes as C
+    lib = _lib.load()
+    rng = np.random.default_rng(33)
+    dtype = torch.bfloat16
+    H, d, Lq, Lkv, B = 4, 64, 200, 333, 2
+    E = H * d
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    q, k, v = _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype)
+    x = nb.jl_zeros((E, Lq, B), dtype, DEV)
+    h0, Hs = 1, 2
+    lse = torch.empty((B, Hs, Lq), dtype=torch.float32, device=DEV)
+    alpha = nb.jl_empty((Lkv, Lq, Hs, B), dtype, DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    p = _lib.AttnParams()
+    p.dtype = _lib.BF16
+    p.d, p.dv, p.H, p.Lq, p.Lkv, p.B = d, d, Hs, Lq, Lkv, B
+    off = h0 * d * 2
+    p.q, p.k, p.v, p.x = q.data_ptr() + off, k.data_ptr() + off, v.data_ptr() + off, x.data_ptr() + off
+    p.q_stride_l = p.k_stride_l = p.v_stride_l = p.x_stride_l = E
+    p.q_stride_b, p.x_stride_b = E * Lq, E * Lq
+    p.k_stride_b = p.v_stride_b = E * Lkv
+    p.lse, p.alpha, p.status = lse.data_ptr(), alpha.data_ptr(), status.data_ptr()
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.nnlib_b200_attn_path(p) == _lib.PATH_UMMA
+    assert lib.nnlib_b200_attn_fwd(C.byref(p), st) == 0
+    assert lib.nnlib_b200_attn_scores(C.byref(p), st) == 0
+    lse2 = torch.empty_like(lse)
+    p.lse = lse2.data_ptr()
+    assert lib.nnlib_b200_attn_stats(C.byref(p), st) == 0
+    x2 = nb.jl_zeros((E, Lq, B), dtype, DEV)
+    p.x = x2.data_ptr() + off
+    assert lib.nnlib_b200_attn_apply(C.byref(p), st) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    yo, ao = O.dot_product_attention(qn, kn, vn, nheads=H)
+    xs = nb.jl_to_numpy(x)
+    _close(xs[h0 * d:(h0 + Hs) * d], yo[h0 * d:(h0 + Hs) * d], dtype, "x shard")
+    assert (xs[:h0 * d] == 0).all() and (xs[(h0 + Hs) * d:] == 0).all(), "wrote outside the shard"
+    _close(nb.jl_to_numpy(alpha), ao[:, :, h0:h0 + Hs], dtype, "alpha shard")
+    np.testing.assert_allclose(lse.cpu().numpy(), lse2.cpu().numpy(), atol=2e-3)
+    # lse is the natural-log sum of exponentials of the scaled logits
+    logits = np.einsum("ehjb,ehib->jihb", O.split_heads(kn, H), O.split_heads(qn, H)) / math.sqrt(d)
+    want_lse = np.log(np.exp(logits - logits.max(0)).sum(0)) + logits.max(0)        # (Lq, H, B)
+    np.testing.assert_allclose(lse.cpu().numpy().transpose(2, 1, 0), want_lse[:, h0:h0 + Hs], atol=2e-2)
+    # attn_apply (x = V·α from the stored bf16 scores) agrees with the fused x
+    _close(nb.jl_to_numpy(x2)[h0 * d:(h0 + Hs) * d], yo[h0 * d:(h0 + Hs) * d], dtype, "apply x")
+
+
+def test_abi_attention_one_call_with_workspace():
+    import ctypes as C
+    lib = _lib.load()
+    rng = np.random.default_rng(34)
+    dtype = torch.float16
+    H, d, L, B = 2, 128, 160, 1
+    qn = _round_to(rng.standard_normal((H * d, L, B)), dtype)
+    q = _dev(qn, dtype)
+    x = nb.jl_empty((H * d, L, B), dtype, DEV)
+    alpha = nb.jl_empty((L, L, H, B), dtype, DEV)
+    p = _lib.AttnParams()
+    p.dtype = _lib.F16
+    p.d, p.dv, p.H, p.Lq, p.Lkv, p.B = d, d, H, L, L, B
+    p.q = p.k = p.v = q.data_ptr()
+    p.x, p.alpha = x.data_ptr(), alpha.data_ptr()
+    p.causal = 1
+    need = lib.nnlib_b200_workspace_bytes(C.byref(p))
+    assert need == L * H * B * 4
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.nnlib_b200_attention(C.byref(p), ws.data_ptr(), need - 1, st) == _lib.WORKSPACE_TOO_SMALL
+    assert lib.nnlib_b200_attention(C.byref(p), ws.data_ptr(), need, st) == 0
+    torch.cuda.synchronize()
+    yo, ao = O.dot_product_attention(qn, qn, qn, mask=O.make_causal_mask(qn), nheads=H)
+    _close(nb.jl_to_numpy(x), yo, dtype, "x")
+    _close(nb.jl_to_numpy(alpha), ao, dtype, "alpha")
+
+
+def test_causal_check_kernel():
+    import ctypes as C
+    lib = _lib.load()
+    L = 77
+    m = nb.jl_empty((L, L), torch.bool, DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.nnlib_b200_causal_fill(m.view(torch.uint8).data_ptr(), L, st) == 0
+    assert lib.nnlib_b200_causal_check(m.view(torch.uint8).data_ptr(), L, flag.data_ptr(), st) == 0
+    assert flag.item() == 1
+    m[5, 3] = True   # below the diagonal
+    assert lib.nnlib_b200_causal_check(m.view(torch.uint8).data_ptr(), L, flag.data_ptr(), st) == 0
+    assert flag.item() == 0
+
+
+# --------------------------------------------------------------------------
+# benchmark configurations (BASELINE.json configs 2-5), full size where the
+# oracle finishes in seconds, otherwise row-sampled
+# --------------------------------------------------------------------------
+
+def _sample_rows(L):
+    base = [0, 1, 127, 128, 129, 255, 256, L // 2, L - 129, L - 128, L - 2, L - 1]
+    return np.array(sorted({r for r in base if 0 <= r < L}))
+
+
+def _check_rows(q, k, v, y, lse, H, units, dtype, *, causal=False, mask=None, bias=None):
+    qn, kn, vn = (nb.jl_to_numpy(t) for t in (q, k, v))
+    yn = nb.jl_to_numpy(y)
+    d = qn.shape[0] // H
+    rows = _sample_rows(qn.shape[1])
+    for (b, h) in units:
+        xr, ar, lr = O.attention_rows(qn, kn, vn, H, rows, b, h, causal=causal, mask=mask, bias=bias)
+        _close(yn[h * d:(h + 1) * d][:, rows, b], xr.astype(np.float32), dtype, f"x rows of unit {(b, h)}")
+        if lse is not None:
+            np.testing.assert_allclose(lse[rows, h, b], lr, atol=2e-2)
+
+
+def test_config2_encoder_key_padding():
+    # bf16, E=768, nheads=12, L=512, batch=32 → batch 8 here (same shape class), α returned
+    rng = np.random.default_rng(40)
+    dtype, E, H, L, B = torch.bfloat16, 768, 12, 512, 8
+    lens = rng.integers(256, 513, size=B)
+    mask = (np.arange(L)[:, None, None, None] < lens[None, None, None, :])
+    _run_case(dtype, E, H, L, L, B, mask=mask, seed=40)
+
+
+def test_config3_decoder_causal_row_sampled():
+    # bf16, E=4096, nheads=32, L=4096, causal; batch 2 of the 8 (each batch is an independent unit set)
+    dtype, E, H, L, B = torch.bfloat16, 4096, 32, 4096, 2
+    g = torch.Generator(device=DEV).manual_seed(41)
+    q, k, v = (nb.jl_empty((E, L, B), dtype, DEV) for _ in range(3))
+    for t in (q, k, v):
+        t.normal_(generator=g)
+    y, a = nb.dot_product_attention(q, k, v, mask=nb.make_causal_mask(q), nheads=H)
+    assert not a.is_materialized
+    lse = a._problem.lse.cpu().numpy()
+    _check_rows(q, k, v, y, lse, H, [(0, 0), (1, 31), (0, 17)], dtype, causal=True)
+
+
+def test_config4_cross_attention_bias_dropout():
+    # fp16 q (1024, 256, B), k/v (1024, 2048, B), nheads=16, bias (Lkv, Lq, H, B) ~ N(0, 0.5), p=0.1; B=2 of 16
+    rng = np.random.default_rng(42)
+    dtype, E, H, Lq, Lkv, B, p = torch.float16, 1024, 16, 256, 2048, 2, 0.1
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    bn = _round_to(0.5 * rng.standard_normal((Lkv, Lq, H, B)), dtype)
+    fd = nb.PhiloxDropout(p, seed=0xB200, offset=0)
+    y, a = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), _dev(bn, dtype),
+                                    nheads=H, fdrop=fd)
+    keep = P.keep_mask((Lkv, Lq, H, B), p, 0xB200, 0)
+    fdrop_o = lambda al: al * keep / np.float32(1 - p)
+    yo, ao = O.dot_product_attention(qn, kn, vn, bn, nheads=H, fdrop=fdrop_o)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x")
+    an = np.asarray(a)
+    assert ((an > 0) == (keep & (ao > 0))).mean() > 0.9999   # f16 underflow may zero a few tiny scores
+    _close(an, ao, dtype, "alpha'")
+
+
+def test_config5_long_context_row_sampled():
+    # bf16, E=2048, nheads=16, L=32768, causal; one batch of the 8
+    dtype, E, H, L, B = torch.bfloat16, 2048, 16, 32768, 1
+    g = torch.Generator(device=DEV).manual_seed(43)
+    q, k, v = (nb.jl_empty((E, L, B), dtype, DEV) for _ in range(3))
+    for t in (q, k, v):
+        t.normal_(generator=g)
+    y, a = nb.dot_product_attention(q, k, v, mask=nb.CausalMask(), nheads=H)
+    lse = a._problem.lse.cpu().numpy()
+    _check_rows(q, k, v, y, lse, H, [(0, 0), (0, 15)], dtype, causal=True)
+
+
+def test_linearity_in_v_full_size():
+    """Size-independent property at config-3 size: attention is linear in v, so
+    x(v1 + v2) = x(v1) + x(v2) up to rounding, and x(v = const) = const."""
+    dtype, E, H, L, B = torch.bfloat16, 4096, 32, 4096, 1
+    g = torch.Generator(device=DEV).manual_seed(44)
+    q, k = (nb.jl_empty((E, L, B), dtype, DEV) for _ in range(2))
+    q.normal_(generator=g); k.normal_(generator=g)
+    ones = nb.jl_empty((E, L, B), dtype, DEV); ones.fill_(1.0)
+    y, _ = nb.dot_product_attention(q, k, ones, mask=nb.CausalMask(), nheads=H)
+    assert (y.float() - 1).abs().max().item() <= 2e-2
