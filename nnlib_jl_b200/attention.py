@@ -106,7 +106,8 @@ def _bcast_strides(name: str, t: torch.Tensor, full: tuple) -> list:
 class _Problem:
     """Everything one call of the library needs, kept alive together."""
 
-    def __init__(self, q, k, v, bias, mask, nheads, dropout: Optional[PhiloxDropout], need_v: bool):
+    def __init__(self, q, k, v, bias, mask, nheads, dropout: Optional[PhiloxDropout], need_v: bool,
+                 rng_origin=None):
         self.dev = q.device
         self.dtype = q.dtype
         E, Lq, B = q.shape
@@ -156,6 +157,9 @@ class _Problem:
             p.dropout_p = dropout.p
             p.philox_seed = dropout.seed & 0xFFFFFFFFFFFFFFFF
             p.philox_offset = dropout.take_offset() & 0xFFFFFFFFFFFFFFFF
+            if rng_origin is not None:
+                # this call is a shard: (first head, first batch, heads of the whole problem)
+                p.rng_h0, p.rng_b0, p.rng_H = (int(v_) for v_ in rng_origin)
         self.p = p
 
     def alloc_lse(self):
@@ -353,6 +357,19 @@ def _fused(q, k, v, bias, mask, nheads, dropout):
         with torch.cuda.device(pr.dev):
             _check(_lib.load().nnlib_b200_attn_fwd(C.byref(pr.p), _stream()), "attn_fwd")
     return x, LazyAttnScores(pr, (pr.Lkv, pr.Lq, pr.H, pr.B))
+
+
+def _fused_with_origin(q, k, v, bias, mask, nheads, dropout, rng_origin):
+    """The fused call for a shard of a larger problem (see ``shard.py``):
+    ``rng_origin`` places the shard's heads and batches in the whole problem so
+    that dropout draws the whole problem's mask.  Returns x only."""
+    pr = _Problem(q, k, v, bias, mask, nheads, dropout, need_v=True, rng_origin=rng_origin)
+    x = pr.alloc_x()
+    pr.alloc_lse()
+    if pr.Lq > 0 and pr.B > 0:
+        with torch.cuda.device(pr.dev):
+            _check(_lib.load().nnlib_b200_attn_fwd(C.byref(pr.p), _stream()), "attn_fwd")
+    return x
 
 
 def _unfused(q, k, v, bias, mask, nheads, fdrop):
