@@ -259,6 +259,14 @@ def run_ours(args, w):
     nb.device_health(dev)
 
     # ---- end-to-end timing from pinned host buffers ------------------------
+    if args.no_e2e:
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"note": "kernel-only run (--no-e2e): not a bench line", "ms_per_step": ms_total / args.steps,
+                              "tflops": algorithmic_flops(w) / (ms_total / args.steps * 1e-3) / 1e12}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     hq, hk, hv = (torch.empty(t.permute(2, 1, 0).shape, dtype=tdtype).pin_memory() for t in (q, k, v))
     for h, t in ((hq, q), (hk, k), (hv, v)):
         h.copy_(t.permute(2, 1, 0))
@@ -340,9 +348,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (smaller profiler captures)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        w["B"] = args.batch
+        w["desc"] += f" [batch overridden to {args.batch}]"
     if args.impl == "reference":
         run_reference(args, w)
     else:

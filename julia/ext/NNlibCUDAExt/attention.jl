@@ -1,0 +1,333 @@
+# B200 attention methods for NNlibCUDAExt.
+#
+# Add `include("attention.jl")` to ext/NNlibCUDAExt/NNlibCUDAExt.jl (after
+# `include("utils.jl")`).  The methods below are strictly more specific than the
+# generic ones in src/attention.jl (:52 and :112), so dense `CuArray`s of
+# Float16 / BFloat16 / Float32 dispatch here and everything else (views,
+# PermutedDimsArray, Float64, complex) keeps running the generic code.  The N-d
+# wrapper (src/attention.jl:40-50) reaches the 3-d method unchanged because
+# `reshape(::CuArray)` is a `CuArray`.
+#
+# All arithmetic happens in libnnlib_b200.so (C ABI: include/nnlib_b200.h),
+# called with device pointers on the task's current stream.  No cuBLAS, cuDNN
+# or KernelAbstractions on this path.
+#
+# NOTE: this file mirrors, statement for statement, the Python ctypes caller
+# (nnlib_jl_b200/attention.py), which is the tested one: no Julia toolchain was
+# available where the library was developed, so this source has not been
+# executed.  test/ext_cuda/attention.jl is the test to run first.
+
+using CUDA: CuArray, DenseCuArray, CuPtr, CU_NULL, stream, device, device!, devices
+import NNlib: dot_product_attention, dot_product_attention_scores, make_causal_mask
+
+# BFloat16 lives in Core from Julia 1.11 on; with BFloat16s.jl loaded on 1.10 use its type instead.
+const _BF16 = isdefined(Core, :BFloat16) ? Core.BFloat16 : Union{}
+const B200Float = Union{Float16,_BF16,Float32}
+
+const libnnlib_b200 = Ref{String}(get(ENV, "NNLIB_B200_LIB", "libnnlib_b200"))
+
+_b200_dtype(::Type{Float16}) = Int32(0)
+_b200_dtype(::Type{Float32}) = Int32(2)
+_b200_dtype(::Type{T}) where {T} = T === _BF16 ? Int32(1) : throw(ArgumentError("unsupported eltype $T"))
+
+# Mirror of `nnlib_b200_attn_params` (include/nnlib_b200.h): same order, same types.
+Base.@kwdef struct B200AttnParams
+    struct_size::Csize_t = 0
+    dtype::Int32 = 0
+    bias_dtype::Int32 = 0
+    d::Int64 = 0; dv::Int64 = 0; H::Int64 = 0; Lq::Int64 = 0; Lkv::Int64 = 0; B::Int64 = 0
+    q::CuPtr{Cvoid} = CU_NULL; k::CuPtr{Cvoid} = CU_NULL; v::CuPtr{Cvoid} = CU_NULL; x::CuPtr{Cvoid} = CU_NULL
+    q_stride_l::Int64 = 0; q_stride_b::Int64 = 0
+    k_stride_l::Int64 = 0; k_stride_b::Int64 = 0
+    v_stride_l::Int64 = 0; v_stride_b::Int64 = 0
+    x_stride_l::Int64 = 0; x_stride_b::Int64 = 0
+    bias::CuPtr{Cvoid} = CU_NULL
+    bias_stride::NTuple{4,Int64} = (0, 0, 0, 0)
+    mask::CuPtr{UInt8} = CU_NULL
+    mask_stride::NTuple{4,Int64} = (0, 0, 0, 0)
+    causal::Int32 = 0
+    nan_on_fully_masked::Int32 = 1
+    scale::Float32 = 0f0
+    dropout_p::Float32 = 0f0
+    philox_seed::UInt64 = 0
+    philox_offset::UInt64 = 0
+    rng_h0::Int64 = 0; rng_b0::Int64 = 0; rng_H::Int64 = 0
+    lse::CuPtr{Float32} = CU_NULL
+    lse_stride_b::Int64 = 0
+    alpha::CuPtr{Cvoid} = CU_NULL
+    alpha_stride_b::Int64 = 0
+    status::CuPtr{Int32} = CU_NULL
+end
+
+function _b200_check(rc::Cint, where::String)
+    rc == 0 && return nothing
+    msg = unsafe_string(ccall((:nnlib_b200_strerror, libnnlib_b200[]), Cstring, (Cint,), rc))
+    rc == -1 ? throw(ArgumentError("$where: $msg")) : error("$where: $msg [$rc]")
+end
+
+for name in (:attn_fwd, :attn_stats, :attn_scores, :attn_apply)
+    fn = Symbol(:_b200_, name)
+    sym = QuoteNode(Symbol(:nnlib_b200_, name))
+    @eval function $fn(p::B200AttnParams)
+        rc = ccall(($sym, libnnlib_b200[]), Cint, (Ref{B200AttnParams}, Ptr{Cvoid}), p, stream().handle)
+        _b200_check(rc, $(string(name)))
+    end
+end
+
+"""
+    PhiloxDropout(p; seed, offset=0)
+
+`fdrop` that the fused kernels run in place: whether score `(j, i, h, b)` survives
+is a pure function of `(seed, offset)` and the position (Philox4x32-10), with the
+keep rule of `NNlib.dropout` (keep iff `u > p`, survivors scaled by `1/(1-p)`).
+Every use consumes one offset.
+"""
+mutable struct PhiloxDropout
+    p::Float32
+    seed::UInt64
+    offset::UInt64
+    function PhiloxDropout(p::Real; seed::Integer=rand(UInt64), offset::Integer=0)
+        0 <= p < 1 || throw(ArgumentError("PhiloxDropout expects a probability 0 <= p < 1"))
+        new(Float32(p), UInt64(seed), UInt64(offset))
+    end
+end
+_take_offset!(d::PhiloxDropout) = (o = d.offset; d.offset += 1; o)
+
+"Sentinel for `mask=`: the causal pattern `kv <= query` without the `(L, L)` Bool matrix."
+struct CausalMask end
+
+# Bool matrices known to hold make_causal_mask's pattern, by device address.
+const _known_causal = Dict{CuPtr{Bool},Int}()
+
+function make_causal_mask(x::CuArray; dims::Int=2)
+    len = size(x, dims)
+    mask = similar(x, Bool, (len, len))
+    rc = ccall((:nnlib_b200_causal_fill, libnnlib_b200[]), Cint, (CuPtr{UInt8}, Int64, Ptr{Cvoid}),
+               reinterpret(CuPtr{UInt8}, pointer(mask)), len, stream().handle)
+    _b200_check(rc, "causal_fill")
+    _known_causal[pointer(mask)] = len
+    finalizer(m -> delete!(_known_causal, pointer(m)), mask)
+    return mask
+end
+
+function _is_causal_matrix(mask::DenseCuArray{Bool,2}, Lq, Lkv)
+    (Lq == Lkv && size(mask) == (Lkv, Lq)) || return false
+    get(_known_causal, pointer(mask), -1) == Lq && return true
+    flag = CUDA.zeros(Int32, 1)
+    rc = ccall((:nnlib_b200_causal_check, libnnlib_b200[]), Cint, (CuPtr{UInt8}, Int64, CuPtr{Int32}, Ptr{Cvoid}),
+               reinterpret(CuPtr{UInt8}, pointer(mask)), Lq, pointer(flag), stream().handle)
+    _b200_check(rc, "causal_check")
+    return Array(flag)[1] == 1
+end
+_is_causal_matrix(mask, Lq, Lkv) = false
+
+# element strides of a bias/mask against the (Lkv, Lq, H, B) scores; 0 where it broadcasts
+function _bcast_strides(name, t::AbstractArray, full::NTuple{4,Int})
+    ndims(t) <= 4 || throw(ArgumentError("$name has $(ndims(t)) dimensions; scores have 4"))
+    ntuple(4) do dim
+        sz = size(t, dim)
+        sz == 1 ? 0 : sz == full[dim] ? Int64(stride(t, dim)) :
+            throw(ArgumentError("$name of size $(size(t)) does not broadcast to scores of size $full"))
+    end
+end
+
+function _b200_params(q::DenseCuArray{T,3}, k::DenseCuArray{T,3}, v, bias, mask, nheads, dropout;
+                      rng_origin=nothing) where {T}
+    E, Lq, B = size(q); Lkv = size(k, 2); H = nheads
+    Ev = v === nothing ? E : size(v, 1)
+    full = (Lkv, Lq, H, B)
+    causal = false
+    mptr = CuPtr{UInt8}(0); mstr = (0, 0, 0, 0)
+    if mask isa CausalMask
+        causal = true
+    elseif mask !== nothing
+        eltype(mask) === Bool || throw(ArgumentError("mask must be a Bool array"))
+        if _is_causal_matrix(mask, Lq, Lkv)
+            causal = true
+        else
+            mstr = _bcast_strides("mask", mask, full)
+            mptr = reinterpret(CuPtr{UInt8}, pointer(mask))
+        end
+    end
+    bptr = CuPtr{Cvoid}(0); bstr = (0, 0, 0, 0); bdt = Int32(0)
+    if bias !== nothing
+        bstr = _bcast_strides("bias", bias, full)
+        bptr = reinterpret(CuPtr{Cvoid}, pointer(bias)); bdt = _b200_dtype(eltype(bias))
+    end
+    p, seed, off = 0f0, UInt64(0), UInt64(0)
+    if dropout !== nothing && dropout.p > 0
+        p, seed, off = dropout.p, dropout.seed, _take_offset!(dropout)
+    end
+    h0, b0, Htot = rng_origin === nothing ? (0, 0, 0) : rng_origin
+    B200AttnParams(; struct_size=sizeof(B200AttnParams), dtype=_b200_dtype(T), bias_dtype=bdt,
+        d=E ÷ H, dv=Ev ÷ H, H, Lq, Lkv, B,
+        q=reinterpret(CuPtr{Cvoid}, pointer(q)), k=reinterpret(CuPtr{Cvoid}, pointer(k)),
+        v=v === nothing ? CuPtr{Cvoid}(0) : reinterpret(CuPtr{Cvoid}, pointer(v)),
+        bias=bptr, bias_stride=bstr, mask=mptr, mask_stride=mstr, causal=Int32(causal),
+        dropout_p=p, philox_seed=seed, philox_offset=off, rng_h0=h0, rng_b0=b0, rng_H=Htot)
+end
+
+_with(p::B200AttnParams; kw...) = B200AttnParams(; (f => getfield(p, f) for f in fieldnames(B200AttnParams))..., kw...)
+
+"""
+    LazyAttnScores{T} <: AbstractArray{T,N}
+
+The `α` of `(x, α) = dot_product_attention(...)` on the B200 path.  The fused
+kernel keeps one log-sum-exp per query; the `(kv_len, q_len, nheads, batch...)`
+array is rebuilt from it (with the same dropout mask) by a second kernel the
+first time an element is needed.  `x, _ = dot_product_attention(...)` never
+pays for it.
+"""
+mutable struct LazyAttnScores{T,N} <: AbstractArray{T,N}
+    dims::NTuple{N,Int}
+    params::B200AttnParams
+    keep::Any                                  # q, k, bias, mask, lse: kept alive for the rebuild
+    value::Union{Nothing,CuArray{T,4}}
+end
+Base.size(a::LazyAttnScores) = a.dims
+function materialize!(a::LazyAttnScores{T}) where {T}
+    if a.value === nothing
+        p = a.params
+        α = CuArray{T}(undef, p.Lkv, p.Lq, p.H, p.B)
+        GC.@preserve a α _b200_attn_scores(_with(p; alpha=reinterpret(CuPtr{Cvoid}, pointer(α))))
+        a.value = α
+    end
+    return reshape(a.value, a.dims)
+end
+Base.reshape(a::LazyAttnScores{T}, dims::Dims{N}) where {T,N} =
+    (prod(dims) == prod(a.dims) || throw(DimensionMismatch()); LazyAttnScores{T,N}(dims, a.params, (a.keep, a), a.value))
+Base.getindex(a::LazyAttnScores, I...) = CUDA.@allowscalar materialize!(a)[I...]
+Base.Array(a::LazyAttnScores) = Array(materialize!(a))
+Base.collect(a::LazyAttnScores) = Array(a)
+CUDA.CuArray(a::LazyAttnScores) = materialize!(a)
+Base.Broadcast.broadcastable(a::LazyAttnScores) = materialize!(a)
+Base.sum(a::LazyAttnScores; kw...) = sum(materialize!(a); kw...)
+
+function dot_product_attention(q::DenseCuArray{T,3}, k::DenseCuArray{T,3}, v::DenseCuArray{T,3}, bias=nothing;
+                               fdrop=identity, mask=nothing, nheads=1) where {T<:B200Float}
+    # the reference's four checks, same order and text (src/attention.jl:55-78)
+    (all(size.((q, k, v), 1) .% nheads .== 0)) || throw(ArgumentError("""
+    First dimension in query, key and value must be divisible by `nheads`.
+    Instead:
+    - size(q): $(size(q))
+    - size(k): $(size(k))
+    - size(v): $(size(v))
+    - nheads: $nheads
+    """))
+    (size(q, 3) == size(k, 3) == size(v, 3)) || throw(ArgumentError("""
+    Batch dimensions have to be the same. Instead:
+    - size(q): $(size(q))
+    - size(k): $(size(k))
+    - size(v): $(size(v))
+    """))
+    size(q, 1) == size(k, 1) || throw(ArgumentError("""
+    First dimension in query and key has to be the same. Instead:
+    - size(q): $(size(q))
+    - size(k): $(size(k))
+    """))
+    size(k, 2) == size(v, 2) || throw(ArgumentError("""
+    Second dimension in key and value has to be the same. Instead:
+    - size(k): $(size(k))
+    - size(v): $(size(v))
+    """))
+    Ev, Lq, B = size(v, 1), size(q, 2), size(q, 3); Lkv = size(k, 2)
+    x = similar(q, T, (Ev, Lq, B))
+    lse = CuArray{Float32}(undef, Lq, nheads, B)
+    if fdrop === identity || fdrop isa PhiloxDropout
+        p = _b200_params(q, k, v, bias, mask, nheads, fdrop isa PhiloxDropout ? fdrop : nothing)
+        p = _with(p; x=reinterpret(CuPtr{Cvoid}, pointer(x)), lse=pointer(lse))
+        GC.@preserve q k v x lse bias mask (Lq > 0 && B > 0 && _b200_attn_fwd(p))
+        α = LazyAttnScores{T,4}((Lkv, Lq, nheads, B), p, (q, k, bias, mask, lse), nothing)
+        return x, α
+    else
+        # opaque fdrop: materialise α, let the caller's function transform it, x = V·α′ (src/attention.jl:91-98)
+        p = _b200_params(q, k, v, bias, mask, nheads, nothing)
+        α = CuArray{T}(undef, Lkv, Lq, nheads, B)
+        p = _with(p; x=reinterpret(CuPtr{Cvoid}, pointer(x)), lse=pointer(lse), alpha=reinterpret(CuPtr{Cvoid}, pointer(α)))
+        GC.@preserve q k v x lse α bias mask begin
+            if Lq > 0 && B > 0
+                _b200_attn_stats(p); _b200_attn_scores(p)
+            end
+            α′ = convert(CuArray{T,4}, fdrop(α))
+            size(α′) == size(α) || throw(ArgumentError("fdrop must return an array of the scores' size"))
+            GC.@preserve α′ (Lq > 0 && B > 0 &&
+                _b200_attn_apply(_with(p; alpha=reinterpret(CuPtr{Cvoid}, pointer(α′)))))
+            return x, α′
+        end
+    end
+end
+
+function dot_product_attention_scores(q::DenseCuArray{T,4}, k::DenseCuArray{T,4}, bias=nothing;
+                                      fdrop=identity, mask=nothing) where {T<:B200Float}
+    d, H, Lq, B = size(q); Lkv = size(k, 3)
+    q3, k3 = reshape(q, d * H, Lq, B), reshape(k, d * H, Lkv, B)
+    dropout = fdrop isa PhiloxDropout ? fdrop : nothing
+    α = CuArray{T}(undef, Lkv, Lq, H, B)
+    lse = CuArray{Float32}(undef, Lq, H, B)
+    p = _with(_b200_params(q3, k3, nothing, bias, mask, H, dropout);
+              lse=pointer(lse), alpha=reinterpret(CuPtr{Cvoid}, pointer(α)))
+    GC.@preserve q k α lse bias mask if Lq > 0 && B > 0 && Lkv > 0
+        _b200_attn_stats(p); _b200_attn_scores(p)
+    end
+    return (dropout === nothing && fdrop !== identity) ? fdrop(α) : α
+end
+
+# ---------------------------------------------------------------------------
+# multi-GPU driver: the independent (batch, head) units over the devices of one box,
+# one Julia task per device, no collective (every unit is a separate problem,
+# src/attention.jl:87-99).
+# ---------------------------------------------------------------------------
+"Contiguous, balanced unit ranges (unit u = b*H + h) as (b0, nb, h0, nh) rectangles, one list per shard."
+function partition_units(B::Int, H::Int, n::Int)
+    total = B * H; base, extra = divrem(total, n)
+    plan = Vector{Vector{NTuple{4,Int}}}(); u = 0
+    for r in 0:n-1
+        cnt = base + (r < extra ? 1 : 0); rects = NTuple{4,Int}[]; stop = u + cnt
+        while u < stop
+            b, h = divrem(u, H)
+            if h == 0 && stop - u >= H
+                nb = (stop - u) ÷ H; push!(rects, (b, nb, 0, H)); u += nb * H
+            else
+                nh = min(H - h, stop - u); push!(rects, (b, 1, h, nh)); u += nh
+            end
+        end
+        push!(plan, rects)
+    end
+    return plan
+end
+
+"""
+    sharded_attention(q, k, v; nheads, mask=nothing, fdrop=identity, devs=collect(devices()))
+
+`dot_product_attention` of host arrays `q, k, v` with the units spread over `devs`.
+Returns `x` on the host and a vector of per-device `(ok, error)` status; a failing
+device does not disturb the slices of the others.
+"""
+function sharded_attention(q::Array{T,3}, k::Array{T,3}, v::Array{T,3}; nheads=1, mask=nothing,
+                           fdrop=identity, devs=collect(devices())) where {T}
+    E, Lq, B = size(q); Ev = size(v, 1); d, dv = E ÷ nheads, Ev ÷ nheads
+    x = Array{T}(undef, Ev, Lq, B)
+    drop = fdrop isa PhiloxDropout ? PhiloxDropout(fdrop.p; seed=fdrop.seed, offset=_take_offset!(fdrop)) : nothing
+    plan = partition_units(B, nheads, length(devs))
+    status = Vector{Any}(undef, length(devs))
+    @sync for (r, dev) in enumerate(devs)
+        Threads.@spawn try
+            device!(dev)
+            for (b0, nb, h0, nh) in plan[r]
+                bs = b0+1:b0+nb
+                qd = CuArray(q[h0*d+1:(h0+nh)*d, :, bs]); kd = CuArray(k[h0*d+1:(h0+nh)*d, :, bs])
+                vd = CuArray(v[h0*dv+1:(h0+nh)*dv, :, bs])
+                xd = similar(qd, T, (nh * dv, Lq, nb)); lse = CuArray{Float32}(undef, Lq, nh, nb)
+                dr = drop === nothing ? nothing : PhiloxDropout(drop.p; seed=drop.seed, offset=drop.offset)
+                p = _b200_params(qd, kd, vd, nothing, mask, nh, dr; rng_origin=(h0, b0, nheads))
+                p = _with(p; x=reinterpret(CuPtr{Cvoid}, pointer(xd)), lse=pointer(lse))
+                GC.@preserve qd kd vd xd lse _b200_attn_fwd(p)
+                x[h0*dv+1:(h0+nh)*dv, :, bs] .= Array(xd)
+            end
+            status[r] = (true, nothing)
+        catch err
+            status[r] = (false, err)
+        end
+    end
+    return x, status
+end

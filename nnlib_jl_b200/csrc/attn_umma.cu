@@ -33,6 +33,16 @@ namespace nb200 {
 
 __device__ int g_umma_abort = 0;  // sticky: a bounded wait ran out somewhere
 
+#ifdef NB200_TRACE
+// Development aid: per-phase clock stamps of one CTA (block 0), read back by a
+// test harness.  Not compiled into the shipped library.
+__device__ long long g_trace[3][64][8];
+#define NB_TRACE(role, j, slot) \
+  do { if (blockIdx.x == NB200_TRACE_BLOCK && (j) < 64) g_trace[role][j][slot] = clock64(); } while (0)
+#else
+#define NB_TRACE(role, j, slot) do { } while (0)
+#endif
+
 namespace {
 
 using namespace ptx;
@@ -233,15 +243,19 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (!have_v) { ok = mbar_wait(&bars->v_full[sv], (j / C::kStages) & 1, abort_flag); have_v = true; }
             if (!ok) break;
             tc_fence_after();
+            NB_TRACE(2, j, t * 4 + 0);
             issue_pv(t, sv, j == 0);
+            NB_TRACE(2, j, t * 4 + 1);
             if (j == n_t[t] - 1) umma_commit(&bars->o_full[t]);
           }
           if (j + 1 < n_t[t]) {
             if (!have_k) { ok = mbar_wait(&bars->k_full[sk], ((j + 1) / C::kStages) & 1, abort_flag); have_k = true; }
             if (!ok) break;
             tc_fence_after();
+            NB_TRACE(2, j, t * 4 + 2);
             issue_qk(t, sk);
             umma_commit(&bars->s_full[t]);
+            NB_TRACE(2, j, t * 4 + 3);
           }
         }
         if (!ok) break;
@@ -271,14 +285,17 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     bool ok = true;
 
     for (int j = 0; j < n_t[t]; ++j) {
+      if (r == 0) NB_TRACE(t, j, 0);
       ok = mbar_wait(&bars->s_full[t], j & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (r == 0) NB_TRACE(t, j, 1);
       uint32_t sr[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
       tmem_wait_ld();
+      if (r == 0) NB_TRACE(t, j, 2);
 
       const int j0 = j * kBN;
       float mx = neg_inf();
@@ -316,6 +333,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c2;
       }
 
+      if (r == 0) NB_TRACE(t, j, 3);
       // raise the reference maximum only when it is far behind (or not set yet)
       const float m_new = fmaxf(m_used, mx);
       const bool raise = m_new > m_used + kRescaleGap || (m_used == neg_inf() && m_new > neg_inf());
@@ -337,6 +355,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (raise) m_used = m_new;
       const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
 
+      if (r == 0) NB_TRACE(t, j, 4);
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       if (EXTRAS) {
 #pragma unroll
@@ -359,6 +378,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      if (r == 0) NB_TRACE(t, j, 5);
 
       if (!STATS) {
         if (EXTRAS && a.dropout_p > 0.f) {
@@ -388,6 +408,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full[t]);
+      if (r == 0) NB_TRACE(t, j, 6);
     }
 
     // ------------------------------------------------------------ epilogue
@@ -805,6 +826,12 @@ cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st) {
 #undef NB_SC
   return cudaErrorInvalidValue;
 }
+
+#ifdef NB200_TRACE
+extern "C" __attribute__((visibility("default"))) int nnlib_b200_trace_dump(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 3 * 64 * 8);
+}
+#endif
 
 // Reads and clears the sticky "a bounded wait ran out" flag of the current
 // device.  Synchronises the stream.
