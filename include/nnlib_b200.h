@@ -153,6 +153,24 @@ NNLIB_B200_API int nnlib_b200_attention(const nnlib_b200_attn_params* p, void* w
                          size_t workspace_bytes, void* stream);
 NNLIB_B200_API size_t nnlib_b200_workspace_bytes(const nnlib_b200_attn_params* p);
 
+/* The same result as nnlib_b200_attention (x and alpha), for callers that
+   cannot provide a workspace because they cannot allocate device memory where
+   they call from: all of the device belongs to a memory pool (a cudaMalloc
+   would fail or stall every stream), the call site is one where the host
+   language's array allocator must not run, or the caller was handed input and
+   output pointers and nothing else.  The log-sum-exp goes to a fixed 4 MiB
+   array inside the library's device image instead (held by every GPU that
+   loads the library, until exit), so a call may cover at most
+   NNLIB_B200_STATIC_MAX_QUERIES queries (Lq*H*B); beyond that it returns
+   NNLIB_B200_WORKSPACE_TOO_SMALL and does nothing.  p->lse is ignored.  All
+   calls on a device share the array: calls that can overlap on the GPU race
+   and must be serialised by the caller; nothing needs clearing between calls.
+   The first call on each device resolves the array's address and should be
+   made before any stream capture.  Allocates nothing, ever.
+   This entry point has no counterpart in the reference. */
+#define NNLIB_B200_STATIC_MAX_QUERIES 1048576ull
+NNLIB_B200_API int nnlib_b200_attention_static(const nnlib_b200_attn_params* p, void* stream);
+
 /* make_causal_mask (src/attention.jl:149-153): fill an (L, L) byte matrix
    with m[i + L*j] = (i <= j). */
 NNLIB_B200_API int nnlib_b200_causal_fill(uint8_t* mask, int64_t L, void* stream);

@@ -21,6 +21,8 @@ CUDA_ERROR = -3
 TIMEOUT = -4
 WORKSPACE_TOO_SMALL = -5
 
+STATIC_MAX_QUERIES = 1 << 20
+
 PATH_SIMT = 1
 PATH_UMMA = 2
 
@@ -35,6 +37,7 @@ EXPORTS = (
     "nnlib_b200_attn_apply",
     "nnlib_b200_attention",
     "nnlib_b200_workspace_bytes",
+    "nnlib_b200_attention_static",
     "nnlib_b200_causal_fill",
     "nnlib_b200_causal_check",
     "nnlib_b200_attn_path",
@@ -104,6 +107,8 @@ def load() -> C.CDLL:
         fn.restype = C.c_int
     lib.nnlib_b200_attention.argtypes = [P, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.nnlib_b200_attention.restype = C.c_int
+    lib.nnlib_b200_attention_static.argtypes = [P, C.c_void_p]
+    lib.nnlib_b200_attention_static.restype = C.c_int
     lib.nnlib_b200_workspace_bytes.argtypes = [P]
     lib.nnlib_b200_workspace_bytes.restype = C.c_size_t
     lib.nnlib_b200_causal_fill.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
