@@ -3,7 +3,8 @@
 // One CTA owns 256 consecutive queries (two 128-row tiles) of one (head,
 // batch) unit and walks over the keys/values in 128-row tiles:
 //
-//   warp 0      TMA producer: Q once, then a ring of K and V tiles
+//   warp 0      TMA producer of Q (once) and of the ring of K tiles
+//   warp 3      TMA producer of the ring of V tiles
 //   warp 1      issues every tcgen05.mma:  S_t = Q_t K_j^T   (smem x smem -> TMEM)
 //                                          O_t += P_t V_j    (TMEM x smem -> TMEM)
 //   warp 2      allocates / frees the 512 TMEM columns
@@ -36,7 +37,7 @@ __device__ int g_umma_abort = 0;  // sticky: a bounded wait ran out somewhere
 #ifdef NB200_TRACE
 // Development aid: per-phase clock stamps of one CTA (block 0), read back by a
 // test harness.  Not compiled into the shipped library.
-__device__ long long g_trace[3][64][8];
+__device__ long long g_trace[4][64][8];
 #define NB_TRACE(role, j, slot) \
   do { if (blockIdx.x == NB200_TRACE_BLOCK && (j) < 64) g_trace[role][j][slot] = clock64(); } while (0)
 #else
@@ -61,23 +62,33 @@ template <int D>
 struct Cfg {
   static constexpr int kChunks = D / 64;
   static constexpr int kTileBytes = kChunks * kChunkBytes;
-  static constexpr int kStages = (D == 128) ? 2 : 4;
+  // A K tile is released early in the round after its last use, a V tile only at the end of its
+  // round, so V needs the deeper ring to keep a full round of copy latency hidden.
+  static constexpr int kStagesK = (D == 128) ? 2 : 4;
+  static constexpr int kStagesV = (D == 128) ? 3 : 4;
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + kQT * kTileBytes;
-  static constexpr int kVOff = kKOff + kStages * kTileBytes;
-  static constexpr int kBarOff = kVOff + kStages * kTileBytes;
+  static constexpr int kVOff = kKOff + kStagesK * kTileBytes;
+  static constexpr int kBarOff = kVOff + kStagesV * kTileBytes;
   static constexpr int kSmemBytes = kBarOff + 512 + 1024;  // barrier block + alignment slack
 };
+static_assert(Cfg<128>::kSmemBytes <= 232448 && Cfg<64>::kSmemBytes <= 232448, "shared memory budget");
 
 struct Barriers {
   uint64_t q_full[kQT];
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
-  uint64_t s_full[kQT], p_full[kQT], o_full[kQT];
+  uint64_t s_full[kQT], p_half[kQT][2], o_full[kQT];
   uint32_t tmem_base;
   int abort_flag;
 };
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -108,21 +119,22 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int h = unit % a.H, b = unit / a.H;
   const int q0 = qb * (kQT * kBM);
 
-  int n_t[kQT];
-#pragma unroll
-  for (int t = 0; t < kQT; ++t) {
-    const int qs = q0 + t * kBM;
-    int kv_end = a.Lkv;
-    if (a.causal) kv_end = min(kv_end, qs + kBM);
-    n_t[t] = (qs < a.Lq) ? (kv_end + kBN - 1) / kBN : 0;
+  // number of kv tiles each query tile walks over
+  int n_t0, n_t1;
+  {
+    int kv_end0 = a.Lkv, kv_end1 = a.Lkv;
+    if (a.causal) { kv_end0 = min(kv_end0, q0 + kBM); kv_end1 = min(kv_end1, q0 + 2 * kBM); }
+    n_t0 = (q0 < a.Lq) ? (kv_end0 + kBN - 1) / kBN : 0;
+    n_t1 = (q0 + kBM < a.Lq) ? (kv_end1 + kBN - 1) / kBN : 0;
   }
-  const int n_kv = max(n_t[0], n_t[1]);
+  const int n_kv = max(n_t0, n_t1);
 
   if (threadIdx.x == 0) {
     for (int t = 0; t < kQT; ++t) {
       mbar_init(&bars->q_full[t], 1);
       mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t], 4);
+      mbar_init(&bars->p_half[t][0], 4);
+      mbar_init(&bars->p_half[t][1], 4);
       mbar_init(&bars->o_full[t], 1);
     }
     for (int s = 0; s < 4; ++s) {
@@ -144,22 +156,17 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t tmem = bars->tmem_base;
   const bool start_ok = (*abort_flag == 0);
 
-  const uint32_t q_smem = smem_u32(smem + C::kQOff);
-  const uint32_t k_smem = smem_u32(smem + C::kKOff);
-  const uint32_t v_smem = smem_u32(smem + C::kVOff);
-
-  // the softmax threads hold a whole 128-wide score row in registers: move the
-  // register budget from the copy / issue warps to them
+  // The softmax threads hold a whole 128-wide score row in registers: move the
+  // register budget from the copy / issue warps to them.
   if (warp < 4) {
-  setmaxnreg_dec<40>();
-  if (start_ok && warp == 0) {
-    // ------------------------------------------------------------ producer
-    if (lane == 0) {
+    setmaxnreg_dec<72>();
+    if (start_ok && warp == 0 && lane == 0) {
+      // ------------------------------------------------- producer of Q and K
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
-      if (!STATS) prefetch_tensormap(&tm_v);
+#pragma unroll
       for (int t = 0; t < kQT; ++t) {
-        if (n_t[t] == 0) continue;
+        if ((t == 0 ? n_t0 : n_t1) == 0) continue;
         mbar_arrive_expect_tx(&bars->q_full[t], C::kTileBytes);
         for (int c = 0; c < C::kChunks; ++c)
           tma_load_3d(smem + C::kQOff + t * C::kTileBytes + c * kChunkBytes, &tm_q, &bars->q_full[t],
@@ -167,292 +174,332 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       bool ok = true;
       int j = 0;
-      for (; j < n_kv && ok; ++j) {
-        const int s = j % C::kStages;
-        if (j >= C::kStages) ok = mbar_wait(&bars->k_empty[s], ((j / C::kStages) - 1) & 1, abort_flag);
+      for (; j < n_kv; ++j) {
+        const int s = j % C::kStagesK;
+        if (j >= C::kStagesK) ok = mbar_wait(&bars->k_empty[s], ((j / C::kStagesK) - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->k_full[s], C::kTileBytes);
         for (int c = 0; c < C::kChunks; ++c)
           tma_load_3d(smem + C::kKOff + s * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->k_full[s],
                       h * D + c * 64, j * kBN, b);
-        if (!STATS) {
-          if (j >= C::kStages) ok = mbar_wait(&bars->v_empty[s], ((j / C::kStages) - 1) & 1, abort_flag);
-          if (!ok) break;
-          mbar_arrive_expect_tx(&bars->v_full[s], C::kTileBytes);
-          for (int c = 0; c < C::kChunks; ++c)
-            tma_load_3d(smem + C::kVOff + s * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full[s],
-                        h * D + c * 64, j * kBN, b);
-        }
       }
       if (*abort_flag) {
         // give copies still in flight a bounded chance to land before the CTA leaves
-        for (int jj = max(0, j - C::kStages); jj < j; ++jj) {
-          const int s = jj % C::kStages;
-          mbar_wait_drain(&bars->k_full[s], (jj / C::kStages) & 1, kDrainNs);
-          if (!STATS) mbar_wait_drain(&bars->v_full[s], (jj / C::kStages) & 1, kDrainNs);
-        }
+        for (int jj = max(0, j - C::kStagesK); jj < j; ++jj)
+          mbar_wait_drain(&bars->k_full[jj % C::kStagesK], (jj / C::kStagesK) & 1, kDrainNs);
       }
-    }
-  } else if (start_ok && warp == 1) {
-    // ---------------------------------------------------------- MMA issuer
-    if (lane == 0 && n_kv > 0) {
+    } else if (!STATS && start_ok && warp == 3 && lane == 0) {
+      // ------------------------------------------------------ producer of V
+      // (its own thread: a K tile must never queue behind a V slot that is still in use)
+      prefetch_tensormap(&tm_v);
+      bool ok = true;
+      int j = 0;
+      for (; j < n_kv; ++j) {
+        const int s = j % C::kStagesV;
+        if (j >= C::kStagesV) ok = mbar_wait(&bars->v_empty[s], ((j / C::kStagesV) - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars->v_full[s], C::kTileBytes);
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_3d(smem + C::kVOff + s * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full[s],
+                      h * D + c * 64, j * kBN, b);
+      }
+      if (*abort_flag) {
+        for (int jj = max(0, j - C::kStagesV); jj < j; ++jj)
+          mbar_wait_drain(&bars->v_full[jj % C::kStagesV], (jj / C::kStagesV) & 1, kDrainNs);
+      }
+    } else if (start_ok && warp == 1 && lane == 0 && n_kv > 0) {
+      // -------------------------------------------------------- MMA issuer
+      // One thread issues for both query tiles, tile 0 then tile 1 in every round; serving them in
+      // turn is also what keeps the two softmax warpgroups half a period apart.  Descriptors: the
+      // high word is constant, the low word is the tile address (>>4) plus the leading-byte-offset
+      // field; stepping along K only adds to the address field.
       constexpr uint32_t idesc_qk = make_idesc_f16(BF16, kBM, kBN, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(BF16, kBM, D, false, true);
+      constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1 KB, sm_100 version, 128B swizzle
+      constexpr uint32_t lbo_k = (16u >> 4) << 16;                          // K-major operands: unused, 16
+      constexpr uint32_t lbo_v = (static_cast<uint32_t>(kChunkBytes) >> 4) << 16;  // V: next 64-wide dv block
+      constexpr uint32_t tile16 = C::kTileBytes >> 4;
+      const uint32_t q_lo = (smem_u32(smem + C::kQOff) >> 4) | lbo_k;
+      const uint32_t k_lo = (smem_u32(smem + C::kKOff) >> 4) | lbo_k;
+      const uint32_t v_lo = (smem_u32(smem + C::kVOff) >> 4) | lbo_v;
       bool ok = true;
 
-      auto issue_qk = [&](int t, int stage) {
-        const uint32_t qa = q_smem + t * C::kTileBytes, ka = k_smem + stage * C::kTileBytes;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
-          umma_ss(tmem + t * kBN, make_smem_desc_sw128(qa + off, 16, 1024), make_smem_desc_sw128(ka + off, 16, 1024),
-                  idesc_qk, kk > 0 ? 1u : 0u);
-        }
-      };
-      auto issue_pv = [&](int t, int stage, bool first) {
-        const uint32_t va = v_smem + stage * C::kTileBytes;
-#pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          umma_ts(tmem + kQT * kBN + t * D, tmem + t * kBN + kk * 8,
-                  make_smem_desc_sw128(va + kk * 2048, kChunkBytes, 1024), idesc_pv, (first && kk == 0) ? 0u : 1u);
-        }
-      };
+#define NB_ISSUE_QK(T_, STAGE_)                                                                  \
+  do {                                                                                           \
+    _Pragma("unroll") for (int kk = 0; kk < D / 16; ++kk) {                                      \
+      const uint32_t off = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;                        \
+      umma_ss_lohi(tmem + (T_) * kBN, q_lo + (T_) * tile16 + off, k_lo + (STAGE_) * tile16 + off, desc_hi, \
+                   idesc_qk, kk > 0 ? 1u : 0u);                                                  \
+    }                                                                                            \
+  } while (0)
+#define NB_ISSUE_PV(T_, STAGE_, KK0_, KK1_, FIRST_)                                              \
+  do {                                                                                           \
+    _Pragma("unroll") for (int kk = (KK0_); kk < (KK1_); ++kk) {                                 \
+      umma_ts_lohi(tmem + kQT * kBN + (T_) * D, tmem + (T_) * kBN + kk * 8,                      \
+                   v_lo + (STAGE_) * tile16 + kk * (2048 >> 4), desc_hi, idesc_pv,               \
+                   ((FIRST_) && kk == 0) ? 0u : 1u);                                             \
+    }                                                                                            \
+  } while (0)
 
-      for (int t = 0; t < kQT && ok; ++t)
-        if (n_t[t] > 0) ok = mbar_wait(&bars->q_full[t], 0, abort_flag);
-      // first score tiles
+      if (n_t0 > 0) ok = mbar_wait(&bars->q_full[0], 0, abort_flag);
+      if (ok && n_t1 > 0) ok = mbar_wait(&bars->q_full[1], 0, abort_flag);
       if (ok) ok = mbar_wait(&bars->k_full[0], 0, abort_flag);
       if (ok) {
-        tc_fence_after();
-        for (int t = 0; t < kQT; ++t) {
-          if (n_t[t] == 0) continue;
-          issue_qk(t, 0);
-          umma_commit(&bars->s_full[t]);
-        }
+        if (n_t0 > 0) { NB_ISSUE_QK(0, 0); umma_commit(&bars->s_full[0]); }
+        if (n_t1 > 0) { NB_ISSUE_QK(1, 0); umma_commit(&bars->s_full[1]); }
         umma_commit(&bars->k_empty[0]);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int sv = j % C::kStages;
-        const int sk = (j + 1) % C::kStages;
-        bool have_v = false, have_k = false;
-        for (int t = 0; t < kQT && ok; ++t) {
-          if (j >= n_t[t]) continue;
-          ok = mbar_wait(&bars->p_full[t], j & 1, abort_flag);  // P_t(j) stored (or S_t(j) consumed)
-          if (!ok) break;
+        const int sv = j % C::kStagesV;
+        const int sk = (j + 1) % C::kStagesK;
+        const uint32_t par = j & 1;
+        // operand tiles first: they land long before the probabilities are ready, so these two
+        // waits cost nothing on the softmax -> MMA -> softmax chain
+        NB_TRACE(3, j, 0);
+        if (!STATS) ok = mbar_wait(&bars->v_full[sv], (j / C::kStagesV) & 1, abort_flag);
+        NB_TRACE(3, j, 1);
+        if (ok && j + 1 < n_kv) ok = mbar_wait(&bars->k_full[sk], ((j + 1) / C::kStagesK) & 1, abort_flag);
+        NB_TRACE(3, j, 2);
+#pragma unroll
+        for (int t = 0; t < kQT; ++t) {
+          const int nt = (t == 0) ? n_t0 : n_t1;
+          if (!ok || j >= nt) continue;
+          // first half of P_t(j) is in TMEM (STATS: S_t(j) has been read)
+          ok = mbar_wait(&bars->p_half[t][0], par, abort_flag);
+          if (!ok) continue;
+          tc_fence_after();
+          NB_TRACE(2, j, t * 4 + 0);
           if (!STATS) {
-            if (!have_v) { ok = mbar_wait(&bars->v_full[sv], (j / C::kStages) & 1, abort_flag); have_v = true; }
-            if (!ok) break;
-            tc_fence_after();
-            NB_TRACE(2, j, t * 4 + 0);
-            issue_pv(t, sv, j == 0);
+            NB_ISSUE_PV(t, sv, 0, kBN / 32, j == 0);
             NB_TRACE(2, j, t * 4 + 1);
-            if (j == n_t[t] - 1) umma_commit(&bars->o_full[t]);
-          }
-          if (j + 1 < n_t[t]) {
-            if (!have_k) { ok = mbar_wait(&bars->k_full[sk], ((j + 1) / C::kStages) & 1, abort_flag); have_k = true; }
-            if (!ok) break;
+            ok = mbar_wait(&bars->p_half[t][1], par, abort_flag);
+            if (!ok) continue;
             tc_fence_after();
             NB_TRACE(2, j, t * 4 + 2);
-            issue_qk(t, sk);
-            umma_commit(&bars->s_full[t]);
-            NB_TRACE(2, j, t * 4 + 3);
+            NB_ISSUE_PV(t, sv, kBN / 32, kBN / 16, false);
           }
+          if (j + 1 < nt) {
+            NB_ISSUE_QK(t, sk);
+            umma_commit(&bars->s_full[t]);
+          } else if (!STATS) {
+            umma_commit(&bars->o_full[t]);
+          }
+          NB_TRACE(2, j, t * 4 + 3);
         }
         if (!ok) break;
+        NB_TRACE(3, j, 3);
         if (!STATS) umma_commit(&bars->v_empty[sv]);
+        NB_TRACE(3, j, 4);
         if (j + 1 < n_kv) umma_commit(&bars->k_empty[sk]);
+        NB_TRACE(3, j, 5);
       }
+#undef NB_ISSUE_QK
+#undef NB_ISSUE_PV
     }
-  }
   } else {
-  setmaxnreg_inc<232>();
-  if (start_ok) {
-    // ------------------------------------------------------- softmax warps
+    setmaxnreg_inc<216>();
     const int t = (warp - 4) >> 2;        // query tile of this warpgroup
-    const int wq = warp & 3;              // TMEM lane quarter this warp may touch
-    const int r = wq * 32 + lane;         // row inside the tile
-    const int i = q0 + t * kBM + r;       // query index
-    const bool row_ok = i < a.Lq;
-    const uint32_t lane_base = tmem + (static_cast<uint32_t>(wq * 32) << 16);
-    const uint32_t tS = lane_base + t * kBN;
-    const uint32_t tO = lane_base + kQT * kBN + t * D;
-    const float c2 = a.scale * kLog2e;
-    const int lim = a.causal ? min(i, a.Lkv - 1) : a.Lkv - 1;  // last kv index this row attends to
-    const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
+    const int nt = (t == 0) ? n_t0 : n_t1;
+    if (start_ok && nt > 0) {
+      // ----------------------------------------------------- softmax warps
+      const int wq = warp & 3;              // TMEM lane quarter this warp may touch
+      const int r = wq * 32 + lane;         // row inside the tile
+      const int i = q0 + t * kBM + r;       // query index
+      const bool row_ok = i < a.Lq;
+      const uint32_t lane_base = tmem + (static_cast<uint32_t>(wq * 32) << 16);
+      const uint32_t tS = lane_base + t * kBN;
+      const uint32_t tO = lane_base + kQT * kBN + t * D;
+      const float c2 = a.scale * kLog2e;
+      const int lim = a.causal ? min(i, a.Lkv - 1) : a.Lkv - 1;  // last kv index this row attends to
+      const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
 
-    float m_used = neg_inf();  // running maximum (scaled, base 2) the stored exponentials refer to
-    float l = 0.f;             // running sum of exponentials
-    bool ok = true;
+      float m_used = neg_inf();  // running maximum (scaled, base 2) the stored exponentials refer to
+      float l = 0.f;             // running sum of exponentials
+      bool ok = true;
 
-    for (int j = 0; j < n_t[t]; ++j) {
-      if (r == 0) NB_TRACE(t, j, 0);
-      ok = mbar_wait(&bars->s_full[t], j & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      if (r == 0) NB_TRACE(t, j, 1);
-      uint32_t sr[4][32];
+      for (int j = 0; j < nt; ++j) {
+        if (r == 0) NB_TRACE(t, j, 0);
+        ok = mbar_wait(&bars->s_full[t], j & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (r == 0) NB_TRACE(t, j, 1);
+        uint32_t sr[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
-      tmem_wait_ld();
-      if (r == 0) NB_TRACE(t, j, 2);
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
+        tmem_wait_ld();
+        if (r == 0) NB_TRACE(t, j, 2);
 
-      const int j0 = j * kBN;
-      float mx = neg_inf();
-      if (EXTRAS) {
-        // logits in scaled base-2 units, bias added, masks applied
-        const long long bias_row = (long long)i * a.bias_s[1] + (long long)h * a.bias_s[2] + (long long)b * a.bias_s[3];
-        const long long mask_row = (long long)i * a.mask_s[1] + (long long)h * a.mask_s[2] + (long long)b * a.mask_s[3];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int jj = j0 + c * 32 + e;
-            float tv = __uint_as_float(sr[c][e]) * c2;
-            bool keep = (jj <= lim) && row_ok;
-            if (keep && a.bias) tv = fmaf(load_bias(a.bias, bias_row + jj * a.bias_s[0], a.bias_dtype), kLog2e, tv);
-            if (keep && a.mask) keep = a.mask[mask_row + jj * a.mask_s[0]] != 0;
-            tv = keep ? tv : neg_inf();
-            sr[c][e] = __float_as_uint(tv);
-            mx = fmaxf(mx, tv);
-          }
+        const int j0 = j * kBN;
+        if (STATS) {
+          // S is in registers: the MMA warp may overwrite it with the next tile's scores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->p_half[t][0]);
         }
-      } else {
-        if (j0 + kBN - 1 > lim) {
+
+        // ---- logits -> (masked, biased) values the exponentials are taken of
+        if (EXTRAS) {
+          // scaled base-2 units, bias added, masks applied
+          const long long bias_row = (long long)i * a.bias_s[1] + (long long)h * a.bias_s[2] + (long long)b * a.bias_s[3];
+          const long long mask_row = (long long)i * a.mask_s[1] + (long long)h * a.mask_s[2] + (long long)b * a.mask_s[3];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int jj = j0 + c * 32 + e;
+              float tv = __uint_as_float(sr[c][e]) * c2;
+              bool keep = (jj <= lim) && row_ok;
+              if (keep && a.bias) tv = fmaf(load_bias(a.bias, bias_row + jj * a.bias_s[0], a.bias_dtype), kLog2e, tv);
+              if (keep && a.mask) keep = a.mask[mask_row + jj * a.mask_s[0]] != 0;
+              sr[c][e] = __float_as_uint(keep ? tv : neg_inf());
+            }
+          }
+        } else if (j0 + kBN - 1 > lim) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int e = 0; e < 32; ++e)
               if (j0 + c * 32 + e > lim) sr[c][e] = 0xff800000u;
         }
-        float mx4[4] = {neg_inf(), neg_inf(), neg_inf(), neg_inf()};
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sr[c][e]));
-        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c2;
-      }
+        // EXTRAS values are already scaled; plain logits get scale*log2(e) inside the exponential's FMA
+        const float cs = EXTRAS ? 1.f : c2;
 
-      if (r == 0) NB_TRACE(t, j, 3);
-      // raise the reference maximum only when it is far behind (or not set yet)
-      const float m_new = fmaxf(m_used, mx);
-      const bool raise = m_new > m_used + kRescaleGap || (m_used == neg_inf() && m_new > neg_inf());
-      if (!STATS && j > 0 && __any_sync(0xffffffffu, raise)) {
-        const float f = raise ? ex2_approx(m_used - m_new) : 1.f;  // m_used = -inf gives 0: O is still 0 there
-        l *= f;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(tO + c * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
-          tmem_st32(tO + c * 32, o);
-        }
-      } else if (raise) {
-        l *= (m_used == neg_inf()) ? 0.f : ex2_approx(m_used - m_new);
-      }
-      if (raise) m_used = m_new;
-      const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[32];
+        // exponentials of 64 keys (chunks 2*HF, 2*HF+1) relative to REF, packed into pk, summed into sum4
+#define NB_EXP_HALF(HF, REF)                                                                       \
+  do {                                                                                             \
+    const float nref_ = -(REF);                                                                    \
+    _Pragma("unroll") for (int cc = 0; cc < 2; ++cc) {                                             \
+      _Pragma("unroll") for (int e = 0; e < 32; e += 2) {                                          \
+        float p0 = ex2_approx(fmaf(__uint_as_float(sr[(HF) * 2 + cc][e]), cs, nref_));             \
+        float p1 = ex2_approx(fmaf(__uint_as_float(sr[(HF) * 2 + cc][e + 1]), cs, nref_));         \
+        sum4[(e >> 1) & 3] += p0 + p1;                                                             \
+        pk[cc * 16 + (e >> 1)] = pack2<BF16>(p0, p1);                                              \
+      }                                                                                            \
+    }                                                                                              \
+  } while (0)
 
-      if (r == 0) NB_TRACE(t, j, 4);
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      if (EXTRAS) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float p = ex2_approx(__uint_as_float(sr[c][e]) - m_sub);
-            sum4[e & 3] += p;
-            sr[c][e] = __float_as_uint(p);
-          }
-      } else {
-        const float nm = -m_sub;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float p = ex2_approx(fmaf(__uint_as_float(sr[c][e]), c2, nm));
-            sum4[e & 3] += p;
-            sr[c][e] = __float_as_uint(p);
-          }
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      if (r == 0) NB_TRACE(t, j, 5);
-
-      if (!STATS) {
-        if (EXTRAS && a.dropout_p > 0.f) {
-          // one Philox call decides four neighbouring keys of this row
+        // full-tile maximum (3-input max: 64 instructions); independent of the first exponentials below
+        float mx;
+        {
+          float m0 = neg_inf(), m1 = neg_inf(), m2 = neg_inf(), m3 = neg_inf();
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              unsigned int w[4];
-              dropout_words(a, srow, (unsigned int)(j0 >> 2) + c * 8 + g, w);
-#pragma unroll
-              for (int u = 0; u < 4; ++u)
-                if (!(w[u] > a.drop_thresh)) sr[c][g * 4 + u] = 0u;
+            for (int e = 0; e < 32; e += 8) {
+              m0 = max3(m0, __uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
+              m1 = max3(m1, __uint_as_float(sr[c][e + 2]), __uint_as_float(sr[c][e + 3]));
+              m2 = max3(m2, __uint_as_float(sr[c][e + 4]), __uint_as_float(sr[c][e + 5]));
+              m3 = max3(m3, __uint_as_float(sr[c][e + 6]), __uint_as_float(sr[c][e + 7]));
             }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * cs;
         }
-        uint32_t pk[2][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; e += 2)
-            pk[c >> 1][(c & 1) * 16 + (e >> 1)] =
-                pack2<BF16>(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
-        tmem_st32(tS, pk[0]);
-        tmem_st32(tS + 32, pk[1]);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full[t]);
-      if (r == 0) NB_TRACE(t, j, 6);
-    }
+        const float m_new = fmaxf(m_used, mx);
+        const bool raise = m_new > m_used + kRescaleGap;   // also true for m_used = -inf < m_new
 
-    // ------------------------------------------------------------ epilogue
-    if (ok && n_t[t] > 0) {
-      const bool dead = !(l > 0.f);
-      if (a.lse && row_ok) {
-        a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = dead ? neg_inf() : (m_used + log2f(l)) * kLn2;
+        if (!STATS) {
+          // First 64 exponentials against the running reference while the maximum above is still being
+          // reduced (different pipes).  Later tiles almost never move the reference; when one does, the
+          // half is simply redone below.  The very first tile has no reference yet and skips the guess.
+          const bool guess = (j > 0);
+          if (guess) NB_EXP_HALF(0, (m_used == neg_inf()) ? 0.f : m_used);
+          if (!guess || __any_sync(0xffffffffu, raise)) {
+            if (j > 0) {
+              const float f = raise ? ex2_approx(m_used - m_new) : 1.f;  // m_used = -inf gives 0: O is still 0 there
+              l *= f;
+#pragma unroll
+              for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tO + c * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+                tmem_st32(tO + c * 32, o);
+              }
+            }
+            if (raise) m_used = m_new;
+            sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
+            NB_EXP_HALF(0, (m_used == neg_inf()) ? 0.f : m_used);
+          }
+          if (r == 0) NB_TRACE(t, j, 3);
+          const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            if (hf == 1) NB_EXP_HALF(1, m_sub);
+            if (EXTRAS && a.dropout_p > 0.f) {
+              // one Philox call decides four neighbouring keys of this row; the row sum keeps the dropped ones
+#pragma unroll
+              for (int g = 0; g < 16; ++g) {
+                unsigned int w[4];
+                dropout_words(a, srow, (unsigned int)(j0 >> 2) + hf * 16 + g, w);
+                if (!(w[0] > a.drop_thresh)) pk[g * 2] &= 0xffff0000u;
+                if (!(w[1] > a.drop_thresh)) pk[g * 2] &= 0x0000ffffu;
+                if (!(w[2] > a.drop_thresh)) pk[g * 2 + 1] &= 0xffff0000u;
+                if (!(w[3] > a.drop_thresh)) pk[g * 2 + 1] &= 0x0000ffffu;
+              }
+            }
+            tmem_st32(tS + hf * 32, pk);
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_half[t][hf]);
+            if (r == 0) NB_TRACE(t, j, 4 + hf);
+          }
+        } else {
+          // statistics only: running maximum and sum
+          if (raise) {
+            l *= (m_used == neg_inf()) ? 0.f : ex2_approx(m_used - m_new);
+            m_used = m_new;
+          }
+          const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
+          NB_EXP_HALF(0, m_sub);
+          NB_EXP_HALF(1, m_sub);
+        }
+#undef NB_EXP_HALF
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if (r == 0) NB_TRACE(t, j, 6);
       }
-      if (!STATS) {
-        ok = mbar_wait(&bars->o_full[t], 0, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-          tc_fence_after();
-          float inv = dead ? (a.nan_fm ? __int_as_float(0x7fc00000) : 0.f) : a.inv_keep / l;
-          uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
-                          2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * D);
+
+      // ---------------------------------------------------------- epilogue
+      if (ok) {
+        const bool dead = !(l > 0.f);
+        if (a.lse && row_ok) {
+          a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = dead ? neg_inf() : (m_used + log2f(l)) * kLn2;
+        }
+        if (!STATS) {
+          ok = mbar_wait(&bars->o_full[t], 0, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (ok) {
+            tc_fence_after();
+            const float inv = dead ? (a.nan_fm ? __int_as_float(0x7fc00000) : 0.f) : a.inv_keep / l;
+            uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
+                            2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * D);
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tO + c * 32, o);
-            tmem_wait_ld();
-            if (row_ok) {
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tO + c * 32, o);
+              tmem_wait_ld();
+              if (row_ok) {
 #pragma unroll
-              for (int e = 0; e < 32; e += 8) {
-                uint4 v;
-                float f[8];
+                for (int e = 0; e < 32; e += 8) {
+                  float f[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                  const float ov = __uint_as_float(o[e + u]);
-                  f[u] = dead ? (a.nan_fm ? inv : 0.f) : ov * inv;
+                  for (int u = 0; u < 8; ++u) f[u] = dead ? inv : __uint_as_float(o[e + u]) * inv;
+                  uint4 v;
+                  v.x = pack2<BF16>(f[0], f[1]);
+                  v.y = pack2<BF16>(f[2], f[3]);
+                  v.z = pack2<BF16>(f[4], f[5]);
+                  v.w = pack2<BF16>(f[6], f[7]);
+                  *reinterpret_cast<uint4*>(xrow + (c * 32 + e) * 2) = v;
                 }
-                v.x = pack2<BF16>(f[0], f[1]);
-                v.y = pack2<BF16>(f[2], f[3]);
-                v.z = pack2<BF16>(f[4], f[5]);
-                v.w = pack2<BF16>(f[6], f[7]);
-                *reinterpret_cast<uint4*>(xrow + (c * 32 + e) * 2) = v;
               }
             }
           }
         }
       }
     }
-  }
-
   }
 
   // ---------------------------------------------------------------- teardown
@@ -467,7 +514,6 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (a.status) atomicExch(a.status, NNLIB_B200_TIMEOUT);
   }
 }
-
 
 // ===========================================================================
 // Scores kernel: alpha (after dropout) rebuilt from Q, K, bias, masks and the
@@ -829,7 +875,7 @@ cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st) {
 
 #ifdef NB200_TRACE
 extern "C" __attribute__((visibility("default"))) int nnlib_b200_trace_dump(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 3 * 64 * 8);
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 4 * 64 * 8);
 }
 #endif
 

@@ -53,6 +53,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a phase (no hardware suspend): the cheap way to pass a barrier that
+// has usually completed long ago.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Every wait in these kernels is bounded: after `limit_ns` without the phase
 // completing, the waiter raises the CTA-wide abort flag (shared memory) and
 // returns false; all other waiters of the CTA see the flag and give up too,
@@ -60,19 +76,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
+  // hot phase: nothing but the barrier, so a completed phase is seen at once
 #pragma unroll 1
-  for (int it = 0; it < 128; ++it)
+  for (int it = 0; it < 4096; ++it)
     if (mbar_try_wait(bar, parity)) return true;
+  // slow phase: the clock and the abort flag are looked at once per 32 polls
   const unsigned long long t0 = globaltimer_ns();
 #pragma unroll 1
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int it = 0; it < 32; ++it)
+      if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       *abort_flag = 1;
       return false;
     }
   }
+}
+
+// Whole-warp wait: lane 0 polls, the result is broadcast.  256 threads polling one barrier keep
+// the shared-memory pipe so busy that every other barrier operation of the CTA slows down.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // Bounded wait that ignores the abort flag: used on the way out of an aborted
@@ -214,6 +243,36 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same two instructions with the descriptors given as (low word, shared high
+// word): along K only the address field in the low word changes.
+__device__ __forceinline__ void umma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // The mbarrier receives one arrival when every tcgen05 operation this thread
 // issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
