@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "extras.cuh"
 #include "launchers.h"
 #include "umma.cuh"
 
@@ -316,9 +317,17 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       float m_used = neg_inf();  // running maximum (scaled, base 2) the stored exponentials refer to
       float l = 0.f;             // running sum of exponentials
       bool ok = true;
+      RowSide rs;
+      if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
 
       for (int j = 0; j < nt; ++j) {
         if (r == 0) NB_TRACE(t, j, 0);
+        // bias / mask of the first 64 keys of this tile: in flight while the scores are awaited
+        uint4 bq[2][4], mq[2][2];
+        if (EXTRAS) {
+          side_issue(rs, j * kBN, a.Lkv, bq[0], mq[0]);
+          side_issue(rs, j * kBN + 32, a.Lkv, bq[1], mq[1]);
+        }
         ok = mbar_wait(&bars->s_full[t], j & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -340,20 +349,11 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
         // ---- logits -> (masked, biased) values the exponentials are taken of
         if (EXTRAS) {
-          // scaled base-2 units, bias added, masks applied
-          const long long bias_row = (long long)i * a.bias_s[1] + (long long)h * a.bias_s[2] + (long long)b * a.bias_s[3];
-          const long long mask_row = (long long)i * a.mask_s[1] + (long long)h * a.mask_s[2] + (long long)b * a.mask_s[3];
+          // scaled base-2 units, bias added, masks applied; the loads of chunk c+2 start as chunk c is consumed
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int jj = j0 + c * 32 + e;
-              float tv = __uint_as_float(sr[c][e]) * c2;
-              bool keep = (jj <= lim) && row_ok;
-              if (keep && a.bias) tv = fmaf(load_bias(a.bias, bias_row + jj * a.bias_s[0], a.bias_dtype), kLog2e, tv);
-              if (keep && a.mask) keep = a.mask[mask_row + jj * a.mask_s[0]] != 0;
-              sr[c][e] = __float_as_uint(keep ? tv : neg_inf());
-            }
+            side_apply(rs, sr[c], bq[c & 1], mq[c & 1], j0 + c * 32, a.Lkv, lim, row_ok, c2);
+            if (c + 2 < 4) side_issue(rs, j0 + (c + 2) * 32, a.Lkv, bq[c & 1], mq[c & 1]);
           }
         } else if (j0 + kBN - 1 > lim) {
 #pragma unroll
@@ -547,19 +547,17 @@ struct ScBarriers {
   int abort_flag;
 };
 
-// write n (<= 128) scores of one query, given as 64 packed pairs
+// write min(n, 32) scores of one query, given as 16 packed pairs (n <= 0: nothing)
 template <typename T>
-__device__ __forceinline__ void store_score_row(T* dst, const uint32_t (&pk)[64], int n) {
-  if (n == 128 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+__device__ __forceinline__ void store_score_chunk(T* dst, const uint32_t (&pk)[16], int n) {
+  if (n >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
-    for (int e = 0; e < 64; e += 4) {
-      uint4 v = make_uint4(pk[e], pk[e + 1], pk[e + 2], pk[e + 3]);
-      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(dst) + e * 4) = v;
-    }
+    for (int e = 0; e < 16; e += 4)
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(dst) + e * 4) = make_uint4(pk[e], pk[e + 1], pk[e + 2], pk[e + 3]);
   } else {
     unsigned short* d16 = reinterpret_cast<unsigned short*>(dst);
 #pragma unroll
-    for (int e = 0; e < 64; ++e) {
+    for (int e = 0; e < 16; ++e) {
       if (2 * e < n) d16[2 * e] = static_cast<unsigned short>(pk[e] & 0xffffu);
       if (2 * e + 1 < n) d16[2 * e + 1] = static_cast<unsigned short>(pk[e] >> 16);
     }
@@ -567,7 +565,7 @@ __device__ __forceinline__ void store_score_row(T* dst, const uint32_t (&pk)[64]
 }
 
 template <int D, bool BF16, bool EXTRAS>
-__global__ void __launch_bounds__(kScThreads)
+__global__ void __launch_bounds__(kScThreads, 2)
 attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const AttnArgs a, const int n_qtiles) {
   using C = ScCfg<D>;
@@ -667,69 +665,83 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     const float lse2 = dead ? 0.f : lse_nat * kLog2e;
     const float dead_val = a.nan_fm ? __int_as_float(0x7fc00000) : 0.f;
     T* arow = reinterpret_cast<T*>(a.alpha) + ((long long)i + (long long)a.Lq * h) * a.Lkv + a.alpha_sb * b;
-    const long long bias_row = (long long)i * a.bias_s[1] + (long long)h * a.bias_s[2] + (long long)b * a.bias_s[3];
-    const long long mask_row = (long long)i * a.mask_s[1] + (long long)h * a.mask_s[2] + (long long)b * a.mask_s[3];
+    RowSide rs;
+    if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
 
     for (int j = 0; j < n_total; ++j) {
       const int j0 = j * kBN;
-      const int nvalid = min(kBN, a.Lkv - j0);
-      uint32_t pk[64];
       if (j < n_live) {
         const int sb = j & 1;
+        uint4 bq[2][4], mq[2][2];
+        if (EXTRAS) {   // bias / mask of the first 64 keys: in flight while the scores are awaited
+          side_issue(rs, j0, a.Lkv, bq[0], mq[0]);
+          side_issue(rs, j0 + 32, a.Lkv, bq[1], mq[1]);
+        }
         bool ok = mbar_wait(&bars->s_full[sb], (j >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        uint32_t sr[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(lane_base + sb * kBN + c * 32, sr[c]);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->s_empty[sb]);
-
+        // 32 keys at a time (the next 32 scores are fetched from TMEM meanwhile):
+        // logits -> probabilities -> dropout -> 64 bytes of the score row
+        uint32_t sr[2][32];
+        tmem_ld32(lane_base + sb * kBN, sr[0]);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int jj = j0 + c * 32 + e;
-            float tv = __uint_as_float(sr[c][e]) * c2;
-            bool keep = (jj <= lim) && row_ok;
-            if (EXTRAS) {
-              if (keep && a.bias) tv = fmaf(load_bias(a.bias, bias_row + jj * a.bias_s[0], a.bias_dtype), kLog2e, tv);
-              if (keep && a.mask) keep = a.mask[mask_row + jj * a.mask_s[0]] != 0;
-            }
-            float al = keep ? ex2_approx(tv - lse2) : 0.f;
-            if (dead) al = dead_val;
-            sr[c][e] = __float_as_uint(al);
+          const int jc = j0 + c * 32;
+          tmem_wait_ld();
+          if (c + 1 < 4) {
+            tmem_ld32(lane_base + sb * kBN + (c + 1) * 32, sr[(c + 1) & 1]);
+          } else {
+            // the whole tile is in registers: the issuer may refill this buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->s_empty[sb]);
           }
-        }
-        if (EXTRAS && a.dropout_p > 0.f) {
+          if (EXTRAS) {
+            side_apply(rs, sr[c & 1], bq[c & 1], mq[c & 1], jc, a.Lkv, lim, row_ok, c2);
+            if (c + 2 < 4) side_issue(rs, j0 + (c + 2) * 32, a.Lkv, bq[c & 1], mq[c & 1]);
+          }
+          uint32_t pk[16];
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int e = 0; e < 32; e += 2) {
+            float a0, a1;
+            if (EXTRAS) {
+              a0 = ex2_approx(__uint_as_float(sr[c & 1][e]) - lse2);        // -inf (masked) gives 0
+              a1 = ex2_approx(__uint_as_float(sr[c & 1][e + 1]) - lse2);
+            } else {
+              a0 = (jc + e <= lim) ? ex2_approx(fmaf(__uint_as_float(sr[c & 1][e]), c2, -lse2)) : 0.f;
+              a1 = (jc + e + 1 <= lim) ? ex2_approx(fmaf(__uint_as_float(sr[c & 1][e + 1]), c2, -lse2)) : 0.f;
+            }
+            if (dead) { a0 = dead_val; a1 = dead_val; }
+            sr[c & 1][e] = __float_as_uint(a0);
+            sr[c & 1][e + 1] = __float_as_uint(a1);
+          }
+          if (EXTRAS && a.dropout_p > 0.f) {
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
               unsigned int w[4];
-              dropout_words(a, srow, (unsigned int)(j0 >> 2) + c * 8 + g, w);
+              dropout_words(a, srow, (unsigned int)(jc >> 2) + g, w);
 #pragma unroll
               for (int u = 0; u < 4; ++u) {
-                const float al = __uint_as_float(sr[c][g * 4 + u]);
-                sr[c][g * 4 + u] = __float_as_uint((w[u] > a.drop_thresh) ? al * a.inv_keep : 0.f);
+                const float al = __uint_as_float(sr[c & 1][g * 4 + u]);
+                sr[c & 1][g * 4 + u] = __float_as_uint((w[u] > a.drop_thresh) ? al * a.inv_keep : 0.f);
               }
             }
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
+          }
 #pragma unroll
           for (int e = 0; e < 32; e += 2)
-            pk[c * 16 + (e >> 1)] = pack2<BF16>(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
-      } else {
+            pk[e >> 1] = pack2<BF16>(__uint_as_float(sr[c & 1][e]), __uint_as_float(sr[c & 1][e + 1]));
+          if (row_ok) store_score_chunk<T>(arow + jc, pk, a.Lkv - jc);
+        }
+      } else if (row_ok) {
         // tiles entirely above the causal diagonal
         const uint32_t z = dead ? pack2<BF16>(dead_val, dead_val) : 0u;
+        uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 64; ++e) pk[e] = z;
+        for (int e = 0; e < 16; ++e) pk[e] = z;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) store_score_chunk<T>(arow + j0 + c * 32, pk, a.Lkv - (j0 + c * 32));
       }
-      if (row_ok) store_score_row<T>(arow + j0, pk, nvalid);
     }
   }
 

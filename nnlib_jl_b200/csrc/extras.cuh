@@ -1,0 +1,123 @@
+// Bias and Bool-mask access for one query row of the tensor-core kernels.
+//
+// A softmax / epilogue thread owns one query row and walks over its keys in
+// chunks of 32.  bias (NNlib.jl src/attention.jl:129-131) and mask (:133-138)
+// may have any strides; when the key stride is 1 and the row starts on a
+// 16-byte boundary, a chunk is fetched with 16-byte loads that are issued one
+// chunk ahead of their use, otherwise element by element.
+#pragma once
+
+#include "common.cuh"
+
+namespace nb200 {
+
+struct RowSide {
+  const unsigned char* bias_row;  // address of bias(kv = 0) of this row (nullptr: no bias or row out of range)
+  const unsigned char* mask_row;  // address of mask(kv = 0) of this row
+  long long bias_s0, mask_s0;     // key strides in elements
+  int bias_dtype;
+  bool bias_vec;                  // 2-byte elements, key stride 1, 16-byte aligned row
+  bool mask_vec;                  // key stride 1, 16-byte aligned row
+};
+
+__device__ __forceinline__ RowSide make_row_side(const AttnArgs& a, int i, int h, int b, bool row_ok) {
+  RowSide rs;
+  rs.bias_row = nullptr;
+  rs.mask_row = nullptr;
+  rs.bias_s0 = a.bias_s[0];
+  rs.mask_s0 = a.mask_s[0];
+  rs.bias_dtype = a.bias_dtype;
+  rs.bias_vec = false;
+  rs.mask_vec = false;
+  if (row_ok && a.bias) {
+    const long long off = (long long)i * a.bias_s[1] + (long long)h * a.bias_s[2] + (long long)b * a.bias_s[3];
+    const int esz = (a.bias_dtype == NNLIB_B200_F32) ? 4 : 2;
+    rs.bias_row = reinterpret_cast<const unsigned char*>(a.bias) + off * esz;
+    rs.bias_vec = (esz == 2) && (a.bias_s[0] == 1) && ((reinterpret_cast<unsigned long long>(rs.bias_row) & 15ull) == 0);
+  }
+  if (row_ok && a.mask) {
+    const long long off = (long long)i * a.mask_s[1] + (long long)h * a.mask_s[2] + (long long)b * a.mask_s[3];
+    rs.mask_row = a.mask + off;
+    rs.mask_vec = (a.mask_s[0] == 1) && ((reinterpret_cast<unsigned long long>(rs.mask_row) & 15ull) == 0);
+  }
+  return rs;
+}
+
+// Start the 16-byte loads of keys jj0 .. jj0+31 (only when the whole chunk lies inside the array).
+__device__ __forceinline__ void side_issue(const RowSide& rs, int jj0, int Lkv, uint4 (&bq)[4], uint4 (&mq)[2]) {
+  const bool inside = jj0 + 32 <= Lkv;
+  if (rs.bias_vec && inside) {
+    const uint4* p = reinterpret_cast<const uint4*>(rs.bias_row + (long long)jj0 * 2);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) bq[v] = __ldg(p + v);
+  }
+  if (rs.mask_vec && inside) {
+    const uint4* p = reinterpret_cast<const uint4*>(rs.mask_row + jj0);
+#pragma unroll
+    for (int v = 0; v < 2; ++v) mq[v] = __ldg(p + v);
+  }
+}
+
+__device__ __forceinline__ unsigned int u4_word(const uint4& q, int w) {
+  return w == 0 ? q.x : (w == 1 ? q.y : (w == 2 ? q.z : q.w));
+}
+
+// s[e] (raw q·k of keys jj0+e) -> scaled base-2 logit with bias added, or -inf where the key is
+// masked, beyond `lim` (causal / end of the keys) or the row is out of range.
+__device__ __forceinline__ void side_apply(const RowSide& rs, unsigned int (&s)[32], const uint4 (&bq)[4],
+                                           const uint4 (&mq)[2], int jj0, int Lkv, int lim, bool row_ok, float c2) {
+  constexpr float kLog2eF = 1.4426950408889634f;
+  const bool inside = jj0 + 32 <= Lkv;
+  float tv[32];
+#pragma unroll
+  for (int e = 0; e < 32; ++e) tv[e] = __uint_as_float(s[e]) * c2;
+  // ---- bias
+  if (rs.bias_row) {
+    if (rs.bias_vec && inside) {
+      if (rs.bias_dtype == NNLIB_B200_BF16) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const unsigned int w = u4_word(bq[e >> 3], (e >> 1) & 3);
+          tv[e] = fmaf(__uint_as_float(w << 16), kLog2eF, tv[e]);
+          tv[e + 1] = fmaf(__uint_as_float(w & 0xffff0000u), kLog2eF, tv[e + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const unsigned int w = u4_word(bq[e >> 3], (e >> 1) & 3);
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+          tv[e] = fmaf(f.x, kLog2eF, tv[e]);
+          tv[e + 1] = fmaf(f.y, kLog2eF, tv[e + 1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (jj0 + e <= lim) tv[e] = fmaf(load_bias(rs.bias_row, (jj0 + e) * rs.bias_s0, rs.bias_dtype), kLog2eF, tv[e]);
+    }
+  }
+  // ---- mask
+  unsigned int keep_bits = 0xffffffffu;
+  if (rs.mask_row) {
+    if (rs.mask_vec && inside) {
+      keep_bits = 0;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const unsigned int w = u4_word(mq[e >> 4], (e >> 2) & 3);
+        if ((w >> ((e & 3) * 8)) & 0xffu) keep_bits |= 1u << e;
+      }
+    } else {
+      keep_bits = 0;
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (jj0 + e <= lim && rs.mask_row[(jj0 + e) * rs.mask_s0] != 0) keep_bits |= 1u << e;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    const bool keep = row_ok && (jj0 + e <= lim) && ((keep_bits >> e) & 1u);
+    s[e] = keep ? __float_as_uint(tv[e]) : 0xff800000u;
+  }
+}
+
+}  // namespace nb200
