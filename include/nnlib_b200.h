@@ -171,6 +171,29 @@ NNLIB_B200_API size_t nnlib_b200_workspace_bytes(const nnlib_b200_attn_params* p
 #define NNLIB_B200_STATIC_MAX_QUERIES 1048576ull
 NNLIB_B200_API int nnlib_b200_attention_static(const nnlib_b200_attn_params* p, void* stream);
 
+/* Gradient buffers of nnlib_b200_attn_bwd.  dx, dq, dk, dv have the element type of the forward
+   arrays; dq (E, Lq, B), dk (E, Lkv, B), dv (Ev, Lkv, B) are written dense. */
+typedef struct nnlib_b200_attn_grads {
+  size_t struct_size;        /* = sizeof(nnlib_b200_attn_grads) */
+  const void* dx;            /* cotangent of x, (Ev, Lq, B) */
+  int64_t dx_stride_l, dx_stride_b;   /* element strides, 0 = dense */
+  void* dq;
+  void* dk;
+  void* dv;
+  float* dbias;              /* optional float32 accumulator, indexed like bias with dbias_stride
+                                (a stride of 0 sums over that dimension); the CALLER zeroes it first */
+  int64_t dbias_stride[4];
+  float* delta;              /* scratch, Lq*H*B float32 */
+} nnlib_b200_attn_grads;
+
+/* Pullback of x = dot_product_attention(q, k, v, bias; mask, nheads, fdrop)[1]: what Zygote composes
+   from rrule(batched_mul) (src/batched/batchedmul.jl:96-110), the softmax pullback
+   (src/softmax.jl:84-116) and the dropout pullback (src/dropout.jl:106-122) on this path.
+   p describes the forward call and must carry its outputs x and lse; dropout parameters must be the
+   forward's, so that the same scores are dropped. */
+NNLIB_B200_API int nnlib_b200_attn_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g,
+                                       void* stream);
+
 /* make_causal_mask (src/attention.jl:149-153): fill an (L, L) byte matrix
    with m[i + L*j] = (i <= j). */
 NNLIB_B200_API int nnlib_b200_causal_fill(uint8_t* mask, int64_t L, void* stream);

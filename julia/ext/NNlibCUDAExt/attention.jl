@@ -331,3 +331,51 @@ function sharded_attention(q::Array{T,3}, k::Array{T,3}, v::Array{T,3}; nheads=1
     end
     return x, status
 end
+
+# ---------------------------------------------------------------------------
+# Reverse rule.  The generic path is differentiated by Zygote through rrule(batched_mul),
+# rrule(softmax) and rrule(dropout); an opaque ccall has no adjoint, so the B200 method brings its
+# own: nnlib_b200_attn_bwd recomputes the scores from the saved log-sum-exp and replays the Philox
+# dropout mask.  fdrop must be `identity` or a `PhiloxDropout`; other callables keep the generic rules
+# (Zygote differentiates the materialise → fdrop → attn_apply sequence only if those steps have rules,
+# so such calls should go through the generic method when gradients are needed).
+# ---------------------------------------------------------------------------
+using ChainRulesCore: ChainRulesCore, NoTangent, ZeroTangent, unthunk
+
+Base.@kwdef struct B200AttnGrads
+    struct_size::Csize_t = 0
+    dx::CuPtr{Cvoid} = CU_NULL
+    dx_stride_l::Int64 = 0; dx_stride_b::Int64 = 0
+    dq::CuPtr{Cvoid} = CU_NULL; dk::CuPtr{Cvoid} = CU_NULL; dv::CuPtr{Cvoid} = CU_NULL
+    dbias::CuPtr{Float32} = CU_NULL
+    dbias_stride::NTuple{4,Int64} = (0, 0, 0, 0)
+    delta::CuPtr{Float32} = CU_NULL
+end
+
+function ChainRulesCore.rrule(::typeof(dot_product_attention), q::DenseCuArray{T,3}, k::DenseCuArray{T,3},
+                              v::DenseCuArray{T,3}, bias=nothing; fdrop=identity, mask=nothing,
+                              nheads=1) where {T<:B200Float}
+    (fdrop === identity || fdrop isa PhiloxDropout) ||
+        throw(ArgumentError("the B200 attention rrule needs fdrop = identity or a PhiloxDropout"))
+    x, α = dot_product_attention(q, k, v, bias; fdrop, mask, nheads)
+    p = α.params                     # forward description incl. x, lse and the dropout offset that was used
+    function attention_pullback(Δ)
+        dx = convert(CuArray{T,3}, unthunk(Δ[1]))   # the cotangent of α is not supported (α is lazy)
+        dq, dk, dv = similar(q), similar(k), similar(v)
+        delta = CuArray{Float32}(undef, p.Lq * p.H * p.B)
+        dbias32 = bias === nothing ? nothing : CUDA.zeros(Float32, size(bias))
+        g = B200AttnGrads(; struct_size=sizeof(B200AttnGrads), dx=reinterpret(CuPtr{Cvoid}, pointer(dx)),
+            dq=reinterpret(CuPtr{Cvoid}, pointer(dq)), dk=reinterpret(CuPtr{Cvoid}, pointer(dk)),
+            dv=reinterpret(CuPtr{Cvoid}, pointer(dv)), delta=pointer(delta),
+            dbias=dbias32 === nothing ? CuPtr{Float32}(0) : pointer(dbias32),
+            dbias_stride=dbias32 === nothing ? (0, 0, 0, 0) : _bcast_strides("bias", dbias32, (p.Lkv, p.Lq, p.H, p.B)))
+        GC.@preserve q k v x α dx dq dk dv delta dbias32 bias mask begin
+            rc = ccall((:nnlib_b200_attn_bwd, libnnlib_b200[]), Cint,
+                       (Ref{B200AttnParams}, Ref{B200AttnGrads}, Ptr{Cvoid}), p, g, stream().handle)
+            _b200_check(rc, "attn_bwd")
+        end
+        dbias = bias === nothing ? NoTangent() : convert(typeof(bias), dbias32)
+        return (NoTangent(), dq, dk, dv, dbias)
+    end
+    return (x, α), attention_pullback
+end

@@ -7,12 +7,13 @@ tensors, computed by the hand-written sm_100a kernels of ``libnnlib_b200.so``
 independent (batch, head) units of one call over the GPUs of a box.
 """
 from .attention import (ArgumentError, CausalMask, LazyAttnScores, PhiloxDropout, device_health,
-                        dot_product_attention, dot_product_attention_scores, identity, make_causal_mask)
+                        dot_product_attention, dot_product_attention_pullback, dot_product_attention_scores, identity,
+                        make_causal_mask)
 from .layout import (as_column_major, is_column_major, jl_empty, jl_from_numpy, jl_reshape, jl_to_numpy,
                      jl_zeros)
 
 __all__ = [
     "ArgumentError", "CausalMask", "LazyAttnScores", "PhiloxDropout", "device_health",
-    "dot_product_attention", "dot_product_attention_scores", "identity", "make_causal_mask",
+    "dot_product_attention", "dot_product_attention_pullback", "dot_product_attention_scores", "identity", "make_causal_mask",
     "as_column_major", "is_column_major", "jl_empty", "jl_from_numpy", "jl_reshape", "jl_to_numpy", "jl_zeros",
 ]

@@ -38,6 +38,7 @@ EXPORTS = (
     "nnlib_b200_attention",
     "nnlib_b200_workspace_bytes",
     "nnlib_b200_attention_static",
+    "nnlib_b200_attn_bwd",
     "nnlib_b200_causal_fill",
     "nnlib_b200_causal_check",
     "nnlib_b200_attn_path",
@@ -83,6 +84,22 @@ class AttnParams(C.Structure):
             self.nan_on_fully_masked = 1
 
 
+class AttnGrads(C.Structure):
+    """Mirror of ``nnlib_b200_attn_grads``."""
+
+    _fields_ = [
+        ("struct_size", C.c_size_t),
+        ("dx", C.c_void_p), ("dx_stride_l", C.c_int64), ("dx_stride_b", C.c_int64),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("dbias", C.c_void_p), ("dbias_stride", C.c_int64 * 4),
+        ("delta", C.c_void_p),
+    ]
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.struct_size = C.sizeof(AttnGrads)
+
+
 _lib = None
 
 
@@ -109,6 +126,8 @@ def load() -> C.CDLL:
     lib.nnlib_b200_attention.restype = C.c_int
     lib.nnlib_b200_attention_static.argtypes = [P, C.c_void_p]
     lib.nnlib_b200_attention_static.restype = C.c_int
+    lib.nnlib_b200_attn_bwd.argtypes = [P, C.POINTER(AttnGrads), C.c_void_p]
+    lib.nnlib_b200_attn_bwd.restype = C.c_int
     lib.nnlib_b200_workspace_bytes.argtypes = [P]
     lib.nnlib_b200_workspace_bytes.restype = C.c_size_t
     lib.nnlib_b200_causal_fill.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]

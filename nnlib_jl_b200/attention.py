@@ -33,6 +33,7 @@ __all__ = [
     "PhiloxDropout",
     "dot_product_attention",
     "dot_product_attention_scores",
+    "dot_product_attention_pullback",
     "make_causal_mask",
     "identity",
     "device_health",
@@ -370,6 +371,53 @@ def _fused_with_origin(q, k, v, bias, mask, nheads, dropout, rng_origin):
         with torch.cuda.device(pr.dev):
             _check(_lib.load().nnlib_b200_attn_fwd(C.byref(pr.p), _stream()), "attn_fwd")
     return x
+
+
+def dot_product_attention_pullback(q, k, v, bias=None, *, fdrop: Callable = identity, mask=None, nheads: int = 1):
+    """``rrule``-style forward: returns ``(x, α, back)`` where ``back(dx)`` gives ``(dq, dk, dv, dbias)``,
+    the cotangents Zygote would compose from the reference's rules for ``batched_mul``, ``softmax`` and
+    ``dropout`` on this path (``src/batched/batchedmul.jl:96-110``, ``src/softmax.jl:84-116``,
+    ``src/dropout.jl:106-122``).  3-d inputs; ``fdrop`` must be ``identity`` or a :class:`PhiloxDropout`
+    (the pullback replays its mask).  ``dbias`` has the shape and element type of ``bias`` (None without)."""
+    for name, t in (("query", q), ("key", k), ("value", v)):
+        _require_dense_cuda(name, t)
+    if not (q.ndim == k.ndim == v.ndim == 3):
+        raise TypeError("the pullback is defined for 3-d (features, length, batch) arrays")
+    nheads = int(nheads)
+    _validate_3d(q, k, v, nheads)
+    if not (fdrop is None or fdrop is identity or isinstance(fdrop, PhiloxDropout)):
+        raise ArgumentError("pullback: fdrop must be identity or a PhiloxDropout")
+    dropout = fdrop if isinstance(fdrop, PhiloxDropout) else None
+    pr = _Problem(q, k, v, bias, mask, nheads, dropout, need_v=True)
+    x = pr.alloc_x()
+    pr.alloc_lse()
+    lib = _lib.load()
+    if pr.Lq > 0 and pr.B > 0:
+        with torch.cuda.device(pr.dev):
+            _check(lib.nnlib_b200_attn_fwd(C.byref(pr.p), _stream()), "attn_fwd")
+    alpha = LazyAttnScores(pr, (pr.Lkv, pr.Lq, pr.H, pr.B))
+
+    def back(dx: torch.Tensor):
+        _require_dense_cuda("dx", dx)
+        if tuple(dx.shape) != tuple(x.shape) or dx.dtype != x.dtype:
+            raise ArgumentError(f"dx must have size {tuple(x.shape)} and eltype {x.dtype}")
+        dq = jl_empty(q.shape, q.dtype, pr.dev)
+        dk = jl_empty(k.shape, k.dtype, pr.dev)
+        dv = jl_empty(v.shape, v.dtype, pr.dev)
+        delta = torch.empty(pr.Lq * pr.H * pr.B, dtype=torch.float32, device=pr.dev)
+        g = _lib.AttnGrads()
+        g.dx, g.dq, g.dk, g.dv, g.delta = dx.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr()
+        dbias32 = None
+        if bias is not None:
+            dbias32 = torch.zeros(tuple(bias.shape)[::-1], dtype=torch.float32, device=pr.dev)
+            dbias32 = dbias32.permute(*range(bias.ndim - 1, -1, -1)) if bias.ndim else dbias32
+            g.dbias = dbias32.data_ptr()
+            g.dbias_stride = (C.c_int64 * 4)(*_bcast_strides("bias", dbias32, (pr.Lkv, pr.Lq, pr.H, pr.B)))
+        with torch.cuda.device(pr.dev):
+            _check(lib.nnlib_b200_attn_bwd(C.byref(pr.p), C.byref(g), _stream()), "attn_bwd")
+        return dq, dk, dv, (None if dbias32 is None else dbias32.to(bias.dtype))
+
+    return x, alpha, back
 
 
 def _unfused(q, k, v, bias, mask, nheads, fdrop):

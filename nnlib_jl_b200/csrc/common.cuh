@@ -40,6 +40,18 @@ struct AttnArgs {
   int d, dv, H, Lq, Lkv, B;
 };
 
+// Kernel-side view of nnlib_b200_attn_grads (defaults filled in).
+struct BwdArgs {
+  const void* dx;
+  long long dx_sl, dx_sb;
+  void* dq;
+  void* dk;
+  void* dv;
+  float* dbias;
+  long long dbias_s[4];
+  float* delta;
+};
+
 // ---- element types --------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<__half> {

@@ -15,6 +15,10 @@ cudaError_t simt_apply(const AttnArgs& a, int dtype, cudaStream_t st);
 cudaError_t causal_fill(unsigned char* m, long long L, cudaStream_t st);
 cudaError_t causal_check(const unsigned char* m, long long L, int* flag, cudaStream_t st);
 
+// backward on CUDA cores (attn_bwd_simt.cu)
+bool simt_bwd_supports(int d, int dv);
+cudaError_t simt_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_t st);
+
 // tcgen05 + TMA kernels (attn_umma.cu)
 bool umma_supports(const AttnArgs& a, int dtype, bool need_v);
 cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t st);

@@ -257,3 +257,40 @@ def attention_rows(q, k, v, nheads, rows, b, h, *, causal=False, mask=None,
         lse = m + np.log(np.sum(np.exp(logits - m), axis=0))
     x = vh @ alpha
     return x, alpha, lse
+
+
+# --------------------------------------------------------------------------
+# gradient of the path (what Zygote composes from the reference's rrules)
+# --------------------------------------------------------------------------
+
+def dot_product_attention_grad(q, k, v, dy, bias=None, *, mask=None, nheads=1, keep=None, p=0.0):
+    """Pullback of ``y = dot_product_attention(q, k, v, bias; mask, nheads, fdrop)[1]`` for 3-d inputs,
+    assembled from the reference's own rules: ``rrule(batched_mul)`` (``dA = dC·Bᵀ``, ``dB = Aᵀ·dC``,
+    ``src/batched/batchedmul.jl:96-110``), ``∇softmax`` (``dx = y .* (dy .- sum(dy .* y; dims))``,
+    ``src/softmax.jl:84-110``), the dropout pullback (``dy .* keep ./ (1-p)``, ``src/dropout.jl:106-122``),
+    ``ifelse`` masking (no gradient through masked entries) and the ``1/sqrt(d)`` scaling of q
+    (``src/attention.jl:118``).  ``keep`` is the Bool ``(Lkv, Lq, H, B)`` dropout mask (None: no dropout).
+    Returns ``(dq, dk, dv, dbias)``; ``dbias`` has the shape of ``bias`` (None without bias)."""
+    q, k, v, dy = (np.asarray(a, dtype=np.float64) for a in (q, k, v, dy))
+    d = q.shape[0] // nheads
+    q4, k4, v4, dy4 = (split_heads(a, nheads) for a in (q, k, v, dy))          # (d, H, L, B)
+    scale = 1.0 / math.sqrt(d)
+    fdrop = (lambda a: a) if keep is None else (lambda a: a * keep / (1.0 - p))
+    alpha = dot_product_attention_scores(q4, k4, None if bias is None else np.asarray(bias, dtype=np.float64),
+                                         mask=mask)                            # pre-dropout (Lkv, Lq, H, B)
+    alpha_d = fdrop(alpha)
+    # x[e,h,i,b] = Σ_j v[e,h,j,b] α'[j,i,h,b]
+    dv4 = np.einsum("ehib,jihb->ehjb", dy4, alpha_d)
+    dalpha_d = np.einsum("ehib,ehjb->jihb", dy4, v4)
+    dalpha = dalpha_d if keep is None else dalpha_d * keep / (1.0 - p)
+    dlogits = alpha * (dalpha - np.sum(dalpha * alpha, axis=0, keepdims=True))  # ∇softmax over kv
+    if mask is not None:
+        dlogits = np.where(np.broadcast_to(_bcast_to_scores(mask).astype(bool), dlogits.shape), dlogits, 0.0)
+    dq4 = scale * np.einsum("jihb,ehjb->ehib", dlogits, k4)
+    dk4 = scale * np.einsum("jihb,ehib->ehjb", dlogits, q4)
+    dbias = None
+    if bias is not None:
+        b4 = _bcast_to_scores(bias)
+        axes = tuple(ax for ax in range(4) if b4.shape[ax] == 1 and dlogits.shape[ax] != 1)
+        dbias = np.sum(dlogits, axis=axes, keepdims=True).reshape(np.asarray(bias).shape)
+    return join_heads(dq4), join_heads(dk4), join_heads(dv4), dbias

@@ -527,3 +527,96 @@ def test_linearity_in_v_full_size():
     ones = nb.jl_empty((E, L, B), dtype, DEV); ones.fill_(1.0)
     y, _ = nb.dot_product_attention(q, k, ones, mask=nb.CausalMask(), nheads=H)
     assert (y.float() - 1).abs().max().item() <= 2e-2
+
+
+# --------------------------------------------------------------------------
+# multi-GPU driver on real devices (one host thread per entry of `devices`)
+# --------------------------------------------------------------------------
+
+def test_sharded_driver_on_device_matches_single_call():
+    """Three shards (worker threads) over the visible GPUs — with one GPU they share it — so that the
+    unit ranges cut through a batch: head-range rectangles, pointer-free slicing, and the dropout
+    origin of each shard are exercised.  The sharded x must equal the unsharded call bit for bit."""
+    from nnlib_jl_b200.shard import ShardedAttention
+    ndev = torch.cuda.device_count()
+    devices = [f"cuda:{i % ndev}" for i in range(3)]
+    rng = np.random.default_rng(50)
+    dtype, E, H, Lq, Lkv, B = torch.bfloat16, 256, 4, 200, 260, 2      # 8 units over 3 shards: 3 + 3 + 2
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    mask = rng.random((Lkv, 1, 1, B)) > 0.2
+    mask[0] = True
+    q, k, v = (nb.jl_from_numpy(a, dtype=dtype) for a in (qn, kn, vn))           # host arrays
+    m_host = nb.jl_from_numpy(mask)
+    drv = ShardedAttention(devices)
+    x = drv(q, k, v, mask=m_host, nheads=H, fdrop=nb.PhiloxDropout(0.2, seed=5, offset=9))
+    assert not x.is_cuda and tuple(x.shape) == (E, Lq, B)
+    y, _ = nb.dot_product_attention(q.to(DEV), k.to(DEV), v.to(DEV), mask=m_host.to(DEV), nheads=H,
+                                    fdrop=nb.PhiloxDropout(0.2, seed=5, offset=9))
+    assert torch.equal(x, y.cpu())
+    keep = P.keep_mask((Lkv, Lq, H, B), 0.2, 5, 9)
+    yo, _ = O.dot_product_attention(qn, kn, vn, mask=mask, nheads=H, fdrop=lambda a: a * keep / np.float32(0.8))
+    _close(nb.jl_to_numpy(x), yo, dtype, "sharded x")
+
+
+# --------------------------------------------------------------------------
+# backward (pullback) against the gradient oracle
+# --------------------------------------------------------------------------
+
+def _grad_close(got, want, dtype, what):
+    """Gradients scale with the problem: compare relative to the oracle's magnitude."""
+    rel = {torch.float32: 2e-4, torch.float16: 1e-2, torch.bfloat16: 4e-2}[dtype]
+    g, w = got.astype(np.float64), want.astype(np.float64)
+    scale = np.abs(w).max() + 1e-30
+    assert np.isfinite(g).all(), what
+    assert np.abs(g - w).max() <= rel * scale, f"{what}: {np.abs(g - w).max() / scale:.3e} of max |grad|"
+
+
+def test_pullback_reference_gradtest_shapes():
+    # test/attention.jl:70-76: q (4,5,1), k = v (4,3,1), bias (3,5), nheads = 2 — Float32 on the device
+    rng = np.random.default_rng(60)
+    qn = rng.random((4, 5, 1), dtype=np.float32); kn = rng.random((4, 3, 1), dtype=np.float32)
+    bn = rng.standard_normal((3, 5)).astype(np.float32)
+    dyn = rng.standard_normal((4, 5, 1)).astype(np.float32)
+    f32 = torch.float32
+    x, a, back = nb.dot_product_attention_pullback(_dev(qn, f32), _dev(kn, f32), _dev(kn, f32), _dev(bn, f32), nheads=2)
+    dq, dk, dv, db = back(_dev(dyn, f32))
+    # k and v are the same array in the reference's test: its gradient is the sum of both roles
+    gq, gk, gv, gb = O.dot_product_attention_grad(qn, kn, kn, dyn, bn, nheads=2)
+    _grad_close(nb.jl_to_numpy(dq), gq, f32, "dq")
+    _grad_close(nb.jl_to_numpy(dk), gk, f32, "dk")
+    _grad_close(nb.jl_to_numpy(dv), gv, f32, "dv")
+    _grad_close(nb.jl_to_numpy(db), gb, f32, "dbias")
+    assert tuple(db.shape) == (3, 5)
+
+
+@pytest.mark.parametrize("dtype,E,H,Lq,Lkv,B,causal,drop", [
+    (torch.float32, 48, 3, 37, 50, 2, False, 0.0),
+    (torch.float32, 32, 2, 40, 40, 1, True, 0.25),
+    (torch.bfloat16, 128, 2, 130, 150, 2, False, 0.1),     # forward on the tensor-core kernels
+    (torch.float16, 256, 2, 129, 129, 1, True, 0.0),
+])
+def test_pullback_matches_gradient_oracle(dtype, E, H, Lq, Lkv, B, causal, drop):
+    rng = np.random.default_rng(61)
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    dyn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    bn = _round_to(0.5 * rng.standard_normal((Lkv, Lq, 1, B)), dtype)
+    pad = (np.arange(Lkv)[:, None, None, None] < rng.integers(Lkv // 2, Lkv + 1, size=B)[None, None, None, :])
+    mask_np = pad
+    if causal:
+        mask_np = pad & O.make_causal_mask(np.zeros((1, Lq)), dims=2)[:, :, None, None]
+    fd = nb.PhiloxDropout(drop, seed=77, offset=2) if drop > 0 else nb.identity
+    x, a, back = nb.dot_product_attention_pullback(
+        _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), _dev(bn, dtype),
+        mask=nb.jl_from_numpy(mask_np, device=DEV), nheads=H, fdrop=fd)
+    dq, dk, dv, db = back(_dev(dyn, dtype))
+    keep = P.keep_mask((Lkv, Lq, H, B), drop, 77, 2) if drop > 0 else None
+    gq, gk, gv, gb = O.dot_product_attention_grad(qn, kn, vn, dyn, bn, mask=mask_np, nheads=H, keep=keep, p=drop)
+    _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq")
+    _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
+    _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+    _grad_close(nb.jl_to_numpy(db), gb, dtype, "dbias")
+    assert tuple(db.shape) == (Lkv, Lq, 1, B)

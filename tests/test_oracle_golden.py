@@ -181,3 +181,40 @@ def test_philox_known_answers():
 def test_keep_mask_rate():
     m = P.keep_mask((64, 16, 2, 2), 0.1, seed=0xB200)
     assert abs(m.mean() - 0.9) < 0.02
+
+
+# ---- gradient oracle: pinned by central finite differences, like the reference's gradtest
+#      (test/attention.jl:70-76 uses FiniteDifferences on q (4,5,1), k = v (4,3,1), bias (3,5), nheads = 2)
+def _fd(fun, x, eps=1e-6):
+    out = np.zeros_like(x)
+    it = np.nditer(x, flags=["multi_index"])
+    for _ in it:
+        i = it.multi_index
+        xp, xm = x.copy(), x.copy()
+        xp[i] += eps
+        xm[i] -= eps
+        out[i] = (fun(xp) - fun(xm)) / (2 * eps)
+    return out
+
+
+@pytest.mark.parametrize("with_mask,with_drop", [(False, False), (True, False), (True, True)])
+def test_gradient_oracle_against_finite_differences(with_mask, with_drop):
+    rng = np.random.default_rng(20)
+    q = rng.random((4, 5, 1)); k = rng.random((4, 3, 1)); v = rng.random((4, 3, 1))
+    bias = rng.standard_normal((3, 5))
+    dy = rng.standard_normal((4, 5, 1))
+    mask = None
+    if with_mask:
+        mask = np.ones((3, 5), dtype=bool); mask[1, 2] = False; mask[2, 0] = False
+    keep, p = None, 0.0
+    fdrop = lambda a: a
+    if with_drop:
+        p = 0.3
+        keep = P.keep_mask((3, 5, 2, 1), p, seed=4)
+        fdrop = lambda a: a * keep / (1 - p)
+    f = lambda q_, k_, v_, b_: (O.dot_product_attention(q_, k_, v_, b_, mask=mask, nheads=2, fdrop=fdrop)[0] * dy).sum()
+    dq, dk, dv, db = O.dot_product_attention_grad(q, k, v, dy, bias, mask=mask, nheads=2, keep=keep, p=p)
+    np.testing.assert_allclose(dq, _fd(lambda t: f(t, k, v, bias), q), atol=1e-6, rtol=1e-6)
+    np.testing.assert_allclose(dk, _fd(lambda t: f(q, t, v, bias), k), atol=1e-6, rtol=1e-6)
+    np.testing.assert_allclose(dv, _fd(lambda t: f(q, k, t, bias), v), atol=1e-6, rtol=1e-6)
+    np.testing.assert_allclose(db, _fd(lambda t: f(q, k, v, t), bias), atol=1e-6, rtol=1e-6)
