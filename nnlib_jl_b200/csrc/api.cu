@@ -155,6 +155,8 @@ int nnlib_b200_attn_apply(const nnlib_b200_attn_params* p, void* stream) {
   const int rc = resolve(p, NEED_V | NEED_ALPHA, &a);
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
+  if (a.Lkv > 0 && !force_simt() && umma_apply_supports(a, p->dtype))
+    return finish(umma_apply(a, p->dtype, (cudaStream_t)stream));
   if (!simt_supports(1, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   return finish(simt_apply(a, p->dtype, (cudaStream_t)stream));
 }

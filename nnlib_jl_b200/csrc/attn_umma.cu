@@ -814,6 +814,165 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   }
 }
 
+// ===========================================================================
+// Apply kernel: x = V · alpha' for scores the caller already holds (the second
+// batched_mul of NNlib.jl src/attention.jl:96-98, used when fdrop is an opaque
+// callable that was applied to the materialised scores).  A plain batched GEMM
+// on the tensor cores, bound by the HBM read of alpha: per (128 queries, unit)
+// CTA, alpha tiles (128 queries x 128 keys, K-major: the keys are contiguous in
+// the (Lkv, Lq, H, B) array) and V tiles (MN-major) stream through a ring,
+// O accumulates in TMEM and is written once.
+//   warps 0-3  epilogue (thread r owns query row r)
+//   warp 4     TMA producer, TMEM allocation
+//   warp 5     MMA issuer
+// ===========================================================================
+constexpr int kApThreads = 192;
+
+template <int D>
+struct ApCfg {
+  static constexpr int kATile = 2 * kChunkBytes;              // 128 queries x 128 keys
+  static constexpr int kVTile = (D / 64) * kChunkBytes;       // 128 keys x D features
+  static constexpr int kStage = kATile + kVTile;
+  static constexpr int kStages = 2;                           // two CTAs per SM keep four tiles in flight
+  static constexpr int kBarOff = kStages * kStage;
+  static constexpr int kSmemBytes = kBarOff + 128 + 1024;
+};
+
+struct ApBarriers {
+  uint64_t full[4], empty[4], o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kApThreads, 2)
+attn_apply_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_v,
+                       const AttnArgs a, const int n_qtiles) {
+  using C = ApCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  ApBarriers* bars = reinterpret_cast<ApBarriers*>(smem + C::kBarOff);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit = blockIdx.x / n_qtiles, qt = blockIdx.x % n_qtiles;
+  const int h = unit % a.H, b = unit / a.H;
+  const int q0 = qt * kBM;
+  const int n_kv = (a.Lkv + kBN - 1) / kBN;
+  constexpr uint32_t kTmemCols = (D <= 64) ? 64 : 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->o_full, 1);
+    bars->abort_flag = *reinterpret_cast<volatile int*>(&g_umma_abort);
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const bool start_ok = (*abort_flag == 0);
+
+  if (start_ok && warp == 4) {
+    if (lane == 0) {
+      prefetch_tensormap(&tm_a);
+      prefetch_tensormap(&tm_v);
+      bool ok = true;
+      int j = 0;
+      for (; j < n_kv; ++j) {
+        const int s = j % C::kStages;
+        if (j >= C::kStages) ok = mbar_wait(&bars->empty[s], ((j / C::kStages) - 1) & 1, abort_flag);
+        if (!ok) break;
+        uint8_t* st = smem + s * C::kStage;
+        mbar_arrive_expect_tx(&bars->full[s], C::kStage);
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(st + c * kChunkBytes, &tm_a, &bars->full[s], j * kBN + c * 64, q0, h, b);
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(st + C::kATile + c * kChunkBytes, &tm_v, &bars->full[s], h * D + c * 64, j * kBN, b);
+      }
+      if (*abort_flag)
+        for (int jj = max(0, j - C::kStages); jj < j; ++jj)
+          mbar_wait_drain(&bars->full[jj % C::kStages], (jj / C::kStages) & 1, kDrainNs);
+    }
+  } else if (start_ok && warp == 5) {
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idesc = make_idesc_f16(BF16, kBM, D, false, true);   // A K-major, B (= V) MN-major
+      constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t lbo_k = (16u >> 4) << 16;
+      constexpr uint32_t lbo_v = (static_cast<uint32_t>(kChunkBytes) >> 4) << 16;
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j % C::kStages;
+        ok = mbar_wait(&bars->full[s], (j / C::kStages) & 1, abort_flag);
+        if (!ok) break;
+        const uint32_t a_lo = (smem_u32(smem + s * C::kStage) >> 4) | lbo_k;
+        const uint32_t v_lo = (smem_u32(smem + s * C::kStage + C::kATile) >> 4) | lbo_v;
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
+          umma_ss_lohi(tmem, a_lo + aoff, v_lo + kk * (2048 >> 4), desc_hi, idesc, (j == 0 && kk == 0) ? 0u : 1u);
+        }
+        umma_commit(&bars->empty[s]);
+      }
+      if (ok) umma_commit(&bars->o_full);
+    }
+  } else if (start_ok && warp < 4) {
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    const int i = q0 + warp * 32 + lane;
+    const bool row_ok = i < a.Lq;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) + 2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * D);
+    bool ok = true;
+    if (n_kv > 0) {
+      ok = mbar_wait(&bars->o_full, 0, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) tc_fence_after();
+    }
+    if (ok) {
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (n_kv > 0) {
+          tmem_ld32(lane_base + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 v;
+            v.x = pack2<BF16>(__uint_as_float(o[e]), __uint_as_float(o[e + 1]));
+            v.y = pack2<BF16>(__uint_as_float(o[e + 2]), __uint_as_float(o[e + 3]));
+            v.z = pack2<BF16>(__uint_as_float(o[e + 4]), __uint_as_float(o[e + 5]));
+            v.w = pack2<BF16>(__uint_as_float(o[e + 6]), __uint_as_float(o[e + 7]));
+            *reinterpret_cast<uint4*>(xrow + (c * 32 + e) * 2) = v;
+          }
+        }
+      }
+    }
+    (void)sizeof(T);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) {
+    atomicExch(&g_umma_abort, 1);
+    if (a.status) atomicExch(a.status, NNLIB_B200_TIMEOUT);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -937,6 +1096,40 @@ cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t
 #undef NB_FWD_ST
 #undef NB_FWD
   return cudaErrorInvalidValue;
+}
+
+bool umma_apply_supports(const AttnArgs& a, int dtype) {
+  if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
+  if (!(a.dv == 64 || a.dv == 128)) return false;
+  if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1) return false;
+  if (a.Lkv % 8 != 0 || !aligned16(a.alpha) || a.alpha_sb % 8 != 0) return false;
+  if ((long long)a.Lkv * a.Lq * 2 >= (1ll << 40)) return false;
+  if (!aligned16(a.v) || !aligned16(a.x) || !stride_ok(a.v_sl) || !stride_ok(a.v_sb) || !stride_ok(a.x_sl) ||
+      !stride_ok(a.x_sb))
+    return false;
+  return encode_tiled_fn() != nullptr;
+}
+
+cudaError_t umma_apply(const AttnArgs& a, int dtype, cudaStream_t st) {
+  CUtensorMap ma, mv;
+  if (!make_alpha_map(&ma, a, dtype)) return cudaErrorInvalidValue;
+  if (!make_map(&mv, a.v, dtype, (long long)a.H * a.dv, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
+  const int n_qtiles = (a.Lq + kBM - 1) / kBM;
+  const long long blocks = (long long)n_qtiles * a.H * a.B;
+  if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+  const bool bf16 = dtype == NNLIB_B200_BF16;
+#define NB_AP(DD, BF)                                                                                        \
+  do {                                                                                                       \
+    auto kern = attn_apply_umma_kernel<DD, BF>;                                                              \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ApCfg<DD>::kSmemBytes); \
+    if (e != cudaSuccess) return e;                                                                          \
+    kern<<<(unsigned)blocks, kApThreads, ApCfg<DD>::kSmemBytes, st>>>(ma, mv, a, n_qtiles);                  \
+  } while (0)
+  if (a.dv == 128) { if (bf16) NB_AP(128, true); else NB_AP(128, false); }
+  else             { if (bf16) NB_AP(64, true);  else NB_AP(64, false); }
+#undef NB_AP
+  count_launch();
+  return cudaGetLastError();
 }
 
 cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st) {

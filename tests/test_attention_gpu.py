@@ -620,3 +620,25 @@ def test_pullback_matches_gradient_oracle(dtype, E, H, Lq, Lkv, B, causal, drop)
     _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
     _grad_close(nb.jl_to_numpy(db), gb, dtype, "dbias")
     assert tuple(db.shape) == (Lkv, Lq, 1, B)
+
+
+@pytest.mark.parametrize("dtype,E,H,Lq,Lkv,B", [(torch.bfloat16, 256, 2, 200, 264, 2), (torch.float16, 128, 2, 129, 520, 1)])
+def test_opaque_fdrop_on_tensor_cores(dtype, E, H, Lq, Lkv, B):
+    """fdrop is an arbitrary callable: stats -> scores -> fdrop -> x = V·α′ (src/attention.jl:91-98), with the
+    last product on the tcgen05 apply kernel (16-bit types, 16-byte aligned score rows)."""
+    rng = np.random.default_rng(70)
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    keep_np = rng.random((Lkv, Lq, H, B)) > 0.3
+    keep = nb.jl_from_numpy(keep_np, device=DEV)
+    fdrop = lambda al: al * keep / 0.7
+    y, a = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), nheads=H, fdrop=fdrop)
+    an = nb.jl_to_numpy(a)
+    assert ((an > 0) == keep_np).mean() > 0.999       # returned scores are post-fdrop
+    # x must be V·α′ for the α′ that was returned (rounded to the element type)
+    v4 = O.split_heads(vn, H)
+    x4 = O.batched_mul(np.transpose(v4, (0, 2, 1, 3)), an)
+    _close(nb.jl_to_numpy(y), O.join_heads(np.transpose(x4, (0, 2, 1, 3))), dtype, "x = V·alpha'")
+    yo, _ = O.dot_product_attention(qn, kn, vn, nheads=H, fdrop=lambda al: al * keep_np / np.float32(0.7))
+    _close(nb.jl_to_numpy(y), yo, dtype, "x vs oracle")
