@@ -39,6 +39,7 @@ EXPORTS = (
     "nnlib_b200_workspace_bytes",
     "nnlib_b200_attention_static",
     "nnlib_b200_attn_bwd",
+    "nnlib_b200_attn_bwd_path",
     "nnlib_b200_causal_fill",
     "nnlib_b200_causal_check",
     "nnlib_b200_attn_path",
@@ -128,6 +129,8 @@ def load() -> C.CDLL:
     lib.nnlib_b200_attention_static.restype = C.c_int
     lib.nnlib_b200_attn_bwd.argtypes = [P, C.POINTER(AttnGrads), C.c_void_p]
     lib.nnlib_b200_attn_bwd.restype = C.c_int
+    lib.nnlib_b200_attn_bwd_path.argtypes = [P, C.POINTER(AttnGrads)]
+    lib.nnlib_b200_attn_bwd_path.restype = C.c_int
     lib.nnlib_b200_workspace_bytes.argtypes = [P]
     lib.nnlib_b200_workspace_bytes.restype = C.c_size_t
     lib.nnlib_b200_causal_fill.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]

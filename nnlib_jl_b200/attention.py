@@ -413,6 +413,7 @@ def dot_product_attention_pullback(q, k, v, bias=None, *, fdrop: Callable = iden
             dbias32 = dbias32.permute(*range(bias.ndim - 1, -1, -1)) if bias.ndim else dbias32
             g.dbias = dbias32.data_ptr()
             g.dbias_stride = (C.c_int64 * 4)(*_bcast_strides("bias", dbias32, (pr.Lkv, pr.Lq, pr.H, pr.B)))
+        back.path = lib.nnlib_b200_attn_bwd_path(C.byref(pr.p), C.byref(g))   # PATH_UMMA / PATH_SIMT, for tests
         with torch.cuda.device(pr.dev):
             _check(lib.nnlib_b200_attn_bwd(C.byref(pr.p), C.byref(g), _stream()), "attn_bwd")
         return dq, dk, dv, (None if dbias32 is None else dbias32.to(bias.dtype))

@@ -161,30 +161,48 @@ int nnlib_b200_attn_apply(const nnlib_b200_attn_params* p, void* stream) {
   return finish(simt_apply(a, p->dtype, (cudaStream_t)stream));
 }
 
-int nnlib_b200_attn_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g, void* stream) {
-  AttnArgs a;
-  const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN, &a);
+// shared front half of attn_bwd / attn_bwd_path: validates and resolves both argument blocks
+static int resolve_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g, AttnArgs* a, BwdArgs* b) {
+  const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN, a);
   if (rc) return rc;
   if (!g || g->struct_size != sizeof(nnlib_b200_attn_grads)) return NNLIB_B200_INVALID_ARG;
-  const bool empty = (a.Lq == 0 || a.B == 0);
-  if (!empty && (!g->dx || !g->dq || !g->delta || (a.Lkv > 0 && (!g->dk || !g->dv)))) return NNLIB_B200_INVALID_ARG;
-  BwdArgs b;
-  std::memset(&b, 0, sizeof(b));
-  const long long Ev = (long long)a.H * a.dv;
-  b.dx = g->dx;
-  b.dx_sl = g->dx_stride_l ? g->dx_stride_l : Ev;
-  b.dx_sb = g->dx_stride_b ? g->dx_stride_b : b.dx_sl * a.Lq;
-  if (b.dx_sl < Ev || b.dx_sb < 0) return NNLIB_B200_INVALID_ARG;
-  b.dq = g->dq; b.dk = g->dk; b.dv = g->dv;
-  b.dbias = g->dbias;
+  const bool empty = (a->Lq == 0 || a->B == 0);
+  if (!empty && (!g->dx || !g->dq || !g->delta || (a->Lkv > 0 && (!g->dk || !g->dv)))) return NNLIB_B200_INVALID_ARG;
+  std::memset(b, 0, sizeof(*b));
+  const long long Ev = (long long)a->H * a->dv;
+  b->dx = g->dx;
+  b->dx_sl = g->dx_stride_l ? g->dx_stride_l : Ev;
+  b->dx_sb = g->dx_stride_b ? g->dx_stride_b : b->dx_sl * a->Lq;
+  if (b->dx_sl < Ev || b->dx_sb < 0) return NNLIB_B200_INVALID_ARG;
+  b->dq = g->dq; b->dk = g->dk; b->dv = g->dv;
+  b->dbias = g->dbias;
   for (int i = 0; i < 4; ++i) {
     if (g->dbias_stride[i] < 0) return NNLIB_B200_INVALID_ARG;
-    b.dbias_s[i] = g->dbias_stride[i];
+    b->dbias_s[i] = g->dbias_stride[i];
   }
-  b.delta = g->delta;
-  if (!simt_bwd_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  b->delta = g->delta;
+  return NNLIB_B200_OK;
+}
+
+int nnlib_b200_attn_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g, void* stream) {
+  AttnArgs a;
+  BwdArgs b;
+  const int rc = resolve_bwd(p, g, &a, &b);
+  if (rc) return rc;
   if (a.B == 0 || (a.Lq == 0 && a.Lkv == 0)) return NNLIB_B200_OK;
+  if (!force_simt() && umma_bwd_supports(a, b, p->dtype)) return finish(umma_bwd(a, b, p->dtype, (cudaStream_t)stream));
+  if (!simt_bwd_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   return finish(simt_bwd(a, b, p->dtype, (cudaStream_t)stream));
+}
+
+int nnlib_b200_attn_bwd_path(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g) {
+  AttnArgs a;
+  BwdArgs b;
+  const int rc = resolve_bwd(p, g, &a, &b);
+  if (rc) return rc;
+  if (!force_simt() && umma_bwd_supports(a, b, p->dtype)) return NNLIB_B200_PATH_UMMA;
+  if (!simt_bwd_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  return NNLIB_B200_PATH_SIMT;
 }
 
 size_t nnlib_b200_workspace_bytes(const nnlib_b200_attn_params* p) {

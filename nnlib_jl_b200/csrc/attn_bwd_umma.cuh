@@ -1,0 +1,471 @@
+// Backward of plain / causal attention on the sm_100a tensor cores.  Included
+// by attn_umma.cu (shares its helpers, constants and the sticky abort flag).
+//
+// The gradients Zygote composes from NNlib.jl's rules for this path
+// (rrule(batched_mul) src/batched/batchedmul.jl:96-110, ∇softmax
+// src/softmax.jl:84-110, the 1/sqrt(d) scaling src/attention.jl:118) are, with
+//   P_ij  = exp(scale q_i·k_j - lse_i)          (recomputed from the saved lse)
+//   D_i   = dx_i · x_i
+//   dS_ij = P_ij (dx_i·v_j - D_i)
+//   dq_i = scale Σ_j dS_ij k_j,   dk_j = scale Σ_i dS_ij q_i,   dv_j = Σ_i P_ij dx_i.
+// One kernel template covers both halves.  A CTA keeps one 128-row tile pair
+// (A, B) resident and streams a ring of 128-row tile pairs (A', B'):
+//   DKV = false  (dq):      A = Q_i,  B = dX_i,  ring A' = K_j, B' = V_j
+//   DKV = true   (dk, dv):  A = K_j,  B = V_j,   ring A' = Q_i, B' = dX_i
+// and per ring step issues   S = A A'^T,  dP = B B'^T   (both 128x128 in TMEM),
+// lets the four compute warps turn them into P and dS (thread r owns row r of
+// the resident tile), and accumulates
+//   DKV = false:  dQ += dS · K_j                       (dS from TMEM, K_j MN-major)
+//   DKV = true:   dV += P^T · dX_i  (P^T from shared memory),  dK += dS^T · Q_i.
+// dS (half precision) overwrites the first 64 columns of dP in TMEM.
+//   warps 0-3  compute warps        warp 4  TMA producer, TMEM allocation
+//   warp 5     MMA issuer
+// TMEM columns: S [0,128)  dP [128,256)  accumulator 0 [256,256+D)  accumulator 1 [384,384+D).
+#pragma once
+
+namespace {
+
+constexpr int kBwThreads = 192;
+
+template <int D>
+struct BwCfg {
+  static constexpr int kTile = (D / 64) * kChunkBytes;  // 128 rows x D halves
+  static constexpr int kStages = 2;
+  static constexpr int kFixOff = 0;                      // resident pair
+  static constexpr int kRingOff = 2 * kTile;             // ring of pairs
+  static constexpr int kPOff = kRingOff + kStages * 2 * kTile;  // P^T tile (DKV only): 128 x 128 halves
+  static constexpr int kBarOffDq = kPOff;
+  static constexpr int kBarOffDkv = kPOff + 2 * kChunkBytes;
+  static constexpr int kSmemDq = kBarOffDq + 256 + 1024;
+  static constexpr int kSmemDkv = kBarOffDkv + 256 + 1024;
+};
+static_assert(BwCfg<128>::kSmemDkv <= 232448, "shared memory budget");
+
+struct BwBarriers {
+  uint64_t fix_full, full[2], empty[2];
+  uint64_t s_full, dp_full, s_read, ds_ready, acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// eight consecutive halves (one 16-byte load) times eight more, accumulated in fp32
+template <bool BF16>
+__device__ __forceinline__ float dot8(const uint4& x, const uint4& y, float acc) {
+  const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float2 fx, fy;
+    if (BF16) {
+      fx = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xs[e]));
+      fy = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ys[e]));
+    } else {
+      fx = __half22float2(*reinterpret_cast<const __half2*>(&xs[e]));
+      fy = __half22float2(*reinterpret_cast<const __half2*>(&ys[e]));
+    }
+    acc = fmaf(fx.x, fy.x, acc);
+    acc = fmaf(fx.y, fy.y, acc);
+  }
+  return acc;
+}
+
+// four consecutive floats of a per-query array (lse or D), entries past `n` replaced by `fill`
+__device__ __forceinline__ float4 load_col4(const float* p, int idx, int n, bool vec, float fill) {
+  if (vec && idx + 3 < n) return __ldg(reinterpret_cast<const float4*>(p + idx));
+  float4 r;
+  r.x = (idx + 0 < n) ? __ldg(p + idx + 0) : fill;
+  r.y = (idx + 1 < n) ? __ldg(p + idx + 1) : fill;
+  r.z = (idx + 2 < n) ? __ldg(p + idx + 2) : fill;
+  r.w = (idx + 3 < n) ? __ldg(p + idx + 3) : fill;
+  return r;
+}
+
+// score row held as raw TMEM words: element e lives in su[e / 32][e % 32]
+#define NB_SR(e) __uint_as_float(su[(e) >> 5][(e) & 31])
+#define NB_SR_SET(e, val) su[(e) >> 5][(e) & 31] = __float_as_uint(val)
+
+template <int D, bool BF16, bool DKV>
+__global__ void __launch_bounds__(kBwThreads, 1)
+attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_constant__ CUtensorMap tm_fb,
+                     const __grid_constant__ CUtensorMap tm_ra, const __grid_constant__ CUtensorMap tm_rb,
+                     const AttnArgs a, const BwdArgs g, const int n_tiles) {
+  using C = BwCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  BwBarriers* bars = reinterpret_cast<BwBarriers*>(smem + (DKV ? C::kBarOffDkv : C::kBarOffDq));
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // block -> (unit, resident tile); the tiles with the longest causal walk come first
+  const int unit = blockIdx.x / n_tiles;
+  const int tix = DKV ? (blockIdx.x % n_tiles) : (n_tiles - 1 - (blockIdx.x % n_tiles));
+  const int h = unit % a.H, b = unit / a.H;
+  const int t0 = tix * 128;             // first row of the resident tile (query for dq, key for dk/dv)
+
+  // ring range: tiles r_first .. r_first + n - 1 of the other sequence
+  int r_first = 0, n;
+  if (!DKV) {
+    const int kv_end = a.causal ? min(a.Lkv, t0 + 128) : a.Lkv;
+    n = (kv_end + 127) / 128;
+  } else {
+    const int n_q = (a.Lq + 127) / 128;
+    r_first = a.causal ? tix : 0;       // query tiles before the key tile never see it
+    n = max(0, n_q - r_first);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->fix_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->s_read, 4);
+    mbar_init(&bars->ds_ready, 4);
+    mbar_init(&bars->acc_full, 1);
+    bars->abort_flag = *reinterpret_cast<volatile int*>(&g_umma_abort);
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const bool start_ok = (*abort_flag == 0);
+  constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
+
+  if (start_ok && warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n > 0) {
+      prefetch_tensormap(&tm_fa);
+      prefetch_tensormap(&tm_fb);
+      prefetch_tensormap(&tm_ra);
+      prefetch_tensormap(&tm_rb);
+      mbar_arrive_expect_tx(&bars->fix_full, 2 * C::kTile);
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_3d(smem + C::kFixOff + c * kChunkBytes, &tm_fa, &bars->fix_full, h * D + c * 64, t0, b);
+        tma_load_3d(smem + C::kFixOff + C::kTile + c * kChunkBytes, &tm_fb, &bars->fix_full, h * D + c * 64, t0, b);
+      }
+      bool ok = true;
+      int it = 0;
+      for (; it < n; ++it) {
+        const int s = it % C::kStages;
+        if (it >= C::kStages) ok = mbar_wait(&bars->empty[s], ((it / C::kStages) - 1) & 1, abort_flag);
+        if (!ok) break;
+        uint8_t* st = smem + C::kRingOff + s * 2 * C::kTile;
+        const int row = (r_first + it) * 128;
+        mbar_arrive_expect_tx(&bars->full[s], 2 * C::kTile);
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_3d(st + c * kChunkBytes, &tm_ra, &bars->full[s], h * D + c * 64, row, b);
+          tma_load_3d(st + C::kTile + c * kChunkBytes, &tm_rb, &bars->full[s], h * D + c * 64, row, b);
+        }
+      }
+      if (*abort_flag) {
+        mbar_wait_drain(&bars->fix_full, 0, kDrainNs);
+        for (int jj = max(0, it - C::kStages); jj < it; ++jj)
+          mbar_wait_drain(&bars->full[jj % C::kStages], (jj / C::kStages) & 1, kDrainNs);
+      }
+    }
+  } else if (start_ok && warp == 5) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_nt = make_idesc_f16(BF16, 128, 128, false, false);  // both operands K-major
+      constexpr uint32_t idesc_acc = make_idesc_f16(BF16, 128, D, false, true);    // B MN-major
+      constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t lbo_k = (16u >> 4) << 16;
+      constexpr uint32_t lbo_mn = (static_cast<uint32_t>(kChunkBytes) >> 4) << 16;
+      constexpr uint32_t tile16 = C::kTile >> 4;
+      const uint32_t fix_a = (smem_u32(smem + C::kFixOff) >> 4) | lbo_k;
+      const uint32_t fix_b = fix_a + tile16;
+      const uint32_t ring_k = (smem_u32(smem + C::kRingOff) >> 4) | lbo_k;    // ring tiles read K-major
+      const uint32_t ring_mn = (smem_u32(smem + C::kRingOff) >> 4) | lbo_mn;  // ring tiles read MN-major
+      const uint32_t p_lo = (smem_u32(smem + C::kPOff) >> 4) | lbo_k;
+      bool ok = mbar_wait(&bars->fix_full, 0, abort_flag);
+
+      // products that consume what the compute warps made of ring step `pit`
+      auto issue_acc = [&](int pit) {
+        const uint32_t st16 = (pit % C::kStages) * 2 * tile16;
+        if (DKV) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {   // dV += P^T dX_i
+            const uint32_t aoff = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
+            umma_ss_lohi(tmem + kColAcc0, p_lo + aoff, ring_mn + st16 + tile16 + kk * (2048 >> 4), desc_hi, idesc_acc,
+                         (pit == 0 && kk == 0) ? 0u : 1u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)     // dK += dS^T Q_i
+            umma_ts_lohi(tmem + kColAcc1, tmem + kColDP + kk * 8, ring_mn + st16 + kk * (2048 >> 4), desc_hi, idesc_acc,
+                         (pit == 0 && kk == 0) ? 0u : 1u);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)     // dQ += dS K_j
+            umma_ts_lohi(tmem + kColAcc0, tmem + kColDP + kk * 8, ring_mn + st16 + kk * (2048 >> 4), desc_hi, idesc_acc,
+                         (pit == 0 && kk == 0) ? 0u : 1u);
+        }
+        umma_commit(&bars->empty[pit % C::kStages]);
+      };
+
+      for (int it = 0; it < n && ok; ++it) {
+        const int s = it % C::kStages;
+        const uint32_t st16 = s * 2 * tile16;
+        ok = mbar_wait(&bars->full[s], (it / C::kStages) & 1, abort_flag);
+        if (ok && it > 0) ok = mbar_wait(&bars->s_read, (it - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {   // S = A A'^T
+          const uint32_t off = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
+          umma_ss_lohi(tmem + kColS, fix_a + off, ring_k + st16 + off, desc_hi, idesc_nt, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->s_full);
+        if (it > 0) {
+          ok = mbar_wait(&bars->ds_ready, (it - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_acc(it - 1);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {   // dP = B B'^T
+          const uint32_t off = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
+          umma_ss_lohi(tmem + kColDP, fix_b + off, ring_k + st16 + tile16 + off, desc_hi, idesc_nt, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->dp_full);
+      }
+      if (ok) ok = mbar_wait(&bars->ds_ready, (n - 1) & 1, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_acc(n - 1);
+        umma_commit(&bars->acc_full);
+      }
+    }
+  } else if (start_ok && warp < 4) {
+    // ----------------------------------------------------------- compute warps
+    const int r = warp * 32 + lane;       // row of the resident tile = TMEM lane
+    const int row = t0 + r;               // query (dq) or key (dk/dv) index
+    const bool row_ok = row < (DKV ? a.Lkv : a.Lq);
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const float c2 = a.scale * kLog2e;
+    const float pos_inf = __int_as_float(0x7f800000);
+    const float* lse_u = a.lse + (long long)a.Lq * h + a.lse_sb * b;
+    float* delta_u = g.delta + (long long)a.Lq * h + (long long)a.Lq * a.H * b;
+    bool ok = true;
+
+    // per-row constants of the dq half: lse_i (base 2) and D_i = dx_i · x_i
+    float lse2_row = pos_inf, dl_row = 0.f;
+    if (!DKV && row_ok) {
+      lse2_row = __ldg(lse_u + row) * kLog2e;
+      const uint4* dxr = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(g.dx) +
+                         2ll * ((long long)row * g.dx_sl + (long long)b * g.dx_sb + (long long)h * D));
+      const uint4* xr = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.x) +
+                        2ll * ((long long)row * a.x_sl + (long long)b * a.x_sb + (long long)h * D));
+#pragma unroll
+      for (int e = 0; e < D / 8; ++e) dl_row = dot8<BF16>(__ldg(dxr + e), __ldg(xr + e), dl_row);
+      delta_u[row] = dl_row;
+    }
+    // dk/dv half: lse and D are per COLUMN (query), read with broadcast loads
+    const bool vec = ((reinterpret_cast<uintptr_t>(lse_u) | reinterpret_cast<uintptr_t>(delta_u)) & 15u) == 0;
+
+    for (int it = 0; it < n && ok; ++it) {
+      const uint32_t par = it & 1;
+      const int c0 = (r_first + it) * 128;   // first column: key (dq) or query (dk/dv) index
+      ok = mbar_wait(&bars->s_full, par, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t su[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(lane_base + kColS + c * 32, su[c]);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_read);
+
+      if (!DKV) {
+        const int lim = row_ok ? (a.causal ? min(row, a.Lkv - 1) : a.Lkv - 1) : -1;  // last key of this row
+#pragma unroll
+        for (int e = 0; e < 128; ++e) NB_SR_SET(e, ex2_approx(fmaf(NB_SR(e), c2, -lse2_row)));
+        if (c0 + 127 > lim) {
+#pragma unroll
+          for (int e = 0; e < 128; ++e)
+            if (c0 + e > lim) NB_SR_SET(e, 0.f);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 128; e += 4) {
+          const float4 L = load_col4(lse_u, c0 + e, a.Lq, vec, pos_inf);
+          NB_SR_SET(e + 0, ex2_approx(fmaf(NB_SR(e + 0), c2, -L.x * kLog2e)));
+          NB_SR_SET(e + 1, ex2_approx(fmaf(NB_SR(e + 1), c2, -L.y * kLog2e)));
+          NB_SR_SET(e + 2, ex2_approx(fmaf(NB_SR(e + 2), c2, -L.z * kLog2e)));
+          NB_SR_SET(e + 3, ex2_approx(fmaf(NB_SR(e + 3), c2, -L.w * kLog2e)));
+        }
+        // queries before this key (causal) and padded key rows contribute nothing
+        const int cmin = row_ok ? (a.causal ? row - c0 : 0) : 128;
+        if (cmin > 0) {
+#pragma unroll
+          for (int e = 0; e < 128; ++e)
+            if (e < cmin) NB_SR_SET(e, 0.f);
+        }
+      }
+
+      ok = mbar_wait(&bars->dp_full, par, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+
+      if (DKV) {
+        // P^T as the K-major A operand of dV += P^T dX: row r, 16-byte pieces in 128-byte-swizzled order.
+        // (dp_full also tells that the previous step's products have finished reading this tile.)
+        uint8_t* prow = smem + C::kPOff + r * 128;
+#pragma unroll
+        for (int piece = 0; piece < 16; ++piece) {
+          uint4 v;
+          v.x = pack2<BF16>(NB_SR(piece * 8 + 0), NB_SR(piece * 8 + 1));
+          v.y = pack2<BF16>(NB_SR(piece * 8 + 2), NB_SR(piece * 8 + 3));
+          v.z = pack2<BF16>(NB_SR(piece * 8 + 4), NB_SR(piece * 8 + 5));
+          v.w = pack2<BF16>(NB_SR(piece * 8 + 6), NB_SR(piece * 8 + 7));
+          *reinterpret_cast<uint4*>(prow + (piece >> 3) * kChunkBytes + (((piece & 7) ^ (r & 7)) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+      }
+
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 2 + cc;
+          uint32_t dp[32];
+          tmem_ld32(lane_base + kColDP + c * 32, dp);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            float4 Dl = make_float4(dl_row, dl_row, dl_row, dl_row);
+            if (DKV) Dl = load_col4(delta_u, c0 + c * 32 + e, a.Lq, vec, 0.f);
+            const float d0 = (__uint_as_float(dp[e + 0]) - Dl.x) * NB_SR(c * 32 + e + 0);
+            const float d1 = (__uint_as_float(dp[e + 1]) - Dl.y) * NB_SR(c * 32 + e + 1);
+            const float d2 = (__uint_as_float(dp[e + 2]) - Dl.z) * NB_SR(c * 32 + e + 2);
+            const float d3 = (__uint_as_float(dp[e + 3]) - Dl.w) * NB_SR(c * 32 + e + 3);
+            pk[cc * 16 + e / 2] = pack2<BF16>(d0, d1);
+            pk[cc * 16 + e / 2 + 1] = pack2<BF16>(d2, d3);
+          }
+        }
+        tmem_st32(lane_base + kColDP + half * 32, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->ds_ready);
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    if (ok && n > 0) {
+      ok = mbar_wait(&bars->acc_full, 0, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) tc_fence_after();
+    }
+    if (ok) {
+      const long long Lrow = DKV ? a.Lkv : a.Lq;
+      const long long dense = 2ll * (((long long)row + Lrow * b) * ((long long)a.H * D) + (long long)h * D);
+      constexpr int kOuts = DKV ? 2 : 1;
+#pragma unroll
+      for (int which = 0; which < kOuts; ++which) {
+        // accumulator 0: dq (dq half) or dv (dk/dv half); accumulator 1: dk
+        uint8_t* out = reinterpret_cast<uint8_t*>(DKV ? (which == 0 ? g.dv : g.dk) : g.dq) + dense;
+        const float mul = (DKV && which == 0) ? 1.f : a.scale;
+        const uint32_t col = which == 0 ? kColAcc0 : kColAcc1;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (n > 0) {
+            tmem_ld32(lane_base + col + c * 32, o);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0u;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 v;
+              v.x = pack2<BF16>(__uint_as_float(o[e]) * mul, __uint_as_float(o[e + 1]) * mul);
+              v.y = pack2<BF16>(__uint_as_float(o[e + 2]) * mul, __uint_as_float(o[e + 3]) * mul);
+              v.z = pack2<BF16>(__uint_as_float(o[e + 4]) * mul, __uint_as_float(o[e + 5]) * mul);
+              v.w = pack2<BF16>(__uint_as_float(o[e + 6]) * mul, __uint_as_float(o[e + 7]) * mul);
+              *reinterpret_cast<uint4*>(out + (c * 32 + e) * 2) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag) {
+    atomicExch(&g_umma_abort, 1);
+    if (a.status) atomicExch(a.status, NNLIB_B200_TIMEOUT);
+  }
+}
+
+#undef NB_SR
+#undef NB_SR_SET
+
+template <int D, bool BF16, bool DKV>
+cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const CUtensorMap& ra, const CUtensorMap& rb,
+                            const AttnArgs& a, const BwdArgs& g, cudaStream_t st) {
+  auto kern = attn_bwd_umma_kernel<D, BF16, DKV>;
+  constexpr int smem = DKV ? BwCfg<D>::kSmemDkv : BwCfg<D>::kSmemDq;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  const int n_tiles = ((DKV ? a.Lkv : a.Lq) + 127) / 128;
+  const long long blocks = (long long)n_tiles * a.H * a.B;
+  if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+  kern<<<(unsigned)blocks, kBwThreads, smem, st>>>(fa, fb, ra, rb, a, g, n_tiles);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// The tensor-core backward covers the training case that has no side inputs: half-precision,
+// d = dv in {64, 128}, no bias, no Bool mask array (causal is fine), no dropout.
+bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype) {
+  if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
+  if (!(a.d == 64 || a.d == 128) || a.dv != a.d) return false;
+  if (a.bias || a.mask || a.dropout_p > 0.f || g.dbias) return false;
+  if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1 || !a.lse || !g.delta) return false;
+  const void* ptrs[] = {a.q, a.k, a.v, a.x, g.dx, g.dq, g.dk, g.dv};
+  for (const void* p : ptrs)
+    if (!p || !aligned16(p)) return false;
+  const long long strides[] = {a.q_sl, a.q_sb, a.k_sl, a.k_sb, a.v_sl, a.v_sb, a.x_sl, a.x_sb, g.dx_sl, g.dx_sb};
+  for (long long s : strides)
+    if (!stride_ok(s)) return false;
+  return encode_tiled_fn() != nullptr;
+}
+
+cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_t st) {
+  CUtensorMap mq, mk, mv, mdx;
+  const long long E = (long long)a.H * a.d;
+  if (!make_map(&mq, a.q, dtype, E, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
+  if (!make_map(&mk, a.k, dtype, E, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
+  if (!make_map(&mv, a.v, dtype, E, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
+  if (!make_map(&mdx, g.dx, dtype, E, a.Lq, a.B, g.dx_sl, g.dx_sb)) return cudaErrorInvalidValue;
+  const bool bf16 = dtype == NNLIB_B200_BF16;
+  cudaError_t e;
+#define NB_BW(DD, BF)                                                        \
+  do {                                                                       \
+    e = launch_bwd_umma<DD, BF, false>(mq, mdx, mk, mv, a, g, st);           \
+    if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true>(mk, mv, mq, mdx, a, g, st); \
+  } while (0)
+  if (a.d == 128) { if (bf16) NB_BW(128, true); else NB_BW(128, false); }
+  else            { if (bf16) NB_BW(64, true);  else NB_BW(64, false); }
+#undef NB_BW
+  return e;
+}

@@ -1179,4 +1179,7 @@ cudaError_t umma_take_abort(int* out, cudaStream_t st) {
   return e;
 }
 
+// tensor-core backward (same translation unit: it shares the helpers above)
+#include "attn_bwd_umma.cuh"
+
 }  // namespace nb200

@@ -622,6 +622,89 @@ def test_pullback_matches_gradient_oracle(dtype, E, H, Lq, Lkv, B, causal, drop)
     assert tuple(db.shape) == (Lkv, Lq, 1, B)
 
 
+@pytest.mark.parametrize("dtype,E,H,Lq,Lkv,B,causal", [
+    (torch.bfloat16, 128, 2, 200, 264, 2, False),    # d = 64, ragged tiles
+    (torch.bfloat16, 256, 2, 300, 300, 1, True),     # d = 128, causal with a partial last tile
+    (torch.float16, 128, 1, 129, 520, 1, False),     # d = 128, many key tiles
+    (torch.float16, 128, 2, 384, 384, 2, True),      # d = 64, whole tiles
+])
+def test_pullback_on_tensor_cores(dtype, E, H, Lq, Lkv, B, causal):
+    """Plain / causal attention of 16-bit arrays: the backward runs on the tcgen05 kernels and matches the
+    gradient oracle (and the CUDA-core backward, which the other pullback tests pin)."""
+    rng = np.random.default_rng(62)
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    dyn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    mask = nb.make_causal_mask(_dev(qn, dtype)) if causal else None
+    mask_np = (np.arange(Lkv)[:, None] <= np.arange(Lq)[None, :]) if causal else None
+    x, a, back = nb.dot_product_attention_pullback(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype),
+                                                   mask=mask, nheads=H)
+    dq, dk, dv, db = back(_dev(dyn, dtype))
+    assert back.path == nb._lib.PATH_UMMA
+    assert db is None
+    nb.device_health()
+    gq, gk, gv, _ = O.dot_product_attention_grad(qn, kn, vn, dyn, None, mask=mask_np, nheads=H)
+    _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq")
+    _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
+    _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+
+
+@pytest.mark.parametrize("Lq,Lkv", [(100, 300), (515, 130)])
+def test_abi_backward_causal_flag_on_a_head_slice(Lq, Lkv):
+    """C ABI: causal flag with kv_len != q_len (keys past the last query get zero gradient) on a shard that
+    owns heads 1..2 of 4 through pointer offsets and the parent's strides; tcgen05 backward kernels."""
+    import ctypes as C
+    lib = _lib.load()
+    rng = np.random.default_rng(63)
+    dtype = torch.bfloat16
+    H, d, B = 4, 128, 2
+    E = H * d
+    h0, Hs = 1, 2
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    dyn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    q, k, v, dx = _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), _dev(dyn, dtype)
+    x = nb.jl_zeros((E, Lq, B), dtype, DEV)
+    lse = torch.empty((B, Hs, Lq), dtype=torch.float32, device=DEV)
+    delta = torch.empty((B, Hs, Lq), dtype=torch.float32, device=DEV)
+    dq = nb.jl_zeros((Hs * d, Lq, B), dtype, DEV)
+    dk = nb.jl_zeros((Hs * d, Lkv, B), dtype, DEV)
+    dv = nb.jl_zeros((Hs * d, Lkv, B), dtype, DEV)
+    p = _lib.AttnParams()
+    p.dtype = _lib.BF16
+    p.d, p.dv, p.H, p.Lq, p.Lkv, p.B = d, d, Hs, Lq, Lkv, B
+    off = h0 * d * 2
+    p.q, p.k, p.v, p.x = q.data_ptr() + off, k.data_ptr() + off, v.data_ptr() + off, x.data_ptr() + off
+    p.q_stride_l = p.k_stride_l = p.v_stride_l = p.x_stride_l = E
+    p.q_stride_b, p.x_stride_b = E * Lq, E * Lq
+    p.k_stride_b = p.v_stride_b = E * Lkv
+    p.lse = lse.data_ptr()
+    p.causal = 1
+    g = _lib.AttnGrads()
+    g.dx = dx.data_ptr() + off
+    g.dx_stride_l, g.dx_stride_b = E, E * Lq
+    g.dq, g.dk, g.dv, g.delta = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr()
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.nnlib_b200_attn_fwd(C.byref(p), st) == 0
+    assert lib.nnlib_b200_attn_bwd_path(C.byref(p), C.byref(g)) == _lib.PATH_UMMA
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), C.byref(g), st) == 0
+    nb.device_health()
+    mask_np = np.arange(Lkv)[:, None] <= np.arange(Lq)[None, :]
+    sl = slice(h0 * d, (h0 + Hs) * d)
+    gq, gk, gv, _ = O.dot_product_attention_grad(qn[sl], kn[sl], vn[sl], dyn[sl], None, mask=mask_np, nheads=Hs)
+    _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq")
+    _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
+    _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+    if Lkv > Lq:
+        assert (nb.jl_to_numpy(dk)[:, Lq:] == 0).all() and (nb.jl_to_numpy(dv)[:, Lq:] == 0).all()
+    # D_i = dx_i · x_i is left in the scratch array
+    dl = (nb.jl_to_numpy(dx).astype(np.float64)[sl] * nb.jl_to_numpy(x).astype(np.float64)[sl])
+    want_delta = dl.reshape(Hs, d, Lq, B).sum(1).transpose(2, 0, 1)          # (B, Hs, Lq)
+    np.testing.assert_allclose(delta.cpu().numpy(), want_delta, rtol=1e-3, atol=1e-3)
+
+
 @pytest.mark.parametrize("dtype,E,H,Lq,Lkv,B", [(torch.bfloat16, 256, 2, 200, 264, 2), (torch.float16, 128, 2, 129, 520, 1)])
 def test_opaque_fdrop_on_tensor_cores(dtype, E, H, Lq, Lkv, B):
     """fdrop is an arbitrary callable: stats -> scores -> fdrop -> x = V·α′ (src/attention.jl:91-98), with the
