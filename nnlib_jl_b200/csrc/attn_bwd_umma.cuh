@@ -9,44 +9,50 @@
 //   dS_ij = P_ij (dx_i·v_j - D_i)
 //   dq_i = scale Σ_j dS_ij k_j,   dk_j = scale Σ_i dS_ij q_i,   dv_j = Σ_i P_ij dx_i.
 // One kernel template covers both halves.  A CTA keeps one 128-row tile pair
-// (A, B) resident and streams a ring of 128-row tile pairs (A', B'):
-//   DKV = false  (dq):      A = Q_i,  B = dX_i,  ring A' = K_j, B' = V_j
-//   DKV = true   (dk, dv):  A = K_j,  B = V_j,   ring A' = Q_i, B' = dX_i
+// (A, B) resident and streams two rings of 128-row tiles (A', B'):
+//   DKV = false  (dq):      A = Q_i,  B = dX_i,  rings A' = K_j, B' = V_j
+//   DKV = true   (dk, dv):  A = K_j,  B = V_j,   rings A' = Q_i, B' = dX_i
 // and per ring step issues   S = A A'^T,  dP = B B'^T   (both 128x128 in TMEM),
-// lets the four compute warps turn them into P and dS (thread r owns row r of
-// the resident tile), and accumulates
+// lets the compute warps turn them into P and dS, and accumulates
 //   DKV = false:  dQ += dS · K_j                       (dS from TMEM, K_j MN-major)
 //   DKV = true:   dV += P^T · dX_i  (P^T from shared memory),  dK += dS^T · Q_i.
-// dS (half precision) overwrites the first 64 columns of dP in TMEM.
-//   warps 0-3  compute warps        warp 4  TMA producer, TMEM allocation
-//   warp 5     MMA issuer
+//   warps 0-3   compute, columns 0-63 of the step (thread r owns row r of the resident tile)
+//   warps 4-7   compute, columns 64-127
+//   warp 8      TMA producer of the resident pair and of ring A'; TMEM allocation
+//   warp 9      MMA issuer
+//   warp 10     TMA producer of ring B'
 // TMEM columns: S [0,128)  dP [128,256)  accumulator 0 [256,256+D)  accumulator 1 [384,384+D).
+// dS (half precision) overwrites dP: columns [128,160) for ring rows 0-63, [192,224) for rows 64-127.
 #pragma once
 
 namespace {
 
-constexpr int kBwThreads = 192;
+constexpr int kBwThreads = 352;
 
-template <int D>
+template <int D, bool DKV>
 struct BwCfg {
   static constexpr int kTile = (D / 64) * kChunkBytes;  // 128 rows x D halves
-  static constexpr int kStages = 2;
-  static constexpr int kFixOff = 0;                      // resident pair
-  static constexpr int kRingOff = 2 * kTile;             // ring of pairs
-  static constexpr int kPOff = kRingOff + kStages * 2 * kTile;  // P^T tile (DKV only): 128 x 128 halves
-  static constexpr int kBarOffDq = kPOff;
-  static constexpr int kBarOffDkv = kPOff + 2 * kChunkBytes;
-  static constexpr int kSmemDq = kBarOffDq + 256 + 1024;
-  static constexpr int kSmemDkv = kBarOffDkv + 256 + 1024;
+  // Ring A' feeds S early and the accumulation late; ring B' of the dq half (V) is free as soon as dP
+  // is done, so the dq half can afford a third A' stage.  The dk/dv half keeps P^T in shared memory.
+  static constexpr int kStagesA = DKV ? 2 : 3;
+  static constexpr int kStagesB = 2;
+  static constexpr int kFixOff = 0;                               // resident pair
+  static constexpr int kAOff = 2 * kTile;
+  static constexpr int kBOff = kAOff + kStagesA * kTile;
+  static constexpr int kPOff = kBOff + kStagesB * kTile;          // P^T tile (DKV): 128 x 128 halves
+  static constexpr int kColOff = kPOff + (DKV ? 2 * kChunkBytes : 0);  // per-query lse, D of two ring tiles (DKV)
+  static constexpr int kBarOff = kColOff + (DKV ? 2048 : 0);
+  static constexpr int kSmemBytes = kBarOff + 256;                // no slack: the kernel checks its 1 KB alignment
 };
-static_assert(BwCfg<128>::kSmemDkv <= 232448, "shared memory budget");
+static_assert(BwCfg<128, true>::kSmemBytes <= 232448 && BwCfg<128, false>::kSmemBytes <= 232448, "shared memory budget");
 
 struct BwBarriers {
-  uint64_t fix_full, full[2], empty[2];
-  uint64_t s_full, dp_full, s_read, ds_ready, acc_full;
+  uint64_t fix_full, a_full[3], a_empty[3], b_full[2], b_empty[2];
+  uint64_t s_full, dp_full, s_read, ds_ready, acc_full, col_ready;
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(BwBarriers) <= 256, "barrier block");
 
 // eight consecutive halves (one 16-byte load) times eight more, accumulated in fp32
 template <bool BF16>
@@ -68,16 +74,14 @@ __device__ __forceinline__ float dot8(const uint4& x, const uint4& y, float acc)
   return acc;
 }
 
-// four consecutive floats of a per-query array (lse or D), entries past `n` replaced by `fill`
-__device__ __forceinline__ float4 load_col4(const float* p, int idx, int n, bool vec, float fill) {
-  if (vec && idx + 3 < n) return __ldg(reinterpret_cast<const float4*>(p + idx));
-  float4 r;
-  r.x = (idx + 0 < n) ? __ldg(p + idx + 0) : fill;
-  r.y = (idx + 1 < n) ? __ldg(p + idx + 1) : fill;
-  r.z = (idx + 2 < n) ? __ldg(p + idx + 2) : fill;
-  r.w = (idx + 3 < n) ? __ldg(p + idx + 3) : fill;
-  return r;
-}
+#ifdef NB200_TRACE
+#ifndef NB200_TRACE_DKV
+#define NB200_TRACE_DKV 0
+#endif
+#define BW_TRACE(role, j, slot) do { if (DKV == (NB200_TRACE_DKV != 0)) NB_TRACE(role, j, slot); } while (0)
+#else
+#define BW_TRACE(role, j, slot) do { } while (0)
+#endif
 
 // score row held as raw TMEM words: element e lives in su[e / 32][e % 32]
 #define NB_SR(e) __uint_as_float(su[(e) >> 5][(e) & 31])
@@ -88,10 +92,17 @@ __global__ void __launch_bounds__(kBwThreads, 1)
 attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_constant__ CUtensorMap tm_fb,
                      const __grid_constant__ CUtensorMap tm_ra, const __grid_constant__ CUtensorMap tm_rb,
                      const AttnArgs a, const BwdArgs g, const int n_tiles) {
-  using C = BwCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  BwBarriers* bars = reinterpret_cast<BwBarriers*>(smem + (DKV ? C::kBarOffDkv : C::kBarOffDq));
+  using C = BwCfg<D, DKV>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    // the swizzled tiles need 1 KB alignment and the budget leaves no room to round up: refuse cleanly
+    if (threadIdx.x == 0) {
+      atomicExch(&g_umma_abort, 1);
+      if (a.status) atomicExch(a.status, NNLIB_B200_CUDA_ERROR);
+    }
+    return;
+  }
+  BwBarriers* bars = reinterpret_cast<BwBarriers*>(smem + C::kBarOff);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -114,19 +125,24 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->fix_full, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&bars->a_full[s], 1);
+      mbar_init(&bars->a_empty[s], 1);
+    }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->empty[s], 1);
+      mbar_init(&bars->b_full[s], 1);
+      mbar_init(&bars->b_empty[s], 1);
     }
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->dp_full, 1);
-    mbar_init(&bars->s_read, 4);
-    mbar_init(&bars->ds_ready, 4);
+    mbar_init(&bars->s_read, 8);
+    mbar_init(&bars->ds_ready, 8);
     mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->col_ready, 8);
     bars->abort_flag = *reinterpret_cast<volatile int*>(&g_umma_abort);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
   }
@@ -137,13 +153,12 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
   const bool start_ok = (*abort_flag == 0);
   constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
 
-  if (start_ok && warp == 4) {
-    // ------------------------------------------------------------ TMA producer
+  if (start_ok && warp == 8) {
+    // ------------------------------------- TMA producer: resident pair and ring A'
     if (lane == 0 && n > 0) {
       prefetch_tensormap(&tm_fa);
       prefetch_tensormap(&tm_fb);
       prefetch_tensormap(&tm_ra);
-      prefetch_tensormap(&tm_rb);
       mbar_arrive_expect_tx(&bars->fix_full, 2 * C::kTile);
       for (int c = 0; c < D / 64; ++c) {
         tma_load_3d(smem + C::kFixOff + c * kChunkBytes, &tm_fa, &bars->fix_full, h * D + c * 64, t0, b);
@@ -152,24 +167,42 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       bool ok = true;
       int it = 0;
       for (; it < n; ++it) {
-        const int s = it % C::kStages;
-        if (it >= C::kStages) ok = mbar_wait(&bars->empty[s], ((it / C::kStages) - 1) & 1, abort_flag);
+        const int s = it % C::kStagesA;
+        if (it >= C::kStagesA) ok = mbar_wait(&bars->a_empty[s], ((it / C::kStagesA) - 1) & 1, abort_flag);
         if (!ok) break;
-        uint8_t* st = smem + C::kRingOff + s * 2 * C::kTile;
-        const int row = (r_first + it) * 128;
-        mbar_arrive_expect_tx(&bars->full[s], 2 * C::kTile);
-        for (int c = 0; c < D / 64; ++c) {
-          tma_load_3d(st + c * kChunkBytes, &tm_ra, &bars->full[s], h * D + c * 64, row, b);
-          tma_load_3d(st + C::kTile + c * kChunkBytes, &tm_rb, &bars->full[s], h * D + c * 64, row, b);
-        }
+        BW_TRACE(3, it, 0);
+        mbar_arrive_expect_tx(&bars->a_full[s], C::kTile);
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(smem + C::kAOff + s * C::kTile + c * kChunkBytes, &tm_ra, &bars->a_full[s], h * D + c * 64,
+                      (r_first + it) * 128, b);
       }
       if (*abort_flag) {
         mbar_wait_drain(&bars->fix_full, 0, kDrainNs);
-        for (int jj = max(0, it - C::kStages); jj < it; ++jj)
-          mbar_wait_drain(&bars->full[jj % C::kStages], (jj / C::kStages) & 1, kDrainNs);
+        for (int jj = max(0, it - C::kStagesA); jj < it; ++jj)
+          mbar_wait_drain(&bars->a_full[jj % C::kStagesA], (jj / C::kStagesA) & 1, kDrainNs);
       }
     }
-  } else if (start_ok && warp == 5) {
+  } else if (start_ok && warp == 10) {
+    // ------------------------------------------------- TMA producer: ring B'
+    if (lane == 0 && n > 0) {
+      prefetch_tensormap(&tm_rb);
+      bool ok = true;
+      int it = 0;
+      for (; it < n; ++it) {
+        const int s = it % C::kStagesB;
+        if (it >= C::kStagesB) ok = mbar_wait(&bars->b_empty[s], ((it / C::kStagesB) - 1) & 1, abort_flag);
+        if (!ok) break;
+        BW_TRACE(3, it, 1);
+        mbar_arrive_expect_tx(&bars->b_full[s], C::kTile);
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(smem + C::kBOff + s * C::kTile + c * kChunkBytes, &tm_rb, &bars->b_full[s], h * D + c * 64,
+                      (r_first + it) * 128, b);
+      }
+      if (*abort_flag)
+        for (int jj = max(0, it - C::kStagesB); jj < it; ++jj)
+          mbar_wait_drain(&bars->b_full[jj % C::kStagesB], (jj / C::kStagesB) & 1, kDrainNs);
+    }
+  } else if (start_ok && warp == 9) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_nt = make_idesc_f16(BF16, 128, 128, false, false);  // both operands K-major
@@ -180,59 +213,73 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       constexpr uint32_t tile16 = C::kTile >> 4;
       const uint32_t fix_a = (smem_u32(smem + C::kFixOff) >> 4) | lbo_k;
       const uint32_t fix_b = fix_a + tile16;
-      const uint32_t ring_k = (smem_u32(smem + C::kRingOff) >> 4) | lbo_k;    // ring tiles read K-major
-      const uint32_t ring_mn = (smem_u32(smem + C::kRingOff) >> 4) | lbo_mn;  // ring tiles read MN-major
+      const uint32_t ra_k = (smem_u32(smem + C::kAOff) >> 4) | lbo_k;     // ring A' read K-major (for S)
+      const uint32_t ra_mn = (smem_u32(smem + C::kAOff) >> 4) | lbo_mn;   // ring A' read MN-major (accumulation)
+      const uint32_t rb_k = (smem_u32(smem + C::kBOff) >> 4) | lbo_k;     // ring B' read K-major (for dP)
+      const uint32_t rb_mn = (smem_u32(smem + C::kBOff) >> 4) | lbo_mn;   // ring B' read MN-major (dV)
       const uint32_t p_lo = (smem_u32(smem + C::kPOff) >> 4) | lbo_k;
-      bool ok = mbar_wait(&bars->fix_full, 0, abort_flag);
 
+      auto issue_s = [&](int it) {           // S = A A'^T
+        const uint32_t st = (it % C::kStagesA) * tile16;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
+          umma_ss_lohi(tmem + kColS, fix_a + off, ra_k + st + off, desc_hi, idesc_nt, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->s_full);
+      };
       // products that consume what the compute warps made of ring step `pit`
       auto issue_acc = [&](int pit) {
-        const uint32_t st16 = (pit % C::kStages) * 2 * tile16;
+        const uint32_t sa = (pit % C::kStagesA) * tile16, sb = (pit % C::kStagesB) * tile16;
         if (DKV) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {   // dV += P^T dX_i
             const uint32_t aoff = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
-            umma_ss_lohi(tmem + kColAcc0, p_lo + aoff, ring_mn + st16 + tile16 + kk * (2048 >> 4), desc_hi, idesc_acc,
+            umma_ss_lohi(tmem + kColAcc0, p_lo + aoff, rb_mn + sb + kk * (2048 >> 4), desc_hi, idesc_acc,
                          (pit == 0 && kk == 0) ? 0u : 1u);
           }
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)     // dK += dS^T Q_i
-            umma_ts_lohi(tmem + kColAcc1, tmem + kColDP + kk * 8, ring_mn + st16 + kk * (2048 >> 4), desc_hi, idesc_acc,
-                         (pit == 0 && kk == 0) ? 0u : 1u);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)     // dQ += dS K_j
-            umma_ts_lohi(tmem + kColAcc0, tmem + kColDP + kk * 8, ring_mn + st16 + kk * (2048 >> 4), desc_hi, idesc_acc,
-                         (pit == 0 && kk == 0) ? 0u : 1u);
+          umma_commit(&bars->b_empty[pit % C::kStagesB]);
         }
-        umma_commit(&bars->empty[pit % C::kStages]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)       // dQ += dS K_j   or   dK += dS^T Q_i
+          umma_ts_lohi(tmem + (DKV ? kColAcc1 : kColAcc0), tmem + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
+                       ra_mn + sa + kk * (2048 >> 4), desc_hi, idesc_acc, (pit == 0 && kk == 0) ? 0u : 1u);
+        umma_commit(&bars->a_empty[pit % C::kStagesA]);
       };
 
+      bool ok = mbar_wait(&bars->fix_full, 0, abort_flag);
+      if (ok) ok = mbar_wait(&bars->a_full[0], 0, abort_flag);
+      if (ok) issue_s(0);
       for (int it = 0; it < n && ok; ++it) {
-        const int s = it % C::kStages;
-        const uint32_t st16 = s * 2 * tile16;
-        ok = mbar_wait(&bars->full[s], (it / C::kStages) & 1, abort_flag);
-        if (ok && it > 0) ok = mbar_wait(&bars->s_read, (it - 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {   // S = A A'^T
-          const uint32_t off = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
-          umma_ss_lohi(tmem + kColS, fix_a + off, ring_k + st16 + off, desc_hi, idesc_nt, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars->s_full);
+        BW_TRACE(2, it, 0);
         if (it > 0) {
           ok = mbar_wait(&bars->ds_ready, (it - 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
+          BW_TRACE(2, it, 1);
           issue_acc(it - 1);
         }
+        const int sb = it % C::kStagesB;
+        ok = mbar_wait(&bars->b_full[sb], (it / C::kStagesB) & 1, abort_flag);
+        if (!ok) break;
+        BW_TRACE(2, it, 2);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {   // dP = B B'^T
           const uint32_t off = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
-          umma_ss_lohi(tmem + kColDP, fix_b + off, ring_k + st16 + tile16 + off, desc_hi, idesc_nt, kk > 0 ? 1u : 0u);
+          umma_ss_lohi(tmem + kColDP, fix_b + off, rb_k + sb * tile16 + off, desc_hi, idesc_nt, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars->dp_full);
+        if (!DKV) umma_commit(&bars->b_empty[sb]);   // V_j is not needed again
+        BW_TRACE(2, it, 3);
+        if (it + 1 < n) {
+          ok = mbar_wait(&bars->a_full[(it + 1) % C::kStagesA], ((it + 1) / C::kStagesA) & 1, abort_flag);
+          BW_TRACE(2, it, 4);
+          if (ok) ok = mbar_wait(&bars->s_read, it & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          BW_TRACE(2, it, 5);
+          issue_s(it + 1);
+        }
       }
       if (ok) ok = mbar_wait(&bars->ds_ready, (n - 1) & 1, abort_flag);
       if (ok) {
@@ -241,19 +288,24 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         umma_commit(&bars->acc_full);
       }
     }
-  } else if (start_ok && warp < 4) {
+  } else if (start_ok && warp < 8) {
     // ----------------------------------------------------------- compute warps
-    const int r = warp * 32 + lane;       // row of the resident tile = TMEM lane
-    const int row = t0 + r;               // query (dq) or key (dk/dv) index
+    const int half = warp >> 2;               // which 64 columns of every step this thread handles
+    const int wq = warp & 3;                  // TMEM lane quarter this warp may touch
+    const int r = wq * 32 + lane;             // row of the resident tile = TMEM lane
+    const int row = t0 + r;                   // query (dq) or key (dk/dv) index
     const bool row_ok = row < (DKV ? a.Lkv : a.Lq);
-    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(wq * 32) << 16);
+    const uint32_t tS = lane_base + kColS + half * 64, tDP = lane_base + kColDP + half * 64;
     const float c2 = a.scale * kLog2e;
     const float pos_inf = __int_as_float(0x7f800000);
     const float* lse_u = a.lse + (long long)a.Lq * h + a.lse_sb * b;
     float* delta_u = g.delta + (long long)a.Lq * h + (long long)a.Lq * a.H * b;
+    float* col_lse = reinterpret_cast<float*>(smem + C::kColOff);   // [2][128] lse (base 2) of the ring tile's queries
+    float* col_dl = col_lse + 256;                                  // [2][128] D of the ring tile's queries
     bool ok = true;
 
-    // per-row constants of the dq half: lse_i (base 2) and D_i = dx_i · x_i
+    // dq half: per-row constants lse_i (base 2) and D_i = dx_i · x_i
     float lse2_row = pos_inf, dl_row = 0.f;
     if (!DKV && row_ok) {
       lse2_row = __ldg(lse_u + row) * kLog2e;
@@ -263,101 +315,123 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
                         2ll * ((long long)row * a.x_sl + (long long)b * a.x_sb + (long long)h * D));
 #pragma unroll
       for (int e = 0; e < D / 8; ++e) dl_row = dot8<BF16>(__ldg(dxr + e), __ldg(xr + e), dl_row);
-      delta_u[row] = dl_row;
+      if (half == 0) delta_u[row] = dl_row;
     }
-    // dk/dv half: lse and D are per COLUMN (query), read with broadcast loads
-    const bool vec = ((reinterpret_cast<uintptr_t>(lse_u) | reinterpret_cast<uintptr_t>(delta_u)) & 15u) == 0;
+    // dk/dv half: lse and D belong to the COLUMNS (queries of the ring tile).  Thread (half, r) fetches
+    // one of the 256 values a step ahead and parks it in shared memory for everyone.
+    auto col_fetch = [&](int it) -> float {
+      const int qi = (r_first + it) * 128 + r;
+      if (qi >= a.Lq) return half == 0 ? pos_inf : 0.f;     // padded query: P = exp2(-inf) = 0
+      return half == 0 ? __ldg(lse_u + qi) * kLog2e : __ldg(delta_u + qi);
+    };
+    auto col_store = [&](int it, float v) {
+      (half == 0 ? col_lse : col_dl)[(it & 1) * 128 + r] = v;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->col_ready);
+    };
+    if (DKV && n > 0) col_store(0, col_fetch(0));
 
     for (int it = 0; it < n && ok; ++it) {
       const uint32_t par = it & 1;
-      const int c0 = (r_first + it) * 128;   // first column: key (dq) or query (dk/dv) index
+      const int c0 = (r_first + it) * 128 + half * 64;   // first column of this thread: key (dq) or query (dk/dv)
+      float col_next = 0.f;
+      if (DKV && it + 1 < n) col_next = col_fetch(it + 1);
+      if (threadIdx.x == 0) BW_TRACE(0, it, 0);
       ok = mbar_wait(&bars->s_full, par, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t su[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(lane_base + kColS + c * 32, su[c]);
+      if (threadIdx.x == 0) BW_TRACE(0, it, 1);
+      uint32_t su[2][32];
+      tmem_ld32(tS, su[0]);
+      tmem_ld32(tS + 32, su[1]);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_read);
+      if (threadIdx.x == 0) BW_TRACE(0, it, 2);
 
       if (!DKV) {
         const int lim = row_ok ? (a.causal ? min(row, a.Lkv - 1) : a.Lkv - 1) : -1;  // last key of this row
 #pragma unroll
-        for (int e = 0; e < 128; ++e) NB_SR_SET(e, ex2_approx(fmaf(NB_SR(e), c2, -lse2_row)));
-        if (c0 + 127 > lim) {
+        for (int e = 0; e < 64; ++e) NB_SR_SET(e, ex2_approx(fmaf(NB_SR(e), c2, -lse2_row)));
+        if (c0 + 63 > lim) {
 #pragma unroll
-          for (int e = 0; e < 128; ++e)
+          for (int e = 0; e < 64; ++e)
             if (c0 + e > lim) NB_SR_SET(e, 0.f);
         }
       } else {
+        ok = mbar_wait(&bars->col_ready, par, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float4* L4 = reinterpret_cast<const float4*>(col_lse + par * 128 + half * 64);
 #pragma unroll
-        for (int e = 0; e < 128; e += 4) {
-          const float4 L = load_col4(lse_u, c0 + e, a.Lq, vec, pos_inf);
-          NB_SR_SET(e + 0, ex2_approx(fmaf(NB_SR(e + 0), c2, -L.x * kLog2e)));
-          NB_SR_SET(e + 1, ex2_approx(fmaf(NB_SR(e + 1), c2, -L.y * kLog2e)));
-          NB_SR_SET(e + 2, ex2_approx(fmaf(NB_SR(e + 2), c2, -L.z * kLog2e)));
-          NB_SR_SET(e + 3, ex2_approx(fmaf(NB_SR(e + 3), c2, -L.w * kLog2e)));
+        for (int e = 0; e < 64; e += 4) {
+          const float4 L = L4[e >> 2];
+          NB_SR_SET(e + 0, ex2_approx(fmaf(NB_SR(e + 0), c2, -L.x)));
+          NB_SR_SET(e + 1, ex2_approx(fmaf(NB_SR(e + 1), c2, -L.y)));
+          NB_SR_SET(e + 2, ex2_approx(fmaf(NB_SR(e + 2), c2, -L.z)));
+          NB_SR_SET(e + 3, ex2_approx(fmaf(NB_SR(e + 3), c2, -L.w)));
         }
         // queries before this key (causal) and padded key rows contribute nothing
-        const int cmin = row_ok ? (a.causal ? row - c0 : 0) : 128;
+        const int cmin = row_ok ? (a.causal ? row - c0 : 0) : 64;
         if (cmin > 0) {
 #pragma unroll
-          for (int e = 0; e < 128; ++e)
+          for (int e = 0; e < 64; ++e)
             if (e < cmin) NB_SR_SET(e, 0.f);
         }
       }
 
+      if (threadIdx.x == 0) BW_TRACE(0, it, 3);
       ok = mbar_wait(&bars->dp_full, par, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (threadIdx.x == 0) BW_TRACE(0, it, 4);
 
       if (DKV) {
         // P^T as the K-major A operand of dV += P^T dX: row r, 16-byte pieces in 128-byte-swizzled order.
         // (dp_full also tells that the previous step's products have finished reading this tile.)
-        uint8_t* prow = smem + C::kPOff + r * 128;
+        uint8_t* prow = smem + C::kPOff + half * kChunkBytes + r * 128;
 #pragma unroll
-        for (int piece = 0; piece < 16; ++piece) {
+        for (int piece = 0; piece < 8; ++piece) {
           uint4 v;
           v.x = pack2<BF16>(NB_SR(piece * 8 + 0), NB_SR(piece * 8 + 1));
           v.y = pack2<BF16>(NB_SR(piece * 8 + 2), NB_SR(piece * 8 + 3));
           v.z = pack2<BF16>(NB_SR(piece * 8 + 4), NB_SR(piece * 8 + 5));
           v.w = pack2<BF16>(NB_SR(piece * 8 + 6), NB_SR(piece * 8 + 7));
-          *reinterpret_cast<uint4*>(prow + (piece >> 3) * kChunkBytes + (((piece & 7) ^ (r & 7)) << 4)) = v;
+          *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) << 4)) = v;
         }
         fence_proxy_async_smem();
       }
+      if (threadIdx.x == 0) BW_TRACE(0, it, 5);
 
+      uint32_t pk[32];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t pk[32];
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t dp[32];
+        tmem_ld32(tDP + cc * 32, dp);
+        tmem_wait_ld();
+        const float4* D4 = reinterpret_cast<const float4*>(col_dl + par * 128 + half * 64 + cc * 32);
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = half * 2 + cc;
-          uint32_t dp[32];
-          tmem_ld32(lane_base + kColDP + c * 32, dp);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            float4 Dl = make_float4(dl_row, dl_row, dl_row, dl_row);
-            if (DKV) Dl = load_col4(delta_u, c0 + c * 32 + e, a.Lq, vec, 0.f);
-            const float d0 = (__uint_as_float(dp[e + 0]) - Dl.x) * NB_SR(c * 32 + e + 0);
-            const float d1 = (__uint_as_float(dp[e + 1]) - Dl.y) * NB_SR(c * 32 + e + 1);
-            const float d2 = (__uint_as_float(dp[e + 2]) - Dl.z) * NB_SR(c * 32 + e + 2);
-            const float d3 = (__uint_as_float(dp[e + 3]) - Dl.w) * NB_SR(c * 32 + e + 3);
-            pk[cc * 16 + e / 2] = pack2<BF16>(d0, d1);
-            pk[cc * 16 + e / 2 + 1] = pack2<BF16>(d2, d3);
-          }
+        for (int e = 0; e < 32; e += 4) {
+          float4 Dl = make_float4(dl_row, dl_row, dl_row, dl_row);
+          if (DKV) Dl = D4[e >> 2];
+          const float d0 = (__uint_as_float(dp[e + 0]) - Dl.x) * NB_SR(cc * 32 + e + 0);
+          const float d1 = (__uint_as_float(dp[e + 1]) - Dl.y) * NB_SR(cc * 32 + e + 1);
+          const float d2 = (__uint_as_float(dp[e + 2]) - Dl.z) * NB_SR(cc * 32 + e + 2);
+          const float d3 = (__uint_as_float(dp[e + 3]) - Dl.w) * NB_SR(cc * 32 + e + 3);
+          pk[cc * 16 + e / 2] = pack2<BF16>(d0, d1);
+          pk[cc * 16 + e / 2 + 1] = pack2<BF16>(d2, d3);
         }
-        tmem_st32(lane_base + kColDP + half * 32, pk);
       }
+      tmem_st32(tDP, pk);     // dS over the first half of this thread's own dP columns
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_ready);
+      if (threadIdx.x == 0) BW_TRACE(0, it, 6);
+      if (DKV && it + 1 < n) col_store(it + 1, col_next);
     }
 
     // ---------------------------------------------------------------- epilogue
@@ -367,35 +441,32 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       if (ok) tc_fence_after();
     }
     if (ok) {
+      // dq half: the two column groups share dQ's 32-column chunks; dk/dv half: group 0 stores dV, group 1 dK
       const long long Lrow = DKV ? a.Lkv : a.Lq;
       const long long dense = 2ll * (((long long)row + Lrow * b) * ((long long)a.H * D) + (long long)h * D);
-      constexpr int kOuts = DKV ? 2 : 1;
+      uint8_t* out = reinterpret_cast<uint8_t*>(DKV ? (half == 0 ? g.dv : g.dk) : g.dq) + dense;
+      const float mul = (DKV && half == 0) ? 1.f : a.scale;
+      const uint32_t col = (DKV && half == 1) ? kColAcc1 : kColAcc0;
 #pragma unroll
-      for (int which = 0; which < kOuts; ++which) {
-        // accumulator 0: dq (dq half) or dv (dk/dv half); accumulator 1: dk
-        uint8_t* out = reinterpret_cast<uint8_t*>(DKV ? (which == 0 ? g.dv : g.dk) : g.dq) + dense;
-        const float mul = (DKV && which == 0) ? 1.f : a.scale;
-        const uint32_t col = which == 0 ? kColAcc0 : kColAcc1;
+      for (int c = 0; c < D / 32; ++c) {
+        if (!DKV && (c & 1) != half) continue;
+        uint32_t o[32];
+        if (n > 0) {
+          tmem_ld32(lane_base + col + c * 32, o);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          if (n > 0) {
-            tmem_ld32(lane_base + col + c * 32, o);
-            tmem_wait_ld();
-          } else {
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
+        if (row_ok) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = 0u;
-          }
-          if (row_ok) {
-#pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              uint4 v;
-              v.x = pack2<BF16>(__uint_as_float(o[e]) * mul, __uint_as_float(o[e + 1]) * mul);
-              v.y = pack2<BF16>(__uint_as_float(o[e + 2]) * mul, __uint_as_float(o[e + 3]) * mul);
-              v.z = pack2<BF16>(__uint_as_float(o[e + 4]) * mul, __uint_as_float(o[e + 5]) * mul);
-              v.w = pack2<BF16>(__uint_as_float(o[e + 6]) * mul, __uint_as_float(o[e + 7]) * mul);
-              *reinterpret_cast<uint4*>(out + (c * 32 + e) * 2) = v;
-            }
+          for (int e = 0; e < 32; e += 8) {
+            uint4 v;
+            v.x = pack2<BF16>(__uint_as_float(o[e]) * mul, __uint_as_float(o[e + 1]) * mul);
+            v.y = pack2<BF16>(__uint_as_float(o[e + 2]) * mul, __uint_as_float(o[e + 3]) * mul);
+            v.z = pack2<BF16>(__uint_as_float(o[e + 4]) * mul, __uint_as_float(o[e + 5]) * mul);
+            v.w = pack2<BF16>(__uint_as_float(o[e + 6]) * mul, __uint_as_float(o[e + 7]) * mul);
+            *reinterpret_cast<uint4*>(out + (c * 32 + e) * 2) = v;
           }
         }
       }
@@ -404,7 +475,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -414,6 +485,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
   }
 }
 
+#undef BW_TRACE
 #undef NB_SR
 #undef NB_SR_SET
 
@@ -421,7 +493,7 @@ template <int D, bool BF16, bool DKV>
 cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const CUtensorMap& ra, const CUtensorMap& rb,
                             const AttnArgs& a, const BwdArgs& g, cudaStream_t st) {
   auto kern = attn_bwd_umma_kernel<D, BF16, DKV>;
-  constexpr int smem = DKV ? BwCfg<D>::kSmemDkv : BwCfg<D>::kSmemDq;
+  constexpr int smem = BwCfg<D, DKV>::kSmemBytes;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   const int n_tiles = ((DKV ? a.Lkv : a.Lq) + 127) / 128;
