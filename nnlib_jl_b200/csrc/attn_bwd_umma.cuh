@@ -22,7 +22,8 @@
 //   warp 9      MMA issuer
 //   warp 10     TMA producer of ring B'
 // TMEM columns: S [0,128)  dP [128,256)  accumulator 0 [256,256+D)  accumulator 1 [384,384+D).
-// dS (half precision) overwrites dP: columns [128,160) for ring rows 0-63, [192,224) for rows 64-127.
+// dS (half precision): the dq half double-buffers it in columns [384,512) (its second accumulator is
+// unused), the dk/dv half writes it over dP: columns [128,160) for ring rows 0-63, [192,224) for rows 64-127.
 #pragma once
 
 namespace {
@@ -49,6 +50,8 @@ static_assert(BwCfg<128, true>::kSmemBytes <= 232448 && BwCfg<128, false>::kSmem
 struct BwBarriers {
   uint64_t fix_full, a_full[3], a_empty[3], b_full[2], b_empty[2];
   uint64_t s_full, dp_full, s_read, ds_ready, acc_full, col_ready;
+  uint64_t dp_read;    // dq half: dP is in registers
+  uint64_t pt_ready;   // dk/dv half: P^T is in shared memory
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -139,6 +142,8 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
     mbar_init(&bars->ds_ready, 8);
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->col_ready, 8);
+    mbar_init(&bars->dp_read, 8);
+    mbar_init(&bars->pt_ready, 8);
     bars->abort_flag = *reinterpret_cast<volatile int*>(&g_umma_abort);
     fence_mbar_init();
   }
@@ -152,6 +157,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
   const uint32_t tmem = bars->tmem_base;
   const bool start_ok = (*abort_flag == 0);
   constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
+  constexpr uint32_t kColDS = 384;   // dq half: two 64-column dS buffers where the dk/dv half keeps its second accumulator
 
   if (start_ok && warp == 8) {
     // ------------------------------------- TMA producer: resident pair and ring A'
@@ -228,65 +234,91 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         }
         umma_commit(&bars->s_full);
       };
-      // products that consume what the compute warps made of ring step `pit`
-      auto issue_acc = [&](int pit) {
-        const uint32_t sa = (pit % C::kStagesA) * tile16, sb = (pit % C::kStagesB) * tile16;
-        if (DKV) {
+      auto issue_dp = [&](int it) {          // dP = B B'^T
+        const uint32_t st = (it % C::kStagesB) * tile16;
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {   // dV += P^T dX_i
-            const uint32_t aoff = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
-            umma_ss_lohi(tmem + kColAcc0, p_lo + aoff, rb_mn + sb + kk * (2048 >> 4), desc_hi, idesc_acc,
-                         (pit == 0 && kk == 0) ? 0u : 1u);
-          }
-          umma_commit(&bars->b_empty[pit % C::kStagesB]);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
+          umma_ss_lohi(tmem + kColDP, fix_b + off, rb_k + st + off, desc_hi, idesc_nt, kk > 0 ? 1u : 0u);
         }
+        umma_commit(&bars->dp_full);
+        if (!DKV) umma_commit(&bars->b_empty[it % C::kStagesB]);   // V_j is not needed again
+      };
+      // dQ += dS K_j  (dq half, dS buffer it&1)   or   dK += dS^T Q_i  (dk/dv half, dS over dP)
+      auto issue_ds_acc = [&](int it) {
+        const uint32_t sa = (it % C::kStagesA) * tile16;
+        const uint32_t ds_col = DKV ? kColDP : (kColDS + (it & 1) * 64);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)       // dQ += dS K_j   or   dK += dS^T Q_i
-          umma_ts_lohi(tmem + (DKV ? kColAcc1 : kColAcc0), tmem + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
-                       ra_mn + sa + kk * (2048 >> 4), desc_hi, idesc_acc, (pit == 0 && kk == 0) ? 0u : 1u);
-        umma_commit(&bars->a_empty[pit % C::kStagesA]);
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts_lohi(tmem + (DKV ? kColAcc1 : kColAcc0), tmem + ds_col + (kk >> 2) * (DKV ? 64 : 32) + (kk & 3) * 8,
+                       ra_mn + sa + kk * (2048 >> 4), desc_hi, idesc_acc, (it == 0 && kk == 0) ? 0u : 1u);
+        umma_commit(&bars->a_empty[it % C::kStagesA]);   // also tells the dq half that dS buffer it&1 is free
+      };
+      auto issue_dv = [&](int it) {          // dV += P^T dX_i
+        const uint32_t sb = (it % C::kStagesB) * tile16;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
+          umma_ss_lohi(tmem + kColAcc0, p_lo + aoff, rb_mn + sb + kk * (2048 >> 4), desc_hi, idesc_acc,
+                       (it == 0 && kk == 0) ? 0u : 1u);
+        }
+        umma_commit(&bars->b_empty[it % C::kStagesB]);   // also tells that P^T has been consumed
       };
 
+      // S and dP of the next step are issued as early as the compute warps allow (they have the
+      // previous S / dP in registers), the accumulating products when dS (and P^T) are ready.
       bool ok = mbar_wait(&bars->fix_full, 0, abort_flag);
       if (ok) ok = mbar_wait(&bars->a_full[0], 0, abort_flag);
       if (ok) issue_s(0);
+      if (ok) ok = mbar_wait(&bars->b_full[0], 0, abort_flag);
+      if (ok) issue_dp(0);
       for (int it = 0; it < n && ok; ++it) {
+        const uint32_t par = it & 1;
+        const bool more = it + 1 < n;
         BW_TRACE(2, it, 0);
-        if (it > 0) {
-          ok = mbar_wait(&bars->ds_ready, (it - 1) & 1, abort_flag);
+        if (more) {
+          ok = mbar_wait(&bars->a_full[(it + 1) % C::kStagesA], ((it + 1) / C::kStagesA) & 1, abort_flag);
+          if (ok) ok = mbar_wait(&bars->s_read, par, abort_flag);
           if (!ok) break;
           tc_fence_after();
           BW_TRACE(2, it, 1);
-          issue_acc(it - 1);
+          issue_s(it + 1);
+          BW_TRACE(2, it, 2);
         }
-        const int sb = it % C::kStagesB;
-        ok = mbar_wait(&bars->b_full[sb], (it / C::kStagesB) & 1, abort_flag);
-        if (!ok) break;
-        BW_TRACE(2, it, 2);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {   // dP = B B'^T
-          const uint32_t off = (kk >> 2) * (kChunkBytes >> 4) + (kk & 3) * 2;
-          umma_ss_lohi(tmem + kColDP, fix_b + off, rb_k + sb * tile16 + off, desc_hi, idesc_nt, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars->dp_full);
-        if (!DKV) umma_commit(&bars->b_empty[sb]);   // V_j is not needed again
-        BW_TRACE(2, it, 3);
-        if (it + 1 < n) {
-          ok = mbar_wait(&bars->a_full[(it + 1) % C::kStagesA], ((it + 1) / C::kStagesA) & 1, abort_flag);
-          BW_TRACE(2, it, 4);
-          if (ok) ok = mbar_wait(&bars->s_read, it & 1, abort_flag);
+        if (!DKV) {
+          if (more) {
+            ok = mbar_wait(&bars->b_full[(it + 1) % C::kStagesB], ((it + 1) / C::kStagesB) & 1, abort_flag);
+            if (ok) ok = mbar_wait(&bars->dp_read, par, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            BW_TRACE(2, it, 3);
+            issue_dp(it + 1);
+          }
+          ok = mbar_wait(&bars->ds_ready, par, abort_flag);
           if (!ok) break;
           tc_fence_after();
+          BW_TRACE(2, it, 4);
+          issue_ds_acc(it);
           BW_TRACE(2, it, 5);
-          issue_s(it + 1);
+        } else {
+          ok = mbar_wait(&bars->ds_ready, par, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          BW_TRACE(2, it, 3);
+          issue_ds_acc(it);
+          if (more) {
+            ok = mbar_wait(&bars->b_full[(it + 1) % C::kStagesB], ((it + 1) / C::kStagesB) & 1, abort_flag);
+            if (!ok) break;
+            issue_dp(it + 1);   // overwrites dS: ordered behind the dK products above
+          }
+          BW_TRACE(2, it, 4);
+          ok = mbar_wait(&bars->pt_ready, par, abort_flag);
+          if (!ok) break;
+          BW_TRACE(2, it, 5);
+          issue_dv(it);
         }
       }
-      if (ok) ok = mbar_wait(&bars->ds_ready, (n - 1) & 1, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_acc(n - 1);
-        umma_commit(&bars->acc_full);
-      }
+      if (ok) umma_commit(&bars->acc_full);
     }
   } else if (start_ok && warp < 8) {
     // ----------------------------------------------------------- compute warps
@@ -389,9 +421,63 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       tc_fence_after();
       if (threadIdx.x == 0) BW_TRACE(0, it, 4);
 
+      // dS = P (dP - D), rounded to the element type: the A operand of the dQ / dK product
+      uint32_t pk[32];
+      if (!DKV) {
+        uint32_t dp[2][32];
+        tmem_ld32(tDP, dp[0]);
+        tmem_ld32(tDP + 32, dp[1]);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->dp_read);   // the next dP may be issued
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) {
+          const float d0 = (__uint_as_float(dp[e >> 5][e & 31]) - dl_row) * NB_SR(e);
+          const float d1 = (__uint_as_float(dp[(e + 1) >> 5][(e + 1) & 31]) - dl_row) * NB_SR(e + 1);
+          pk[e >> 1] = pack2<BF16>(d0, d1);
+        }
+        if (it >= 2) {   // the products of step it-2 have finished reading this dS buffer
+          ok = mbar_wait(&bars->a_empty[(it - 2) % C::kStagesA], ((it - 2) / C::kStagesA) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        tmem_st32(lane_base + kColDS + par * 64 + half * 32, pk);
+      } else {
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t dp[32];
+          tmem_ld32(tDP + cc * 32, dp);
+          tmem_wait_ld();
+          const float4* D4 = reinterpret_cast<const float4*>(col_dl + par * 128 + half * 64 + cc * 32);
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float4 Dl = D4[e >> 2];
+            const float d0 = (__uint_as_float(dp[e + 0]) - Dl.x) * NB_SR(cc * 32 + e + 0);
+            const float d1 = (__uint_as_float(dp[e + 1]) - Dl.y) * NB_SR(cc * 32 + e + 1);
+            const float d2 = (__uint_as_float(dp[e + 2]) - Dl.z) * NB_SR(cc * 32 + e + 2);
+            const float d3 = (__uint_as_float(dp[e + 3]) - Dl.w) * NB_SR(cc * 32 + e + 3);
+            pk[cc * 16 + e / 2] = pack2<BF16>(d0, d1);
+            pk[cc * 16 + e / 2 + 1] = pack2<BF16>(d2, d3);
+          }
+        }
+        tmem_st32(tDP, pk);     // over the first half of this thread's own dP columns
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->ds_ready);
+      if (threadIdx.x == 0) BW_TRACE(0, it, 5);
+
       if (DKV) {
-        // P^T as the K-major A operand of dV += P^T dX: row r, 16-byte pieces in 128-byte-swizzled order.
-        // (dp_full also tells that the previous step's products have finished reading this tile.)
+        // P^T as the K-major A operand of dV += P^T dX: row r, 16-byte pieces in 128-byte-swizzled order,
+        // once the previous step's product has finished reading the tile
+        if (it > 0) {
+          ok = mbar_wait(&bars->b_empty[(it - 1) % C::kStagesB], ((it - 1) / C::kStagesB) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
         uint8_t* prow = smem + C::kPOff + half * kChunkBytes + r * 128;
 #pragma unroll
         for (int piece = 0; piece < 8; ++piece) {
@@ -403,35 +489,11 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
           *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) << 4)) = v;
         }
         fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->pt_ready);
+        if (it + 1 < n) col_store(it + 1, col_next);
       }
-      if (threadIdx.x == 0) BW_TRACE(0, it, 5);
-
-      uint32_t pk[32];
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t dp[32];
-        tmem_ld32(tDP + cc * 32, dp);
-        tmem_wait_ld();
-        const float4* D4 = reinterpret_cast<const float4*>(col_dl + par * 128 + half * 64 + cc * 32);
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          float4 Dl = make_float4(dl_row, dl_row, dl_row, dl_row);
-          if (DKV) Dl = D4[e >> 2];
-          const float d0 = (__uint_as_float(dp[e + 0]) - Dl.x) * NB_SR(cc * 32 + e + 0);
-          const float d1 = (__uint_as_float(dp[e + 1]) - Dl.y) * NB_SR(cc * 32 + e + 1);
-          const float d2 = (__uint_as_float(dp[e + 2]) - Dl.z) * NB_SR(cc * 32 + e + 2);
-          const float d3 = (__uint_as_float(dp[e + 3]) - Dl.w) * NB_SR(cc * 32 + e + 3);
-          pk[cc * 16 + e / 2] = pack2<BF16>(d0, d1);
-          pk[cc * 16 + e / 2 + 1] = pack2<BF16>(d2, d3);
-        }
-      }
-      tmem_st32(tDP, pk);     // dS over the first half of this thread's own dP columns
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->ds_ready);
       if (threadIdx.x == 0) BW_TRACE(0, it, 6);
-      if (DKV && it + 1 < n) col_store(it + 1, col_next);
     }
 
     // ---------------------------------------------------------------- epilogue
