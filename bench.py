@@ -245,6 +245,15 @@ def run_ours(args, w):
             a.materialize()
         return y
 
+    if args.backward:
+        # side measurement, not the bench line: the pullback of the same call (dq, dk, dv from dx)
+        fd = nb.PhiloxDropout(w["dropout"], seed=0xB200, offset=0) if w.get("dropout") else nb.identity
+        _, _, back = nb.dot_product_attention_pullback(q, k, v, bias, mask=kwargs.get("mask"), nheads=H, fdrop=fd)
+        dx = nb.jl_empty((E, Lq, B), tdtype, dev); dx.normal_(generator=g)
+
+        def step():
+            return back(dx)
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -272,11 +281,17 @@ def run_ours(args, w):
     nb.device_health(dev)
 
     # ---- end-to-end timing from pinned host buffers ------------------------
-    if args.no_e2e:
+    if args.no_e2e or args.backward:
         if rank == 0:
             sampler.stop()
-            print(json.dumps({"note": "kernel-only run (--no-e2e): not a bench line", "ms_per_step": ms_total / args.steps,
-                              "tflops": algorithmic_flops(w) / (ms_total / args.steps * 1e-3) / 1e12}), flush=True)
+            # the backward is counted as five products per score tile against the forward's two
+            fl = algorithmic_flops(w) * (2.5 if args.backward else 1.0)
+            note = "backward only (--backward)" if args.backward else "kernel-only run (--no-e2e)"
+            line = {"note": note + ": not a bench line", "ms_per_step": ms_total / args.steps,
+                    "tflops": fl / (ms_total / args.steps * 1e-3) / 1e12, "gpu_launches": int(launches)}
+            if args.backward:
+                line["backward_path"] = {_lib.PATH_UMMA: "tcgen05", _lib.PATH_SIMT: "cuda-core"}.get(back.path)
+            print(json.dumps(line), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -374,6 +389,7 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
+    ap.add_argument("--backward", action="store_true", help="time the pullback (dq, dk, dv) of the workload instead")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (smaller profiler captures)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
     args = ap.parse_args()
