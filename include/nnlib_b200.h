@@ -107,12 +107,13 @@ typedef struct nnlib_b200_attn_params {
 
   float scale;                 /* multiplies q·k; 0 means 1/sqrt(d) (src/attention.jl:118) */
 
-  /* dropout on alpha (fdrop, src/attention.jl:126; keep-rule of src/dropout.jl:77-87):
-     element (j,i,h,b) is kept iff Philox4x32-10(key = seed, counter = position) > p*2^32,
-     kept entries are scaled by 1/(1-p).  p = 0 disables.  The position counter is
-     (j/4, r_lo, r_hi + offset_hi, offset_lo), word j%4, with
-     r = i + Lq*((h + rng_h0) + rng_H*(b + rng_b0)), so that a shard holding a sub-range of heads
-     or batches draws the same mask as the whole problem.  rng_H = 0 means H. */
+  /* dropout on alpha (fdrop, src/attention.jl:126; keep-rule of src/dropout.jl:77-87: keep iff
+     rand > p, kept entries scaled by 1/(1-p)).  The random number of element (j,i,h,b) is a 16-bit
+     lane of Philox4x32-10(key = seed): counter (j/8, r_lo, r_hi + offset_hi, offset_lo), lane j%8 =
+     the low (even j) or high (odd j) half of output word (j%8)/2; the element is dropped iff its lane
+     is < floor(p * 2^16).  p = 0 disables.  r = i + Lq*((h + rng_h0) + rng_H*(b + rng_b0)), so that a
+     shard holding a sub-range of heads or batches draws the same mask as the whole problem.
+     rng_H = 0 means H. */
   float dropout_p;
   uint64_t philox_seed;
   uint64_t philox_offset;

@@ -80,8 +80,8 @@ int resolve(const nnlib_b200_attn_params* p, unsigned need, AttnArgs* out) {
   a.dropout_p = p->dropout_p;
   a.inv_keep = (float)(1.0 / (1.0 - (double)p->dropout_p));
   {
-    const double th = std::floor((double)p->dropout_p * 4294967296.0);
-    a.drop_thresh = (unsigned int)(th > 4294967295.0 ? 4294967295.0 : th);
+    const double th = std::floor((double)p->dropout_p * 65536.0);
+    a.drop_thresh = (unsigned int)(th > 65535.0 ? 65535.0 : th);
   }
   a.key0 = (unsigned int)(p->philox_seed & 0xffffffffull);
   a.key1 = (unsigned int)(p->philox_seed >> 32);

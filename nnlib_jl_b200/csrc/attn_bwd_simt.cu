@@ -39,9 +39,7 @@ __device__ __forceinline__ float logit_qk(const AttnArgs& a, const T* qrow, cons
 // keep/(1-p) factor of score (j, row)
 __device__ __forceinline__ float drop_factor(const AttnArgs& a, unsigned long long srow, int j) {
   if (!(a.dropout_p > 0.f)) return 1.f;
-  unsigned int w[4];
-  dropout_words(a, srow, (unsigned int)j >> 2, w);
-  return (w[j & 3] > a.drop_thresh) ? a.inv_keep : 0.f;
+  return dropout_keep1(a, srow, (unsigned int)j) ? a.inv_keep : 0.f;
 }
 
 // ---- one warp per query row: D_i, dq_i, dbias --------------------------------------------

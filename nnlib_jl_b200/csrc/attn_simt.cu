@@ -103,9 +103,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_simt_kernel(const At
         if (dead_row) al = a.nan_fm ? __int_as_float(0x7fc00000) : 0.f;
         else          al = (t == neg_inf()) ? 0.f : expf(t - lse);
         if (a.dropout_p > 0.f) {
-          unsigned int w[4];
-          dropout_words(a, srow, (unsigned int)j >> 2, w);
-          al = (w[j & 3] > a.drop_thresh) ? al * a.inv_keep : 0.f;
+          al = dropout_keep1(a, srow, (unsigned int)j) ? al * a.inv_keep : 0.f;
         }
         if (MODE == MODE_SCORES) alpha_row[j] = Elem<T>::from_f(al);
       }

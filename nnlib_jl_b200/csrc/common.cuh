@@ -31,7 +31,7 @@ struct AttnArgs {
   int* status;
   long long rng_h0, rng_b0, rng_H;
   unsigned int key0, key1, off_lo, off_hi;
-  unsigned int drop_thresh;  // keep iff philox word > drop_thresh
+  unsigned int drop_thresh;  // floor(p * 2^16): a score is dropped iff its 16-bit lane is below it
   float inv_keep;            // 1/(1-p)
   float dropout_p;
   float scale;               // multiplies q·k (natural units)
@@ -91,25 +91,38 @@ __host__ __device__ __forceinline__ void philox4x32_10(unsigned int& c0, unsigne
   }
 }
 
-// The four random words that cover kv positions 4*j4 .. 4*j4+3 of score row r.
-__device__ __forceinline__ void dropout_words(const AttnArgs& a, unsigned long long r, unsigned int j4,
+// The four random words (eight 16-bit lanes) that cover kv positions 8*j8 .. 8*j8+7 of score row r.
+__device__ __forceinline__ void dropout_words(const AttnArgs& a, unsigned long long r, unsigned int j8,
                                               unsigned int w[4]) {
-  unsigned int c0 = j4, c1 = (unsigned int)r, c2 = (unsigned int)(r >> 32) + a.off_hi, c3 = a.off_lo;
+  unsigned int c0 = j8, c1 = (unsigned int)r, c2 = (unsigned int)(r >> 32) + a.off_hi, c3 = a.off_lo;
   philox4x32_10(c0, c1, c2, c3, a.key0, a.key1);
   w[0] = c0; w[1] = c1; w[2] = c2; w[3] = c3;
 }
 
+// Does score (row r, key j) survive?  Lane j%8: the low (even j) or high (odd j) half of word (j%8)/2.
+__device__ __forceinline__ bool dropout_keep1(const AttnArgs& a, unsigned long long r, unsigned int j) {
+  unsigned int w[4];
+  dropout_words(a, r, j >> 3, w);
+  const unsigned int e = j & 7u;
+  const unsigned int word = (e < 4u) ? ((e < 2u) ? w[0] : w[1]) : ((e < 6u) ? w[2] : w[3]);
+  return ((word >> (16u * (e & 1u))) & 0xffffu) >= a.drop_thresh;
+}
+
 // Keep-bits of 32 consecutive keys (bit e: key 32*c32 + e of score row r survives).  A rolled loop on
-// purpose: the ten Philox rounds of eight calls would otherwise be scheduled together and cost registers.
+// purpose: the ten Philox rounds of several calls would otherwise be scheduled together and cost registers.
 __device__ __forceinline__ unsigned int dropout_keep32(const AttnArgs& a, unsigned long long r, unsigned int c32) {
   unsigned int bits = 0;
 #pragma unroll 1
-  for (int g = 0; g < 8; ++g) {
+  for (int g = 0; g < 4; ++g) {
     unsigned int w[4];
-    dropout_words(a, r, c32 * 8 + g, w);
-    const unsigned int nib = (w[0] > a.drop_thresh ? 1u : 0u) | (w[1] > a.drop_thresh ? 2u : 0u) |
-                             (w[2] > a.drop_thresh ? 4u : 0u) | (w[3] > a.drop_thresh ? 8u : 0u);
-    bits |= nib << (4 * g);
+    dropout_words(a, r, c32 * 4 + g, w);
+    unsigned int byte = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      byte |= ((w[e] & 0xffffu) >= a.drop_thresh ? 1u : 0u) << (2 * e);
+      byte |= ((w[e] >> 16) >= a.drop_thresh ? 1u : 0u) << (2 * e + 1);
+    }
+    bits |= byte << (8 * g);
   }
   return bits;
 }

@@ -42,9 +42,9 @@ def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
 
 
 def drop_threshold(p: float) -> int:
-    """Keep iff the 32-bit random word is ``> floor(p * 2**32)`` — the integer
-    form of the reference's ``rand > p``."""
-    return min(int(np.floor(float(np.float32(p)) * 4294967296.0)), 0xFFFFFFFF)
+    """A score is dropped iff its 16-bit random lane is ``< floor(p * 2**16)`` — the
+    integer form of the reference's keep rule ``rand > p``."""
+    return min(int(np.floor(float(np.float32(p)) * 65536.0)), 0xFFFF)
 
 
 def keep_mask(shape4, p: float, seed: int, offset: int = 0, h0: int = 0, b0: int = 0, H_total=None) -> np.ndarray:
@@ -58,15 +58,17 @@ def keep_mask(shape4, p: float, seed: int, offset: int = 0, h0: int = 0, b0: int
     b = np.arange(B, dtype=np.uint64).reshape(1, 1, 1, B) + np.uint64(b0)
     r = i + np.uint64(Lq) * (h + np.uint64(H_total) * b)
     off_lo, off_hi = offset & 0xFFFFFFFF, (offset >> 32) & 0xFFFFFFFF
-    c0 = j >> np.uint64(2)
+    c0 = j >> np.uint64(3)
     c1 = r & _MASK32
     c2 = ((r >> np.uint64(32)) + np.uint64(off_hi)) & _MASK32
     c3 = np.uint64(off_lo)
     w = philox4x32_10(c0, c1, c2, c3, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
     w = np.stack(np.broadcast_arrays(*w), axis=0)            # (4, Lkv, Lq, H, B)
-    sel = np.broadcast_to((j & np.uint64(3)).astype(np.int64), w.shape[1:])
-    word = np.take_along_axis(w, sel[None], axis=0)[0]
-    return word > np.uint32(drop_threshold(p))
+    lane = j & np.uint64(7)                                   # eight 16-bit lanes per Philox call
+    sel = np.broadcast_to((lane >> np.uint64(1)).astype(np.int64), w.shape[1:])
+    word = np.take_along_axis(w, sel[None], axis=0)[0].astype(np.uint32)
+    half = (word >> (np.uint32(16) * (lane & np.uint64(1)).astype(np.uint32))) & np.uint32(0xFFFF)
+    return half >= np.uint32(drop_threshold(p))
 
 
 class PhiloxDropout:

@@ -7,9 +7,10 @@ the counter-based generator Philox4x32-10 (Salmon, Moraes, Dror, Shaw:
 "Parallel random numbers: as easy as 1, 2, 3", SC'11).  This file restates
 that published algorithm independently of the package's own host copy, is
 pinned by the Random123 known-answer vectors in the tests, and defines which
-score positions survive: position (j, i, h, b) keeps its score iff word
-``j % 4`` of ``philox(counter = (j // 4, r_lo, r_hi + off_hi, off_lo), key =
-seed)`` is ``> floor(p * 2**32)`` with ``r = i + Lq*((h+h0) + H_total*(b+b0))``.
+score positions survive: position (j, i, h, b) is dropped iff 16-bit lane
+``j % 8`` (low half of an output word for even j, high half for odd j, word
+``(j % 8) // 2``) of ``philox(counter = (j // 8, r_lo, r_hi + off_hi, off_lo),
+key = seed)`` is ``< floor(p * 2**16)``, with ``r = i + Lq*((h+h0) + H_total*(b+b0))``.
 """
 from __future__ import annotations
 
@@ -53,17 +54,20 @@ def keep_mask(shape4, p, seed, offset=0, h0=0, b0=0, H_total=None):
     """Bool array (Lkv, Lq, H, B): True where the score survives dropout."""
     Lkv, Lq, H, B = (int(s) for s in shape4)
     H_total = H if H_total is None else int(H_total)
-    thresh = min(int(np.floor(float(np.float32(p)) * 2.0 ** 32)), U32)
+    thresh = min(int(np.floor(float(np.float32(p)) * 2.0 ** 16)), 0xFFFF)
     out = np.empty((Lkv, Lq, H, B), dtype=bool)
     j = np.arange(Lkv, dtype=np.uint64)
     for b in range(B):
         for h in range(H):
             i = np.arange(Lq, dtype=np.uint64)
             r = i + np.uint64(Lq) * np.uint64((h + h0) + H_total * (b + b0))
-            words = philox4x32_10_np((j >> np.uint64(2))[:, None], (r & np.uint64(U32))[None, :],
+            words = philox4x32_10_np((j >> np.uint64(3))[:, None], (r & np.uint64(U32))[None, :],
                                      (((r >> np.uint64(32)) + np.uint64((offset >> 32) & U32)) & np.uint64(U32))[None, :],
                                      np.uint64(offset & U32), seed & U32, (seed >> 32) & U32)
             w = np.stack(words, axis=0)                       # (4, Lkv, Lq)
-            sel = (j & np.uint64(3)).astype(np.int64)[None, :, None]
-            out[:, :, h, b] = np.take_along_axis(w, np.broadcast_to(sel, (1, Lkv, Lq)), axis=0)[0] > thresh
+            lane = (j & np.uint64(7)).astype(np.int64)
+            sel = (lane >> 1)[None, :, None]
+            word = np.take_along_axis(w, np.broadcast_to(sel, (1, Lkv, Lq)), axis=0)[0]
+            half = (word >> (np.uint64(16) * (lane & 1).astype(np.uint64))[:, None]) & np.uint64(0xFFFF)
+            out[:, :, h, b] = half >= np.uint64(thresh)
     return out
