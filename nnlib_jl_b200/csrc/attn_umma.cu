@@ -102,14 +102,17 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-// XM: 0 = plain (optionally causal), 1 = Bool mask only, 2 = bias and/or dropout (and mask)
+// XM = side + 3*drop.  side: 0 = no side input (optionally causal), 1 = Bool mask array only,
+// 2 = bias (and mask); drop: dropout code compiled in.  Each combination is its own kernel so that
+// the registers of one feature (bias prefetch buffers, Philox state) are not paid for by the others.
 template <int D, bool BF16, int XM, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qblocks) {
   using C = Cfg<D>;
-  constexpr bool EXTRAS = XM != 0;
-  constexpr bool XBIAS = XM == 2;     // bias / dropout code compiled in
+  constexpr bool EXTRAS = (XM % 3) != 0;
+  constexpr bool XBIAS = (XM % 3) == 2;   // bias code compiled in
+  constexpr bool DROP = XM >= 3;          // dropout code compiled in
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kBarOff);
@@ -431,8 +434,8 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
             if (hf == 1) NB_EXP_HALF(1, m_sub);
-            if (XBIAS && a.dropout_p > 0.f) {
-              // one Philox call decides four neighbouring keys of this row; the row sum keeps the dropped ones
+            if (DROP) {
+              // one Philox call decides eight neighbouring keys of this row; the row sum keeps the dropped ones
 #pragma unroll
               for (int cc = 0; cc < 2; ++cc) {
                 const unsigned int kb = dropout_keep32(a, srow, (unsigned int)(j0 >> 5) + hf * 2 + cc);
@@ -1082,18 +1085,33 @@ cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t
     return cudaErrorInvalidValue;
   }
   const bool bf16 = dtype == NNLIB_B200_BF16;
-  const int xm = (a.bias != nullptr || a.dropout_p > 0.f) ? 2 : (a.mask != nullptr ? 1 : 0);
+  const int side = a.bias != nullptr ? 2 : (a.mask != nullptr ? 1 : 0);
+  const int xm = side + ((!stats_only && a.dropout_p > 0.f) ? 3 : 0);   // the statistics ignore dropout
 #define NB_FWD(DD, BF, EX, ST) return launch_fwd<DD, BF, EX, ST>(mq, mk, mv, a, st)
-#define NB_FWD_ST(DD, BF, EX) \
-  do { if (stats_only) NB_FWD(DD, BF, EX, true); else NB_FWD(DD, BF, EX, false); } while (0)
-#define NB_FWD_EX(DD, BF) \
-  do { if (xm == 2) NB_FWD_ST(DD, BF, 2); else if (xm == 1) NB_FWD_ST(DD, BF, 1); else NB_FWD_ST(DD, BF, 0); } while (0)
+#define NB_FWD_EX(DD, BF)                                \
+  do {                                                   \
+    if (stats_only) {                                    \
+      switch (xm) {                                      \
+        case 0: NB_FWD(DD, BF, 0, true);                 \
+        case 1: NB_FWD(DD, BF, 1, true);                 \
+        default: NB_FWD(DD, BF, 2, true);                \
+      }                                                  \
+    } else {                                             \
+      switch (xm) {                                      \
+        case 0: NB_FWD(DD, BF, 0, false);                \
+        case 1: NB_FWD(DD, BF, 1, false);                \
+        case 2: NB_FWD(DD, BF, 2, false);                \
+        case 3: NB_FWD(DD, BF, 3, false);                \
+        case 4: NB_FWD(DD, BF, 4, false);                \
+        default: NB_FWD(DD, BF, 5, false);               \
+      }                                                  \
+    }                                                    \
+  } while (0)
 #define NB_FWD_BF(DD) \
   do { if (bf16) NB_FWD_EX(DD, true); else NB_FWD_EX(DD, false); } while (0)
   if (a.d == 128) NB_FWD_BF(128); else NB_FWD_BF(64);
 #undef NB_FWD_BF
 #undef NB_FWD_EX
-#undef NB_FWD_ST
 #undef NB_FWD
   return cudaErrorInvalidValue;
 }
