@@ -334,6 +334,13 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           side_issue<XBIAS>(rs, j * kBN, a.Lkv, bq[0], mq[0]);
           side_issue<XBIAS>(rs, j * kBN + 32, a.Lkv, bq[1], mq[1]);
         }
+        // which of this tile's 128 scores survive dropout depends on their position only: drawn while
+        // the tensor core still works on the scores
+        unsigned int kb[4] = {0u, 0u, 0u, 0u};
+        if (DROP) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) kb[c] = dropout_keep32(a, srow, (unsigned int)(j * kBN >> 5) + c);
+        }
         ok = mbar_wait(&bars->s_full[t], j & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -435,15 +442,15 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int hf = 0; hf < 2; ++hf) {
             if (hf == 1) NB_EXP_HALF(1, m_sub);
             if (DROP) {
-              // one Philox call decides eight neighbouring keys of this row; the row sum keeps the dropped ones
+              // the row sum keeps the dropped scores (dropout follows the softmax)
 #pragma unroll
               for (int cc = 0; cc < 2; ++cc) {
-                const unsigned int kb = dropout_keep32(a, srow, (unsigned int)(j0 >> 5) + hf * 2 + cc);
+                const unsigned int kbc = kb[hf * 2 + cc];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                   // pk[cc*16 + e] holds keys 2e (low half) and 2e+1 (high half) of this 32-key chunk
-                  const unsigned int m = (((kb >> (2 * e)) & 1u) ? 0x0000ffffu : 0u) |
-                                         (((kb >> (2 * e + 1)) & 1u) ? 0xffff0000u : 0u);
+                  const unsigned int m = (((kbc >> (2 * e)) & 1u) ? 0x0000ffffu : 0u) |
+                                         (((kbc >> (2 * e + 1)) & 1u) ? 0xffff0000u : 0u);
                   pk[cc * 16 + e] &= m;
                 }
               }

@@ -108,11 +108,11 @@ __device__ __forceinline__ bool dropout_keep1(const AttnArgs& a, unsigned long l
   return ((word >> (16u * (e & 1u))) & 0xffffu) >= a.drop_thresh;
 }
 
-// Keep-bits of 32 consecutive keys (bit e: key 32*c32 + e of score row r survives).  A rolled loop on
-// purpose: the ten Philox rounds of several calls would otherwise be scheduled together and cost registers.
+// Keep-bits of 32 consecutive keys (bit e: key 32*c32 + e of score row r survives).  Two calls at a time:
+// their ten rounds interleave (each round waits on the previous one's multiplies), more would cost registers.
 __device__ __forceinline__ unsigned int dropout_keep32(const AttnArgs& a, unsigned long long r, unsigned int c32) {
   unsigned int bits = 0;
-#pragma unroll 1
+#pragma unroll 2
   for (int g = 0; g < 4; ++g) {
     unsigned int w[4];
     dropout_words(a, r, c32 * 4 + g, w);
