@@ -26,6 +26,8 @@
 // Per-query log-sum-exp is stored so that the scores can be rebuilt later.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "extras.cuh"
 #include "launchers.h"
@@ -72,16 +74,24 @@ struct Cfg {
   static constexpr int kVOff = kKOff + kStagesK * kTileBytes;
   static constexpr int kBarOff = kVOff + kStagesV * kTileBytes;
   static constexpr int kSmemBytes = kBarOff + 512 + 1024;  // barrier block + alignment slack
+  // staged-bias variant (d = 64): per query tile two half tiles (64 keys x 128 queries) of the bias
+  static constexpr int kBiasOff = kBarOff;
+  static constexpr int kBiasBytes = kQT * 2 * kChunkBytes;
+  static constexpr int kBarOffStaged = kBiasOff + kBiasBytes;
+  static constexpr int kSmemBytesStaged = kBarOffStaged + 512 + 1024;
 };
 static_assert(Cfg<128>::kSmemBytes <= 232448 && Cfg<64>::kSmemBytes <= 232448, "shared memory budget");
+static_assert(Cfg<64>::kSmemBytesStaged <= 232448, "shared memory budget (staged bias)");
 
 struct Barriers {
   uint64_t q_full[kQT];
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
   uint64_t s_full[kQT], p_half[kQT][2], o_full[kQT];
+  uint64_t bias_full[kQT][2], bias_empty[kQT][2];   // staged bias half tiles
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(Barriers) <= 512, "barrier block");
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 
@@ -105,17 +115,22 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // XM = side + 3*drop.  side: 0 = no side input (optionally causal), 1 = Bool mask array only,
 // 2 = bias (and mask); drop: dropout code compiled in.  Each combination is its own kernel so that
 // the registers of one feature (bias prefetch buffers, Philox state) are not paid for by the others.
-template <int D, bool BF16, int XM, bool STATS>
+// BSM: the bias tiles arrive in shared memory by TMA (a whole round ahead, issued by the otherwise
+// idle warp 2) instead of through per-thread loads; needs a 16-bit bias with key stride 1 whose rows
+// the tensor map can address (the host decides).
+template <int D, bool BF16, int XM, bool STATS, bool BSM>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                     const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qblocks) {
+                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
+                     const AttnArgs a, const int n_qblocks) {
   using C = Cfg<D>;
   constexpr bool EXTRAS = (XM % 3) != 0;
   constexpr bool XBIAS = (XM % 3) == 2;   // bias code compiled in
   constexpr bool DROP = XM >= 3;          // dropout code compiled in
+  static_assert(!BSM || (XBIAS && D == 64 && !STATS), "staged bias: d = 64 forward with bias only");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kBarOff);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + (BSM ? C::kBarOffStaged : C::kBarOff));
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,6 +158,10 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(&bars->p_half[t][0], 4);
       mbar_init(&bars->p_half[t][1], 4);
       mbar_init(&bars->o_full[t], 1);
+      for (int hf = 0; hf < 2; ++hf) {
+        mbar_init(&bars->bias_full[t][hf], 1);
+        mbar_init(&bars->bias_empty[t][hf], 4);
+      }
     }
     for (int s = 0; s < 4; ++s) {
       mbar_init(&bars->k_full[s], 1);
@@ -213,6 +232,36 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (*abort_flag) {
         for (int jj = max(0, j - C::kStagesV); jj < j; ++jj)
           mbar_wait_drain(&bars->v_full[jj % C::kStagesV], (jj / C::kStagesV) & 1, kDrainNs);
+      }
+    } else if (BSM && start_ok && warp == 2 && lane == 0) {
+      // --------------------------------------------------- producer of bias
+      // half tile (64 keys x 128 queries) = one 128-byte-swizzled box; a slot is refilled for the
+      // next round as soon as the four softmax warps of the tile have read it
+      prefetch_tensormap(&tm_b);
+      const int hb = a.bias_s[2] ? h : 0, bb = a.bias_s[3] ? b : 0;   // broadcast dimensions have extent 1
+      bool ok = true;
+      int j = 0;
+      for (; j < n_kv && ok; ++j) {
+#pragma unroll
+        for (int t = 0; t < kQT; ++t) {
+          if (j >= ((t == 0) ? n_t0 : n_t1)) continue;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            if (j > 0 && ok) ok = mbar_wait(&bars->bias_empty[t][hf], (j - 1) & 1, abort_flag);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&bars->bias_full[t][hf], kChunkBytes);
+            tma_load_4d(smem + C::kBiasOff + (t * 2 + hf) * kChunkBytes, &tm_b, &bars->bias_full[t][hf],
+                        j * kBN + hf * 64, q0 + t * kBM, hb, bb);
+          }
+        }
+      }
+      if (*abort_flag) {
+        for (int t = 0; t < kQT; ++t)
+          for (int hf = 0; hf < 2; ++hf) {
+            const int nt = (t == 0) ? n_t0 : n_t1;
+            const int last = min(j, nt) - 1;
+            if (last >= 0) mbar_wait_drain(&bars->bias_full[t][hf], last & 1, kDrainNs);
+          }
       }
     } else if (start_ok && warp == 1 && lane == 0 && n_kv > 0) {
       // -------------------------------------------------------- MMA issuer
@@ -331,8 +380,8 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // bias / mask of the first 64 keys of this tile: in flight while the scores are awaited
         uint4 bq[2][4], mq[2][2];
         if (EXTRAS) {
-          side_issue<XBIAS>(rs, j * kBN, a.Lkv, bq[0], mq[0]);
-          side_issue<XBIAS>(rs, j * kBN + 32, a.Lkv, bq[1], mq[1]);
+          side_issue<XBIAS && !BSM>(rs, j * kBN, a.Lkv, bq[0], mq[0]);
+          side_issue<XBIAS && !BSM>(rs, j * kBN + 32, a.Lkv, bq[1], mq[1]);
         }
         // which of this tile's 128 scores survive dropout depends on their position only: drawn while
         // the tensor core still works on the scores
@@ -365,9 +414,27 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           // scaled base-2 units, bias added, masks applied; the loads of chunk c+2 start as chunk c is consumed
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            side_apply<XBIAS>(rs, sr[c], bq[c & 1], mq[c & 1], j0 + c * 32, a.Lkv, lim, row_ok, c2);
-            if (c + 2 < 4) side_issue<XBIAS>(rs, j0 + (c + 2) * 32, a.Lkv, bq[c & 1], mq[c & 1]);
+            if (BSM) {
+              // this thread's 32 bias values of chunk c from the staged half tile (row r, swizzled pieces)
+              const int hf = c >> 1;
+              if ((c & 1) == 0) {
+                ok = mbar_wait(&bars->bias_full[t][hf], j & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+              }
+              const uint8_t* brow = smem + C::kBiasOff + (t * 2 + hf) * kChunkBytes + r * 128;
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                bq[c & 1][v] = *reinterpret_cast<const uint4*>(brow + ((((c & 1) * 4 + v) ^ (r & 7)) << 4));
+              if ((c & 1) == 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->bias_empty[t][hf]);
+              }
+            }
+            side_apply<XBIAS, BSM>(rs, sr[c], bq[c & 1], mq[c & 1], j0 + c * 32, a.Lkv, lim, row_ok, c2);
+            if (c + 2 < 4) side_issue<XBIAS && !BSM>(rs, j0 + (c + 2) * 32, a.Lkv, bq[c & 1], mq[c & 1]);
           }
+          if (!ok) break;
         } else if (j0 + kBN - 1 > lim) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -1019,18 +1086,29 @@ bool make_map(CUtensorMap* m, const void* base, int dtype, long long feat, long 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 bool stride_ok(long long s) { return s > 0 && (s % 8) == 0 && s * 2 < (1ll << 40); }
 
-template <int D, bool BF16, int XM, bool STATS>
-cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
-                       cudaStream_t st) {
-  auto kern = attn_fwd_umma_kernel<D, BF16, XM, STATS>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::kSmemBytes);
+template <int D, bool BF16, int XM, bool STATS, bool BSM>
+cudaError_t launch_fwd_impl(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mb,
+                            const AttnArgs& a, cudaStream_t st) {
+  auto kern = attn_fwd_umma_kernel<D, BF16, XM, STATS, BSM>;
+  constexpr int smem = BSM ? Cfg<D>::kSmemBytesStaged : Cfg<D>::kSmemBytes;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   const int n_qblocks = (a.Lq + kQT * kBM - 1) / (kQT * kBM);
   const long long blocks = (long long)n_qblocks * a.H * a.B;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kThreads, Cfg<D>::kSmemBytes, st>>>(mq, mk, mv, a, n_qblocks);
+  kern<<<(unsigned)blocks, kThreads, smem, st>>>(mq, mk, mv, mb, a, n_qblocks);
   count_launch();
   return cudaGetLastError();
+}
+
+// `mb` != nullptr: the bias can be staged through shared memory by TMA (d = 64 forward with bias)
+template <int D, bool BF16, int XM, bool STATS>
+cudaError_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap* mb,
+                       const AttnArgs& a, cudaStream_t st) {
+  if constexpr (D == 64 && (XM % 3) == 2 && !STATS) {
+    if (mb) return launch_fwd_impl<D, BF16, XM, STATS, true>(mq, mk, mv, *mb, a, st);
+  }
+  return launch_fwd_impl<D, BF16, XM, STATS, false>(mq, mk, mv, mq, a, st);
 }
 
 template <int D, bool BF16, int XM, bool TST>
@@ -1059,6 +1137,35 @@ bool make_alpha_map(CUtensorMap* m, const AttnArgs& a, int dtype) {
   const CUresult r = fn(m, dtype == NNLIB_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                         4, a.alpha, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Tensor map over the bias array as (Lkv, Lq, H or 1, B or 1) with 64-key x 128-query boxes, for the
+// staged-bias forward.  Possible when the bias has 16-bit elements, key stride 1, query / head / batch
+// strides that are multiples of 8 elements (0 = broadcast for head and batch) and a 16-byte aligned base.
+bool make_bias_map(CUtensorMap* m, const AttnArgs& a) {
+  static const bool disabled = [] {
+    const char* e = std::getenv("NNLIB_B200_NO_STAGED_BIAS");
+    return e && e[0] && e[0] != '0';
+  }();
+  if (disabled) return false;
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || !a.bias) return false;
+  if (a.bias_dtype != NNLIB_B200_F16 && a.bias_dtype != NNLIB_B200_BF16) return false;
+  if (a.bias_s[0] != 1 || !aligned16(a.bias)) return false;
+  if (a.bias_s[1] <= 0 || a.bias_s[1] % 8 != 0 || a.bias_s[2] % 8 != 0 || a.bias_s[3] % 8 != 0) return false;
+  const long long lim = 1ll << 39;
+  if (a.bias_s[1] >= lim || a.bias_s[2] >= lim || a.bias_s[3] >= lim) return false;
+  const cuuint64_t row = (cuuint64_t)a.bias_s[1] * 2;
+  const cuuint64_t dims[4] = {(cuuint64_t)a.Lkv, (cuuint64_t)a.Lq, (cuuint64_t)(a.bias_s[2] ? a.H : 1),
+                              (cuuint64_t)(a.bias_s[3] ? a.B : 1)};
+  const cuuint64_t strides[3] = {row, a.bias_s[2] ? (cuuint64_t)a.bias_s[2] * 2 : row,
+                                 a.bias_s[3] ? (cuuint64_t)a.bias_s[3] * 2 : row};
+  const cuuint32_t box[4] = {64, 128, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(m, a.bias_dtype == NNLIB_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        4, const_cast<void*>(a.bias), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
@@ -1094,7 +1201,10 @@ cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t
   const bool bf16 = dtype == NNLIB_B200_BF16;
   const int side = a.bias != nullptr ? 2 : (a.mask != nullptr ? 1 : 0);
   const int xm = side + ((!stats_only && a.dropout_p > 0.f) ? 3 : 0);   // the statistics ignore dropout
-#define NB_FWD(DD, BF, EX, ST) return launch_fwd<DD, BF, EX, ST>(mq, mk, mv, a, st)
+  CUtensorMap mbias;
+  const CUtensorMap* mb = nullptr;
+  if (side == 2 && !stats_only && a.d == 64 && make_bias_map(&mbias, a)) mb = &mbias;
+#define NB_FWD(DD, BF, EX, ST) return launch_fwd<DD, BF, EX, ST>(mq, mk, mv, mb, a, st)
 #define NB_FWD_EX(DD, BF)                                \
   do {                                                   \
     if (stats_only) {                                    \

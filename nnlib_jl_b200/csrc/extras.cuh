@@ -65,14 +65,16 @@ __device__ __forceinline__ unsigned int u4_word(const uint4& q, int w) {
 
 // s[e] (raw q·k of keys jj0+e) -> scaled base-2 logit with bias added, or -inf where the key is
 // masked, beyond `lim` (causal / end of the keys) or the row is out of range.  Works in place.
-template <bool WITH_BIAS>
+// BIAS_STAGED: bq was filled from a shared-memory copy of the bias tile (zero beyond the array), so the
+// vector form applies to every chunk.
+template <bool WITH_BIAS, bool BIAS_STAGED = false>
 __device__ __forceinline__ void side_apply(const RowSide& rs, unsigned int (&s)[32], const uint4 (&bq)[4],
                                            const uint4 (&mq)[2], int jj0, int Lkv, int lim, bool row_ok, float c2) {
   constexpr float kLog2eF = 1.4426950408889634f;
   const bool inside = jj0 + 32 <= Lkv;
   const int lim_e = row_ok ? lim - jj0 : -1;   // element e of the chunk is in range iff e <= lim_e
   // ---- scale (+ bias)
-  if (WITH_BIAS && rs.bias_row && rs.bias_vec && inside) {
+  if (WITH_BIAS && rs.bias_row && (BIAS_STAGED || (rs.bias_vec && inside))) {
     if (rs.bias_dtype == NNLIB_B200_BF16) {
 #pragma unroll
       for (int e = 0; e < 32; e += 2) {
