@@ -1,4 +1,4 @@
-// Backward of plain / causal attention on the sm_100a tensor cores.  Included
+// Backward of attention without bias and dropout (plain, causal, Bool mask) on the sm_100a tensor cores.  Included
 // by attn_umma.cu (shares its helpers, constants and the sticky abort flag).
 //
 // The gradients Zygote composes from NNlib.jl's rules for this path
@@ -77,6 +77,30 @@ __device__ __forceinline__ float dot8(const uint4& x, const uint4& y, float acc)
   return acc;
 }
 
+// 64 Bool-mask bytes p[e * stride], e = 0..63, packed four to a word; entries e >= n_valid read as 0.
+// vec16: stride 1 and p 16-byte aligned, so a full group takes four 16-byte loads.
+__device__ __forceinline__ void load_mask64(const unsigned char* p, long long stride, int n_valid, bool vec16,
+                                            unsigned int (&mw)[16]) {
+  if (vec16 && n_valid >= 64) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(p) + v);
+      mw[4 * v + 0] = q.x; mw[4 * v + 1] = q.y; mw[4 * v + 2] = q.z; mw[4 * v + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int w = 0; w < 16; ++w) {
+      unsigned int word = 0;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = 4 * w + u;
+        if (e < n_valid && __ldg(p + (long long)e * stride) != 0) word |= 1u << (8 * u);
+      }
+      mw[w] = word;
+    }
+  }
+}
+
 #ifdef NB200_TRACE
 #ifndef NB200_TRACE_DKV
 #define NB200_TRACE_DKV 0
@@ -90,7 +114,8 @@ __device__ __forceinline__ float dot8(const uint4& x, const uint4& y, float acc)
 #define NB_SR(e) __uint_as_float(su[(e) >> 5][(e) & 31])
 #define NB_SR_SET(e, val) su[(e) >> 5][(e) & 31] = __float_as_uint(val)
 
-template <int D, bool BF16, bool DKV>
+// MASKED: a Bool mask array (NNlib.jl src/attention.jl:133-138, any broadcast strides) takes part.
+template <int D, bool BF16, bool DKV, bool MASKED>
 __global__ void __launch_bounds__(kBwThreads, 1)
 attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_constant__ CUtensorMap tm_fb,
                      const __grid_constant__ CUtensorMap tm_ra, const __grid_constant__ CUtensorMap tm_rb,
@@ -340,13 +365,17 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
     // dq half: per-row constants lse_i (base 2) and D_i = dx_i · x_i
     float lse2_row = pos_inf, dl_row = 0.f;
     if (!DKV && row_ok) {
-      lse2_row = __ldg(lse_u + row) * kLog2e;
+      // a query that attends to nothing (lse = -inf, possible with a mask array) gets and gives no gradient
+      const float lse_nat = __ldg(lse_u + row);
+      const bool dead = lse_nat == neg_inf();
+      lse2_row = dead ? pos_inf : lse_nat * kLog2e;
       const uint4* dxr = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(g.dx) +
                          2ll * ((long long)row * g.dx_sl + (long long)b * g.dx_sb + (long long)h * D));
       const uint4* xr = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.x) +
                         2ll * ((long long)row * a.x_sl + (long long)b * a.x_sb + (long long)h * D));
 #pragma unroll
       for (int e = 0; e < D / 8; ++e) dl_row = dot8<BF16>(__ldg(dxr + e), __ldg(xr + e), dl_row);
+      if (dead) dl_row = 0.f;   // its x is NaN (or 0)
       if (half == 0) delta_u[row] = dl_row;
     }
     // dk/dv half: lse and D belong to the COLUMNS (queries of the ring tile).  Thread (half, r) fetches
@@ -354,8 +383,21 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
     auto col_fetch = [&](int it) -> float {
       const int qi = (r_first + it) * 128 + r;
       if (qi >= a.Lq) return half == 0 ? pos_inf : 0.f;     // padded query: P = exp2(-inf) = 0
-      return half == 0 ? __ldg(lse_u + qi) * kLog2e : __ldg(delta_u + qi);
+      if (half == 1) return __ldg(delta_u + qi);
+      const float l = __ldg(lse_u + qi);
+      return (l == neg_inf()) ? pos_inf : l * kLog2e;         // dead query: P = 0
     };
+    // Bool mask array: the dq half reads the 64 keys of its row per step; in the dk/dv half a thread owns
+    // a key and needs the step's 64 queries -- one byte for the whole kernel when the mask does not depend
+    // on the query (key padding), else a strided gather per step
+    const unsigned char* mask_p = nullptr;
+    bool mask_row_keep = true;
+    const bool mask_per_step = MASKED && (!DKV || a.mask_s[1] != 0);
+    if (MASKED && row_ok) {
+      mask_p = a.mask + (long long)h * a.mask_s[2] + (long long)b * a.mask_s[3] + (long long)row * a.mask_s[DKV ? 0 : 1];
+      if (DKV && a.mask_s[1] == 0) mask_row_keep = __ldg(mask_p) != 0;
+    }
+    const long long mask_step = MASKED ? a.mask_s[DKV ? 1 : 0] : 0;   // stride along the columns of a step
     auto col_store = [&](int it, float v) {
       (half == 0 ? col_lse : col_dl)[(it & 1) * 128 + r] = v;
       __syncwarp();
@@ -368,6 +410,12 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       const int c0 = (r_first + it) * 128 + half * 64;   // first column of this thread: key (dq) or query (dk/dv)
       float col_next = 0.f;
       if (DKV && it + 1 < n) col_next = col_fetch(it + 1);
+      unsigned int mw[16];
+      if (mask_per_step && mask_p) {
+        const unsigned char* mp = mask_p + (long long)c0 * mask_step;
+        load_mask64(mp, mask_step, (DKV ? a.Lq : a.Lkv) - c0,
+                    mask_step == 1 && (reinterpret_cast<uintptr_t>(mp) & 15u) == 0, mw);
+      }
       if (threadIdx.x == 0) BW_TRACE(0, it, 0);
       ok = mbar_wait(&bars->s_full, par, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -392,6 +440,11 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
           for (int e = 0; e < 64; ++e)
             if (c0 + e > lim) NB_SR_SET(e, 0.f);
         }
+        if (MASKED && mask_p) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e)
+            if (((mw[e >> 2] >> ((e & 3) * 8)) & 0xffu) == 0u) NB_SR_SET(e, 0.f);
+        }
       } else {
         ok = mbar_wait(&bars->col_ready, par, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -406,11 +459,16 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
           NB_SR_SET(e + 3, ex2_approx(fmaf(NB_SR(e + 3), c2, -L.w)));
         }
         // queries before this key (causal) and padded key rows contribute nothing
-        const int cmin = row_ok ? (a.causal ? row - c0 : 0) : 64;
+        const int cmin = (row_ok && mask_row_keep) ? (a.causal ? row - c0 : 0) : 64;
         if (cmin > 0) {
 #pragma unroll
           for (int e = 0; e < 64; ++e)
             if (e < cmin) NB_SR_SET(e, 0.f);
+        }
+        if (mask_per_step && mask_p) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e)
+            if (((mw[e >> 2] >> ((e & 3) * 8)) & 0xffu) == 0u) NB_SR_SET(e, 0.f);
         }
       }
 
@@ -551,10 +609,10 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 #undef NB_SR
 #undef NB_SR_SET
 
-template <int D, bool BF16, bool DKV>
+template <int D, bool BF16, bool DKV, bool MASKED>
 cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const CUtensorMap& ra, const CUtensorMap& rb,
                             const AttnArgs& a, const BwdArgs& g, cudaStream_t st) {
-  auto kern = attn_bwd_umma_kernel<D, BF16, DKV>;
+  auto kern = attn_bwd_umma_kernel<D, BF16, DKV, MASKED>;
   constexpr int smem = BwCfg<D, DKV>::kSmemBytes;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
@@ -568,12 +626,12 @@ cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const 
 
 }  // namespace
 
-// The tensor-core backward covers the training case that has no side inputs: half-precision,
-// d = dv in {64, 128}, no bias, no Bool mask array (causal is fine), no dropout.
+// The tensor-core backward covers half-precision arrays with d = dv in {64, 128}, the causal flag and
+// Bool mask arrays; bias (its gradient needs a reduction) and dropout take the CUDA-core kernels.
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype) {
   if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
   if (!(a.d == 64 || a.d == 128) || a.dv != a.d) return false;
-  if (a.bias || a.mask || a.dropout_p > 0.f || g.dbias) return false;
+  if (a.bias || a.dropout_p > 0.f || g.dbias) return false;
   if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1 || !a.lse || !g.delta) return false;
   const void* ptrs[] = {a.q, a.k, a.v, a.x, g.dx, g.dq, g.dk, g.dv};
   for (const void* p : ptrs)
@@ -593,10 +651,15 @@ cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_
   if (!make_map(&mdx, g.dx, dtype, E, a.Lq, a.B, g.dx_sl, g.dx_sb)) return cudaErrorInvalidValue;
   const bool bf16 = dtype == NNLIB_B200_BF16;
   cudaError_t e;
-#define NB_BW(DD, BF)                                                        \
-  do {                                                                       \
-    e = launch_bwd_umma<DD, BF, false>(mq, mdx, mk, mv, a, g, st);           \
-    if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true>(mk, mv, mq, mdx, a, g, st); \
+#define NB_BW(DD, BF)                                                                            \
+  do {                                                                                           \
+    if (a.mask) {                                                                                \
+      e = launch_bwd_umma<DD, BF, false, true>(mq, mdx, mk, mv, a, g, st);                       \
+      if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true, true>(mk, mv, mq, mdx, a, g, st);  \
+    } else {                                                                                     \
+      e = launch_bwd_umma<DD, BF, false, false>(mq, mdx, mk, mv, a, g, st);                      \
+      if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true, false>(mk, mv, mq, mdx, a, g, st); \
+    }                                                                                            \
   } while (0)
   if (a.d == 128) { if (bf16) NB_BW(128, true); else NB_BW(128, false); }
   else            { if (bf16) NB_BW(64, true);  else NB_BW(64, false); }

@@ -650,6 +650,64 @@ def test_pullback_on_tensor_cores(dtype, E, H, Lq, Lkv, B, causal):
     _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
 
 
+@pytest.mark.parametrize("dtype,E,H,Lq,Lkv,B,kind", [
+    (torch.bfloat16, 128, 2, 200, 264, 2, "keypad"),     # (Lkv, 1, 1, B): one byte per key in the dk/dv half
+    (torch.float16, 256, 2, 130, 150, 2, "full"),        # (Lkv, Lq, H, B): gathered per step
+    (torch.bfloat16, 128, 2, 257, 136, 1, "matrix"),     # (Lkv, Lq) broadcast over heads and batch
+])
+def test_pullback_with_mask_on_tensor_cores(dtype, E, H, Lq, Lkv, B, kind):
+    """Bool mask arrays (src/attention.jl:133-138) in the tcgen05 backward."""
+    rng = np.random.default_rng(64)
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    dyn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    if kind == "keypad":
+        mask_np = np.arange(Lkv)[:, None, None, None] < rng.integers(Lkv // 2, Lkv + 1, size=B)[None, None, None, :]
+    elif kind == "full":
+        mask_np = rng.random((Lkv, Lq, H, B)) > 0.4
+        mask_np[0] = True
+    else:
+        mask_np = rng.random((Lkv, Lq)) > 0.5
+        mask_np[3] = True
+    x, a, back = nb.dot_product_attention_pullback(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype),
+                                                   mask=nb.jl_from_numpy(mask_np, device=DEV), nheads=H)
+    dq, dk, dv, db = back(_dev(dyn, dtype))
+    assert back.path == _lib.PATH_UMMA
+    nb.device_health()
+    gq, gk, gv, _ = O.dot_product_attention_grad(qn, kn, vn, dyn, None, mask=mask_np, nheads=H)
+    _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq")
+    _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
+    _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+
+
+def test_pullback_fully_masked_query_gives_no_gradient():
+    """A query that attends to nothing has NaN output (src/softmax.jl:71-76); the library lets no gradient
+    flow through it (both backward paths), so the other queries' gradients stay finite."""
+    rng = np.random.default_rng(65)
+    dtype, E, H, Lq, Lkv, B = torch.bfloat16, 128, 2, 140, 136, 1
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    dyn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    mask_np = rng.random((Lkv, Lq)) > 0.3
+    mask_np[0] = True
+    dead = 77
+    mask_np[:, dead] = False
+    x, a, back = nb.dot_product_attention_pullback(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype),
+                                                   mask=nb.jl_from_numpy(mask_np, device=DEV), nheads=H)
+    assert np.isnan(nb.jl_to_numpy(x)[:, dead]).all()
+    dq, dk, dv, _ = back(_dev(dyn, dtype))
+    assert back.path == _lib.PATH_UMMA
+    live = np.arange(Lq) != dead
+    gq, gk, gv, _ = O.dot_product_attention_grad(qn[:, live], kn, vn, dyn[:, live], None, mask=mask_np[:, live], nheads=H)
+    dqn = nb.jl_to_numpy(dq)
+    assert (dqn[:, dead] == 0).all()
+    _grad_close(dqn[:, live], gq, dtype, "dq")
+    _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
+    _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+
+
 @pytest.mark.parametrize("Lq,Lkv", [(100, 300), (515, 130)])
 def test_abi_backward_causal_flag_on_a_head_slice(Lq, Lkv):
     """C ABI: causal flag with kv_len != q_len (keys past the last query get zero gradient) on a shard that
