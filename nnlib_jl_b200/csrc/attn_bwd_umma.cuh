@@ -1,4 +1,4 @@
-// Backward of attention without bias and dropout (plain, causal, Bool mask) on the sm_100a tensor cores.  Included
+// Backward of attention without bias (plain, causal, Bool mask, dropout) on the sm_100a tensor cores.  Included
 // by attn_umma.cu (shares its helpers, constants and the sticky abort flag).
 //
 // The gradients Zygote composes from NNlib.jl's rules for this path
@@ -115,7 +115,9 @@ __device__ __forceinline__ void load_mask64(const unsigned char* p, long long st
 #define NB_SR_SET(e, val) su[(e) >> 5][(e) & 31] = __float_as_uint(val)
 
 // MASKED: a Bool mask array (NNlib.jl src/attention.jl:133-138, any broadcast strides) takes part.
-template <int D, bool BF16, bool DKV, bool MASKED>
+// DROP: the forward dropped scores (src/dropout.jl:77-87); the same Philox positions are drawn again:
+// alpha' = P keep/(1-p) feeds dV, and dS = P (keep/(1-p) dP - D).
+template <int D, bool BF16, bool DKV, bool MASKED, bool DROP>
 __global__ void __launch_bounds__(kBwThreads, 1)
 attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_constant__ CUtensorMap tm_fb,
                      const __grid_constant__ CUtensorMap tm_ra, const __grid_constant__ CUtensorMap tm_rb,
@@ -416,6 +418,40 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         load_mask64(mp, mask_step, (DKV ? a.Lq : a.Lkv) - c0,
                     mask_step == 1 && (reinterpret_cast<uintptr_t>(mp) & 15u) == 0, mw);
       }
+      // which of this thread's 64 scores survived the forward's dropout (bit e: column c0 + e)
+      unsigned int kb[2] = {0xffffffffu, 0xffffffffu};
+      if (DROP) {
+        if (!DKV) {
+          // a row of scores: eight consecutive keys share one Philox call, as in the forward
+          const unsigned long long srow = score_row(a, row_ok ? row : 0, h, b);
+          kb[0] = dropout_keep32(a, srow, (unsigned int)(c0 >> 5));
+          kb[1] = dropout_keep32(a, srow, (unsigned int)(c0 >> 5) + 1u);
+        } else {
+          // a column of scores (one key, 64 queries): lane L draws the call of (query L%8 of an 8-query
+          // block, key group L/8 of this warp's 32 keys) and the lanes trade the 8-bit results
+          const unsigned int j8 = (unsigned int)(t0 + wq * 32) / 8u + (unsigned int)(lane >> 3);
+          kb[0] = kb[1] = 0u;
+#pragma unroll 2
+          for (int cb = 0; cb < 8; ++cb) {
+            const int qi = c0 + cb * 8 + (lane & 7);
+            unsigned int w[4];
+            dropout_words(a, score_row(a, qi, h, b), j8, w);
+            unsigned int byte = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              byte |= ((w[e] & 0xffffu) >= a.drop_thresh ? 1u : 0u) << (2 * e);
+              byte |= ((w[e] >> 16) >= a.drop_thresh ? 1u : 0u) << (2 * e + 1);
+            }
+            unsigned int bits8 = 0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const unsigned int other = __shfl_sync(0xffffffffu, byte, q + (lane & 24));
+              bits8 |= ((other >> (lane & 7)) & 1u) << q;
+            }
+            kb[cb >> 2] |= bits8 << ((cb & 3) * 8);
+          }
+        }
+      }
       if (threadIdx.x == 0) BW_TRACE(0, it, 0);
       ok = mbar_wait(&bars->s_full, par, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -491,8 +527,13 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         if (lane == 0) mbar_arrive(&bars->dp_read);   // the next dP may be issued
 #pragma unroll
         for (int e = 0; e < 64; e += 2) {
-          const float d0 = (__uint_as_float(dp[e >> 5][e & 31]) - dl_row) * NB_SR(e);
-          const float d1 = (__uint_as_float(dp[(e + 1) >> 5][(e + 1) & 31]) - dl_row) * NB_SR(e + 1);
+          float g0 = __uint_as_float(dp[e >> 5][e & 31]), g1 = __uint_as_float(dp[(e + 1) >> 5][(e + 1) & 31]);
+          if (DROP) {
+            g0 = ((kb[e >> 5] >> (e & 31)) & 1u) ? g0 * a.inv_keep : 0.f;
+            g1 = ((kb[(e + 1) >> 5] >> ((e + 1) & 31)) & 1u) ? g1 * a.inv_keep : 0.f;
+          }
+          const float d0 = (g0 - dl_row) * NB_SR(e);
+          const float d1 = (g1 - dl_row) * NB_SR(e + 1);
           pk[e >> 1] = pack2<BF16>(d0, d1);
         }
         if (it >= 2) {   // the products of step it-2 have finished reading this dS buffer
@@ -512,10 +553,19 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 #pragma unroll
           for (int e = 0; e < 32; e += 4) {
             const float4 Dl = D4[e >> 2];
-            const float d0 = (__uint_as_float(dp[e + 0]) - Dl.x) * NB_SR(cc * 32 + e + 0);
-            const float d1 = (__uint_as_float(dp[e + 1]) - Dl.y) * NB_SR(cc * 32 + e + 1);
-            const float d2 = (__uint_as_float(dp[e + 2]) - Dl.z) * NB_SR(cc * 32 + e + 2);
-            const float d3 = (__uint_as_float(dp[e + 3]) - Dl.w) * NB_SR(cc * 32 + e + 3);
+            float g0 = __uint_as_float(dp[e + 0]), g1 = __uint_as_float(dp[e + 1]);
+            float g2 = __uint_as_float(dp[e + 2]), g3 = __uint_as_float(dp[e + 3]);
+            if (DROP) {
+              const unsigned int k4 = kb[cc] >> e;
+              g0 = (k4 & 1u) ? g0 * a.inv_keep : 0.f;
+              g1 = (k4 & 2u) ? g1 * a.inv_keep : 0.f;
+              g2 = (k4 & 4u) ? g2 * a.inv_keep : 0.f;
+              g3 = (k4 & 8u) ? g3 * a.inv_keep : 0.f;
+            }
+            const float d0 = (g0 - Dl.x) * NB_SR(cc * 32 + e + 0);
+            const float d1 = (g1 - Dl.y) * NB_SR(cc * 32 + e + 1);
+            const float d2 = (g2 - Dl.z) * NB_SR(cc * 32 + e + 2);
+            const float d3 = (g3 - Dl.w) * NB_SR(cc * 32 + e + 3);
             pk[cc * 16 + e / 2] = pack2<BF16>(d0, d1);
             pk[cc * 16 + e / 2 + 1] = pack2<BF16>(d2, d3);
           }
@@ -537,6 +587,11 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
           if (!ok) break;
         }
         uint8_t* prow = smem + C::kPOff + half * kChunkBytes + r * 128;
+        if (DROP) {   // dV takes the scores the forward multiplied V with: alpha' = P keep/(1-p)
+#pragma unroll
+          for (int e = 0; e < 64; ++e)
+            NB_SR_SET(e, ((kb[e >> 5] >> (e & 31)) & 1u) ? NB_SR(e) * a.inv_keep : 0.f);
+        }
 #pragma unroll
         for (int piece = 0; piece < 8; ++piece) {
           uint4 v;
@@ -609,10 +664,10 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 #undef NB_SR
 #undef NB_SR_SET
 
-template <int D, bool BF16, bool DKV, bool MASKED>
+template <int D, bool BF16, bool DKV, bool MASKED, bool DROP>
 cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const CUtensorMap& ra, const CUtensorMap& rb,
                             const AttnArgs& a, const BwdArgs& g, cudaStream_t st) {
-  auto kern = attn_bwd_umma_kernel<D, BF16, DKV, MASKED>;
+  auto kern = attn_bwd_umma_kernel<D, BF16, DKV, MASKED, DROP>;
   constexpr int smem = BwCfg<D, DKV>::kSmemBytes;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
@@ -626,12 +681,12 @@ cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const 
 
 }  // namespace
 
-// The tensor-core backward covers half-precision arrays with d = dv in {64, 128}, the causal flag and
-// Bool mask arrays; bias (its gradient needs a reduction) and dropout take the CUDA-core kernels.
+// The tensor-core backward covers half-precision arrays with d = dv in {64, 128}, the causal flag, Bool
+// mask arrays and Philox dropout; bias (its gradient needs a reduction) takes the CUDA-core kernels.
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype) {
   if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
   if (!(a.d == 64 || a.d == 128) || a.dv != a.d) return false;
-  if (a.bias || a.dropout_p > 0.f || g.dbias) return false;
+  if (a.bias || g.dbias) return false;
   if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1 || !a.lse || !g.delta) return false;
   const void* ptrs[] = {a.q, a.k, a.v, a.x, g.dx, g.dq, g.dk, g.dv};
   for (const void* p : ptrs)
@@ -651,18 +706,20 @@ cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_
   if (!make_map(&mdx, g.dx, dtype, E, a.Lq, a.B, g.dx_sl, g.dx_sb)) return cudaErrorInvalidValue;
   const bool bf16 = dtype == NNLIB_B200_BF16;
   cudaError_t e;
+#define NB_BW2(DD, BF, MK, DR)                                                                   \
+  do {                                                                                           \
+    e = launch_bwd_umma<DD, BF, false, MK, DR>(mq, mdx, mk, mv, a, g, st);                       \
+    if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true, MK, DR>(mk, mv, mq, mdx, a, g, st);  \
+  } while (0)
 #define NB_BW(DD, BF)                                                                            \
   do {                                                                                           \
-    if (a.mask) {                                                                                \
-      e = launch_bwd_umma<DD, BF, false, true>(mq, mdx, mk, mv, a, g, st);                       \
-      if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true, true>(mk, mv, mq, mdx, a, g, st);  \
-    } else {                                                                                     \
-      e = launch_bwd_umma<DD, BF, false, false>(mq, mdx, mk, mv, a, g, st);                      \
-      if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true, false>(mk, mv, mq, mdx, a, g, st); \
-    }                                                                                            \
+    const bool dr = a.dropout_p > 0.f;                                                           \
+    if (a.mask) { if (dr) NB_BW2(DD, BF, true, true); else NB_BW2(DD, BF, true, false); }        \
+    else        { if (dr) NB_BW2(DD, BF, false, true); else NB_BW2(DD, BF, false, false); }      \
   } while (0)
   if (a.d == 128) { if (bf16) NB_BW(128, true); else NB_BW(128, false); }
   else            { if (bf16) NB_BW(64, true);  else NB_BW(64, false); }
 #undef NB_BW
+#undef NB_BW2
   return e;
 }

@@ -681,6 +681,39 @@ def test_pullback_with_mask_on_tensor_cores(dtype, E, H, Lq, Lkv, B, kind):
     _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
 
 
+@pytest.mark.parametrize("dtype,E,H,Lq,Lkv,B,causal,keypad,drop", [
+    (torch.bfloat16, 128, 2, 200, 264, 2, False, False, 0.2),
+    (torch.float16, 256, 2, 300, 300, 1, True, False, 0.1),
+    (torch.bfloat16, 192, 3, 140, 333, 2, False, True, 0.3),
+])
+def test_pullback_with_dropout_on_tensor_cores(dtype, E, H, Lq, Lkv, B, causal, keypad, drop):
+    """The tcgen05 backward replays the forward's Philox mask (src/dropout.jl:106-122 pullback): the dq half
+    draws rows of scores like the forward, the dk/dv half columns (lanes trade the calls by shuffles)."""
+    rng = np.random.default_rng(66)
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    dyn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    mask, mask_np = None, None
+    if causal:
+        mask = nb.make_causal_mask(_dev(qn, dtype))
+        mask_np = np.arange(Lkv)[:, None] <= np.arange(Lq)[None, :]
+    if keypad:
+        mask_np = np.arange(Lkv)[:, None, None, None] < rng.integers(Lkv // 2, Lkv + 1, size=B)[None, None, None, :]
+        mask = nb.jl_from_numpy(mask_np, device=DEV)
+    fd = nb.PhiloxDropout(drop, seed=91, offset=3)
+    x, a, back = nb.dot_product_attention_pullback(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype),
+                                                   mask=mask, nheads=H, fdrop=fd)
+    dq, dk, dv, db = back(_dev(dyn, dtype))
+    assert back.path == _lib.PATH_UMMA
+    nb.device_health()
+    keep = P.keep_mask((Lkv, Lq, H, B), drop, 91, 3)
+    gq, gk, gv, _ = O.dot_product_attention_grad(qn, kn, vn, dyn, None, mask=mask_np, nheads=H, keep=keep, p=drop)
+    _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq")
+    _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
+    _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+
+
 def test_pullback_fully_masked_query_gives_no_gradient():
     """A query that attends to nothing has NaN output (src/softmax.jl:71-76); the library lets no gradient
     flow through it (both backward paths), so the other queries' gradients stay finite."""
