@@ -82,6 +82,38 @@ def test_null_params_and_missing_outputs(lib):
     assert lib.nnlib_b200_attention(None, None, 0, None) == _lib.INVALID_ARG
 
 
+def _grads(**kw):
+    g = _lib.AttnGrads()
+    g.dx = g.dq = g.dk = g.dv = g.delta = 0x3000   # fake non-null pointers, never dereferenced here
+    for k, v in kw.items():
+        setattr(g, k, v)
+    return g
+
+
+def test_backward_argument_checks_and_path_without_a_gpu(lib):
+    p = _params(lse=0x2000)
+    # the forward's lse is required, so are dx / dq / dk / dv / delta, and the struct size is checked
+    assert lib.nnlib_b200_attn_bwd(C.byref(_params()), C.byref(_grads()), None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), None, None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), C.byref(_grads(dx=None)), None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), C.byref(_grads(delta=None)), None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), C.byref(_grads(struct_size=8)), None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), C.byref(_grads(dx_stride_l=8)), None) == _lib.INVALID_ARG
+    g = _grads()
+    g.dbias_stride[1] = -1
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), C.byref(g), None) == _lib.INVALID_ARG
+    # the same validation in front of the path query; without a driver only the CUDA-core path is on offer
+    assert lib.nnlib_b200_attn_bwd_path(C.byref(_params()), C.byref(_grads())) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_bwd_path(C.byref(p), C.byref(_grads())) in (_lib.PATH_SIMT, _lib.PATH_UMMA)
+    assert lib.nnlib_b200_attn_bwd_path(C.byref(_params(lse=0x2000, dtype=_lib.F32)), C.byref(_grads())) == _lib.PATH_SIMT
+    assert lib.nnlib_b200_attn_bwd_path(C.byref(_params(lse=0x2000, d=2048, dv=2048)), C.byref(_grads())) \
+        == _lib.UNSUPPORTED_SHAPE
+    # empty problems are fine and launch nothing
+    before = lib.nnlib_b200_launch_count()
+    assert lib.nnlib_b200_attn_bwd(C.byref(_params(lse=0x2000, B=0)), C.byref(_grads()), None) == _lib.OK
+    assert lib.nnlib_b200_launch_count() == before
+
+
 def test_empty_problems_enqueue_nothing(lib):
     before = lib.nnlib_b200_launch_count()
     assert lib.nnlib_b200_attn_fwd(C.byref(_params(Lq=0)), None) == _lib.OK
