@@ -196,8 +196,9 @@ NNLIB_B200_API int nnlib_b200_attn_bwd(const nnlib_b200_attn_params* p, const nn
                                        void* stream);
 
 /* NNLIB_B200_PATH_* that attn_bwd would take for (p, g), or a negative error.  The tensor-core
-   backward covers 16-bit element types with d = dv in {64, 128}, the causal flag, Bool mask arrays
-   and dropout; bias (dbias), Float32 and other head sizes run on the CUDA-core kernels. */
+   backward covers 16-bit element types with d = dv in {64, 128} and every option of the forward
+   (causal flag, Bool mask arrays, dropout, bias with dbias); Float32 arrays and other head sizes
+   run on the CUDA-core kernels. */
 NNLIB_B200_API int nnlib_b200_attn_bwd_path(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g);
 
 /* make_causal_mask (src/attention.jl:149-153): fill an (L, L) byte matrix

@@ -336,7 +336,9 @@ end
 # Reverse rule.  The generic path is differentiated by Zygote through rrule(batched_mul),
 # rrule(softmax) and rrule(dropout); an opaque ccall has no adjoint, so the B200 method brings its
 # own: nnlib_b200_attn_bwd recomputes the scores from the saved log-sum-exp and replays the Philox
-# dropout mask.  fdrop must be `identity` or a `PhiloxDropout`; other callables keep the generic rules
+# dropout mask (tcgen05 kernels for Float16 / BFloat16 with head sizes 64 and 128 — causal flag, Bool
+# masks, dropout and bias / dbias included —, CUDA-core kernels otherwise; nnlib_b200_attn_bwd_path
+# tells which).  fdrop must be `identity` or a `PhiloxDropout`; other callables keep the generic rules
 # (Zygote differentiates the materialise → fdrop → attn_apply sequence only if those steps have rules,
 # so such calls should go through the generic method when gradients are needed).
 # ---------------------------------------------------------------------------

@@ -246,10 +246,11 @@ int nnlib_b200_attn_path(const nnlib_b200_attn_params* p) {
 }
 
 int nnlib_b200_device_health(void* stream) {
-  int v = 0;
-  const cudaError_t e = umma_take_abort(&v, (cudaStream_t)stream);
+  int v = 0, w = 0;
+  cudaError_t e = umma_take_abort(&v, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = umma_bwd_take_abort(&w, (cudaStream_t)stream);
   if (e != cudaSuccess) return finish(e);
-  return v ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
+  return (v || w) ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
 }
 
 const char* nnlib_b200_strerror(int code) {

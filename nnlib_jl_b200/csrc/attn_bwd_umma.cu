@@ -1,5 +1,4 @@
-// Backward of attention without bias (plain, causal, Bool mask, dropout) on the sm_100a tensor cores.  Included
-// by attn_umma.cu (shares its helpers, constants and the sticky abort flag).
+// Backward of attention (plain, causal, Bool mask, dropout, bias) on the sm_100a tensor cores.
 //
 // The gradients Zygote composes from NNlib.jl's rules for this path
 // (rrule(batched_mul) src/batched/batchedmul.jl:96-110, ∇softmax
@@ -24,7 +23,24 @@
 // TMEM columns: S [0,128)  dP [128,256)  accumulator 0 [256,256+D)  accumulator 1 [384,384+D).
 // dS (half precision): the dq half double-buffers it in columns [384,512) (its second accumulator is
 // unused), the dk/dv half writes it over dP: columns [128,160) for ring rows 0-63, [192,224) for rows 64-127.
-#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "launchers.h"
+#include "umma.cuh"
+#include "umma_shared.cuh"
+
+namespace nb200 {
+
+__device__ int g_bwd_abort = 0;  // sticky: a bounded wait of a backward kernel ran out
+
+#ifdef NB200_TRACE
+// Development aid: per-phase clock stamps of one CTA, read back by a test harness.  Not compiled into
+// the shipped library.
+__device__ long long g_trace_bwd[4][64][8];
+#define NB_TRACE(role, j, slot) \
+  do { if (blockIdx.x == NB200_TRACE_BLOCK && (j) < 64) g_trace_bwd[role][j][slot] = clock64(); } while (0)
+#endif
 
 namespace {
 
@@ -101,6 +117,32 @@ __device__ __forceinline__ void load_mask64(const unsigned char* p, long long st
   }
 }
 
+// 64 bias values of 16 bits, p[e * stride] (stride in elements), packed two to a word; entries
+// e >= n_valid read as 0.  vec16: stride 1 and p 16-byte aligned.
+__device__ __forceinline__ void load_bias16x64(const unsigned char* p, long long stride, int n_valid, bool vec16,
+                                               unsigned int (&bw)[32]) {
+  if (vec16 && n_valid >= 64) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(p) + v);
+      bw[4 * v + 0] = q.x; bw[4 * v + 1] = q.y; bw[4 * v + 2] = q.z; bw[4 * v + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int w = 0; w < 32; ++w) {
+      unsigned int lo = 0, hi = 0;
+      if (2 * w < n_valid) lo = __ldg(reinterpret_cast<const unsigned short*>(p + 2ll * (2 * w) * stride));
+      if (2 * w + 1 < n_valid) hi = __ldg(reinterpret_cast<const unsigned short*>(p + 2ll * (2 * w + 1) * stride));
+      bw[w] = lo | (hi << 16);
+    }
+  }
+}
+__device__ __forceinline__ float bias16_value(unsigned int word, int odd, int dtype) {
+  const unsigned int h = odd ? (word >> 16) : (word & 0xffffu);
+  if (dtype == NNLIB_B200_BF16) return __uint_as_float(h << 16);
+  return __half2float(__ushort_as_half((unsigned short)h));
+}
+
 #ifdef NB200_TRACE
 #ifndef NB200_TRACE_DKV
 #define NB200_TRACE_DKV 0
@@ -117,17 +159,21 @@ __device__ __forceinline__ void load_mask64(const unsigned char* p, long long st
 // MASKED: a Bool mask array (NNlib.jl src/attention.jl:133-138, any broadcast strides) takes part.
 // DROP: the forward dropped scores (src/dropout.jl:77-87); the same Philox positions are drawn again:
 // alpha' = P keep/(1-p) feeds dV, and dS = P (keep/(1-p) dP - D).
-template <int D, bool BF16, bool DKV, bool MASKED, bool DROP>
+// BIAS: the logits carried an additive bias (src/attention.jl:129-131); it is added again and the dq
+// half writes its gradient dbias = dS (reduced over the bias' broadcast dimensions by atomic adds).
+// FEAT = MASKED | DROP << 1 | BIAS << 2.
+template <int D, bool BF16, bool DKV, int FEAT>
 __global__ void __launch_bounds__(kBwThreads, 1)
 attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_constant__ CUtensorMap tm_fb,
                      const __grid_constant__ CUtensorMap tm_ra, const __grid_constant__ CUtensorMap tm_rb,
                      const AttnArgs a, const BwdArgs g, const int n_tiles) {
   using C = BwCfg<D, DKV>;
+  constexpr bool MASKED = (FEAT & 1) != 0, DROP = (FEAT & 2) != 0, BIAS = (FEAT & 4) != 0;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
     // the swizzled tiles need 1 KB alignment and the budget leaves no room to round up: refuse cleanly
     if (threadIdx.x == 0) {
-      atomicExch(&g_umma_abort, 1);
+      atomicExch(&g_bwd_abort, 1);
       if (a.status) atomicExch(a.status, NNLIB_B200_CUDA_ERROR);
     }
     return;
@@ -171,7 +217,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
     mbar_init(&bars->col_ready, 8);
     mbar_init(&bars->dp_read, 8);
     mbar_init(&bars->pt_ready, 8);
-    bars->abort_flag = *reinterpret_cast<volatile int*>(&g_umma_abort);
+    bars->abort_flag = *reinterpret_cast<volatile int*>(&g_bwd_abort);
     fence_mbar_init();
   }
   if (warp == 8) {
@@ -186,6 +232,11 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
   constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
   constexpr uint32_t kColDS = 384;   // dq half: two 64-column dS buffers where the dk/dv half keeps its second accumulator
 
+  // the compute threads hold 64 scores plus side inputs in registers: move the register budget of the
+  // copy / issue warps to them
+  // (each setmaxnreg sits inside its role's branch: the register allocator budgets per region)
+  if (warp >= 8) {
+  setmaxnreg_dec<72>();
   if (start_ok && warp == 8) {
     // ------------------------------------- TMA producer: resident pair and ring A'
     if (lane == 0 && n > 0) {
@@ -347,7 +398,10 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       }
       if (ok) umma_commit(&bars->acc_full);
     }
-  } else if (start_ok && warp < 8) {
+  }
+  } else {
+  setmaxnreg_inc<200>();
+  if (start_ok) {
     // ----------------------------------------------------------- compute warps
     const int half = warp >> 2;               // which 64 columns of every step this thread handles
     const int wq = warp & 3;                  // TMEM lane quarter this warp may touch
@@ -400,6 +454,27 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       if (DKV && a.mask_s[1] == 0) mask_row_keep = __ldg(mask_p) != 0;
     }
     const long long mask_step = MASKED ? a.mask_s[DKV ? 1 : 0] : 0;   // stride along the columns of a step
+    // bias: like the mask, a row of 64 keys per step in the dq half, a column of 64 queries in the dk/dv
+    // half (one value for the whole kernel when the bias does not depend on the query)
+    const int bias_esz = (BIAS && a.bias_dtype == NNLIB_B200_F32) ? 4 : 2;
+    const unsigned char* bias_p = nullptr;
+    float bias_uniform = 0.f;
+    const bool bias_per_step = BIAS && (!DKV || a.bias_s[1] != 0);
+    const long long bias_step = BIAS ? a.bias_s[DKV ? 1 : 0] : 0;
+    if (BIAS && row_ok) {
+      bias_p = reinterpret_cast<const unsigned char*>(a.bias) +
+               ((long long)h * a.bias_s[2] + (long long)b * a.bias_s[3] + (long long)row * a.bias_s[DKV ? 0 : 1]) * bias_esz;
+      if (DKV && a.bias_s[1] == 0) bias_uniform = load_bias(bias_p, 0, a.bias_dtype) * kLog2e;
+    }
+    // dbias (dq half): plain stores when every score has its own element, atomic adds when a stride of 0
+    // folds several scores onto one
+    float* dbias_p = nullptr;
+    bool dbias_exclusive = false;
+    if (BIAS && !DKV && g.dbias && row_ok) {
+      dbias_p = g.dbias + (long long)row * g.dbias_s[1] + (long long)h * g.dbias_s[2] + (long long)b * g.dbias_s[3];
+      dbias_exclusive = g.dbias_s[0] != 0 && (g.dbias_s[1] != 0 || a.Lq == 1) && (g.dbias_s[2] != 0 || a.H == 1) &&
+                        (g.dbias_s[3] != 0 || a.B == 1);
+    }
     auto col_store = [&](int it, float v) {
       (half == 0 ? col_lse : col_dl)[(it & 1) * 128 + r] = v;
       __syncwarp();
@@ -417,6 +492,13 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         const unsigned char* mp = mask_p + (long long)c0 * mask_step;
         load_mask64(mp, mask_step, (DKV ? a.Lq : a.Lkv) - c0,
                     mask_step == 1 && (reinterpret_cast<uintptr_t>(mp) & 15u) == 0, mw);
+      }
+      unsigned int bw[32];
+      const bool bias16 = bias_per_step && bias_p && bias_esz == 2;
+      if (bias16) {
+        const unsigned char* bp = bias_p + (long long)c0 * bias_step * 2;
+        load_bias16x64(bp, bias_step, (DKV ? a.Lq : a.Lkv) - c0,
+                       bias_step == 1 && (reinterpret_cast<uintptr_t>(bp) & 15u) == 0, bw);
       }
       // which of this thread's 64 scores survived the forward's dropout (bit e: column c0 + e)
       unsigned int kb[2] = {0xffffffffu, 0xffffffffu};
@@ -469,8 +551,27 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 
       if (!DKV) {
         const int lim = row_ok ? (a.causal ? min(row, a.Lkv - 1) : a.Lkv - 1) : -1;  // last key of this row
+        if (BIAS && bias_p) {
+          if (bias16) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) NB_SR_SET(e, ex2_approx(fmaf(NB_SR(e), c2, -lse2_row)));
+            for (int e = 0; e < 64; ++e)
+              NB_SR_SET(e, ex2_approx(fmaf(NB_SR(e), c2, fmaf(bias16_value(bw[e >> 1], e & 1, a.bias_dtype), kLog2e, -lse2_row))));
+          } else {   // Float32 bias: fetched here, eight at a time
+#pragma unroll
+            for (int e0 = 0; e0 < 64; e0 += 8) {
+              float bv[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                bv[u] = (c0 + e0 + u < a.Lkv) ? __ldg(reinterpret_cast<const float*>(bias_p) + (long long)(c0 + e0 + u) * bias_step) : 0.f;
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                NB_SR_SET(e0 + u, ex2_approx(fmaf(NB_SR(e0 + u), c2, fmaf(bv[u], kLog2e, -lse2_row))));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) NB_SR_SET(e, ex2_approx(fmaf(NB_SR(e), c2, -lse2_row)));
+        }
         if (c0 + 63 > lim) {
 #pragma unroll
           for (int e = 0; e < 64; ++e)
@@ -489,10 +590,25 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 #pragma unroll
         for (int e = 0; e < 64; e += 4) {
           const float4 L = L4[e >> 2];
-          NB_SR_SET(e + 0, ex2_approx(fmaf(NB_SR(e + 0), c2, -L.x)));
-          NB_SR_SET(e + 1, ex2_approx(fmaf(NB_SR(e + 1), c2, -L.y)));
-          NB_SR_SET(e + 2, ex2_approx(fmaf(NB_SR(e + 2), c2, -L.z)));
-          NB_SR_SET(e + 3, ex2_approx(fmaf(NB_SR(e + 3), c2, -L.w)));
+          float b0 = bias_uniform, b1 = bias_uniform, b2 = bias_uniform, b3 = bias_uniform;   // 0 without bias
+          if (BIAS && bias_per_step && bias_p) {
+            if (bias16) {
+              b0 = bias16_value(bw[e >> 1], 0, a.bias_dtype) * kLog2e;
+              b1 = bias16_value(bw[e >> 1], 1, a.bias_dtype) * kLog2e;
+              b2 = bias16_value(bw[(e >> 1) + 1], 0, a.bias_dtype) * kLog2e;
+              b3 = bias16_value(bw[(e >> 1) + 1], 1, a.bias_dtype) * kLog2e;
+            } else {
+              const float* bf = reinterpret_cast<const float*>(bias_p);
+              b0 = (c0 + e + 0 < a.Lq) ? __ldg(bf + (long long)(c0 + e + 0) * bias_step) * kLog2e : 0.f;
+              b1 = (c0 + e + 1 < a.Lq) ? __ldg(bf + (long long)(c0 + e + 1) * bias_step) * kLog2e : 0.f;
+              b2 = (c0 + e + 2 < a.Lq) ? __ldg(bf + (long long)(c0 + e + 2) * bias_step) * kLog2e : 0.f;
+              b3 = (c0 + e + 3 < a.Lq) ? __ldg(bf + (long long)(c0 + e + 3) * bias_step) * kLog2e : 0.f;
+            }
+          }
+          NB_SR_SET(e + 0, ex2_approx(fmaf(NB_SR(e + 0), c2, b0 - L.x)));
+          NB_SR_SET(e + 1, ex2_approx(fmaf(NB_SR(e + 1), c2, b1 - L.y)));
+          NB_SR_SET(e + 2, ex2_approx(fmaf(NB_SR(e + 2), c2, b2 - L.z)));
+          NB_SR_SET(e + 3, ex2_approx(fmaf(NB_SR(e + 3), c2, b3 - L.w)));
         }
         // queries before this key (causal) and padded key rows contribute nothing
         const int cmin = (row_ok && mask_row_keep) ? (a.causal ? row - c0 : 0) : 64;
@@ -535,6 +651,21 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
           const float d0 = (g0 - dl_row) * NB_SR(e);
           const float d1 = (g1 - dl_row) * NB_SR(e + 1);
           pk[e >> 1] = pack2<BF16>(d0, d1);
+          if (BIAS && dbias_p) {
+            // gradient of the bias = dS (masked and dropped-out positions included: they are zero / scaled)
+            float* o0 = dbias_p + (long long)(c0 + e) * g.dbias_s[0];
+            if (dbias_exclusive) {
+              if (g.dbias_s[0] == 1 && c0 + e + 1 < a.Lkv && (reinterpret_cast<uintptr_t>(o0) & 7u) == 0) {
+                *reinterpret_cast<float2*>(o0) = make_float2(d0, d1);
+              } else {
+                if (c0 + e < a.Lkv) *o0 = d0;
+                if (c0 + e + 1 < a.Lkv) *(o0 + g.dbias_s[0]) = d1;
+              }
+            } else {
+              if (c0 + e < a.Lkv) atomicAdd(o0, d0);
+              if (c0 + e + 1 < a.Lkv) atomicAdd(o0 + g.dbias_s[0], d1);
+            }
+          }
         }
         if (it >= 2) {   // the products of step it-2 have finished reading this dS buffer
           ok = mbar_wait(&bars->a_empty[(it - 2) % C::kStagesA], ((it - 2) / C::kStagesA) & 1, abort_flag);
@@ -647,6 +778,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       }
     }
   }
+  }   // compute warps
 
   tc_fence_before();
   __syncthreads();
@@ -655,7 +787,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
     tmem_dealloc(tmem, 512);
   }
   if (threadIdx.x == 0 && *abort_flag) {
-    atomicExch(&g_umma_abort, 1);
+    atomicExch(&g_bwd_abort, 1);
     if (a.status) atomicExch(a.status, NNLIB_B200_TIMEOUT);
   }
 }
@@ -664,10 +796,10 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 #undef NB_SR
 #undef NB_SR_SET
 
-template <int D, bool BF16, bool DKV, bool MASKED, bool DROP>
+template <int D, bool BF16, bool DKV, int FEAT>
 cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const CUtensorMap& ra, const CUtensorMap& rb,
                             const AttnArgs& a, const BwdArgs& g, cudaStream_t st) {
-  auto kern = attn_bwd_umma_kernel<D, BF16, DKV, MASKED, DROP>;
+  auto kern = attn_bwd_umma_kernel<D, BF16, DKV, FEAT>;
   constexpr int smem = BwCfg<D, DKV>::kSmemBytes;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
@@ -681,12 +813,12 @@ cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const 
 
 }  // namespace
 
-// The tensor-core backward covers half-precision arrays with d = dv in {64, 128}, the causal flag, Bool
-// mask arrays and Philox dropout; bias (its gradient needs a reduction) takes the CUDA-core kernels.
+// The tensor-core backward covers half-precision arrays with d = dv in {64, 128} and every feature of the
+// forward: causal flag, Bool mask arrays, Philox dropout and bias (any element type and strides).
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype) {
   if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
   if (!(a.d == 64 || a.d == 128) || a.dv != a.d) return false;
-  if (a.bias || g.dbias) return false;
+  if (g.dbias && !a.bias) return false;
   if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1 || !a.lse || !g.delta) return false;
   const void* ptrs[] = {a.q, a.k, a.v, a.x, g.dx, g.dq, g.dk, g.dv};
   for (const void* p : ptrs)
@@ -706,20 +838,52 @@ cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_
   if (!make_map(&mdx, g.dx, dtype, E, a.Lq, a.B, g.dx_sl, g.dx_sb)) return cudaErrorInvalidValue;
   const bool bf16 = dtype == NNLIB_B200_BF16;
   cudaError_t e;
-#define NB_BW2(DD, BF, MK, DR)                                                                   \
+#define NB_BW2(DD, BF, FT)                                                                       \
   do {                                                                                           \
-    e = launch_bwd_umma<DD, BF, false, MK, DR>(mq, mdx, mk, mv, a, g, st);                       \
-    if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true, MK, DR>(mk, mv, mq, mdx, a, g, st);  \
+    e = launch_bwd_umma<DD, BF, false, FT>(mq, mdx, mk, mv, a, g, st);                           \
+    if (e == cudaSuccess) e = launch_bwd_umma<DD, BF, true, FT>(mk, mv, mq, mdx, a, g, st);      \
   } while (0)
 #define NB_BW(DD, BF)                                                                            \
   do {                                                                                           \
-    const bool dr = a.dropout_p > 0.f;                                                           \
-    if (a.mask) { if (dr) NB_BW2(DD, BF, true, true); else NB_BW2(DD, BF, true, false); }        \
-    else        { if (dr) NB_BW2(DD, BF, false, true); else NB_BW2(DD, BF, false, false); }      \
+    switch (feat) {                                                                              \
+      case 0: NB_BW2(DD, BF, 0); break;                                                          \
+      case 1: NB_BW2(DD, BF, 1); break;                                                          \
+      case 2: NB_BW2(DD, BF, 2); break;                                                          \
+      case 3: NB_BW2(DD, BF, 3); break;                                                          \
+      case 4: NB_BW2(DD, BF, 4); break;                                                          \
+      case 5: NB_BW2(DD, BF, 5); break;                                                          \
+      case 6: NB_BW2(DD, BF, 6); break;                                                          \
+      default: NB_BW2(DD, BF, 7); break;                                                         \
+    }                                                                                            \
   } while (0)
+  const int feat = (a.mask ? 1 : 0) | (a.dropout_p > 0.f ? 2 : 0) | (a.bias ? 4 : 0);
   if (a.d == 128) { if (bf16) NB_BW(128, true); else NB_BW(128, false); }
   else            { if (bf16) NB_BW(64, true);  else NB_BW(64, false); }
 #undef NB_BW
 #undef NB_BW2
   return e;
 }
+
+#ifdef NB200_TRACE
+extern "C" __attribute__((visibility("default"))) int nnlib_b200_trace_dump_bwd(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace_bwd, sizeof(long long) * 4 * 64 * 8);
+}
+#endif
+
+// Reads and clears the backward kernels' sticky "a bounded wait ran out" flag of the current device.
+// Synchronises the stream.
+cudaError_t umma_bwd_take_abort(int* out, cudaStream_t st) {
+  int v = 0;
+  cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpyFromSymbol(&v, g_bwd_abort, sizeof(int));
+  if (e != cudaSuccess) return e;
+  if (v) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_bwd_abort, &zero, sizeof(int));
+  }
+  *out = v;
+  return e;
+}
+
+}  // namespace nb200

@@ -32,6 +32,7 @@
 #include "extras.cuh"
 #include "launchers.h"
 #include "umma.cuh"
+#include "umma_shared.cuh"
 
 namespace nb200 {
 
@@ -49,17 +50,9 @@ __device__ long long g_trace[4][64][8];
 
 namespace {
 
-using namespace ptx;
-
-constexpr int kBM = 128;               // queries per tile
-constexpr int kBN = 128;               // keys per tile
 constexpr int kQT = 2;                 // query tiles per CTA
 constexpr int kThreads = 384;
-constexpr int kChunkBytes = 128 * 128; // 128 rows x 64 halves: one TMA box
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleGap = 8.0f;    // raise the running max only when it grew by > 2^8
-constexpr unsigned long long kDrainNs = 20ull * 1000 * 1000;  // 20 ms for in-flight copies on abort
 
 template <int D>
 struct Cfg {
@@ -92,25 +85,6 @@ struct Barriers {
   int abort_flag;
 };
 static_assert(sizeof(Barriers) <= 512, "barrier block");
-
-__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
-
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float r;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
-
-template <bool BF16>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  if (BF16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  } else {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-}
 
 // XM = side + 3*drop.  side: 0 = no side input (optionally causal), 1 = Bool mask array only,
 // 2 = bias (and mask); drop: dropout code compiled in.  Each combination is its own kernel so that
@@ -1051,41 +1025,6 @@ attn_apply_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-// (features, positions, batch) array with 128-byte-swizzled boxes of 64 features x 128 positions
-bool make_map(CUtensorMap* m, const void* base, int dtype, long long feat, long long len, long long batch,
-              long long stride_l, long long stride_b) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)feat, (cuuint64_t)len, (cuuint64_t)batch};
-  const cuuint64_t strides[2] = {(cuuint64_t)stride_l * 2, (cuuint64_t)stride_b * 2};
-  const cuuint32_t box[3] = {64, 128, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(m, dtype == NNLIB_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                        3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-bool stride_ok(long long s) { return s > 0 && (s % 8) == 0 && s * 2 < (1ll << 40); }
-
 template <int D, bool BF16, int XM, bool STATS, bool BSM>
 cudaError_t launch_fwd_impl(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mb,
                             const AttnArgs& a, cudaStream_t st) {
@@ -1313,8 +1252,5 @@ cudaError_t umma_take_abort(int* out, cudaStream_t st) {
   *out = v;
   return e;
 }
-
-// tensor-core backward (same translation unit: it shares the helpers above)
-#include "attn_bwd_umma.cuh"
 
 }  // namespace nb200

@@ -59,6 +59,11 @@ __device__ __forceinline__ void side_issue(const RowSide& rs, int jj0, int Lkv, 
   }
 }
 
+// bit 7 of every byte of the result is set iff that byte of w is non-zero
+__device__ __forceinline__ unsigned int nonzero_bytes(unsigned int w) {
+  return (w | ((w & 0x7f7f7f7fu) + 0x7f7f7f7fu)) & 0x80808080u;
+}
+
 __device__ __forceinline__ unsigned int u4_word(const uint4& q, int w) {
   return w == 0 ? q.x : (w == 1 ? q.y : (w == 2 ? q.z : q.w));
 }
@@ -106,10 +111,16 @@ __device__ __forceinline__ void side_apply(const RowSide& rs, unsigned int (&s)[
   }
   // ---- range and mask
   if (rs.mask_row && rs.mask_vec && inside) {
+    // most chunks of a padding-style mask are all true: one test instead of 32 byte extractions
+    const unsigned int nz = nonzero_bytes(mq[0].x) & nonzero_bytes(mq[0].y) & nonzero_bytes(mq[0].z) &
+                            nonzero_bytes(mq[0].w) & nonzero_bytes(mq[1].x) & nonzero_bytes(mq[1].y) &
+                            nonzero_bytes(mq[1].z) & nonzero_bytes(mq[1].w);
+    if (nz != 0x80808080u || lim_e < 31) {
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      const unsigned int byte = (u4_word(mq[e >> 4], (e >> 2) & 3) >> ((e & 3) * 8)) & 0xffu;
-      if (e > lim_e || byte == 0u) s[e] = 0xff800000u;
+      for (int e = 0; e < 32; ++e) {
+        const unsigned int byte = (u4_word(mq[e >> 4], (e >> 2) & 3) >> ((e & 3) * 8)) & 0xffu;
+        if (e > lim_e || byte == 0u) s[e] = 0xff800000u;
+      }
     }
   } else if (rs.mask_row) {
 #pragma unroll

@@ -25,8 +25,11 @@ cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t
 cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st);
 bool umma_apply_supports(const AttnArgs& a, int dtype);
 cudaError_t umma_apply(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t umma_take_abort(int* out, cudaStream_t st);
+
+// tcgen05 backward kernels (attn_bwd_umma.cu)
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype);
 cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_t st);
-cudaError_t umma_take_abort(int* out, cudaStream_t st);
+cudaError_t umma_bwd_take_abort(int* out, cudaStream_t st);
 
 }  // namespace nb200

@@ -714,6 +714,40 @@ def test_pullback_with_dropout_on_tensor_cores(dtype, E, H, Lq, Lkv, B, causal, 
     _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
 
 
+@pytest.mark.parametrize("dtype,bias_dtype,E,H,Lq,Lkv,B,bias_shape,causal,drop", [
+    (torch.bfloat16, torch.bfloat16, 128, 2, 200, 264, 2, (264, 200, 2, 2), False, 0.0),   # own element per score
+    (torch.float16, torch.float16, 256, 2, 130, 150, 2, (150, 130), False, 0.2),           # summed over heads, batch
+    (torch.bfloat16, torch.bfloat16, 128, 2, 140, 333, 2, (333, 1, 1, 2), False, 0.0),     # key bias: summed over queries
+    (torch.bfloat16, torch.float32, 128, 2, 257, 257, 1, (257, 257, 2, 1), True, 0.1),     # Float32 bias, causal, odd rows
+])
+def test_pullback_with_bias_on_tensor_cores(dtype, bias_dtype, E, H, Lq, Lkv, B, bias_shape, causal, drop):
+    """Additive bias in the tcgen05 backward: the logits are rebuilt with it and dbias = dS reduced over the
+    bias' broadcast dimensions (test/attention.jl:61-76 checks shapes and gradients w.r.t. bias)."""
+    rng = np.random.default_rng(67)
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    dyn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    bn = _round_to(0.5 * rng.standard_normal(bias_shape), bias_dtype)
+    mask, mask_np = None, None
+    if causal:
+        mask = nb.make_causal_mask(_dev(qn, dtype))
+        mask_np = np.arange(Lkv)[:, None] <= np.arange(Lq)[None, :]
+    fd = nb.PhiloxDropout(drop, seed=92, offset=1) if drop > 0 else nb.identity
+    x, a, back = nb.dot_product_attention_pullback(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype),
+                                                   _dev(bn, bias_dtype), mask=mask, nheads=H, fdrop=fd)
+    dq, dk, dv, db = back(_dev(dyn, dtype))
+    assert back.path == _lib.PATH_UMMA
+    nb.device_health()
+    keep = P.keep_mask((Lkv, Lq, H, B), drop, 92, 1) if drop > 0 else None
+    gq, gk, gv, gb = O.dot_product_attention_grad(qn, kn, vn, dyn, bn, mask=mask_np, nheads=H, keep=keep, p=drop)
+    _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq")
+    _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
+    _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+    assert tuple(db.shape) == tuple(bias_shape)
+    _grad_close(nb.jl_to_numpy(db), gb, bias_dtype if bias_dtype != torch.float32 else dtype, "dbias")
+
+
 def test_pullback_fully_masked_query_gives_no_gradient():
     """A query that attends to nothing has NaN output (src/softmax.jl:71-76); the library lets no gradient
     flow through it (both backward paths), so the other queries' gradients stay finite."""
