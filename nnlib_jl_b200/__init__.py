@@ -9,11 +9,12 @@ independent (batch, head) units of one call over the GPUs of a box.
 from .attention import (ArgumentError, CausalMask, LazyAttnScores, PhiloxDropout, device_health,
                         dot_product_attention, dot_product_attention_pullback, dot_product_attention_scores, identity,
                         make_causal_mask)
+from .hostio import HostPipelinedAttention
 from .layout import (as_column_major, is_column_major, jl_empty, jl_from_numpy, jl_reshape, jl_to_numpy,
                      jl_zeros)
 
 __all__ = [
-    "ArgumentError", "CausalMask", "LazyAttnScores", "PhiloxDropout", "device_health",
+    "ArgumentError", "CausalMask", "HostPipelinedAttention", "LazyAttnScores", "PhiloxDropout", "device_health",
     "dot_product_attention", "dot_product_attention_pullback", "dot_product_attention_scores", "identity", "make_causal_mask",
     "as_column_major", "is_column_major", "jl_empty", "jl_from_numpy", "jl_reshape", "jl_to_numpy", "jl_zeros",
 ]

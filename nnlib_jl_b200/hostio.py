@@ -1,0 +1,114 @@
+"""Attention on arrays that live in host memory.
+
+The reference's method takes arrays wherever they are; a caller whose q, k, v
+sit in (pinned) host memory pays two PCIe crossings around the kernels.  The
+(batch, head) units are independent (NNlib.jl ``src/attention.jl:87-99``), so
+the batch can be cut into chunks and the three engines of the GPU kept busy at
+once: while chunk ``i`` is in the kernels, chunk ``i+1`` crosses the bus on the
+host-to-device copy engine and the result of chunk ``i-1`` returns on the
+device-to-host engine.  The bus is full duplex, so the step costs about
+``max(bytes_in, bytes_out) / bandwidth`` instead of their sum plus the kernels.
+"""
+from __future__ import annotations
+
+import torch
+
+from .attention import ArgumentError, CausalMask, dot_product_attention
+from .layout import jl_empty
+
+__all__ = ["HostPipelinedAttention"]
+
+
+class HostPipelinedAttention:
+    """Reusable pipeline for ``x = dot_product_attention(q, k, v; mask, nheads)[1]`` with q, k, v and x in
+    pinned host memory.
+
+    Host arrays are torch tensors of shape ``(B, L, E)`` (row-major: the memory
+    of Julia's column-major ``(E, L, B)``).  ``mask`` is ``None`` or
+    ``CausalMask()``.  Device staging buffers for two chunks are allocated once
+    in the constructor; :meth:`__call__` enqueues the whole pipeline and returns
+    after the last result byte has been ordered on ``out_stream`` (call
+    ``synchronize()`` or wait on :attr:`done` to read ``hx``).
+    """
+
+    def __init__(self, E: int, Ev: int, Lq: int, Lkv: int, B: int, dtype: torch.dtype, *, nheads: int,
+                 mask=None, chunk: int = 1, device=None):
+        if mask is not None and not isinstance(mask, CausalMask):
+            raise ArgumentError("HostPipelinedAttention: mask must be None or CausalMask()")
+        if chunk < 1 or B < 1:
+            raise ArgumentError("HostPipelinedAttention: batch and chunk must be positive")
+        self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.E, self.Ev, self.Lq, self.Lkv, self.B = int(E), int(Ev), int(Lq), int(Lkv), int(B)
+        self.dtype, self.nheads, self.mask = dtype, int(nheads), mask
+        self.chunk = min(int(chunk), self.B)
+        c = self.chunk
+        # two staging sets: one is being filled while the other is in the kernels
+        self.dq = [jl_empty((E, Lq, c), dtype, self.dev) for _ in range(2)]
+        self.dk = [jl_empty((E, Lkv, c), dtype, self.dev) for _ in range(2)]
+        self.dv = [jl_empty((Ev, Lkv, c), dtype, self.dev) for _ in range(2)]
+        self.dx = [None, None]
+        with torch.cuda.device(self.dev):
+            self.in_stream = torch.cuda.Stream()
+            self.out_stream = torch.cuda.Stream()
+            self.loaded = [torch.cuda.Event() for _ in range(2)]      # staging set s holds its chunk
+            self.computed = [torch.cuda.Event() for _ in range(2)]    # x of staging set s is ready
+            self.drained = [torch.cuda.Event() for _ in range(2)]     # x of staging set s has left the device
+            self.consumed = [torch.cuda.Event() for _ in range(2)]    # the kernels no longer read staging set s
+            self.done = torch.cuda.Event()
+
+    @staticmethod
+    def _check_host(name, t, shape, dtype):
+        if not isinstance(t, torch.Tensor) or t.is_cuda or tuple(t.shape) != tuple(shape) or t.dtype != dtype \
+                or not t.is_contiguous():
+            raise ArgumentError(f"{name} must be a contiguous host tensor of shape {tuple(shape)} and dtype {dtype}")
+        if not t.is_pinned():
+            raise ArgumentError(f"{name} must live in pinned host memory (the copies are asynchronous)")
+
+    def __call__(self, hq: torch.Tensor, hk: torch.Tensor, hv: torch.Tensor, hx: torch.Tensor) -> torch.Tensor:
+        B, c = self.B, self.chunk
+        self._check_host("q", hq, (B, self.Lq, self.E), self.dtype)
+        self._check_host("k", hk, (B, self.Lkv, self.E), self.dtype)
+        self._check_host("v", hv, (B, self.Lkv, self.Ev), self.dtype)
+        self._check_host("x", hx, (B, self.Lq, self.Ev), self.dtype)
+        with torch.cuda.device(self.dev):
+            comp = torch.cuda.current_stream()
+            start = torch.cuda.Event()
+            start.record(comp)
+            self.in_stream.wait_event(start)       # the pipeline starts after earlier work of the caller's stream
+            self.out_stream.wait_event(start)
+            n = (B + c - 1) // c
+            for i in range(n):
+                s = i & 1
+                b0, b1 = i * c, min(B, (i + 1) * c)
+                w = b1 - b0
+                # ---- host -> device (copy engine 1)
+                if i >= 2:
+                    self.in_stream.wait_event(self.consumed[s])       # chunk i-2 no longer needs this set
+                with torch.cuda.stream(self.in_stream):
+                    self.dq[s].permute(2, 1, 0)[:w].copy_(hq[b0:b1], non_blocking=True)
+                    self.dk[s].permute(2, 1, 0)[:w].copy_(hk[b0:b1], non_blocking=True)
+                    self.dv[s].permute(2, 1, 0)[:w].copy_(hv[b0:b1], non_blocking=True)
+                    self.loaded[s].record(self.in_stream)
+                # ---- kernels (caller's stream)
+                comp.wait_event(self.loaded[s])
+                if i >= 2:
+                    comp.wait_event(self.drained[s])                  # x of chunk i-2 has been copied out
+                q, k, v = self.dq[s], self.dk[s], self.dv[s]
+                if w != c:
+                    q, k, v = q[:, :, :w], k[:, :, :w], v[:, :, :w]
+                x, _ = dot_product_attention(q, k, v, mask=self.mask, nheads=self.nheads)
+                self.dx[s] = x                                        # keep alive until copied
+                x.record_stream(self.out_stream)                      # the allocator must not reuse it before the copy
+                self.consumed[s].record(comp)
+                self.computed[s].record(comp)
+                # ---- device -> host (copy engine 2)
+                self.out_stream.wait_event(self.computed[s])
+                with torch.cuda.stream(self.out_stream):
+                    hx[b0:b1].copy_(x.permute(2, 1, 0), non_blocking=True)
+                    self.drained[s].record(self.out_stream)
+            self.done.record(self.out_stream)
+            comp.wait_event(self.done)             # later work on the caller's stream sees hx complete
+        return hx
+
+    def synchronize(self) -> None:
+        self.done.synchronize()

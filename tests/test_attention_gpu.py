@@ -240,6 +240,8 @@ def test_umma_plain_single_tile(dtype, d):
     (64, 3, 257, 129, 1),      # one row / one key past a tile boundary
     (128, 2, 1, 1, 1),         # smallest
     (64, 1, 700, 1500, 1),     # many kv tiles: pipeline wraps around
+    (128, 4, 1, 2000, 2),      # decode-like: one query against a long key sequence
+    (64, 2, 5, 777, 3),
 ])
 def test_umma_shapes(dtype, d, H, Lq, Lkv, B):
     _run_case(dtype, d * H, H, Lq, Lkv, B, seed=21)
@@ -558,6 +560,27 @@ def test_sharded_driver_on_device_matches_single_call():
     keep = P.keep_mask((Lkv, Lq, H, B), 0.2, 5, 9)
     yo, _ = O.dot_product_attention(qn, kn, vn, mask=mask, nheads=H, fdrop=lambda a: a * keep / np.float32(0.8))
     _close(nb.jl_to_numpy(x), yo, dtype, "sharded x")
+
+
+@pytest.mark.parametrize("B,chunk,causal", [(5, 2, True), (3, 1, False), (2, 4, True)])
+def test_host_pipelined_attention_matches_device_call(B, chunk, causal):
+    """q, k, v in pinned host memory, batch cut into chunks whose copies and kernels overlap: the same
+    result as one device call, whatever the chunk size (the last chunk may be partial)."""
+    dtype, E, H, L = torch.bfloat16, 256, 2, 300
+    g = torch.Generator().manual_seed(55)
+    hq, hk, hv = (torch.randn((B, L, E), generator=g).to(dtype).pin_memory() for _ in range(3))
+    hx = torch.zeros((B, L, E), dtype=dtype).pin_memory()
+    mask = nb.CausalMask() if causal else None
+    pipe = nb.HostPipelinedAttention(E, E, L, L, B, dtype, nheads=H, mask=mask, chunk=chunk, device=DEV)
+    for _ in range(2):                      # the second call reuses the staging buffers
+        pipe(hq, hk, hv, hx)
+    pipe.synchronize()
+    q, k, v = (t.to(DEV).permute(2, 1, 0) for t in (hq, hk, hv))
+    y, _ = nb.dot_product_attention(q, k, v, mask=mask, nheads=H)
+    torch.cuda.synchronize()
+    assert torch.equal(hx, y.permute(2, 1, 0).cpu())
+    with pytest.raises(nb.ArgumentError):
+        pipe(hq.clone(), hk, hv, hx)        # not pinned
 
 
 # --------------------------------------------------------------------------
