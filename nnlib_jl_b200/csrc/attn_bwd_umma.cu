@@ -20,6 +20,7 @@
 //   warp 8      TMA producer of the resident pair and of ring A'; TMEM allocation
 //   warp 9      MMA issuer
 //   warp 10     TMA producer of ring B'
+//   warp 11     idle (completes the warpgroup of warps 8-10)
 // TMEM columns: S [0,128)  dP [128,256)  accumulator 0 [256,256+D)  accumulator 1 [384,384+D).
 // dS (half precision): the dq half double-buffers it in columns [384,512) (its second accumulator is
 // unused), the dk/dv half writes it over dP: columns [128,160) for ring rows 0-63, [192,224) for rows 64-127.
@@ -44,7 +45,9 @@ __device__ long long g_trace_bwd[4][64][8];
 
 namespace {
 
-constexpr int kBwThreads = 352;
+// 12 warps = three whole warpgroups: setmaxnreg is a warpgroup-wide instruction, so the copy / issue
+// warps 8-10 need their (idle) fourth warp 11
+constexpr int kBwThreads = 384;
 
 template <int D, bool DKV>
 struct BwCfg {
@@ -400,7 +403,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
     }
   }
   } else {
-  setmaxnreg_inc<200>();
+  setmaxnreg_inc<208>();
   if (start_ok) {
     // ----------------------------------------------------------- compute warps
     const int half = warp >> 2;               // which 64 columns of every step this thread handles
