@@ -390,6 +390,44 @@ def run_ours(args, w):
         dist.destroy_process_group()
 
 
+def run_softmax(args):
+    """Side measurement, not the bench line: the stand-alone softmax / logsoftmax kernels on the sizes the
+    reference's GPU softmax benchmark quotes (benchmark/cuda_softmax/README.md, Float32, dims = 1 and 2) plus one
+    HBM-sized array; algorithmic bytes = one read and one write per element."""
+    import torch
+
+    import nnlib_jl_b200 as nb
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    rows = []
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)       # larger than the 126 MB L2
+    for shape, dims, dt in [((32000, 64), 1, torch.float32), ((10000, 100), 1, torch.float32),
+                            ((1000, 1000), 1, torch.float32), ((256, 1000), 1, torch.float32),
+                            ((256, 10, 32), 2, torch.float32), ((8192, 16384), 1, torch.float32),
+                            ((4096, 32768), 1, torch.bfloat16), ((512, 512, 384), 1, torch.bfloat16)]:
+        x = nb.jl_empty(shape, dt, dev); x.normal_()
+        dy = nb.jl_empty(shape, dt, dev); dy.normal_()
+        y = nb.softmax.softmax(x, dims=dims)
+        for name, fn in (("softmax", lambda: nb.softmax.softmax(x, dims=dims)),
+                         ("softmax_pullback", lambda: nb.softmax.softmax_pullback(dy, y, dims=dims))):
+            for _ in range(3):
+                fn()
+            ts = []
+            for _ in range(max(3, args.steps)):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            us = statistics.median(ts) * 1e3
+            nbytes = x.numel() * x.element_size() * (2 if name == "softmax" else 3)
+            rows.append({"op": name, "size": list(shape), "dims": dims, "dtype": str(dt).replace("torch.", ""),
+                         "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
+                         "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm"], 3)})
+    print(json.dumps({"note": "stand-alone softmax kernels (--softmax): not a bench line; L2 flushed between launches",
+                      "hbm_peak_GBps": peaks["hbm"], "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -400,6 +438,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
     ap.add_argument("--backward", action="store_true", help="time the pullback (dq, dk, dv) of the workload instead")
+    ap.add_argument("--softmax", action="store_true", help="time the stand-alone softmax kernels instead")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (smaller profiler captures)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
     args = ap.parse_args()
@@ -407,7 +446,9 @@ def main():
     if args.batch > 0:
         w["B"] = args.batch
         w["desc"] += f" [batch overridden to {args.batch}]"
-    if args.impl == "reference":
+    if args.softmax:
+        run_softmax(args)
+    elif args.impl == "reference":
         run_reference(args, w)
     else:
         run_ours(args, w)

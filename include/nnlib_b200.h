@@ -201,6 +201,27 @@ NNLIB_B200_API int nnlib_b200_attn_bwd(const nnlib_b200_attn_params* p, const nn
    run on the CUDA-core kernels. */
 NNLIB_B200_API int nnlib_b200_attn_bwd_path(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g);
 
+/* softmax / logsoftmax over one dimension of a dense column-major array and their pullbacks
+   (src/softmax.jl:69-79 _softmax!, :147-157 _logsoftmax!, :98-101 _∇softmax!, :170-190 ∇logsoftmax;
+   CUDA methods in ext/NNlibCUDACUDNNExt/softmax.jl).  The array is seen as (inner, n, outer) with the
+   reduction over the middle extent: for `dims = k` of an N-d array, inner = prod(size[1:k-1]),
+   n = size[k], outer = prod(size[k+1:N]).  Element type as in attn_params.dtype; arithmetic in fp32.
+   Non-finite inputs follow the reference: a column whose maximum is +Inf puts its weight on the +Inf
+   entries in equal shares, a column whose maximum is -Inf or that holds a NaN becomes NaN.
+   x and y (dy, y and dx) may alias. */
+typedef struct nnlib_b200_softmax_params {
+  size_t struct_size;        /* = sizeof(nnlib_b200_softmax_params) */
+  int32_t dtype;             /* NNLIB_B200_F16 / BF16 / F32 */
+  int32_t log;               /* 0: softmax, 1: logsoftmax */
+  int64_t inner, n, outer;
+  const void* x;             /* forward: input.            backward: y = (log)softmax(x) */
+  const void* dy;            /* forward: ignored.          backward: cotangent of y */
+  void* out;                 /* forward: y.                backward: dx */
+} nnlib_b200_softmax_params;
+
+NNLIB_B200_API int nnlib_b200_softmax_fwd(const nnlib_b200_softmax_params* p, void* stream);
+NNLIB_B200_API int nnlib_b200_softmax_bwd(const nnlib_b200_softmax_params* p, void* stream);
+
 /* make_causal_mask (src/attention.jl:149-153): fill an (L, L) byte matrix
    with m[i + L*j] = (i <= j). */
 NNLIB_B200_API int nnlib_b200_causal_fill(uint8_t* mask, int64_t L, void* stream);

@@ -9,6 +9,7 @@ independent (batch, head) units of one call over the GPUs of a box.
 from .attention import (ArgumentError, CausalMask, LazyAttnScores, PhiloxDropout, device_health,
                         dot_product_attention, dot_product_attention_pullback, dot_product_attention_scores, identity,
                         make_causal_mask)
+from . import softmax  # softmax / logsoftmax and pullbacks: nnlib_jl_b200.softmax.softmax(x, dims=...)
 from .hostio import HostPipelinedAttention
 from .layout import (as_column_major, is_column_major, jl_empty, jl_from_numpy, jl_reshape, jl_to_numpy,
                      jl_zeros)

@@ -43,6 +43,8 @@ EXPORTS = (
     "nnlib_b200_causal_fill",
     "nnlib_b200_causal_check",
     "nnlib_b200_attn_path",
+    "nnlib_b200_softmax_fwd",
+    "nnlib_b200_softmax_bwd",
     "nnlib_b200_device_health",
     "nnlib_b200_strerror",
     "nnlib_b200_version",
@@ -101,6 +103,21 @@ class AttnGrads(C.Structure):
         self.struct_size = C.sizeof(AttnGrads)
 
 
+class SoftmaxParams(C.Structure):
+    """Mirror of ``nnlib_b200_softmax_params``."""
+
+    _fields_ = [
+        ("struct_size", C.c_size_t),
+        ("dtype", C.c_int32), ("log", C.c_int32),
+        ("inner", C.c_int64), ("n", C.c_int64), ("outer", C.c_int64),
+        ("x", C.c_void_p), ("dy", C.c_void_p), ("out", C.c_void_p),
+    ]
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.struct_size = C.sizeof(SoftmaxParams)
+
+
 _lib = None
 
 
@@ -137,6 +154,10 @@ def load() -> C.CDLL:
     lib.nnlib_b200_causal_fill.restype = C.c_int
     lib.nnlib_b200_causal_check.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
     lib.nnlib_b200_causal_check.restype = C.c_int
+    lib.nnlib_b200_softmax_fwd.argtypes = [C.POINTER(SoftmaxParams), C.c_void_p]
+    lib.nnlib_b200_softmax_fwd.restype = C.c_int
+    lib.nnlib_b200_softmax_bwd.argtypes = [C.POINTER(SoftmaxParams), C.c_void_p]
+    lib.nnlib_b200_softmax_bwd.restype = C.c_int
     lib.nnlib_b200_attn_path.argtypes = [P]
     lib.nnlib_b200_attn_path.restype = C.c_int
     lib.nnlib_b200_device_health.argtypes = [C.c_void_p]

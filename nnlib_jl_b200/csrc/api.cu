@@ -226,6 +226,28 @@ int nnlib_b200_attention(const nnlib_b200_attn_params* p, void* workspace, size_
   return nnlib_b200_attn_scores(&q, stream);
 }
 
+static int check_softmax(const nnlib_b200_softmax_params* p, bool backward) {
+  if (!p || p->struct_size != sizeof(nnlib_b200_softmax_params)) return NNLIB_B200_INVALID_ARG;
+  if (p->dtype != NNLIB_B200_F16 && p->dtype != NNLIB_B200_BF16 && p->dtype != NNLIB_B200_F32) return NNLIB_B200_INVALID_ARG;
+  if (p->inner < 0 || p->n < 0 || p->outer < 0) return NNLIB_B200_INVALID_ARG;
+  const bool empty = (p->inner == 0 || p->n == 0 || p->outer == 0);
+  if (!empty && (!p->x || !p->out || (backward && !p->dy))) return NNLIB_B200_INVALID_ARG;
+  if (!empty && p->inner > (1ll << 62) / p->n / p->outer) return NNLIB_B200_INVALID_ARG;
+  return empty ? 1 : NNLIB_B200_OK;   // 1: nothing to do
+}
+
+int nnlib_b200_softmax_fwd(const nnlib_b200_softmax_params* p, void* stream) {
+  const int rc = check_softmax(p, false);
+  if (rc) return rc < 0 ? rc : NNLIB_B200_OK;
+  return finish(softmax_forward(p->dtype, p->log != 0, p->x, p->out, p->inner, p->n, p->outer, (cudaStream_t)stream));
+}
+
+int nnlib_b200_softmax_bwd(const nnlib_b200_softmax_params* p, void* stream) {
+  const int rc = check_softmax(p, true);
+  if (rc) return rc < 0 ? rc : NNLIB_B200_OK;
+  return finish(softmax_backward(p->dtype, p->log != 0, p->dy, p->x, p->out, p->inner, p->n, p->outer, (cudaStream_t)stream));
+}
+
 int nnlib_b200_causal_fill(uint8_t* mask, int64_t L, void* stream) {
   if (L < 0 || (L > 0 && !mask)) return NNLIB_B200_INVALID_ARG;
   return finish(causal_fill(mask, L, (cudaStream_t)stream));

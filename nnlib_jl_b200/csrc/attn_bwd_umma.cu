@@ -676,6 +676,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
           if (!ok) break;
           tc_fence_after();
         }
+        __syncwarp();   // the dbias stores above are per-row branches; tcgen05.st wants the whole warp together
         tmem_st32(lane_base + kColDS + par * 64 + half * 32, pk);
       } else {
 #pragma unroll
@@ -704,6 +705,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
             pk[cc * 16 + e / 2 + 1] = pack2<BF16>(d2, d3);
           }
         }
+        __syncwarp();
         tmem_st32(tDP, pk);     // over the first half of this thread's own dP columns
       }
       tmem_wait_st();

@@ -32,4 +32,10 @@ bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype);
 cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_t st);
 cudaError_t umma_bwd_take_abort(int* out, cudaStream_t st);
 
+// softmax / logsoftmax over one dimension (softmax.cu)
+cudaError_t softmax_forward(int dtype, bool log, const void* x, void* y, long long inner, long long n, long long outer,
+                            cudaStream_t st);
+cudaError_t softmax_backward(int dtype, bool log, const void* dy, const void* y, void* dx, long long inner, long long n,
+                             long long outer, cudaStream_t st);
+
 }  // namespace nb200

@@ -1,0 +1,79 @@
+"""``softmax`` / ``logsoftmax`` over one dimension of a column-major CUDA array
+and their pullbacks (NNlib.jl ``src/softmax.jl:56-79, 118-157``; the CUDA
+methods live in ``ext/NNlibCUDACUDNNExt/softmax.jl``), on the library's own
+kernels.  ``dims`` is 1-based like the reference's; a ``Colon`` (all
+dimensions) is spelled ``dims=None``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .attention import _DTYPES, ArgumentError, _check, _require_dense_cuda, _stream
+from .layout import is_column_major, jl_empty
+
+__all__ = ["softmax", "logsoftmax", "softmax_pullback", "logsoftmax_pullback"]
+
+
+def _split(shape, dims: Optional[int]):
+    """(inner, n, outer) of a reduction over Julia dimension ``dims`` (None: all of them)."""
+    shape = tuple(int(s) for s in shape)
+    if dims is None:
+        return 1, math.prod(shape), 1
+    if not (1 <= dims <= max(len(shape), 1)):
+        # reducing over a trailing singleton dimension, as Julia allows: every element is its own column
+        if dims > len(shape):
+            return math.prod(shape), 1, 1
+        raise ArgumentError(f"dims = {dims} is not a dimension of an array of size {shape}")
+    k = dims - 1
+    return math.prod(shape[:k]), shape[k] if shape else 1, math.prod(shape[k + 1:])
+
+
+def _run(x: torch.Tensor, dy: Optional[torch.Tensor], dims, log: bool) -> torch.Tensor:
+    _require_dense_cuda("x", x)
+    if not is_column_major(x):
+        raise ArgumentError("softmax: the array must be dense column-major")
+    if dy is not None:
+        _require_dense_cuda("dy", dy)
+        if tuple(dy.shape) != tuple(x.shape) or dy.dtype != x.dtype or not is_column_major(dy):
+            raise ArgumentError("softmax pullback: dy must match y in size, eltype and layout")
+    out = jl_empty(tuple(x.shape), x.dtype, x.device)
+    inner, n, outer = _split(x.shape, dims)
+    p = _lib.SoftmaxParams()
+    p.dtype = _DTYPES[x.dtype]
+    p.log = 1 if log else 0
+    p.inner, p.n, p.outer = inner, n, outer
+    p.x = x.data_ptr()
+    p.dy = dy.data_ptr() if dy is not None else None
+    p.out = out.data_ptr()
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        if dy is None:
+            _check(lib.nnlib_b200_softmax_fwd(C.byref(p), _stream()), "softmax_fwd")
+        else:
+            _check(lib.nnlib_b200_softmax_bwd(C.byref(p), _stream()), "softmax_bwd")
+    return out
+
+
+def softmax(x: torch.Tensor, *, dims: Optional[int] = 1) -> torch.Tensor:
+    """``softmax(x; dims)`` (``src/softmax.jl:56``)."""
+    return _run(x, None, dims, log=False)
+
+
+def logsoftmax(x: torch.Tensor, *, dims: Optional[int] = 1) -> torch.Tensor:
+    """``logsoftmax(x; dims)`` (``src/softmax.jl:133``)."""
+    return _run(x, None, dims, log=True)
+
+
+def softmax_pullback(dy: torch.Tensor, y: torch.Tensor, *, dims: Optional[int] = 1) -> torch.Tensor:
+    """``∇softmax(dy, y; dims) = y .* (dy .- sum(dy .* y; dims))`` (``src/softmax.jl:84-101``)."""
+    return _run(y, dy, dims, log=False)
+
+
+def logsoftmax_pullback(dy: torch.Tensor, y: torch.Tensor, *, dims: Optional[int] = 1) -> torch.Tensor:
+    """``∇logsoftmax(dy, y; dims) = dy .- sum(dy; dims) .* exp.(y)`` (``src/softmax.jl:164-190``)."""
+    return _run(y, dy, dims, log=True)
