@@ -2,7 +2,7 @@
 and their pullbacks (NNlib.jl ``src/softmax.jl:56-79, 118-157``; the CUDA
 methods live in ``ext/NNlibCUDACUDNNExt/softmax.jl``), on the library's own
 kernels.  ``dims`` is 1-based like the reference's; a ``Colon`` (all
-dimensions) is spelled ``dims=None``.
+dimensions) is spelled ``dims=None``; a tuple of consecutive dimensions is reduced as one.
 """
 from __future__ import annotations
 
@@ -19,18 +19,20 @@ from .layout import is_column_major, jl_empty
 __all__ = ["softmax", "logsoftmax", "softmax_pullback", "logsoftmax_pullback"]
 
 
-def _split(shape, dims: Optional[int]):
-    """(inner, n, outer) of a reduction over Julia dimension ``dims`` (None: all of them)."""
+def _split(shape, dims):
+    """(inner, n, outer) of a reduction over Julia dimension(s) ``dims``: an int, a tuple of consecutive
+    dimensions (they merge into one extent of the column-major array) or None for all of them."""
     shape = tuple(int(s) for s in shape)
     if dims is None:
         return 1, math.prod(shape), 1
-    if not (1 <= dims <= max(len(shape), 1)):
-        # reducing over a trailing singleton dimension, as Julia allows: every element is its own column
-        if dims > len(shape):
-            return math.prod(shape), 1, 1
+    ds = sorted(set(int(d) for d in dims)) if isinstance(dims, (tuple, list)) else [int(dims)]
+    if not ds or ds[0] < 1:
         raise ArgumentError(f"dims = {dims} is not a dimension of an array of size {shape}")
-    k = dims - 1
-    return math.prod(shape[:k]), shape[k] if shape else 1, math.prod(shape[k + 1:])
+    if ds != list(range(ds[0], ds[-1] + 1)):
+        raise ArgumentError(f"dims = {dims}: only consecutive dimensions can be reduced in one pass")
+    full = shape + (1,) * max(0, ds[-1] - len(shape))      # trailing singleton dimensions, as Julia allows
+    lo, hi = ds[0] - 1, ds[-1]
+    return math.prod(full[:lo]), math.prod(full[lo:hi]), math.prod(full[hi:])
 
 
 def _run(x: torch.Tensor, dy: Optional[torch.Tensor], dims, log: bool) -> torch.Tensor:

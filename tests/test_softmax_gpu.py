@@ -32,7 +32,7 @@ def _as_cm(t, dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape,dims", [
     ((5, 7), 1), ((5, 7), 2), ((300, 33), 1), ((2000, 9), 1), ((4100, 3), 1),      # warp- and block-per-column
-    ((256, 10, 32), 2), ((16, 5, 3, 4), 3), ((16, 5, 3, 4), 4), ((7, 9), None), ((3, 4), 3),
+    ((256, 10, 32), 2), ((16, 5, 3, 4), 3), ((16, 5, 3, 4), 4), ((7, 9), None), ((3, 4), 3), ((6, 5, 4), (1, 2)), ((6, 5, 4), (2, 3)),
 ])
 def test_forward_and_pullbacks_match_the_oracle(dtype, shape, dims):
     rng = np.random.default_rng(5)
@@ -79,6 +79,8 @@ def test_argument_checks():
     x = nb.jl_zeros((4, 5), torch.float32, DEV)
     with pytest.raises(nb.ArgumentError):
         SM.softmax(x, dims=0)
+    with pytest.raises(nb.ArgumentError):
+        SM.softmax(nb.jl_zeros((4, 5, 6), torch.float32, DEV), dims=(1, 3))
     with pytest.raises(nb.ArgumentError):
         SM.softmax_pullback(nb.jl_zeros((4, 6), torch.float32, DEV), x)
     with pytest.raises(TypeError):
