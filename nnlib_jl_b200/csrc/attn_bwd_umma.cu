@@ -464,9 +464,12 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
     float bias_uniform = 0.f;
     const bool bias_per_step = BIAS && (!DKV || a.bias_s[1] != 0);
     const long long bias_step = BIAS ? a.bias_s[DKV ? 1 : 0] : 0;
-    if (BIAS && row_ok) {
+    if (BIAS) {
+      // rows past the end of the sequence read the last row's bias (their P is forced to zero below): every
+      // lane of a warp then takes the same path through the loads
+      const long long row_c = min((long long)row, (long long)(DKV ? a.Lkv : a.Lq) - 1);
       bias_p = reinterpret_cast<const unsigned char*>(a.bias) +
-               ((long long)h * a.bias_s[2] + (long long)b * a.bias_s[3] + (long long)row * a.bias_s[DKV ? 0 : 1]) * bias_esz;
+               ((long long)h * a.bias_s[2] + (long long)b * a.bias_s[3] + row_c * a.bias_s[DKV ? 0 : 1]) * bias_esz;
       if (DKV && a.bias_s[1] == 0) bias_uniform = load_bias(bias_p, 0, a.bias_dtype) * kLog2e;
     }
     // dbias (dq half): plain stores when every score has its own element, atomic adds when a stride of 0
@@ -500,8 +503,9 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       const bool bias16 = bias_per_step && bias_p && bias_esz == 2;
       if (bias16) {
         const unsigned char* bp = bias_p + (long long)c0 * bias_step * 2;
-        load_bias16x64(bp, bias_step, (DKV ? a.Lq : a.Lkv) - c0,
-                       bias_step == 1 && (reinterpret_cast<uintptr_t>(bp) & 15u) == 0, bw);
+        // 16-byte loads only when every row of the warp allows them
+        const bool vec = __all_sync(0xffffffffu, bias_step == 1 && (reinterpret_cast<uintptr_t>(bp) & 15u) == 0);
+        load_bias16x64(bp, bias_step, (DKV ? a.Lq : a.Lkv) - c0, vec, bw);
       }
       // which of this thread's 64 scores survived the forward's dropout (bit e: column c0 + e)
       unsigned int kb[2] = {0xffffffffu, 0xffffffffu};
@@ -636,47 +640,29 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
 
       // dS = P (dP - D), rounded to the element type: the A operand of the dQ / dK product
       uint32_t pk[32];
+      uint32_t dpq[2][32];   // dq half: this thread's 64 dP values (kept for the dbias pass below)
+      // dS of score e of the dq half: P (keep/(1-p) dP - D)
+      auto ds_of = [&](int e) -> float {
+        float gval = __uint_as_float(dpq[e >> 5][e & 31]);
+        if (DROP) gval = ((kb[e >> 5] >> (e & 31)) & 1u) ? gval * a.inv_keep : 0.f;
+        return (gval - dl_row) * NB_SR(e);
+      };
       if (!DKV) {
-        uint32_t dp[2][32];
-        tmem_ld32(tDP, dp[0]);
-        tmem_ld32(tDP + 32, dp[1]);
+        tmem_ld32(tDP, dpq[0]);
+        tmem_ld32(tDP + 32, dpq[1]);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->dp_read);   // the next dP may be issued
 #pragma unroll
-        for (int e = 0; e < 64; e += 2) {
-          float g0 = __uint_as_float(dp[e >> 5][e & 31]), g1 = __uint_as_float(dp[(e + 1) >> 5][(e + 1) & 31]);
-          if (DROP) {
-            g0 = ((kb[e >> 5] >> (e & 31)) & 1u) ? g0 * a.inv_keep : 0.f;
-            g1 = ((kb[(e + 1) >> 5] >> ((e + 1) & 31)) & 1u) ? g1 * a.inv_keep : 0.f;
-          }
-          const float d0 = (g0 - dl_row) * NB_SR(e);
-          const float d1 = (g1 - dl_row) * NB_SR(e + 1);
-          pk[e >> 1] = pack2<BF16>(d0, d1);
-          if (BIAS && dbias_p) {
-            // gradient of the bias = dS (masked and dropped-out positions included: they are zero / scaled)
-            float* o0 = dbias_p + (long long)(c0 + e) * g.dbias_s[0];
-            if (dbias_exclusive) {
-              if (g.dbias_s[0] == 1 && c0 + e + 1 < a.Lkv && (reinterpret_cast<uintptr_t>(o0) & 7u) == 0) {
-                *reinterpret_cast<float2*>(o0) = make_float2(d0, d1);
-              } else {
-                if (c0 + e < a.Lkv) *o0 = d0;
-                if (c0 + e + 1 < a.Lkv) *(o0 + g.dbias_s[0]) = d1;
-              }
-            } else {
-              if (c0 + e < a.Lkv) atomicAdd(o0, d0);
-              if (c0 + e + 1 < a.Lkv) atomicAdd(o0 + g.dbias_s[0], d1);
-            }
-          }
-        }
+        for (int e = 0; e < 64; e += 2) pk[e >> 1] = pack2<BF16>(ds_of(e), ds_of(e + 1));
         if (it >= 2) {   // the products of step it-2 have finished reading this dS buffer
           ok = mbar_wait(&bars->a_empty[(it - 2) % C::kStagesA], ((it - 2) / C::kStagesA) & 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
         }
-        __syncwarp();   // the dbias stores above are per-row branches; tcgen05.st wants the whole warp together
+        __syncwarp();
         tmem_st32(lane_base + kColDS + par * 64 + half * 32, pk);
       } else {
 #pragma unroll
@@ -713,6 +699,29 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_ready);
       if (threadIdx.x == 0) BW_TRACE(0, it, 5);
+
+      if (BIAS && !DKV && dbias_p) {
+        // gradient of the bias = dS in fp32 (masked and dropped-out positions included: they are zero /
+        // scaled).  Written after dS has been handed to the tensor core: the stores are per-row branches
+        // and off the products' critical path.
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) {
+          const float d0 = ds_of(e), d1 = ds_of(e + 1);
+          float* o0 = dbias_p + (long long)(c0 + e) * g.dbias_s[0];
+          if (dbias_exclusive) {
+            if (g.dbias_s[0] == 1 && c0 + e + 1 < a.Lkv && (reinterpret_cast<uintptr_t>(o0) & 7u) == 0) {
+              *reinterpret_cast<float2*>(o0) = make_float2(d0, d1);
+            } else {
+              if (c0 + e < a.Lkv) *o0 = d0;
+              if (c0 + e + 1 < a.Lkv) *(o0 + g.dbias_s[0]) = d1;
+            }
+          } else {
+            if (c0 + e < a.Lkv) atomicAdd(o0, d0);
+            if (c0 + e + 1 < a.Lkv) atomicAdd(o0 + g.dbias_s[0], d1);
+          }
+        }
+      }
+      if (BIAS && !DKV) __syncwarp();   // (outside the per-row branch: every lane takes part)
 
       if (DKV) {
         // P^T as the K-major A operand of dV += P^T dX: row r, 16-byte pieces in 128-byte-swizzled order,
@@ -763,6 +772,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         if (!DKV && (c & 1) != half) continue;
         uint32_t o[32];
         if (n > 0) {
+          __syncwarp();   // the stores of the previous chunk are per-row branches
           tmem_ld32(lane_base + col + c * 32, o);
           tmem_wait_ld();
         } else {

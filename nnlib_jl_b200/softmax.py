@@ -36,6 +36,9 @@ def _split(shape, dims):
 
 
 def _run(x: torch.Tensor, dy: Optional[torch.Tensor], dims, log: bool) -> torch.Tensor:
+    if isinstance(x, torch.Tensor) and x.is_cuda and x.numel() == 0:
+        _split(x.shape, dims)                       # still validates dims
+        return jl_empty(tuple(x.shape), x.dtype, x.device)
     _require_dense_cuda("x", x)
     if not is_column_major(x):
         raise ArgumentError("softmax: the array must be dense column-major")

@@ -21,8 +21,19 @@ def _axis(x, dims):
     return dims - 1
 
 
-def softmax(x, dims=1):
+def _pad(x, dims):
+    """Julia lets ``dims`` name trailing singleton dimensions the array does not have: add them."""
     x = np.asarray(x)
+    top = max(dims) if isinstance(dims, (tuple, list)) else (dims or 0)
+    return x.reshape(x.shape + (1,) * max(0, top - x.ndim)), x.shape
+
+
+def softmax(x, dims=1):
+    x, shape = _pad(x, dims)
+    return _softmax(x, dims).reshape(shape)
+
+
+def _softmax(x, dims):
     x = x.astype(np.float64 if x.dtype == np.float64 else np.float32)
     ax = _axis(x, dims)
     with np.errstate(invalid="ignore", over="ignore"):
@@ -33,7 +44,11 @@ def softmax(x, dims=1):
 
 
 def logsoftmax(x, dims=1):
-    x = np.asarray(x)
+    x, shape = _pad(x, dims)
+    return _logsoftmax(x, dims).reshape(shape)
+
+
+def _logsoftmax(x, dims):
     x = x.astype(np.float64 if x.dtype == np.float64 else np.float32)
     ax = _axis(x, dims)
     with np.errstate(invalid="ignore", over="ignore", divide="ignore"):
@@ -43,13 +58,13 @@ def logsoftmax(x, dims=1):
 
 
 def softmax_pullback(dy, y, dims=1):
-    dy, y = np.asarray(dy), np.asarray(y)
+    (y, shape), (dy, _) = _pad(y, dims), _pad(dy, dims)
     ax = _axis(y, dims)
     dx = dy * y
-    return dx - y * np.sum(dx, axis=ax, keepdims=True)
+    return (dx - y * np.sum(dx, axis=ax, keepdims=True)).reshape(shape)
 
 
 def logsoftmax_pullback(dy, y, dims=1):
-    dy, y = np.asarray(dy), np.asarray(y)
+    (y, shape), (dy, _) = _pad(y, dims), _pad(dy, dims)
     ax = _axis(y, dims)
-    return dy - np.sum(dy, axis=ax, keepdims=True) * np.exp(y)
+    return (dy - np.sum(dy, axis=ax, keepdims=True) * np.exp(y)).reshape(shape)
