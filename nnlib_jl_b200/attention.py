@@ -360,6 +360,24 @@ def _fused(q, k, v, bias, mask, nheads, dropout):
     return x, LazyAttnScores(pr, (pr.Lkv, pr.Lq, pr.H, pr.B))
 
 
+def _fused_into(q, k, v, mask, nheads, x_out, lse_out):
+    """The fused call writing into caller-owned buffers (no allocation): ``x_out`` is a column-major
+    ``(Ev, Lq, B)`` array of the inputs' element type, ``lse_out`` a Float32 array of ``Lq*H*B`` elements."""
+    pr = _Problem(q, k, v, None, mask, nheads, None, need_v=True)
+    if tuple(x_out.shape) != (pr.Ev, pr.Lq, pr.B) or x_out.dtype != pr.dtype or not is_column_major(x_out):
+        raise ArgumentError("x_out must be a dense column-major (Ev, Lq, B) array of the inputs' element type")
+    if lse_out.dtype != torch.float32 or lse_out.numel() < pr.Lq * pr.H * pr.B or not lse_out.is_contiguous():
+        raise ArgumentError("lse_out must be a contiguous Float32 array of at least Lq*H*B elements")
+    pr.x = x_out
+    pr.p.x = x_out.data_ptr()
+    pr.lse = lse_out
+    pr.p.lse = lse_out.data_ptr()
+    if pr.Lq > 0 and pr.B > 0:
+        with torch.cuda.device(pr.dev):
+            _check(_lib.load().nnlib_b200_attn_fwd(C.byref(pr.p), _stream()), "attn_fwd")
+    return x_out
+
+
 def _fused_with_origin(q, k, v, bias, mask, nheads, dropout, rng_origin):
     """The fused call for a shard of a larger problem (see ``shard.py``):
     ``rng_origin`` places the shard's heads and batches in the whole problem so

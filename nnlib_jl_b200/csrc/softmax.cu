@@ -79,110 +79,206 @@ __device__ __forceinline__ float fwd_value(const ColStat& c, float x, float log_
 // 16-byte packets: V = 16 / sizeof(T) consecutive elements of a column
 template <typename T> struct Pack { static constexpr int V = 16 / sizeof(T); };
 template <typename T>
-__device__ __forceinline__ void load_pack(const T* p, float (&f)[Pack<T>::V]) {
-  const uint4 q = __ldg(reinterpret_cast<const uint4*>(p));
+__device__ __forceinline__ void unpack(const uint4& q, float (&f)[Pack<T>::V]) {
   const T* e = reinterpret_cast<const T*>(&q);
 #pragma unroll
   for (int u = 0; u < Pack<T>::V; ++u) f[u] = Elem<T>::to_f(e[u]);
 }
 template <typename T>
-__device__ __forceinline__ void store_pack(T* p, const float (&f)[Pack<T>::V]) {
+__device__ __forceinline__ uint4 repack(const float (&f)[Pack<T>::V]) {
   uint4 q;
   T* e = reinterpret_cast<T*>(&q);
 #pragma unroll
   for (int u = 0; u < Pack<T>::V; ++u) e[u] = Elem<T>::from_f(f[u]);
-  *reinterpret_cast<uint4*>(p) = q;
+  return q;
+}
+template <typename T>
+__device__ __forceinline__ uint4 load_raw(const T* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+template <typename T>
+__device__ __forceinline__ void load_pack(const T* p, float (&f)[Pack<T>::V]) { unpack<T>(load_raw<T>(p), f); }
+template <typename T>
+__device__ __forceinline__ void store_pack(T* p, const float (&f)[Pack<T>::V]) {
+  *reinterpret_cast<uint4*>(p) = repack<T>(f);
+}
+
+// branch-free update of the running statistics with one packet of V values: one rescaling exponential
+// per packet instead of a data-dependent branch per value
+template <int V>
+__device__ __forceinline__ void stat_add_pack(ColStat& c, const float (&f)[V]) {
+  float pm = f_ninf();
+  float xv[V];
+#pragma unroll
+  for (int u = 0; u < V; ++u) {
+    const float x = f[u];
+    c.nan |= (x != x) ? 1 : 0;
+    const bool is_inf = (x == f_inf());
+    c.n_inf += is_inf ? 1 : 0;
+    xv[u] = (is_inf || x != x) ? f_ninf() : x;      // +Inf and NaN are accounted for by the flags
+    pm = fmaxf(pm, xv[u]);
+  }
+  const float m_new = fmaxf(c.m, pm);
+  const float m_safe = (m_new == f_ninf()) ? 0.f : m_new;
+  float s = c.s * __expf(c.m - m_safe);              // c.m = -Inf: exp(-Inf) = 0
+#pragma unroll
+  for (int u = 0; u < V; ++u) s += __expf(xv[u] - m_safe);
+  c.s = s;
+  c.m = m_new;
+}
+// (the maximum above ignores +Inf entries; a column that has some is marked here)
+__device__ __forceinline__ void stat_finish(ColStat& c) {
+  if (c.n_inf > 0) c.m = f_inf();
+}
+// output values of a packet given the finished statistics
+template <int MODE, int V>
+__device__ __forceinline__ void fwd_pack(const ColStat& c, float inv_s, float log_s, float (&f)[V]) {
+  const bool special = c.nan || c.m == f_ninf() || c.m == f_inf();
+#pragma unroll
+  for (int u = 0; u < V; ++u) {
+    if (special) f[u] = fwd_value<MODE>(c, f[u], log_s);
+    else f[u] = (MODE == SM_FWD) ? __expf(f[u] - c.m) * inv_s : f[u] - c.m - log_s;
+  }
 }
 
 // ---- reduction dimension contiguous (inner == 1): G threads per column ----------------------------
-// VECT: columns are whole 16-byte packets (n a multiple of the packet, arrays 16-byte aligned)
-template <typename T, int MODE, int G, bool VECT>
-__global__ void __launch_bounds__(256) softmax_cols_kernel(const T* __restrict__ x, const T* __restrict__ dy,
-                                                           T* __restrict__ out, long long n, long long cols) {
-  constexpr int kPerBlock = 256 / G;
+// VECT: columns are whole 16-byte packets (n a multiple of the packet, arrays 16-byte aligned).
+// KP > 0 (with VECT): a thread's packets (at most KP, as raw 16-byte words) stay in registers between
+// the two passes, so the column is read from memory once.
+template <typename T, int MODE, int G, bool VECT, int KP>
+__global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                                                            T* __restrict__ out, long long n, long long cols) {
+  constexpr int kBlock = G > 256 ? G : 256;
+  constexpr int kPerBlock = kBlock / G;
+  constexpr int kWarps = kBlock / 32;
   constexpr int V = Pack<T>::V;
+  constexpr bool FWD = (MODE == SM_FWD || MODE == LSM_FWD);
   const long long np = n / V;   // packets per column (VECT)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = threadIdx.x / G, t = threadIdx.x % G;
-  __shared__ ColStat sh_stat[8];
-  __shared__ float sh_sum[8];
-  for (long long col = (long long)blockIdx.x * kPerBlock + g; col < cols || G == 256; col += (long long)gridDim.x * kPerBlock) {
-    if (G == 256 && col >= cols) break;
+  __shared__ ColStat sh_stat[32];
+  __shared__ float sh_sum[32];
+  for (long long col = (long long)blockIdx.x * kPerBlock + g; col < cols || G >= 256; col += (long long)gridDim.x * kPerBlock) {
+    if (G >= 256 && col >= cols) break;
     const T* xc = x + col * n;
+    const T* dc = FWD ? xc : dy + col * n;
     T* oc = out + col * n;
-    if (MODE == SM_FWD || MODE == LSM_FWD) {
-      ColStat c = stat_init();
-      if (VECT) {
-        for (long long jp = t; jp < np; jp += G) {
-          float f[V];
-          load_pack<T>(xc + jp * V, f);
+    constexpr bool CACHE = KP > 0;
+    uint4 cx[CACHE ? KP : 1];                 // forward: x; pullbacks: y
+    uint4 cd[(CACHE && !FWD) ? KP : 1];       // pullbacks: dy
+    ColStat c = stat_init();
+    float acc = 0.f;
+    // ---- pass 1: column statistics (forward) or the column sum (pullbacks)
+    if (VECT && CACHE) {
 #pragma unroll
-          for (int u = 0; u < V; ++u) stat_add(c, f[u]);
+      for (int k = 0; k < (CACHE ? KP : 1); ++k) {
+        const long long jp = t + (long long)k * G;
+        if (jp < np) {
+          cx[k] = load_raw<T>(xc + jp * V);
+          if (!FWD) cd[k] = load_raw<T>(dc + jp * V);
         }
-      } else {
-        for (long long j = t; j < n; j += G) stat_add(c, Elem<T>::to_f(xc[j]));
       }
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) c = stat_merge(c, stat_shfl_xor(c, off));
-      if (G == 256) {
-        if (lane == 0) sh_stat[warp] = c;
-        __syncthreads();
-        c = sh_stat[0];
-#pragma unroll
-        for (int w = 1; w < 8; ++w) c = stat_merge(c, sh_stat[w]);
-        __syncthreads();
-      }
-      const float log_s = (MODE == LSM_FWD) ? __logf(c.m == f_inf() ? (float)c.n_inf : c.s) : 0.f;
-      if (VECT) {
-        for (long long jp = t; jp < np; jp += G) {
+      for (int k = 0; k < (CACHE ? KP : 1); ++k) {
+        const long long jp = t + (long long)k * G;
+        if (jp < np) {
           float f[V];
-          load_pack<T>(xc + jp * V, f);
+          unpack<T>(cx[k], f);
+          if (FWD) {
+            stat_add_pack<V>(c, f);
+          } else {
+            float d[V];
+            unpack<T>(cd[k], d);
 #pragma unroll
-          for (int u = 0; u < V; ++u) f[u] = fwd_value<MODE>(c, f[u], log_s);
-          store_pack<T>(oc + jp * V, f);
+            for (int u = 0; u < V; ++u) acc += (MODE == SM_BWD) ? d[u] * f[u] : d[u];
+          }
         }
-      } else {
-        for (long long j = t; j < n; j += G) oc[j] = Elem<T>::from_f(fwd_value<MODE>(c, Elem<T>::to_f(xc[j]), log_s));
+      }
+    } else if (VECT) {
+      for (long long jp = t; jp < np; jp += G) {
+        float f[V], d[V];
+        load_pack<T>(xc + jp * V, f);
+        if (FWD) {
+          stat_add_pack<V>(c, f);
+        } else {
+          load_pack<T>(dc + jp * V, d);
+#pragma unroll
+          for (int u = 0; u < V; ++u) acc += (MODE == SM_BWD) ? d[u] * f[u] : d[u];
+        }
       }
     } else {
-      // pullbacks: x holds y = softmax(x) or logsoftmax(x)
-      const T* dc = dy + col * n;
-      float acc = 0.f;
-      if (VECT) {
-        for (long long jp = t; jp < np; jp += G) {
-          float d[V], y[V];
-          load_pack<T>(dc + jp * V, d);
-          if (MODE == SM_BWD) load_pack<T>(xc + jp * V, y);
-#pragma unroll
-          for (int u = 0; u < V; ++u) acc += (MODE == SM_BWD) ? d[u] * y[u] : d[u];
-        }
-      } else {
-        for (long long j = t; j < n; j += G) {
+      for (long long j = t; j < n; j += G) {
+        if (FWD) {
+          stat_add(c, Elem<T>::to_f(xc[j]));
+        } else {
           const float d = Elem<T>::to_f(dc[j]);
           acc += (MODE == SM_BWD) ? d * Elem<T>::to_f(xc[j]) : d;
         }
       }
+    }
+    // ---- reduce over the G threads of the column
+    if (FWD) {
+      stat_finish(c);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) c = stat_merge(c, stat_shfl_xor(c, off));
+      if (G >= 256) {
+        if (lane == 0) sh_stat[warp] = c;
+        __syncthreads();
+        c = sh_stat[0];
+        for (int w = 1; w < kWarps; ++w) c = stat_merge(c, sh_stat[w]);
+        __syncthreads();
+      }
+    } else {
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-      if (G == 256) {
+      if (G >= 256) {
         if (lane == 0) sh_sum[warp] = acc;
         __syncthreads();
         acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) acc += sh_sum[w];
+        for (int w = 0; w < kWarps; ++w) acc += sh_sum[w];
         __syncthreads();
       }
-      if (VECT) {
-        for (long long jp = t; jp < np; jp += G) {
-          float d[V], y[V];
-          load_pack<T>(dc + jp * V, d);
-          load_pack<T>(xc + jp * V, y);
+    }
+    const float sum_or_cnt = (c.m == f_inf()) ? (float)c.n_inf : c.s;
+    const float log_s = (MODE == LSM_FWD) ? __logf(sum_or_cnt) : 0.f;
+    const float inv_s = (MODE == SM_FWD) ? 1.f / c.s : 0.f;
+    // ---- pass 2: write
+    if (VECT && CACHE) {
 #pragma unroll
-          for (int u = 0; u < V; ++u) d[u] = (MODE == SM_BWD) ? y[u] * (d[u] - acc) : d[u] - __expf(y[u]) * acc;
+      for (int k = 0; k < (CACHE ? KP : 1); ++k) {
+        const long long jp = t + (long long)k * G;
+        if (jp < np) {
+          float f[V];
+          unpack<T>(cx[k], f);
+          if (FWD) {
+            fwd_pack<MODE, V>(c, inv_s, log_s, f);
+            store_pack<T>(oc + jp * V, f);
+          } else {
+            float d[V];
+            unpack<T>(cd[k], d);
+#pragma unroll
+            for (int u = 0; u < V; ++u) d[u] = (MODE == SM_BWD) ? f[u] * (d[u] - acc) : d[u] - __expf(f[u]) * acc;
+            store_pack<T>(oc + jp * V, d);
+          }
+        }
+      }
+    } else if (VECT) {
+      for (long long jp = t; jp < np; jp += G) {
+        float f[V], d[V];
+        load_pack<T>(xc + jp * V, f);
+        if (FWD) {
+          fwd_pack<MODE, V>(c, inv_s, log_s, f);
+          store_pack<T>(oc + jp * V, f);
+        } else {
+          load_pack<T>(dc + jp * V, d);
+#pragma unroll
+          for (int u = 0; u < V; ++u) d[u] = (MODE == SM_BWD) ? f[u] * (d[u] - acc) : d[u] - __expf(f[u]) * acc;
           store_pack<T>(oc + jp * V, d);
         }
-      } else {
-        for (long long j = t; j < n; j += G) {
+      }
+    } else {
+      for (long long j = t; j < n; j += G) {
+        if (FWD) {
+          oc[j] = Elem<T>::from_f(fwd_value<MODE>(c, Elem<T>::to_f(xc[j]), log_s));
+        } else {
           const float d = Elem<T>::to_f(dc[j]), y = Elem<T>::to_f(xc[j]);
           oc[j] = Elem<T>::from_f((MODE == SM_BWD) ? y * (d - acc) : d - __expf(y) * acc);
         }
@@ -229,17 +325,32 @@ cudaError_t launch_softmax(const void* x, const void* dy, void* out, long long i
   if (inner == 1) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool vect = (n % Pack<T>::V) == 0 && al16(x) && al16(out) && (dy == nullptr || al16(dy));
-    // a whole block per long column, a warp per short one
-    if (n > 2048) {
-      const long long blocks = outer < 148ll * 16 ? outer : 148ll * 16;
-      if (vect) softmax_cols_kernel<T, MODE, 256, true><<<(unsigned)blocks, 256, 0, st>>>(xp, dp, op, n, outer);
-      else      softmax_cols_kernel<T, MODE, 256, false><<<(unsigned)blocks, 256, 0, st>>>(xp, dp, op, n, outer);
+    const long long np = n / Pack<T>::V;
+    const long long cap = 148ll * 16;
+    // a warp per short column, a 256- or 1024-thread block per long one; the column stays in registers
+    // between the passes whenever a thread's share is small enough (1024-thread blocks have 64 registers
+    // per thread: 8 raw packets forward, 4 + 4 in the pullbacks)
+    constexpr bool FWD = (MODE == SM_FWD || MODE == LSM_FWD);
+    constexpr int kBig = FWD ? 8 : 4;
+#define NB_SM_LAUNCH(GG, VV, KK)                                                                       \
+  do {                                                                                                 \
+    constexpr int kBlock = (GG) > 256 ? (GG) : 256;                                                    \
+    const long long need = (outer + (kBlock / (GG)) - 1) / (kBlock / (GG));                            \
+    const long long blocks = need < cap ? need : cap;                                                  \
+    softmax_cols_kernel<T, MODE, GG, VV, KK><<<(unsigned)blocks, kBlock, 0, st>>>(xp, dp, op, n, outer); \
+  } while (0)
+    if (!vect) {
+      if (n > 2048) NB_SM_LAUNCH(256, false, 0); else NB_SM_LAUNCH(32, false, 0);
+    } else if (np <= 32ll * 8) {
+      NB_SM_LAUNCH(32, true, 8);
+    } else if (np <= 256ll * 8) {
+      NB_SM_LAUNCH(256, true, 8);
+    } else if (np <= 1024ll * kBig) {
+      NB_SM_LAUNCH(1024, true, kBig);
     } else {
-      const long long need = (outer + 7) / 8;
-      const long long blocks = need < 148ll * 16 ? need : 148ll * 16;
-      if (vect) softmax_cols_kernel<T, MODE, 32, true><<<(unsigned)blocks, 256, 0, st>>>(xp, dp, op, n, outer);
-      else      softmax_cols_kernel<T, MODE, 32, false><<<(unsigned)blocks, 256, 0, st>>>(xp, dp, op, n, outer);
+      NB_SM_LAUNCH(1024, true, 0);
     }
+#undef NB_SM_LAUNCH
   } else {
     const long long need = (inner * outer + 255) / 256;
     const long long blocks = need < 148ll * 32 ? need : 148ll * 32;

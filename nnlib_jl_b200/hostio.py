@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-from .attention import ArgumentError, CausalMask, dot_product_attention
+from .attention import ArgumentError, CausalMask, _fused_into
 from .layout import jl_empty
 
 __all__ = ["HostPipelinedAttention"]
@@ -25,7 +25,7 @@ class HostPipelinedAttention:
 
     Host arrays are torch tensors of shape ``(B, L, E)`` (row-major: the memory
     of Julia's column-major ``(E, L, B)``).  ``mask`` is ``None`` or
-    ``CausalMask()``.  Device staging buffers for two chunks are allocated once
+    ``CausalMask()``.  Device staging buffers for two chunks (inputs, output, log-sum-exp) are allocated once
     in the constructor; :meth:`__call__` enqueues the whole pipeline and returns
     after the last result byte has been ordered on ``out_stream`` (call
     ``synchronize()`` or wait on :attr:`done` to read ``hx``).
@@ -46,7 +46,8 @@ class HostPipelinedAttention:
         self.dq = [jl_empty((E, Lq, c), dtype, self.dev) for _ in range(2)]
         self.dk = [jl_empty((E, Lkv, c), dtype, self.dev) for _ in range(2)]
         self.dv = [jl_empty((Ev, Lkv, c), dtype, self.dev) for _ in range(2)]
-        self.dx = [None, None]
+        self.dx = [jl_empty((Ev, Lq, c), dtype, self.dev) for _ in range(2)]
+        self.lse = [torch.empty(Lq * self.nheads * c, dtype=torch.float32, device=self.dev) for _ in range(2)]
         with torch.cuda.device(self.dev):
             self.in_stream = torch.cuda.Stream()
             self.out_stream = torch.cuda.Stream()
@@ -93,12 +94,10 @@ class HostPipelinedAttention:
                 comp.wait_event(self.loaded[s])
                 if i >= 2:
                     comp.wait_event(self.drained[s])                  # x of chunk i-2 has been copied out
-                q, k, v = self.dq[s], self.dk[s], self.dv[s]
+                q, k, v, x = self.dq[s], self.dk[s], self.dv[s], self.dx[s]
                 if w != c:
-                    q, k, v = q[:, :, :w], k[:, :, :w], v[:, :, :w]
-                x, _ = dot_product_attention(q, k, v, mask=self.mask, nheads=self.nheads)
-                self.dx[s] = x                                        # keep alive until copied
-                x.record_stream(self.out_stream)                      # the allocator must not reuse it before the copy
+                    q, k, v, x = q[:, :, :w], k[:, :, :w], v[:, :, :w], x[:, :, :w]
+                _fused_into(q, k, v, self.mask, self.nheads, x, self.lse[s])
                 self.consumed[s].record(comp)
                 self.computed[s].record(comp)
                 # ---- device -> host (copy engine 2)
