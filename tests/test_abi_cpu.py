@@ -114,6 +114,29 @@ def test_backward_argument_checks_and_path_without_a_gpu(lib):
     assert lib.nnlib_b200_launch_count() == before
 
 
+def test_softmax_argument_checks_without_a_gpu(lib):
+    def sp(**kw):
+        p = _lib.SoftmaxParams()
+        p.dtype = _lib.F32
+        p.inner, p.n, p.outer = 1, 8, 4
+        p.x = p.out = p.dy = 0x4000
+        for k, v in kw.items():
+            setattr(p, k, v)
+        return p
+    for fn in (lib.nnlib_b200_softmax_fwd, lib.nnlib_b200_softmax_bwd):
+        assert fn(None, None) == _lib.INVALID_ARG
+        assert fn(C.byref(sp(struct_size=4)), None) == _lib.INVALID_ARG
+        assert fn(C.byref(sp(dtype=5)), None) == _lib.INVALID_ARG
+        assert fn(C.byref(sp(n=-1)), None) == _lib.INVALID_ARG
+        assert fn(C.byref(sp(x=None)), None) == _lib.INVALID_ARG
+        assert fn(C.byref(sp(out=None)), None) == _lib.INVALID_ARG
+        assert fn(C.byref(sp(inner=2 ** 40, n=2 ** 40)), None) == _lib.INVALID_ARG      # size overflow
+    assert lib.nnlib_b200_softmax_bwd(C.byref(sp(dy=None)), None) == _lib.INVALID_ARG
+    before = lib.nnlib_b200_launch_count()
+    assert lib.nnlib_b200_softmax_fwd(C.byref(sp(n=0, x=None, out=None)), None) == _lib.OK    # empty: nothing to do
+    assert lib.nnlib_b200_launch_count() == before
+
+
 def test_empty_problems_enqueue_nothing(lib):
     before = lib.nnlib_b200_launch_count()
     assert lib.nnlib_b200_attn_fwd(C.byref(_params(Lq=0)), None) == _lib.OK
