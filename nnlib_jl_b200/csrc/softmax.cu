@@ -92,6 +92,23 @@ __device__ __forceinline__ uint4 repack(const float (&f)[Pack<T>::V]) {
   for (int u = 0; u < Pack<T>::V; ++u) e[u] = Elem<T>::from_f(f[u]);
   return q;
 }
+// 16-bit types: two values per conversion instruction
+template <>
+__device__ __forceinline__ uint4 repack<__nv_bfloat16>(const float (&f)[8]) {
+  uint4 q;
+  __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) e[u] = __floats2bfloat162_rn(f[2 * u], f[2 * u + 1]);
+  return q;
+}
+template <>
+__device__ __forceinline__ uint4 repack<__half>(const float (&f)[8]) {
+  uint4 q;
+  __half2* e = reinterpret_cast<__half2*>(&q);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) e[u] = __floats2half2_rn(f[2 * u], f[2 * u + 1]);
+  return q;
+}
 template <typename T>
 __device__ __forceinline__ uint4 load_raw(const T* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 template <typename T>
@@ -123,6 +140,18 @@ __device__ __forceinline__ void stat_add_pack(ColStat& c, const float (&f)[V]) {
   for (int u = 0; u < V; ++u) s += __expf(xv[u] - m_safe);
   c.s = s;
   c.m = m_new;
+}
+// first sweep over a register-cached column: maximum and flags only, no exponentials
+template <int V>
+__device__ __forceinline__ void stat_max_pack(ColStat& c, const float (&f)[V]) {
+#pragma unroll
+  for (int u = 0; u < V; ++u) {
+    const float x = f[u];
+    c.nan |= (x != x) ? 1 : 0;
+    const bool is_inf = (x == f_inf());
+    c.n_inf += is_inf ? 1 : 0;
+    c.m = fmaxf(c.m, (is_inf || x != x) ? f_ninf() : x);
+  }
 }
 // (the maximum above ignores +Inf entries; a column that has some is marked here)
 __device__ __forceinline__ void stat_finish(ColStat& c) {
@@ -183,7 +212,7 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
           float f[V];
           unpack<T>(cx[k], f);
           if (FWD) {
-            stat_add_pack<V>(c, f);
+            stat_max_pack<V>(c, f);      // the exponentials follow once the column maximum is known
           } else {
             float d[V];
             unpack<T>(cd[k], d);
@@ -215,6 +244,18 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
       }
     }
     // ---- reduce over the G threads of the column
+    auto group_sum = [&](float v) -> float {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if (G >= 256) {
+        if (lane == 0) sh_sum[warp] = v;
+        __syncthreads();
+        v = 0.f;
+        for (int w = 0; w < kWarps; ++w) v += sh_sum[w];
+        __syncthreads();
+      }
+      return v;
+    };
     if (FWD) {
       stat_finish(c);
 #pragma unroll
@@ -226,16 +267,31 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
         for (int w = 1; w < kWarps; ++w) c = stat_merge(c, sh_stat[w]);
         __syncthreads();
       }
-    } else {
+      if (VECT && CACHE) {
+        // second sweep over the registers: one exponential per element, summed in fp32; softmax keeps the
+        // exponentials (in the element type) in place of x for the write sweep
+        const bool special = c.nan || c.m == f_ninf() || c.m == f_inf();
+        float part = 0.f;
+        if (!special) {
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-      if (G >= 256) {
-        if (lane == 0) sh_sum[warp] = acc;
-        __syncthreads();
-        acc = 0.f;
-        for (int w = 0; w < kWarps; ++w) acc += sh_sum[w];
-        __syncthreads();
+          for (int k = 0; k < (CACHE ? KP : 1); ++k) {
+            const long long jp = t + (long long)k * G;
+            if (jp < np) {
+              float f[V];
+              unpack<T>(cx[k], f);
+#pragma unroll
+              for (int u = 0; u < V; ++u) {
+                f[u] = __expf(f[u] - c.m);
+                part += f[u];
+              }
+              if (MODE == SM_FWD) cx[k] = repack<T>(f);
+            }
+          }
+        }
+        c.s = group_sum(part);
       }
+    } else {
+      acc = group_sum(acc);
     }
     const float sum_or_cnt = (c.m == f_inf()) ? (float)c.n_inf : c.s;
     const float log_s = (MODE == LSM_FWD) ? __logf(sum_or_cnt) : 0.f;
@@ -249,7 +305,13 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
           float f[V];
           unpack<T>(cx[k], f);
           if (FWD) {
-            fwd_pack<MODE, V>(c, inv_s, log_s, f);
+            const bool special = c.nan || c.m == f_ninf() || c.m == f_inf();
+            if (MODE == SM_FWD && !special) {
+#pragma unroll
+              for (int u = 0; u < V; ++u) f[u] *= inv_s;      // f holds exp(x - max) from the second sweep
+            } else {
+              fwd_pack<MODE, V>(c, inv_s, log_s, f);
+            }
             store_pack<T>(oc + jp * V, f);
           } else {
             float d[V];
@@ -329,9 +391,9 @@ cudaError_t launch_softmax(const void* x, const void* dy, void* out, long long i
     const long long cap = 148ll * 16;
     // a warp per short column, a 256- or 1024-thread block per long one; the column stays in registers
     // between the passes whenever a thread's share is small enough (1024-thread blocks have 64 registers
-    // per thread: 8 raw packets forward, 4 + 4 in the pullbacks)
+    // per thread: 8 raw packets for Float32 forward, 4 otherwise, 4 + 4 in the pullbacks)
     constexpr bool FWD = (MODE == SM_FWD || MODE == LSM_FWD);
-    constexpr int kBig = FWD ? 8 : 4;
+    constexpr int kBig = (FWD && sizeof(T) == 4) ? 8 : 4;
 #define NB_SM_LAUNCH(GG, VV, KK)                                                                       \
   do {                                                                                                 \
     constexpr int kBlock = (GG) > 256 ? (GG) : 256;                                                    \
