@@ -256,7 +256,27 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
       }
       return v;
     };
-    if (FWD) {
+    if (FWD && VECT && CACHE) {
+      // register-cached column: only the maximum and the flags exist so far (no exponentials to rescale)
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        c.m = fmaxf(c.m, __shfl_xor_sync(0xffffffffu, c.m, off));
+        c.n_inf += __shfl_xor_sync(0xffffffffu, c.n_inf, off);
+        c.nan |= __shfl_xor_sync(0xffffffffu, c.nan, off);
+      }
+      if (G >= 256) {
+        if (lane == 0) sh_stat[warp] = c;
+        __syncthreads();
+        c = sh_stat[0];
+        for (int w = 1; w < kWarps; ++w) {
+          c.m = fmaxf(c.m, sh_stat[w].m);
+          c.n_inf += sh_stat[w].n_inf;
+          c.nan |= sh_stat[w].nan;
+        }
+        __syncthreads();
+      }
+      stat_finish(c);
+    } else if (FWD) {
       stat_finish(c);
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) c = stat_merge(c, stat_shfl_xor(c, off));
@@ -267,6 +287,8 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
         for (int w = 1; w < kWarps; ++w) c = stat_merge(c, sh_stat[w]);
         __syncthreads();
       }
+    }
+    if (FWD) {
       if (VECT && CACHE) {
         // second sweep over the registers: one exponential per element, summed in fp32; softmax keeps the
         // exponentials (in the element type) in place of x for the write sweep
