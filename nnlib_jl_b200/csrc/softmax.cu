@@ -141,17 +141,12 @@ __device__ __forceinline__ void stat_add_pack(ColStat& c, const float (&f)[V]) {
   c.s = s;
   c.m = m_new;
 }
-// first sweep over a register-cached column: maximum and flags only, no exponentials
-template <int V>
-__device__ __forceinline__ void stat_max_pack(ColStat& c, const float (&f)[V]) {
-#pragma unroll
-  for (int u = 0; u < V; ++u) {
-    const float x = f[u];
-    c.nan |= (x != x) ? 1 : 0;
-    const bool is_inf = (x == f_inf());
-    c.n_inf += is_inf ? 1 : 0;
-    c.m = fmaxf(c.m, (is_inf || x != x) ? f_ninf() : x);
-  }
+// first sweep over a register-cached column: a NaN-propagating maximum is all the common case needs
+// (one instruction per value); +Inf entries are counted only when the maximum turns out to be +Inf
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
 }
 // (the maximum above ignores +Inf entries; a column that has some is marked here)
 __device__ __forceinline__ void stat_finish(ColStat& c) {
@@ -212,7 +207,8 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
           float f[V];
           unpack<T>(cx[k], f);
           if (FWD) {
-            stat_max_pack<V>(c, f);      // the exponentials follow once the column maximum is known
+#pragma unroll
+            for (int u = 0; u < V; ++u) c.m = max_nan(c.m, f[u]);   // the exponentials follow once the maximum is known
           } else {
             float d[V];
             unpack<T>(cd[k], d);
@@ -257,25 +253,33 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
       return v;
     };
     if (FWD && VECT && CACHE) {
-      // register-cached column: only the maximum and the flags exist so far (no exponentials to rescale)
+      // register-cached column: only the (NaN-propagating) maximum exists so far
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        c.m = fmaxf(c.m, __shfl_xor_sync(0xffffffffu, c.m, off));
-        c.n_inf += __shfl_xor_sync(0xffffffffu, c.n_inf, off);
-        c.nan |= __shfl_xor_sync(0xffffffffu, c.nan, off);
-      }
+      for (int off = 16; off > 0; off >>= 1) c.m = max_nan(c.m, __shfl_xor_sync(0xffffffffu, c.m, off));
       if (G >= 256) {
-        if (lane == 0) sh_stat[warp] = c;
+        if (lane == 0) sh_sum[warp] = c.m;
         __syncthreads();
-        c = sh_stat[0];
-        for (int w = 1; w < kWarps; ++w) {
-          c.m = fmaxf(c.m, sh_stat[w].m);
-          c.n_inf += sh_stat[w].n_inf;
-          c.nan |= sh_stat[w].nan;
-        }
+        c.m = sh_sum[0];
+        for (int w = 1; w < kWarps; ++w) c.m = max_nan(c.m, sh_sum[w]);
         __syncthreads();
       }
-      stat_finish(c);
+      if (c.m != c.m) {            // a NaN somewhere in the column
+        c.nan = 1;
+        c.m = 0.f;
+      } else if (c.m == f_inf()) { // rare: count the +Inf entries (src/softmax.jl:71-76 shares the weight among them)
+        float cnt = 0.f;
+#pragma unroll
+        for (int k = 0; k < (CACHE ? KP : 1); ++k) {
+          const long long jp = t + (long long)k * G;
+          if (jp < np) {
+            float f[V];
+            unpack<T>(cx[k], f);
+#pragma unroll
+            for (int u = 0; u < V; ++u) cnt += (f[u] == f_inf()) ? 1.f : 0.f;
+          }
+        }
+        c.n_inf = (int)group_sum(cnt);
+      }
     } else if (FWD) {
       stat_finish(c);
 #pragma unroll
