@@ -73,6 +73,25 @@ def algorithmic_bytes(w, esz: int) -> float:
     return float(n)
 
 
+# stdout carries the JSON line and nothing else: libraries that print there (NCCL's version banner) are
+# sent to stderr by pointing file descriptor 1 at it; the line itself goes to the saved descriptor
+_json_out = None
+
+
+def claim_stdout():
+    global _json_out
+    if _json_out is None:
+        sys.stdout.flush()
+        _json_out = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    out = _json_out if _json_out is not None else sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -191,7 +210,7 @@ def run_reference(args, w):
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(out), flush=True)
+    emit(out)
 
 
 # --------------------------------------------------------------------------
@@ -214,7 +233,6 @@ def run_ours(args, w):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
 
@@ -291,7 +309,7 @@ def run_ours(args, w):
                     "tflops": fl / (ms_total / args.steps * 1e-3) / 1e12, "gpu_launches": int(launches)}
             if args.backward:
                 line["backward_path"] = {_lib.PATH_UMMA: "tcgen05", _lib.PATH_SIMT: "cuda-core"}.get(back.path)
-            print(json.dumps(line), flush=True)
+            emit(line)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -385,7 +403,7 @@ def run_ours(args, w):
         if world == 1 and not args.no_cpu:
             v_cpu, cores, desc = cpu_sample(w, budget_s=args.cpu_budget)
             out["cpu_baseline"] = {"value": v_cpu, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
-        print(json.dumps(out), flush=True)
+        emit(out)
     if world > 1:
         dist.destroy_process_group()
 
@@ -424,8 +442,8 @@ def run_softmax(args):
             rows.append({"op": name, "size": list(shape), "dims": dims, "dtype": str(dt).replace("torch.", ""),
                          "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
                          "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm"], 3)})
-    print(json.dumps({"note": "stand-alone softmax kernels (--softmax): not a bench line; L2 flushed between launches",
-                      "hbm_peak_GBps": peaks["hbm"], "rows": rows}), flush=True)
+    emit({"note": "stand-alone softmax kernels (--softmax): not a bench line; L2 flushed between launches",
+          "hbm_peak_GBps": peaks["hbm"], "rows": rows})
 
 
 def main():
@@ -442,6 +460,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (smaller profiler captures)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
     args = ap.parse_args()
+    claim_stdout()
     w = dict(WORKLOADS[args.workload])
     if args.batch > 0:
         w["B"] = args.batch
