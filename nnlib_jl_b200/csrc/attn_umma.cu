@@ -798,6 +798,7 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int jc = j0 + c * 32;
+          __syncwarp();   // the previous chunk's bias / mask / store code branches per row
           tmem_wait_ld();
           if (c + 1 < 4) {
             tmem_ld32(lane_base + sb * kBN + (c + 1) * 32, sr[(c + 1) & 1]);
