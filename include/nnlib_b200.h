@@ -10,7 +10,27 @@
  * void*.  All entry points enqueue work on that stream and return without
  * synchronising; they never allocate device memory, never change the current
  * device and never throw.  They are re-entrant: several host threads, one per
- * device, may call them at once.
+ * device, may call them at once.  q and x (every pointer when the environment
+ * variable NNLIB_B200_CHECK_POINTERS=1 is set) must be memory of the current
+ * device, else NNLIB_B200_INVALID_ARG.
+ *
+ * Fail-stop behaviour of the tensor-core kernels.  Every wait inside them
+ * (on a copy, on the tensor core, on another warp) is bounded: after 1 s
+ * without progress the thread block gives up, releases what it holds and
+ * returns, so a fault in this library cannot hang the GPU.  From then on the
+ * DEVICE is marked: every later tensor-core launch of this library on it
+ * returns at once WITHOUT writing its outputs, while the entry points keep
+ * returning NNLIB_B200_OK (they never synchronise).  The mark shows in two
+ * places: p->status, when the caller passes one, is set to
+ * NNLIB_B200_TIMEOUT by the launch that gave up and by every launch that was
+ * skipped; nnlib_b200_device_health reports and clears it.  Callers should
+ * pass a status word and look at it (or call device_health) wherever they
+ * synchronise anyway.  It has never fired in a correct run.
+ *
+ * NNLIB_B200_LOG=1 prints one line per call on stderr: entry point, sizes,
+ * options, kernel family (tcgen05 / cuda-core) and, for a call that could
+ * not take the tensor-core kernels, the reason (for instance a pointer that
+ * is not 16-byte aligned).
  *
  * Memory layout = the reference's column-major arrays:
  *   q      (E , Lq , B)   element (e, i, b) at  q[e + q_stride_l*i + q_stride_b*b]
@@ -19,8 +39,12 @@
  *   x      (Ev, Lq , B)   output
  *   alpha  (Lkv, Lq, H, B) element (j, i, h, b) at alpha[j + Lkv*i + Lkv*Lq*h + alpha_stride_b*b]
  *   lse    (Lq, H, B) float32, natural-log sum of exponentials of the scaled,
- *          biased, masked logits of each query (−inf for a query with nothing
- *          to attend to)
+ *          biased, masked logits of each query; −inf for a query with nothing
+ *          to attend to; NaN for a query with a NaN logit; for a query whose
+ *          largest logit is +Inf (a +Inf bias: the reference's softmax then
+ *          gives equal shares to the +Inf keys, src/softmax.jl:73-75) a NaN
+ *          with the quiet bit clear whose low 22 bits count those keys, which
+ *          is what attn_scores needs to rebuild that query's scores
  * with E = H*d, Ev = H*dv; head h owns features h*d .. h*d+d-1
  * (split_heads is a pure reshape, src/attention.jl:158).
  */
@@ -166,11 +190,21 @@ NNLIB_B200_API size_t nnlib_b200_workspace_bytes(const nnlib_b200_attn_params* p
    NNLIB_B200_WORKSPACE_TOO_SMALL and does nothing.  p->lse is ignored.  All
    calls on a device share the array: calls that can overlap on the GPU race
    and must be serialised by the caller; nothing needs clearing between calls.
-   The first call on each device resolves the array's address and should be
-   made before any stream capture.  Allocates nothing, ever.
-   This entry point has no counterpart in the reference. */
+   The first call on each device resolves the array's address; with CUDA's
+   lazy module loading that look-up is also what brings the array into being
+   (the driver reserves its 4 MiB then and may synchronise the device), so
+   make that first call early: before a memory pool claims the rest of the
+   device and before any stream capture.  Later calls do no set-up and reach
+   no allocating routine.  The address is remembered per device ordinal for
+   the life of the process: it assumes the device's primary context is never
+   reset.  This entry point has no counterpart in the reference. */
 #define NNLIB_B200_STATIC_MAX_QUERIES 1048576ull
 NNLIB_B200_API int nnlib_b200_attention_static(const nnlib_b200_attn_params* p, void* stream);
+
+/* Where that fixed array lives on the current device and how large it is (does the same first-call
+   set-up).  For tests and for callers that account for every byte of device memory.  No counterpart in
+   the reference. */
+NNLIB_B200_API int nnlib_b200_static_scratch(void** device_ptr, size_t* bytes);
 
 /* Gradient buffers of nnlib_b200_attn_bwd.  dx, dq, dk, dv have the element type of the forward
    arrays; dq (E, Lq, B), dk (E, Lkv, B), dv (Ev, Lkv, B) are written dense. */
@@ -239,6 +273,13 @@ NNLIB_B200_API int nnlib_b200_attn_path(const nnlib_b200_attn_params* p);
    previous call (the flag is cleared), else NNLIB_B200_OK.  Meant for tests
    and for callers that want to turn a silent abort into an error. */
 NNLIB_B200_API int nnlib_b200_device_health(void* stream);
+
+/* Self-test of the fail-stop path: enqueues one thread block that waits, with the very wait every
+   tensor-core kernel here uses, on a barrier nobody arrives at.  After limit_ns (1 .. 10^9) the wait
+   gives up and the kernel returns by itself: the device is marked as described at the top of this file
+   and *status (optional device int32) is set to NNLIB_B200_TIMEOUT.  Nothing faults or hangs.  Call
+   nnlib_b200_device_health afterwards to clear the mark.  No counterpart in the reference. */
+NNLIB_B200_API int nnlib_b200_selftest_wait_runout(uint64_t limit_ns, int32_t* status, void* stream);
 
 NNLIB_B200_API const char* nnlib_b200_strerror(int code);
 NNLIB_B200_API int nnlib_b200_version(void);

@@ -96,23 +96,21 @@ _take_offset!(d::PhiloxDropout) = (o = d.offset; d.offset += 1; o)
 "Sentinel for `mask=`: the causal pattern `kv <= query` without the `(L, L)` Bool matrix."
 struct CausalMask end
 
-# Bool matrices known to hold make_causal_mask's pattern, by device address.
-const _known_causal = Dict{CuPtr{Bool},Int}()
-
+# Julia arrays carry no modification counter, so a matrix cannot be proven untouched after
+# `make_causal_mask` returned it (`m[1, 3] = true` must change the result).  Every square Bool matrix is
+# therefore read on the device each time it is passed: one pass over L*L bytes and a 4-byte copy back.
+# Callers who want the causal pattern at no cost pass `mask = CausalMask()`.
 function make_causal_mask(x::CuArray; dims::Int=2)
     len = size(x, dims)
     mask = similar(x, Bool, (len, len))
     rc = ccall((:nnlib_b200_causal_fill, libnnlib_b200[]), Cint, (CuPtr{UInt8}, Int64, Ptr{Cvoid}),
                reinterpret(CuPtr{UInt8}, pointer(mask)), len, stream().handle)
     _b200_check(rc, "causal_fill")
-    _known_causal[pointer(mask)] = len
-    finalizer(m -> delete!(_known_causal, pointer(m)), mask)
     return mask
 end
 
 function _is_causal_matrix(mask::DenseCuArray{Bool,2}, Lq, Lkv)
     (Lq == Lkv && size(mask) == (Lkv, Lq)) || return false
-    get(_known_causal, pointer(mask), -1) == Lq && return true
     flag = CUDA.zeros(Int32, 1)
     rc = ccall((:nnlib_b200_causal_check, libnnlib_b200[]), Cint, (CuPtr{UInt8}, Int64, CuPtr{Int32}, Ptr{Cvoid}),
                reinterpret(CuPtr{UInt8}, pointer(mask)), Lq, pointer(flag), stream().handle)

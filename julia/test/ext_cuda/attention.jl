@@ -52,6 +52,16 @@ end
     @test all((α_host[:, :, 2, 1] .> 0) .== mask_host)
 end
 
+@testset "attention: a modified causal matrix is an ordinary mask" begin
+    q = CUDA.rand(Float32, 8, 6, 1)
+    mask = make_causal_mask(q)
+    CUDA.@allowscalar mask[5, 2] = true            # key 5 now visible to query 2
+    α = Array(dot_product_attention(q, q, q; nheads=2, mask)[2])
+    @test all(α[5, 2, :, 1] .> 0)
+    αh = dot_product_attention(Array(q), Array(q), Array(q); nheads=2, mask=Array(mask))[2]
+    @test α ≈ αh atol=1f-5
+end
+
 @testset "attention: dropout" begin
     q = k = v = CUDA.rand(Float32, 10, 10, 10)
     y, α = dot_product_attention(q, k, v; nheads=2, fdrop=x -> dropout(x, 0.5))      # opaque callable

@@ -6,7 +6,7 @@ tensors, computed by the hand-written sm_100a kernels of ``libnnlib_b200.so``
 (``csrc/``; C ABI in ``include/nnlib_b200.h``).  ``shard`` spreads the
 independent (batch, head) units of one call over the GPUs of a box.
 """
-from .attention import (ArgumentError, CausalMask, LazyAttnScores, PhiloxDropout, device_health,
+from .attention import (ArgumentError, CausalMask, LazyAttnScores, PhiloxDropout, check_status, device_health,
                         dot_product_attention, dot_product_attention_pullback, dot_product_attention_scores, identity,
                         make_causal_mask)
 from . import softmax  # softmax / logsoftmax and pullbacks: nnlib_jl_b200.softmax.softmax(x, dims=...)
@@ -15,7 +15,7 @@ from .layout import (as_column_major, is_column_major, jl_empty, jl_from_numpy, 
                      jl_zeros)
 
 __all__ = [
-    "ArgumentError", "CausalMask", "HostPipelinedAttention", "LazyAttnScores", "PhiloxDropout", "device_health",
+    "ArgumentError", "CausalMask", "HostPipelinedAttention", "LazyAttnScores", "PhiloxDropout", "check_status", "device_health",
     "dot_product_attention", "dot_product_attention_pullback", "dot_product_attention_scores", "identity", "make_causal_mask",
     "as_column_major", "is_column_major", "jl_empty", "jl_from_numpy", "jl_reshape", "jl_to_numpy", "jl_zeros",
 ]

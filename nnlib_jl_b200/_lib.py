@@ -38,6 +38,7 @@ EXPORTS = (
     "nnlib_b200_attention",
     "nnlib_b200_workspace_bytes",
     "nnlib_b200_attention_static",
+    "nnlib_b200_static_scratch",
     "nnlib_b200_attn_bwd",
     "nnlib_b200_attn_bwd_path",
     "nnlib_b200_causal_fill",
@@ -46,6 +47,7 @@ EXPORTS = (
     "nnlib_b200_softmax_fwd",
     "nnlib_b200_softmax_bwd",
     "nnlib_b200_device_health",
+    "nnlib_b200_selftest_wait_runout",
     "nnlib_b200_strerror",
     "nnlib_b200_version",
     "nnlib_b200_last_cuda_error",
@@ -144,6 +146,10 @@ def load() -> C.CDLL:
     lib.nnlib_b200_attention.restype = C.c_int
     lib.nnlib_b200_attention_static.argtypes = [P, C.c_void_p]
     lib.nnlib_b200_attention_static.restype = C.c_int
+    lib.nnlib_b200_static_scratch.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]
+    lib.nnlib_b200_static_scratch.restype = C.c_int
+    lib.nnlib_b200_selftest_wait_runout.argtypes = [C.c_uint64, C.c_void_p, C.c_void_p]
+    lib.nnlib_b200_selftest_wait_runout.restype = C.c_int
     lib.nnlib_b200_attn_bwd.argtypes = [P, C.POINTER(AttnGrads), C.c_void_p]
     lib.nnlib_b200_attn_bwd.restype = C.c_int
     lib.nnlib_b200_attn_bwd_path.argtypes = [P, C.POINTER(AttnGrads)]

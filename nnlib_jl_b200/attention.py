@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import threading
 import weakref
 from typing import Callable, Optional
 
@@ -37,6 +38,7 @@ __all__ = [
     "make_causal_mask",
     "identity",
     "device_health",
+    "check_status",
 ]
 
 
@@ -59,8 +61,45 @@ def identity(x):
 
 _DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
 
-# data_ptr -> (version, L) of Bool matrices known to hold make_causal_mask's pattern
-_known_causal: dict = {}
+# id(tensor) -> (weak reference to that tensor, its version counter, L) for the Bool matrices that
+# make_causal_mask built and that no PyTorch operation has written to since.  Nothing else is trusted: a
+# freed matrix's address (and id) can be handed to the next one, so an entry counts only while its weak
+# reference still yields the very object being asked about.
+_made_causal: dict = {}
+_made_causal_lock = threading.Lock()
+
+
+# One int32 per device that every kernel launched through this module reports to: a launch that gave up on
+# a bounded wait, and every launch skipped afterwards, writes NNLIB_B200_TIMEOUT there (see the header of
+# include/nnlib_b200.h, "fail-stop behaviour").  Looked at wherever this module synchronises anyway.
+_status_words: dict = {}
+_status_lock = threading.Lock()
+
+
+def _status_word(dev: torch.device) -> torch.Tensor:
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    with _status_lock:
+        w = _status_words.get(idx)
+        if w is None:
+            w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+            _status_words[idx] = w
+    return w
+
+
+def check_status(device=None) -> None:
+    """Raise :class:`NNlibB200Error` if a kernel launched through this module on ``device`` gave up on a
+    bounded wait (its results, and those of every later launch on that device, are invalid).  Reads one
+    int32 from the device, which waits for the work enqueued so far; the word is cleared."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    with _status_lock:
+        w = _status_words.get(idx)
+    if w is None:
+        return
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        raise _lib.NNlibB200Error(v, "a kernel of an earlier call")
 
 
 def _check(rc: int, where: str):
@@ -161,6 +200,8 @@ class _Problem:
             if rng_origin is not None:
                 # this call is a shard: (first head, first batch, heads of the whole problem)
                 p.rng_h0, p.rng_b0, p.rng_H = (int(v_) for v_ in rng_origin)
+        self.status_word = _status_word(self.dev)
+        p.status = self.status_word.data_ptr()
         self.p = p
 
     def alloc_lse(self):
@@ -180,25 +221,23 @@ class _Problem:
 
 
 def _is_causal_matrix(mask: torch.Tensor, Lq: int, Lkv: int) -> bool:
-    """Is ``mask`` an ``(L, L)`` Bool matrix holding exactly ``kv <= query``?
-    Matrices made by :func:`make_causal_mask` are recognised by address; others
-    are checked once on the device and remembered until they are modified."""
+    """Is ``mask`` an ``(L, L)`` Bool matrix holding exactly ``kv <= query``?  A matrix that
+    :func:`make_causal_mask` returned and that has not been written to since (same object, same version
+    counter) is known to; every other square Bool matrix is read on the device each time it is passed
+    (one pass over it and a 4-byte copy back), so a matrix that was modified, or a new one that landed
+    on a freed one's address, is never mistaken for the causal pattern."""
     if mask.ndim != 2 or Lq != Lkv or tuple(mask.shape) != (Lkv, Lq) or not is_column_major(mask):
         return False
-    key = mask.data_ptr()
-    hit = _known_causal.get(key)
-    if hit is not None and hit[0] == mask._version and hit[1] == Lq:
-        return hit[2]
+    with _made_causal_lock:
+        hit = _made_causal.get(id(mask))
+    if hit is not None and hit[0]() is mask and hit[1] == mask._version and hit[2] == Lq:
+        return True
     lib = _lib.load()
     flag = torch.empty(1, dtype=torch.int32, device=mask.device)
     with torch.cuda.device(mask.device):
         _check(lib.nnlib_b200_causal_check(mask.view(torch.uint8).data_ptr(), Lq, flag.data_ptr(), _stream()),
                "causal_check")
-    res = bool(flag.item())
-    _known_causal[key] = (mask._version, Lq, res)
-    if len(_known_causal) > 64:
-        _known_causal.pop(next(iter(_known_causal)))
-    return res
+    return bool(flag.item())
 
 
 class LazyAttnScores:
@@ -267,6 +306,7 @@ class LazyAttnScores:
         if t.dtype in (torch.bfloat16, torch.float16):
             t = t.float()
         a = t.cpu().numpy()
+        check_status(self._problem.dev)      # the copy synchronised anyway
         return a if dtype is None else a.astype(dtype)
 
     def __getitem__(self, idx):
@@ -496,17 +536,27 @@ def dot_product_attention_scores(q, k, bias=None, *, fdrop: Callable = identity,
 def make_causal_mask(x: torch.Tensor, dims: int = 2) -> torch.Tensor:
     """Bool square matrix ``m`` of side ``size(x, dims)`` with ``m[i, j] = i <= j``
     (``src/attention.jl:149-153``; ``dims`` is 1-based like the reference's),
-    on the device of ``x``.  Passing it as ``mask=`` selects the kernels' causal
-    mode; the matrix itself is never read by them."""
+    on the device of ``x``.  Passing it (unmodified) as ``mask=`` selects the
+    kernels' causal mode without reading the matrix; once it has been written
+    to it is treated like any other Bool mask."""
     if not isinstance(x, torch.Tensor) or not x.is_cuda:
         raise TypeError("make_causal_mask: this method is defined for CUDA arrays only")
     n = int(x.shape[dims - 1])
     m = jl_empty((n, n), torch.bool, x.device)
     with torch.cuda.device(x.device):
         _check(_lib.load().nnlib_b200_causal_fill(m.view(torch.uint8).data_ptr(), n, _stream()), "causal_fill")
-    _known_causal[m.data_ptr()] = (m._version, n, True)
-    weakref.finalize(m, _known_causal.pop, m.data_ptr(), None)
+    key = id(m)
+    with _made_causal_lock:
+        _made_causal[key] = (weakref.ref(m), m._version, n)
+    weakref.finalize(m, _forget_causal, key)
     return m
+
+
+def _forget_causal(key):
+    with _made_causal_lock:
+        hit = _made_causal.get(key)
+        if hit is not None and hit[0]() is None:
+            del _made_causal[key]
 
 
 def device_health(device=None) -> None:
@@ -515,5 +565,8 @@ def device_health(device=None) -> None:
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     with torch.cuda.device(dev):
         rc = _lib.load().nnlib_b200_device_health(_stream())
-    if rc != _lib.OK:
-        raise _lib.NNlibB200Error(rc, "device_health")
+    try:
+        check_status(dev)
+    finally:
+        if rc != _lib.OK:
+            raise _lib.NNlibB200Error(rc, "device_health")

@@ -3,6 +3,7 @@
 // is allocated, nothing synchronises except nnlib_b200_device_health.
 #include <atomic>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -27,9 +28,70 @@ bool force_simt() {
   return v;
 }
 
+// NNLIB_B200_LOG=1: one line per call on stderr (entry point, sizes, options, kernel family and, when the
+// tensor-core kernels were not taken, why) so that a call that silently runs on the CUDA-core kernels —
+// an unaligned pointer, a stride that is not a multiple of 8 elements — can be found.
+bool log_calls() {
+  static const bool v = [] {
+    const char* e = std::getenv("NNLIB_B200_LOG");
+    return e && e[0] && e[0] != '0';
+  }();
+  return v;
+}
+
+// NNLIB_B200_CHECK_POINTERS=1 (implied by NNLIB_B200_LOG=1): every pointer of the struct is looked up,
+// not only q and x.
+bool check_all_pointers() {
+  static const bool v = [] {
+    const char* e = std::getenv("NNLIB_B200_CHECK_POINTERS");
+    return (e && e[0] && e[0] != '0') || log_calls();
+  }();
+  return v;
+}
+
+// Is `ptr` device (or managed) memory of the device that is current on this thread?  NULL passes.
+bool on_current_device(const void* ptr, int dev) {
+  if (!ptr) return true;
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  if (at.type == cudaMemoryTypeManaged) return true;
+  return at.type == cudaMemoryTypeDevice && at.device == dev;
+}
+
+// The caller's arrays must live on the current device: the kernels are launched there and the library
+// never switches devices.  q and x are always looked up (a result written to another GPU's memory, or a
+// host pointer, must not go unnoticed); the remaining pointers under NNLIB_B200_CHECK_POINTERS.
+int check_devices(const nnlib_b200_attn_params* p) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return NNLIB_B200_CUDA_ERROR;
+  }
+  if (!on_current_device(p->q, dev) || !on_current_device(p->x, dev)) return NNLIB_B200_INVALID_ARG;
+  if (check_all_pointers()) {
+    const void* rest[] = {p->k, p->v, p->bias, p->mask, p->lse, p->alpha, p->status};
+    for (const void* r : rest)
+      if (!on_current_device(r, dev)) return NNLIB_B200_INVALID_ARG;
+  }
+  return NNLIB_B200_OK;
+}
+
+void log_call(const char* entry, const nnlib_b200_attn_params* p, const AttnArgs& a, const char* path,
+              const char* why) {
+  if (!log_calls()) return;
+  static const char* const names[] = {"f16", "bf16", "f32"};
+  std::fprintf(stderr,
+               "[nnlib_b200] %s %s d=%d dv=%d H=%d Lq=%d Lkv=%d B=%d causal=%d mask=%d bias=%d dropout=%g -> %s%s%s\n",
+               entry, names[p->dtype], a.d, a.dv, a.H, a.Lq, a.Lkv, a.B, a.causal, a.mask ? 1 : 0, a.bias ? 1 : 0,
+               (double)a.dropout_p, path, why ? ": " : "", why ? why : "");
+}
+
 enum Need : unsigned {
   NEED_V = 1u,      // v and x
-  NEED_LSE_IN = 2u, // lse must be given (read)
+  NEED_LSE_IN = 2u, // lse must be given
   NEED_ALPHA = 4u,  // alpha must be given
   NEED_QK = 8u      // q and k
 };
@@ -37,7 +99,9 @@ enum Need : unsigned {
 int dtype_ok(int dt) { return dt == NNLIB_B200_F16 || dt == NNLIB_B200_BF16 || dt == NNLIB_B200_F32; }
 
 // Validate the caller's struct and turn it into the kernels' argument block.
-int resolve(const nnlib_b200_attn_params* p, unsigned need, AttnArgs* out) {
+// `launching`: the call is about to enqueue kernels, so the arrays' device is checked too (the path queries
+// are pure host logic and skip that).
+int resolve(const nnlib_b200_attn_params* p, unsigned need, AttnArgs* out, bool launching = true) {
   if (!p || p->struct_size != sizeof(nnlib_b200_attn_params)) return NNLIB_B200_INVALID_ARG;
   if (!dtype_ok(p->dtype)) return NNLIB_B200_INVALID_ARG;
   if (p->d < 1 || p->H < 1 || p->Lq < 0 || p->Lkv < 0 || p->B < 0) return NNLIB_B200_INVALID_ARG;
@@ -95,6 +159,10 @@ int resolve(const nnlib_b200_attn_params* p, unsigned need, AttnArgs* out) {
   a.alpha_sb = p->alpha_stride_b ? p->alpha_stride_b : p->Lkv * p->Lq * p->H;
   if (a.lse_sb < p->Lq * p->H || a.alpha_sb < p->Lkv * p->Lq * p->H) return NNLIB_B200_INVALID_ARG;
   a.status = p->status;
+  if (!empty && launching) {
+    const int rc = check_devices(p);
+    if (rc) return rc;
+  }
   *out = a;
   return NNLIB_B200_OK;
 }
@@ -106,10 +174,28 @@ int finish(cudaError_t e) {
 }
 
 bool use_umma(const AttnArgs& a, int dtype, bool need_v) {
-  return !force_simt() && umma_supports(a, dtype, need_v);
+  return !force_simt() && umma_reject_reason(a, dtype, need_v) == nullptr;
+}
+
+// why a call does not run on the tensor-core kernels (for the log)
+const char* simt_reason(const AttnArgs& a, int dtype, bool need_v) {
+  return force_simt() ? "NNLIB_B200_FORCE_SIMT is set" : umma_reject_reason(a, dtype, need_v);
 }
 
 }  // namespace
+
+// Arguments of the x + alpha composite (attn_fwd followed by attn_scores), checked as a whole so that a
+// bad alpha cannot surface after x and lse were already written.  Not exported.
+int attention_validate(const nnlib_b200_attn_params* p) {
+  AttnArgs a;
+  const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN | NEED_ALPHA, &a);
+  if (rc) return rc;
+  if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
+  const bool fwd_ok = use_umma(a, p->dtype, true) || simt_supports(a.d, a.dv);
+  const bool sc_ok = use_umma(a, p->dtype, false) || simt_supports(a.d, 1);
+  return (fwd_ok && sc_ok) ? NNLIB_B200_OK : NNLIB_B200_UNSUPPORTED_SHAPE;
+}
+
 }  // namespace nb200
 
 using namespace nb200;
@@ -122,20 +208,27 @@ int nnlib_b200_attn_fwd(const nnlib_b200_attn_params* p, void* stream) {
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_umma(a, p->dtype, true)) return finish(umma_fwd(a, p->dtype, false, st));
+  if (use_umma(a, p->dtype, true)) {
+    log_call("attn_fwd", p, a, "tcgen05", nullptr);
+    return finish(umma_fwd(a, p->dtype, false, st));
+  }
   if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  log_call("attn_fwd", p, a, "cuda-core", simt_reason(a, p->dtype, true));
   return finish(simt_fwd(a, p->dtype, st));
 }
 
 int nnlib_b200_attn_stats(const nnlib_b200_attn_params* p, void* stream) {
   AttnArgs a;
-  const int rc = resolve(p, NEED_QK, &a);
+  const int rc = resolve(p, NEED_QK | NEED_LSE_IN, &a);   // lse is this entry point's output: required
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
-  if (!a.lse) return NNLIB_B200_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_umma(a, p->dtype, false)) return finish(umma_fwd(a, p->dtype, true, st));
+  if (use_umma(a, p->dtype, false)) {
+    log_call("attn_stats", p, a, "tcgen05", nullptr);
+    return finish(umma_fwd(a, p->dtype, true, st));
+  }
   if (!simt_supports(a.d, 1)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  log_call("attn_stats", p, a, "cuda-core", simt_reason(a, p->dtype, false));
   return finish(simt_stats(a, p->dtype, st));
 }
 
@@ -145,8 +238,12 @@ int nnlib_b200_attn_scores(const nnlib_b200_attn_params* p, void* stream) {
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0 || a.Lkv == 0) return NNLIB_B200_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_umma(a, p->dtype, false)) return finish(umma_scores(a, p->dtype, st));
+  if (use_umma(a, p->dtype, false)) {
+    log_call("attn_scores", p, a, "tcgen05", nullptr);
+    return finish(umma_scores(a, p->dtype, st));
+  }
   if (!simt_supports(a.d, 1)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  log_call("attn_scores", p, a, "cuda-core", simt_reason(a, p->dtype, false));
   return finish(simt_scores(a, p->dtype, st));
 }
 
@@ -155,19 +252,27 @@ int nnlib_b200_attn_apply(const nnlib_b200_attn_params* p, void* stream) {
   const int rc = resolve(p, NEED_V | NEED_ALPHA, &a);
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
-  if (a.Lkv > 0 && !force_simt() && umma_apply_supports(a, p->dtype))
+  if (a.Lkv > 0 && !force_simt() && umma_apply_supports(a, p->dtype)) {
+    log_call("attn_apply", p, a, "tcgen05", nullptr);
     return finish(umma_apply(a, p->dtype, (cudaStream_t)stream));
+  }
   if (!simt_supports(1, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  log_call("attn_apply", p, a, "cuda-core", force_simt() ? "NNLIB_B200_FORCE_SIMT is set"
+                                                         : "16-bit arrays with dv in {64,128}, Lkv % 8 == 0 and "
+                                                           "16-byte aligned rows only");
   return finish(simt_apply(a, p->dtype, (cudaStream_t)stream));
 }
 
 // shared front half of attn_bwd / attn_bwd_path: validates and resolves both argument blocks
-static int resolve_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g, AttnArgs* a, BwdArgs* b) {
-  const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN, a);
+static int resolve_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g, AttnArgs* a, BwdArgs* b,
+                       bool launching = true) {
+  const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN, a, false);   // the device check comes last
   if (rc) return rc;
   if (!g || g->struct_size != sizeof(nnlib_b200_attn_grads)) return NNLIB_B200_INVALID_ARG;
   const bool empty = (a->Lq == 0 || a->B == 0);
-  if (!empty && (!g->dx || !g->dq || !g->delta || (a->Lkv > 0 && (!g->dk || !g->dv)))) return NNLIB_B200_INVALID_ARG;
+  if (!empty && (!g->dx || !g->dq || !g->delta)) return NNLIB_B200_INVALID_ARG;
+  // dk and dv are written (zeros) even when there are no queries, as long as there are keys
+  if (a->B > 0 && a->Lkv > 0 && (!g->dk || !g->dv)) return NNLIB_B200_INVALID_ARG;
   std::memset(b, 0, sizeof(*b));
   const long long Ev = (long long)a->H * a->dv;
   b->dx = g->dx;
@@ -181,6 +286,7 @@ static int resolve_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_gr
     b->dbias_s[i] = g->dbias_stride[i];
   }
   b->delta = g->delta;
+  if (launching && !empty) return check_devices(p);
   return NNLIB_B200_OK;
 }
 
@@ -190,15 +296,20 @@ int nnlib_b200_attn_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_g
   const int rc = resolve_bwd(p, g, &a, &b);
   if (rc) return rc;
   if (a.B == 0 || (a.Lq == 0 && a.Lkv == 0)) return NNLIB_B200_OK;
-  if (!force_simt() && umma_bwd_supports(a, b, p->dtype)) return finish(umma_bwd(a, b, p->dtype, (cudaStream_t)stream));
+  if (!force_simt() && umma_bwd_supports(a, b, p->dtype)) {
+    log_call("attn_bwd", p, a, "tcgen05", nullptr);
+    return finish(umma_bwd(a, b, p->dtype, (cudaStream_t)stream));
+  }
   if (!simt_bwd_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
+  log_call("attn_bwd", p, a, "cuda-core", force_simt() ? "NNLIB_B200_FORCE_SIMT is set"
+                                                       : "16-bit arrays with d = dv in {64,128} and 16-byte aligned rows only");
   return finish(simt_bwd(a, b, p->dtype, (cudaStream_t)stream));
 }
 
 int nnlib_b200_attn_bwd_path(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g) {
   AttnArgs a;
   BwdArgs b;
-  const int rc = resolve_bwd(p, g, &a, &b);
+  const int rc = resolve_bwd(p, g, &a, &b, false);
   if (rc) return rc;
   if (!force_simt() && umma_bwd_supports(a, b, p->dtype)) return NNLIB_B200_PATH_UMMA;
   if (!simt_bwd_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
@@ -221,7 +332,10 @@ int nnlib_b200_attention(const nnlib_b200_attn_params* p, void* workspace, size_
     q.lse = static_cast<float*>(workspace);
     q.lse_stride_b = 0;
   }
-  int rc = nnlib_b200_attn_fwd(&q, stream);
+  // every argument of both halves is checked before the first kernel is enqueued
+  int rc = attention_validate(&q);
+  if (rc) return rc;
+  rc = nnlib_b200_attn_fwd(&q, stream);
   if (rc) return rc;
   return nnlib_b200_attn_scores(&q, stream);
 }
@@ -260,7 +374,7 @@ int nnlib_b200_causal_check(const uint8_t* mask, int64_t L, int32_t* flag, void*
 
 int nnlib_b200_attn_path(const nnlib_b200_attn_params* p) {
   AttnArgs a;
-  const int rc = resolve(p, NEED_QK | NEED_V, &a);
+  const int rc = resolve(p, NEED_QK | NEED_V, &a, false);
   if (rc) return rc;
   if (use_umma(a, p->dtype, true)) return NNLIB_B200_PATH_UMMA;
   if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
@@ -273,6 +387,11 @@ int nnlib_b200_device_health(void* stream) {
   if (e == cudaSuccess) e = umma_bwd_take_abort(&w, (cudaStream_t)stream);
   if (e != cudaSuccess) return finish(e);
   return (v || w) ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
+}
+
+int nnlib_b200_selftest_wait_runout(uint64_t limit_ns, int32_t* status, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return NNLIB_B200_INVALID_ARG;   // at most the kernels' own 1 s
+  return finish(umma_wait_runout(limit_ns, status, (cudaStream_t)stream));
 }
 
 const char* nnlib_b200_strerror(int code) {

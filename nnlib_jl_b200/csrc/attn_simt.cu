@@ -57,10 +57,18 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_simt_kernel(const At
   float lse = 0.f;
   if (MODE == MODE_FWD || MODE == MODE_STATS) {
     // pass A: per-lane online max/sum over the lane's kv positions, then a butterfly merge
+    // +Inf logits are counted apart and a NaN poisons the row (the slow branch of the reference's softmax,
+    // src/softmax.jl:71-76)
     float m = neg_inf(), l = 0.f;
+    int n_inf = 0;
+    bool has_nan = false;
     for (int j = lane; j < a.Lkv; j += 32) {
       const float t = logit_at<T>(a, qs, j, i, h, b);
-      if (t > neg_inf()) {
+      if (t != t) {
+        has_nan = true;
+      } else if (t == __int_as_float(0x7f800000)) {
+        ++n_inf;
+      } else if (t > neg_inf()) {
         if (t > m) { l = l * expf(m - t) + 1.f; m = t; }
         else       { l += expf(t - m); }
       }
@@ -74,8 +82,12 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_simt_kernel(const At
       const float lb = (m2 == neg_inf()) ? 0.f : l2 * expf(m2 - mn);
       l = la + lb;
       m = mn;
+      n_inf += __shfl_xor_sync(0xffffffffu, n_inf, off);
     }
+    has_nan = __any_sync(0xffffffffu, has_nan);
     lse = (l > 0.f) ? m + logf(l) : neg_inf();
+    if (n_inf > 0) lse = lse_inf_rows((float)n_inf);
+    if (has_nan) lse = __int_as_float(0x7fc00000);
     if (a.lse && lane == 0) a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = lse;
   } else if (MODE == MODE_SCORES) {
     lse = a.lse[i + (long long)a.Lq * h + a.lse_sb * b];
@@ -87,6 +99,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_simt_kernel(const At
 #pragma unroll
   for (int r = 0; r < kMaxDvRegs; ++r) acc[r] = 0.f;
   const bool dead_row = (lse == neg_inf());
+  const bool inf_row = lse_is_inf_rows(lse);
+  const bool nan_row = (lse != lse) && !inf_row;
+  const float inf_share = inf_row ? 1.f / lse_inf_count(lse) : 0.f;
   const unsigned long long srow = score_row(a, i, h, b);
   T* alpha_row = reinterpret_cast<T*>(a.alpha) +
                  ((long long)i + (long long)a.Lq * h) * a.Lkv + a.alpha_sb * b;
@@ -100,8 +115,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_simt_kernel(const At
         al = Elem<T>::to_f(alpha_row[j]);
       } else {
         const float t = logit_at<T>(a, qs, j, i, h, b);
-        if (dead_row) al = a.nan_fm ? __int_as_float(0x7fc00000) : 0.f;
-        else          al = (t == neg_inf()) ? 0.f : expf(t - lse);
+        if (dead_row)      al = a.nan_fm ? __int_as_float(0x7fc00000) : 0.f;
+        else if (nan_row)  al = __int_as_float(0x7fc00000);
+        else if (inf_row)  al = (t == __int_as_float(0x7f800000)) ? inf_share : 0.f;
+        else               al = (t == neg_inf()) ? 0.f : expf(t - lse);
         if (a.dropout_p > 0.f) {
           al = dropout_keep1(a, srow, (unsigned int)j) ? al * a.inv_keep : 0.f;
         }

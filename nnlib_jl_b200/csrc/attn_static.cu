@@ -11,8 +11,12 @@
 // in a fixed array that is part of this library's device image.
 //
 // Cost and rules of that arrangement:
-//  * every GPU that loads the library holds the array (4 MiB) until the
-//    process exits, whether or not this entry point is ever called;
+//  * every GPU on which the array has been brought into being holds it
+//    (4 MiB) until the process exits.  With eager module loading that is every
+//    GPU the library is used on; with CUDA's default lazy loading it is the
+//    first call of this entry point on a device (this file holds no kernel, so
+//    nothing else touches its module), which may also synchronise the device.
+//    Make that first call before a memory pool claims the rest of the device;
 //  * a call is limited to NNLIB_B200_STATIC_MAX_QUERIES = 2^20 queries
 //    (Lq * H * B); larger problems are refused, nothing is truncated;
 //  * all calls on one device share the array.  Each call overwrites the
@@ -22,11 +26,14 @@
 //    host threads on the same device) race on it.  Serialise them;
 //  * the first call on each device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current).  Make that first call
-//    ahead of any stream capture.  Later calls do no set-up.
-// No cudaMalloc, cudaFree or any other allocating routine is reached from here.
+//    ahead of any stream capture.  Later calls do no set-up.  The address is
+//    remembered per device ordinal and assumes the primary context is never
+//    reset (cudaDeviceReset would leave a stale address behind).
+// No cudaMalloc, cudaFree or any other allocating routine is called from here.
 #include <mutex>
 
 #include "common.cuh"
+#include "launchers.h"
 
 namespace {
 
@@ -66,6 +73,16 @@ int static_lse_address(float** out) {
 
 }  // namespace
 
+extern "C" int nnlib_b200_static_scratch(void** device_ptr, size_t* bytes) {
+  if (!device_ptr || !bytes) return NNLIB_B200_INVALID_ARG;
+  float* lse = nullptr;
+  const int rc = static_lse_address(&lse);
+  if (rc != NNLIB_B200_OK) return rc;
+  *device_ptr = lse;
+  *bytes = sizeof(float) * kMaxQueries;
+  return NNLIB_B200_OK;
+}
+
 extern "C" int nnlib_b200_attention_static(const nnlib_b200_attn_params* p, void* stream) {
   if (!p || p->struct_size != sizeof(nnlib_b200_attn_params)) return NNLIB_B200_INVALID_ARG;
   if (p->Lq < 0 || p->H < 1 || p->B < 0) return NNLIB_B200_INVALID_ARG;
@@ -79,6 +96,8 @@ extern "C" int nnlib_b200_attention_static(const nnlib_b200_attn_params* p, void
   nnlib_b200_attn_params q = *p;
   q.lse = lse;          // any lse pointer of the caller is ignored: this variant owns the buffer
   q.lse_stride_b = 0;   // dense (Lq, H, B)
+  const int rc_args = nb200::attention_validate(&q);   // both halves, before anything is enqueued
+  if (rc_args != NNLIB_B200_OK) return rc_args;
   const int rc_fwd = nnlib_b200_attn_fwd(&q, stream);
   if (rc_fwd != NNLIB_B200_OK) return rc_fwd;
   return nnlib_b200_attn_scores(&q, stream);

@@ -422,17 +422,29 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[32];
         // exponentials of 64 keys (chunks 2*HF, 2*HF+1) relative to REF, packed into pk, summed into sum4
-#define NB_EXP_HALF(HF, REF)                                                                       \
+        // SEL (a literal): rows whose reference is +Inf put weight 1 on their +Inf logits and 0 elsewhere
+        // (the slow branch of the reference's softmax, src/softmax.jl:73-75) instead of exp2(Inf - Inf)
+#define NB_EXP_HALF(HF, REF, SEL)                                                                  \
   do {                                                                                             \
-    const float nref_ = -(REF);                                                                    \
+    const float ref_ = (REF);                                                                      \
+    const float nref_ = -ref_;                                                                     \
     _Pragma("unroll") for (int cc = 0; cc < 2; ++cc) {                                             \
       _Pragma("unroll") for (int e = 0; e < 32; e += 2) {                                          \
         float p0 = ex2_approx(fmaf(__uint_as_float(sr[(HF) * 2 + cc][e]), cs, nref_));             \
         float p1 = ex2_approx(fmaf(__uint_as_float(sr[(HF) * 2 + cc][e + 1]), cs, nref_));         \
+        if ((SEL) && ref_ == pos_inf()) {                                                          \
+          p0 = (sr[(HF) * 2 + cc][e] == 0x7f800000u) ? 1.f : 0.f;                                  \
+          p1 = (sr[(HF) * 2 + cc][e + 1] == 0x7f800000u) ? 1.f : 0.f;                              \
+        }                                                                                          \
         sum4[(e >> 1) & 3] += p0 + p1;                                                             \
         pk[cc * 16 + (e >> 1)] = pack2<BF16>(p0, p1);                                              \
       }                                                                                            \
     }                                                                                              \
+  } while (0)
+        // one of the two expansions, chosen per warp: the +Inf form only when a row of this warp needs it
+#define NB_EXP_HALF_W(HF, REF)                                                                     \
+  do {                                                                                             \
+    if (XBIAS && infw) NB_EXP_HALF(HF, REF, 1); else NB_EXP_HALF(HF, REF, 0);                      \
   } while (0)
 
         // full-tile maximum (3-input max: 64 instructions); independent of the first exponentials below
@@ -452,13 +464,17 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         const float m_new = fmaxf(m_used, mx);
         const bool raise = m_new > m_used + kRescaleGap;   // also true for m_used = -inf < m_new
+        // A +Inf logit can only come from the bias.  A row that meets one moves its reference to +Inf
+        // (the rescale factor exp2(old - Inf) = 0 clears what it had gathered) and from then on counts
+        // its +Inf logits; the warp takes the selecting form of the exponentials while it has such a row.
+        const bool infw = XBIAS && __any_sync(0xffffffffu, m_new == pos_inf());
 
         if (!STATS) {
           // First 64 exponentials against the running reference while the maximum above is still being
           // reduced (different pipes).  Later tiles almost never move the reference; when one does, the
           // half is simply redone below.  The very first tile has no reference yet and skips the guess.
-          const bool guess = (j > 0);
-          if (guess) NB_EXP_HALF(0, (m_used == neg_inf()) ? 0.f : m_used);
+          const bool guess = (j > 0) && !infw;
+          if (guess) NB_EXP_HALF(0, (m_used == neg_inf()) ? 0.f : m_used, 0);
           if (!guess || __any_sync(0xffffffffu, raise)) {
             if (j > 0) {
               const float f = raise ? ex2_approx(m_used - m_new) : 1.f;  // m_used = -inf gives 0: O is still 0 there
@@ -475,13 +491,13 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             if (raise) m_used = m_new;
             sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
-            NB_EXP_HALF(0, (m_used == neg_inf()) ? 0.f : m_used);
+            NB_EXP_HALF_W(0, (m_used == neg_inf()) ? 0.f : m_used);
           }
           if (r == 0) NB_TRACE(t, j, 3);
           const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
-            if (hf == 1) NB_EXP_HALF(1, m_sub);
+            if (hf == 1) NB_EXP_HALF_W(1, m_sub);
             if (DROP) {
               // the row sum keeps the dropped scores (dropout follows the softmax)
 #pragma unroll
@@ -510,9 +526,10 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             m_used = m_new;
           }
           const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
-          NB_EXP_HALF(0, m_sub);
-          NB_EXP_HALF(1, m_sub);
+          NB_EXP_HALF_W(0, m_sub);
+          NB_EXP_HALF_W(1, m_sub);
         }
+#undef NB_EXP_HALF_W
 #undef NB_EXP_HALF
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         if (r == 0) NB_TRACE(t, j, 6);
@@ -522,7 +539,9 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (ok) {
         const bool dead = !(l > 0.f);
         if (a.lse && row_ok) {
-          a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = dead ? neg_inf() : (m_used + log2f(l)) * kLn2;
+          float lse_v = (l != l) ? __int_as_float(0x7fc00000) : dead ? neg_inf() : (m_used + log2f(l)) * kLn2;
+          if (XBIAS && m_used == pos_inf() && !dead) lse_v = lse_inf_rows(l);   // l = number of +Inf logits
+          a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = lse_v;
         }
         if (!STATS) {
           ok = mbar_wait(&bars->o_full[t], 0, abort_flag);
@@ -742,9 +761,14 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     const int lim = a.causal ? min(i, a.Lkv - 1) : a.Lkv - 1;
     const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
     const float lse_nat = row_ok ? a.lse[i + (long long)a.Lq * h + a.lse_sb * b] : 0.f;
-    const bool dead = (lse_nat == neg_inf());
+    // rows that need a constant instead of an exponential: nothing to attend to (NaN like the reference,
+    // or 0), or a NaN among the logits (the reference's column is NaN throughout)
+    const bool dead = (lse_nat == neg_inf()) || (lse_nat != lse_nat && !lse_is_inf_rows(lse_nat));
     const float lse2 = dead ? 0.f : lse_nat * kLog2e;
-    const float dead_val = a.nan_fm ? __int_as_float(0x7fc00000) : 0.f;
+    const float dead_val = (a.nan_fm || lse_nat != lse_nat) ? __int_as_float(0x7fc00000) : 0.f;
+    // a row whose largest logit is +Inf: equal shares on its +Inf logits (src/softmax.jl:73-75)
+    const bool rinf = XBIAS && lse_is_inf_rows(lse_nat);
+    const float inf_share = rinf ? 1.f / lse_inf_count(lse_nat) : 0.f;
     T* arow = reinterpret_cast<T*>(a.alpha) + ((long long)i + (long long)a.Lq * h) * a.Lkv + a.alpha_sb * b;
     RowSide rs;
     if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
@@ -819,6 +843,10 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             if (EXTRAS) {
               a0 = ex2_approx(__uint_as_float(sr[c & 1][e]) - lse2);        // -inf (masked) gives 0
               a1 = ex2_approx(__uint_as_float(sr[c & 1][e + 1]) - lse2);
+              if (XBIAS && rinf) {
+                a0 = (sr[c & 1][e] == 0x7f800000u) ? inf_share : 0.f;
+                a1 = (sr[c & 1][e + 1] == 0x7f800000u) ? inf_share : 0.f;
+              }
             } else {
               a0 = (jc + e <= lim) ? ex2_approx(fmaf(__uint_as_float(sr[c & 1][e]), c2, -lse2)) : 0.f;
               a1 = (jc + e + 1 <= lim) ? ex2_approx(fmaf(__uint_as_float(sr[c & 1][e + 1]), c2, -lse2)) : 0.f;
@@ -1111,22 +1139,26 @@ bool make_bias_map(CUtensorMap* m, const AttnArgs& a) {
 
 }  // namespace
 
-bool umma_supports(const AttnArgs& a, int dtype, bool need_v) {
-  if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
-  if (!(a.d == 64 || a.d == 128)) return false;
-  if (need_v && a.dv != a.d) return false;
-  if (!(a.scale > 0.f)) return false;
-  if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1) return false;
-  if (!aligned16(a.q) || !aligned16(a.k) || !stride_ok(a.q_sl) || !stride_ok(a.k_sl) || !stride_ok(a.q_sb) ||
-      !stride_ok(a.k_sb))
-    return false;
+// nullptr when the tensor-core kernels take the call, else the reason they do not
+const char* umma_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
+  if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return "element type is not Float16 / BFloat16";
+  if (!(a.d == 64 || a.d == 128)) return "head size d is not 64 or 128";
+  if (need_v && a.dv != a.d) return "dv differs from d";
+  if (!(a.scale > 0.f)) return "scale is not positive";
+  if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1) return "empty problem";
+  if (!aligned16(a.q) || !aligned16(a.k)) return "q or k is not 16-byte aligned";
+  if (!stride_ok(a.q_sl) || !stride_ok(a.k_sl) || !stride_ok(a.q_sb) || !stride_ok(a.k_sb))
+    return "a stride of q or k is not a positive multiple of 8 elements";
   if (need_v) {
-    if (!aligned16(a.v) || !aligned16(a.x) || !stride_ok(a.v_sl) || !stride_ok(a.v_sb) || !stride_ok(a.x_sl) ||
-        !stride_ok(a.x_sb))
-      return false;
+    if (!aligned16(a.v) || !aligned16(a.x)) return "v or x is not 16-byte aligned";
+    if (!stride_ok(a.v_sl) || !stride_ok(a.v_sb) || !stride_ok(a.x_sl) || !stride_ok(a.x_sb))
+      return "a stride of v or x is not a positive multiple of 8 elements";
   }
-  return encode_tiled_fn() != nullptr;
+  if (encode_tiled_fn() == nullptr) return "the driver does not export cuTensorMapEncodeTiled";
+  return nullptr;
 }
+
+bool umma_supports(const AttnArgs& a, int dtype, bool need_v) { return umma_reject_reason(a, dtype, need_v) == nullptr; }
 
 cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
@@ -1237,6 +1269,35 @@ extern "C" __attribute__((visibility("default"))) int nnlib_b200_trace_dump(long
   return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 4 * 64 * 8);
 }
 #endif
+
+// Self-test of the bounded wait: one CTA waits, with the same mbar_wait every kernel here uses, on a
+// barrier that nobody ever arrives at.  The wait gives up after `limit_ns`, the CTA leaves through the
+// same exit the attention kernels take (sticky device flag, optional status word) and the kernel returns
+// by itself.  Nothing faults or hangs; the device stays usable.
+namespace {
+__global__ void wait_runout_kernel(unsigned long long limit_ns, int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag, limit_ns);
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag) {
+    atomicExch(&g_umma_abort, 1);
+    if (status) atomicExch(status, NNLIB_B200_TIMEOUT);
+  }
+}
+}  // namespace
+
+cudaError_t umma_wait_runout(unsigned long long limit_ns, int* status, cudaStream_t st) {
+  wait_runout_kernel<<<1, 32, 0, st>>>(limit_ns, status);
+  count_launch();
+  return cudaGetLastError();
+}
 
 // Reads and clears the sticky "a bounded wait ran out" flag of the current
 // device.  Synchronises the stream.

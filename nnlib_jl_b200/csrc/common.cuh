@@ -134,6 +134,22 @@ __device__ __forceinline__ unsigned long long score_row(const AttnArgs& a, int i
                                      (unsigned long long)a.rng_H * (unsigned long long)(b + a.rng_b0));
 }
 
+// ---- log-sum-exp of a query whose largest logit is +Inf ---------------------------------------------
+// The reference's softmax gives such a query equal shares on its +Inf logits (NNlib.jl src/softmax.jl:73-75),
+// so what the scores kernel needs later is their number, not a logarithm.  It travels in the lse array as a
+// NaN whose quiet bit is clear and whose low 22 bits hold the count (at least 1, saturating); an ordinary
+// NaN (a NaN among the logits: the reference's whole column is NaN) has the quiet bit set.
+__device__ __forceinline__ float lse_inf_rows(float count) {
+  unsigned int n = (count >= 4194303.f) ? 0x3fffffu : (unsigned int)count;
+  if (n == 0u) n = 1u;
+  return __uint_as_float(0x7f800000u | n);
+}
+__device__ __forceinline__ bool lse_is_inf_rows(float lse) {
+  const unsigned int b = __float_as_uint(lse);
+  return (b & 0xffc00000u) == 0x7f800000u && (b & 0x003fffffu) != 0u;
+}
+__device__ __forceinline__ float lse_inf_count(float lse) { return (float)(__float_as_uint(lse) & 0x003fffffu); }
+
 // launch bookkeeping shared by all translation units
 void count_launch(int n = 1);
 void set_last_cuda_error(cudaError_t e);

@@ -6,6 +6,9 @@
 
 namespace nb200 {
 
+// argument check of the x + alpha composites (api.cu): everything attn_fwd and attn_scores would reject
+int attention_validate(const nnlib_b200_attn_params* p);
+
 // CUDA-core kernels (attn_simt.cu)
 bool simt_supports(int d, int dv);
 cudaError_t simt_fwd(const AttnArgs& a, int dtype, cudaStream_t st);
@@ -21,11 +24,13 @@ cudaError_t simt_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_
 
 // tcgen05 + TMA kernels (attn_umma.cu)
 bool umma_supports(const AttnArgs& a, int dtype, bool need_v);
+const char* umma_reject_reason(const AttnArgs& a, int dtype, bool need_v);
 cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t st);
 cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st);
 bool umma_apply_supports(const AttnArgs& a, int dtype);
 cudaError_t umma_apply(const AttnArgs& a, int dtype, cudaStream_t st);
 cudaError_t umma_take_abort(int* out, cudaStream_t st);
+cudaError_t umma_wait_runout(unsigned long long limit_ns, int* status, cudaStream_t st);
 
 // tcgen05 backward kernels (attn_bwd_umma.cu)
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype);

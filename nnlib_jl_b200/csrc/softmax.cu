@@ -110,7 +110,10 @@ __device__ __forceinline__ uint4 repack<__half>(const float (&f)[8]) {
   return q;
 }
 template <typename T>
-__device__ __forceinline__ uint4 load_raw(const T* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// plain (coherent) load: the output may be the input array itself (softmax!(x, x) of the reference), and a
+// column longer than a thread's register share is read a second time after other threads may have
+// written theirs, so the non-coherent path and `__restrict__` are both out
+__device__ __forceinline__ uint4 load_raw(const T* p) { return *reinterpret_cast<const uint4*>(p); }
 template <typename T>
 __device__ __forceinline__ void load_pack(const T* p, float (&f)[Pack<T>::V]) { unpack<T>(load_raw<T>(p), f); }
 template <typename T>
@@ -168,8 +171,7 @@ __device__ __forceinline__ void fwd_pack(const ColStat& c, float inv_s, float lo
 // KP > 0 (with VECT): a thread's packets (at most KP, as raw 16-byte words) stay in registers between
 // the two passes, so the column is read from memory once.
 template <typename T, int MODE, int G, bool VECT, int KP>
-__global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const T* __restrict__ x, const T* __restrict__ dy,
-                                                                            T* __restrict__ out, long long n, long long cols) {
+__global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const T* x, const T* dy, T* out, long long n, long long cols) {
   constexpr int kBlock = G > 256 ? G : 256;
   constexpr int kPerBlock = kBlock / G;
   constexpr int kWarps = kBlock / 32;
@@ -377,8 +379,7 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
 
 // ---- reduction dimension strided (inner > 1): one thread per (i, o), neighbours along i coalesce ----
 template <typename T, int MODE>
-__global__ void __launch_bounds__(256) softmax_strided_kernel(const T* __restrict__ x, const T* __restrict__ dy,
-                                                              T* __restrict__ out, long long inner, long long n,
+__global__ void __launch_bounds__(256) softmax_strided_kernel(const T* x, const T* dy, T* out, long long inner, long long n,
                                                               long long outer) {
   const long long total = inner * outer;
   for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += (long long)gridDim.x * blockDim.x) {

@@ -75,7 +75,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // so the CTA falls through to its teardown instead of hanging the GPU.
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_test_wait(bar, parity)) return true;
   // hot phase: nothing but the barrier, so a completed phase is seen at once
 #pragma unroll 1
@@ -89,7 +90,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     for (int it = 0; it < 32; ++it)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (globaltimer_ns() - t0 > limit_ns) {
       *abort_flag = 1;
       return false;
     }

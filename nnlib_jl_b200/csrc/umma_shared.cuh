@@ -24,6 +24,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr unsigned long long kDrainNs = 20ull * 1000 * 1000;  // 20 ms for in-flight copies on abort
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+__device__ __forceinline__ float pos_inf() { return __int_as_float(0x7f800000); }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;

@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-from .attention import ArgumentError, CausalMask, _fused_into
+from .attention import ArgumentError, CausalMask, _fused_into, check_status
 from .layout import jl_empty
 
 __all__ = ["HostPipelinedAttention"]
@@ -110,4 +110,6 @@ class HostPipelinedAttention:
         return hx
 
     def synchronize(self) -> None:
+        """Wait for the last call's results; raises if one of its kernels gave up on a bounded wait."""
         self.done.synchronize()
+        check_status(self.dev)

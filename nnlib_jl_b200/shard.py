@@ -185,6 +185,8 @@ class ShardedAttention:
                     x[rect.h0 * dv:(rect.h0 + rect.nh) * dv, :, bs].copy_(y, non_blocking=True)
                 if str(res.device).startswith("cuda"):
                     torch.cuda.synchronize(res.device)
+                    from .attention import check_status
+                    check_status(res.device)      # a kernel that gave up fails this shard, not the others
                 res.ok = True
             except BaseException as e:  # reported per shard, never swallowed
                 res.error = e

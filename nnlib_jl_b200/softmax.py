@@ -35,10 +35,10 @@ def _split(shape, dims):
     return math.prod(full[:lo]), math.prod(full[lo:hi]), math.prod(full[hi:])
 
 
-def _run(x: torch.Tensor, dy: Optional[torch.Tensor], dims, log: bool) -> torch.Tensor:
+def _run(x: torch.Tensor, dy: Optional[torch.Tensor], dims, log: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if isinstance(x, torch.Tensor) and x.is_cuda and x.numel() == 0:
         _split(x.shape, dims)                       # still validates dims
-        return jl_empty(tuple(x.shape), x.dtype, x.device)
+        return out if out is not None else jl_empty(tuple(x.shape), x.dtype, x.device)
     _require_dense_cuda("x", x)
     if not is_column_major(x):
         raise ArgumentError("softmax: the array must be dense column-major")
@@ -46,7 +46,14 @@ def _run(x: torch.Tensor, dy: Optional[torch.Tensor], dims, log: bool) -> torch.
         _require_dense_cuda("dy", dy)
         if tuple(dy.shape) != tuple(x.shape) or dy.dtype != x.dtype or not is_column_major(dy):
             raise ArgumentError("softmax pullback: dy must match y in size, eltype and layout")
-    out = jl_empty(tuple(x.shape), x.dtype, x.device)
+    if out is None:
+        out = jl_empty(tuple(x.shape), x.dtype, x.device)
+    else:
+        # softmax!(out, x): the result array is the caller's; it may be x (or dy) itself
+        _require_dense_cuda("out", out)
+        if tuple(out.shape) != tuple(x.shape) or out.dtype != x.dtype or not is_column_major(out) \
+                or out.device != x.device:
+            raise ArgumentError("softmax!: out must match the input in size, eltype, layout and device")
     inner, n, outer = _split(x.shape, dims)
     p = _lib.SoftmaxParams()
     p.dtype = _DTYPES[x.dtype]
@@ -64,21 +71,26 @@ def _run(x: torch.Tensor, dy: Optional[torch.Tensor], dims, log: bool) -> torch.
     return out
 
 
-def softmax(x: torch.Tensor, *, dims: Optional[int] = 1) -> torch.Tensor:
-    """``softmax(x; dims)`` (``src/softmax.jl:56``)."""
-    return _run(x, None, dims, log=False)
+def softmax(x: torch.Tensor, *, dims: Optional[int] = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``softmax(x; dims)`` (``src/softmax.jl:56``); with ``out`` it is ``softmax!(out, x; dims)``
+    (``:66-67``) and ``out`` may be ``x`` itself."""
+    return _run(x, None, dims, log=False, out=out)
 
 
-def logsoftmax(x: torch.Tensor, *, dims: Optional[int] = 1) -> torch.Tensor:
-    """``logsoftmax(x; dims)`` (``src/softmax.jl:133``)."""
-    return _run(x, None, dims, log=True)
+def logsoftmax(x: torch.Tensor, *, dims: Optional[int] = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``logsoftmax(x; dims)`` (``src/softmax.jl:133``); ``out`` as in :func:`softmax`."""
+    return _run(x, None, dims, log=True, out=out)
 
 
-def softmax_pullback(dy: torch.Tensor, y: torch.Tensor, *, dims: Optional[int] = 1) -> torch.Tensor:
-    """``∇softmax(dy, y; dims) = y .* (dy .- sum(dy .* y; dims))`` (``src/softmax.jl:84-101``)."""
-    return _run(y, dy, dims, log=False)
+def softmax_pullback(dy: torch.Tensor, y: torch.Tensor, *, dims: Optional[int] = 1,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``∇softmax(dy, y; dims) = y .* (dy .- sum(dy .* y; dims))`` (``src/softmax.jl:84-101``); with ``out``
+    it is ``∇softmax!(out, dy, y)``, and ``out`` may be ``dy`` or ``y``."""
+    return _run(y, dy, dims, log=False, out=out)
 
 
-def logsoftmax_pullback(dy: torch.Tensor, y: torch.Tensor, *, dims: Optional[int] = 1) -> torch.Tensor:
-    """``∇logsoftmax(dy, y; dims) = dy .- sum(dy; dims) .* exp.(y)`` (``src/softmax.jl:164-190``)."""
-    return _run(y, dy, dims, log=True)
+def logsoftmax_pullback(dy: torch.Tensor, y: torch.Tensor, *, dims: Optional[int] = 1,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``∇logsoftmax(dy, y; dims) = dy .- sum(dy; dims) .* exp.(y)`` (``src/softmax.jl:164-190``); ``out`` as
+    in :func:`softmax_pullback`."""
+    return _run(y, dy, dims, log=True, out=out)

@@ -294,3 +294,33 @@ def dot_product_attention_grad(q, k, v, dy, bias=None, *, mask=None, nheads=1, k
         axes = tuple(ax for ax in range(4) if b4.shape[ax] == 1 and dlogits.shape[ax] != 1)
         dbias = np.sum(dlogits, axis=axes, keepdims=True).reshape(np.asarray(bias).shape)
     return join_heads(dq4), join_heads(dk4), join_heads(dv4), dbias
+
+
+def attention_grad_unit(q, k, v, dy, nheads, b, h, *, causal=False, dtype=np.float64):
+    """Pullback of :func:`dot_product_attention` restricted to ONE ``(b, h)`` unit, in ``dtype`` (Float64):
+    the same rules as :func:`dot_product_attention_grad` (``src/batched/batchedmul.jl:96-110``,
+    ``src/softmax.jl:84-110``, ``src/attention.jl:118``) on the unit's ``(Lkv, Lq)`` score matrix only, so
+    that a single unit of a problem whose whole score array fits nowhere can be checked exactly.  ``q``,
+    ``k``, ``v``, ``dy`` are 3-d ``(E, L, B)`` arrays; returns ``(dq (d, Lq), dk (d, Lkv), dv (dv, Lkv))``
+    of that unit.  Units are independent (``batched_mul`` never mixes batch indices), so these are the
+    unit's slices of the full gradient."""
+    d = q.shape[0] // nheads
+    dv_ = v.shape[0] // nheads
+    qh = np.asarray(q[h * d:(h + 1) * d, :, b], dtype=dtype)            # (d, Lq)
+    kh = np.asarray(k[h * d:(h + 1) * d, :, b], dtype=dtype)            # (d, Lkv)
+    vh = np.asarray(v[h * dv_:(h + 1) * dv_, :, b], dtype=dtype)        # (dv, Lkv)
+    dyh = np.asarray(dy[h * dv_:(h + 1) * dv_, :, b], dtype=dtype)      # (dv, Lq)
+    scale = dtype(1.0 / math.sqrt(d))
+    logits = kh.T @ (qh * scale)                                        # (Lkv, Lq)
+    if causal:
+        keep = np.arange(kh.shape[1])[:, None] <= np.arange(qh.shape[1])[None, :]
+        logits = np.where(keep, logits, -np.inf)
+    alpha = softmax(logits, dims=0)
+    del logits
+    dvh = dyh @ alpha.T                                                 # dv[e,j] = Σ_i dy[e,i] α[j,i]
+    dalpha = vh.T @ dyh                                                 # (Lkv, Lq)
+    dlogits = alpha * (dalpha - np.sum(dalpha * alpha, axis=0, keepdims=True))
+    del alpha, dalpha
+    dqh = scale * (kh @ dlogits)                                        # (d, Lq)
+    dkh = scale * (qh @ dlogits.T)                                      # (d, Lkv)
+    return dqh, dkh, dvh

@@ -7,6 +7,7 @@ evaluated on the upcast inputs:
     bf16 : 2e-2 , 5e-3        f16 : 3e-3 , 1e-3        f32 : 1e-5 (atol, like the reference's GPU tests)
 """
 import math
+import time
 
 import numpy as np
 import pytest
@@ -189,6 +190,55 @@ def test_fully_masked_query_is_nan():
 # --------------------------------------------------------------------------
 # tensor-core path vs oracle on ragged and benchmark shapes
 # --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype,d,Lkv", [
+    (torch.bfloat16, 64, 304),     # bias rows 16-byte aligned: tiles of the bias staged by TMA
+    (torch.float16, 64, 300),      # per-thread bias loads
+    (torch.float16, 128, 304),
+    (torch.float32, 32, 300),      # CUDA-core kernels
+])
+def test_plus_inf_and_nan_logits_follow_the_reference_softmax(dtype, d, Lkv):
+    """src/softmax.jl:71-76 through attention: a +Inf bias means "always attend here" (equal shares on the
+    +Inf keys, also when the first one shows up in a later key tile than finite logits did, and not on a
+    key the mask removes); a NaN bias makes the query's scores and output NaN."""
+    rng = np.random.default_rng(31)
+    H, Lq, B = 2, 150, 1
+    E = d * H
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    bn = _round_to(0.5 * rng.standard_normal((Lkv, Lq, H, B)), dtype)
+    bn[2, 0] = np.inf                      # one key, first tile
+    bn[[1, 290], 1] = np.inf               # two keys, first and last tile
+    bn[200, 5] = np.inf                    # appears after a tile of finite logits
+    bn[[3, 130, 131, 299], 140] = np.inf   # second query tile
+    bn[7, 6] = np.inf                      # on a masked key: the mask wins
+    bn[10, 9] = np.nan
+    mask = np.ones((Lkv, Lq), dtype=bool)
+    mask[7, 6] = False
+    q, k, v, b = (_dev(a, dtype) for a in (qn, kn, vn, bn))
+    m = nb.jl_from_numpy(mask, device=DEV)
+    y, a = nb.dot_product_attention(q, k, v, b, mask=m, nheads=H)
+    yo, ao = O.dot_product_attention(qn, kn, vn, bn, mask=mask, nheads=H)
+    yn, an = nb.jl_to_numpy(y), np.asarray(a)
+    assert np.isnan(an[:, 9]).all() and np.isnan(ao[:, 9]).all()
+    for h in range(H):
+        assert np.isnan(yn[h * d:(h + 1) * d, 9]).all()
+        np.testing.assert_array_equal(an[:, 0, h, 0], ao[:, 0, h, 0])          # exactly one-hot
+        np.testing.assert_array_equal(an[:, 1, h, 0], ao[:, 1, h, 0])          # exactly 0.5 / 0.5
+        np.testing.assert_array_equal(an[:, 5, h, 0], ao[:, 5, h, 0])
+        np.testing.assert_array_equal(an[:, 140, h, 0], ao[:, 140, h, 0])      # 0.25 each
+        assert an[7, 6, h, 0] == 0
+    ok = np.ones(Lq, dtype=bool); ok[9] = False
+    _close(yn[:, ok], yo[:, ok], dtype, "x")
+    _close(an[:, ok], ao[:, ok], dtype, "alpha")
+    # the scores-only entry (statistics kernel + scores kernel)
+    q4, k4 = (nb.jl_reshape(t, (d, H, t.shape[1], B)) for t in (q, k))
+    a2 = nb.jl_to_numpy(nb.dot_product_attention_scores(q4, k4, b, mask=m))
+    np.testing.assert_array_equal(np.isnan(a2), np.isnan(an))
+    np.testing.assert_array_equal(a2[:, [0, 1, 5, 140]], an[:, [0, 1, 5, 140]])
+    _close(a2[:, ok], ao[:, ok], dtype, "alpha (scores entry)")
+
 
 def _run_case(dtype, E, nheads, Lq, Lkv, B, *, causal=False, mask=None, bias=None, Ev=None, seed=0,
               expect_umma=True, check_alpha=True):
@@ -428,6 +478,56 @@ def test_abi_attention_one_call_with_workspace():
     _close(nb.jl_to_numpy(alpha), ao, dtype, "alpha")
 
 
+def test_bounded_wait_runout_is_reported_and_the_device_stays_usable():
+    """The fail-stop path end to end, without faulting or hanging anything: a self-test kernel waits with
+    the library's bounded wait (limit 5 ms here) on a barrier nobody arrives at and returns by itself.
+    Then: the status word says TIMEOUT; the device is marked, so a later tensor-core launch returns at
+    once, leaves its output untouched and reports through ITS status word; the Python wrapper raises at
+    its next synchronisation point; device_health reports the mark once and clears it; and the next
+    ordinary call is correct again."""
+    import ctypes as C
+    lib = _lib.load()
+    rng = np.random.default_rng(35)
+    dtype, H, d, L, B = torch.bfloat16, 2, 64, 200, 1
+    qn, kn, vn = (_round_to(rng.standard_normal((H * d, L, B)), dtype) for _ in range(3))
+    q, k, v = (_dev(a, dtype) for a in (qn, kn, vn))
+    st = torch.cuda.current_stream().cuda_stream
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    t0 = time.perf_counter()
+    assert lib.nnlib_b200_selftest_wait_runout(5_000_000, status.data_ptr(), st) == _lib.OK
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 2.0, "the wait did not run out by itself"
+    assert status.item() == _lib.TIMEOUT
+    try:
+        # a launch on the marked device: skipped, output untouched, status word set
+        x = nb.jl_empty((H * d, L, B), dtype, DEV)
+        x.fill_(7.0)
+        status2 = torch.zeros(1, dtype=torch.int32, device=DEV)
+        p = _lib.AttnParams()
+        p.dtype = _lib.BF16
+        p.d, p.dv, p.H, p.Lq, p.Lkv, p.B = d, d, H, L, L, B
+        p.q, p.k, p.v, p.x, p.status = q.data_ptr(), k.data_ptr(), v.data_ptr(), x.data_ptr(), status2.data_ptr()
+        assert lib.nnlib_b200_attn_path(p) == _lib.PATH_UMMA
+        assert lib.nnlib_b200_attn_fwd(C.byref(p), st) == _lib.OK
+        torch.cuda.synchronize()
+        assert status2.item() == _lib.TIMEOUT
+        assert (x.float() == 7.0).all()
+        # the wrapper passes its own status word and raises where it synchronises anyway
+        y, _ = nb.dot_product_attention(q, k, v, nheads=H)
+        with pytest.raises(_lib.NNlibB200Error) as ei:
+            nb.check_status(DEV)
+        assert ei.value.code == _lib.TIMEOUT
+    finally:
+        # reported once, then clear
+        assert lib.nnlib_b200_device_health(st) == _lib.TIMEOUT
+    assert lib.nnlib_b200_device_health(st) == _lib.OK
+    nb.check_status(DEV)
+    y, a = nb.dot_product_attention(q, k, v, nheads=H)
+    yo, ao = O.dot_product_attention(qn, kn, vn, nheads=H)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x after the mark was cleared")
+    _close(np.asarray(a), ao, dtype, "alpha after the mark was cleared")
+
+
 def test_causal_check_kernel():
     import ctypes as C
     lib = _lib.load()
@@ -441,6 +541,46 @@ def test_causal_check_kernel():
     m[5, 3] = True   # below the diagonal
     assert lib.nnlib_b200_causal_check(m.view(torch.uint8).data_ptr(), L, flag.data_ptr(), st) == 0
     assert flag.item() == 0
+
+
+def test_causal_matrix_is_trusted_only_while_unmodified():
+    """make_causal_mask's result selects the causal mode without being read — until somebody writes to it;
+    any other square Bool matrix is read each time, so neither a modified matrix nor a new matrix that
+    lands on a freed one's address is ever mistaken for the causal pattern."""
+    rng = np.random.default_rng(30)
+    dtype, E, H, L, B = torch.bfloat16, 128, 2, 160, 1
+    qn, kn, vn = (_round_to(rng.standard_normal((E, L, B)), dtype) for _ in range(3))
+    q, k, v = (_dev(a, dtype) for a in (qn, kn, vn))
+    lib = _lib.load()
+
+    def run(mask_dev, mask_np):
+        n0 = lib.nnlib_b200_launch_count()
+        y, _ = nb.dot_product_attention(q, k, v, mask=mask_dev, nheads=H)
+        launches = lib.nnlib_b200_launch_count() - n0
+        yo, _ = O.dot_product_attention(qn, kn, vn, mask=mask_np, nheads=H)
+        _close(nb.jl_to_numpy(y), yo, dtype, "x")
+        return launches
+
+    # (1) fresh make_causal_mask result: one launch (the fused kernel), no check
+    m = nb.make_causal_mask(q)
+    assert run(m, O.make_causal_mask(qn)) == 1
+    # (2) written to (version counter moves): read again, and the new contents count
+    m[5, 2] = True                                   # key 5 visible to query 2
+    mn = O.make_causal_mask(qn).copy(); mn[5, 2] = True
+    assert run(m, mn) == 3                           # flag set + check + fused kernel
+    # (3) a user-built causal matrix is checked on every call, also the second time
+    tri = nb.jl_from_numpy(O.make_causal_mask(qn), device=DEV)
+    assert run(tri, O.make_causal_mask(qn)) == 3
+    assert run(tri, O.make_causal_mask(qn)) == 3
+    # (4) free it and put a random matrix of the same size where it was
+    addr = tri.data_ptr()
+    del tri
+    rn = rng.random((L, L)) > 0.3
+    rn[0, :] = True
+    rnd = nb.jl_from_numpy(rn, device=DEV)
+    if rnd.data_ptr() != addr:
+        pytest.skip("the allocator did not reuse the freed block")
+    run(rnd, rn)
 
 
 # --------------------------------------------------------------------------
@@ -463,6 +603,21 @@ def _check_rows(q, k, v, y, lse, H, units, dtype, *, causal=False, mask=None, bi
         _close(yn[h * d:(h + 1) * d][:, rows, b], xr.astype(np.float32), dtype, f"x rows of unit {(b, h)}")
         if lse is not None:
             np.testing.assert_allclose(lse[rows, h, b], lr, atol=2e-2)
+
+
+def test_config1_float32_exact():
+    """BASELINE config 1 exactly: Float32, E=512, nheads=8 (d=64), Lq=Lkv=128, batch=4, no mask / bias,
+    fdrop = identity, (x, α) returned with α of size (128, 128, 8, 4); whole oracle, atol 1e-5 like the
+    reference's own CPU-vs-GPU tests (test/ext_amdgpu/attention.jl:19-21)."""
+    rng = np.random.default_rng(1234)
+    E, H, L, B = 512, 8, 128, 4
+    qn, kn, vn = (rng.standard_normal((E, L, B), dtype=np.float32) for _ in range(3))
+    y, a = nb.dot_product_attention(_dev(qn, torch.float32), _dev(kn, torch.float32), _dev(vn, torch.float32),
+                                    nheads=H)
+    yo, ao = O.dot_product_attention(qn, kn, vn, nheads=H)
+    assert tuple(y.shape) == (E, L, B) and tuple(a.shape) == (L, L, H, B)
+    np.testing.assert_allclose(nb.jl_to_numpy(y), yo, atol=1e-5, rtol=0)
+    np.testing.assert_allclose(np.asarray(a), ao, atol=1e-5, rtol=0)
 
 
 def test_config2_encoder_key_padding():
@@ -671,6 +826,36 @@ def test_pullback_on_tensor_cores(dtype, E, H, Lq, Lkv, B, causal):
     _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq")
     _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
     _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+
+
+def test_pullback_at_config3_size_unit_sampled():
+    """The tcgen05 backward at the size its throughput is quoted on: bf16, E=4096, nheads=32 (d=128),
+    L=4096, causal (32 key / query tiles per unit: causal tile skipping, ring wrap-around, the lse / D
+    double buffer of the dk/dv half).  Two whole units are compared with the Float64 gradient oracle of a
+    single unit, every row and column of them — rows / keys 0, 127, 128, L-129, L-1 included."""
+    dtype, E, H, L, B = torch.bfloat16, 4096, 32, 4096, 2
+    g = torch.Generator(device=DEV).manual_seed(66)
+    q, k, v, dx = (nb.jl_empty((E, L, B), dtype, DEV) for _ in range(4))
+    for t in (q, k, v, dx):
+        t.normal_(generator=g)
+    x, a, back = nb.dot_product_attention_pullback(q, k, v, mask=nb.make_causal_mask(q), nheads=H)
+    dq, dk, dv, _ = back(dx)
+    assert back.path == nb._lib.PATH_UMMA
+    nb.device_health()
+    d = E // H
+    for (b, h) in [(0, 0), (1, 31)]:
+        sl = slice(h * d, (h + 1) * d)
+        qn, kn, vn, dyn = (t[sl, :, b:b + 1].float().cpu().numpy() for t in (q, k, v, dx))
+        gq, gk, gv = O.attention_grad_unit(qn, kn, vn, dyn, 1, 0, 0, causal=True)
+        for name, got, want in (("dq", dq, gq), ("dk", dk, gk), ("dv", dv, gv)):
+            got_n = got[sl, :, b].float().cpu().numpy()
+            _grad_close(got_n, want, dtype, f"{name} of unit {(b, h)}")
+            # single rows / keys on their own scale (floored at 5 % of the unit's: query 0 attends to one
+            # key only, so its dq is an exact zero in the oracle and pure rounding noise on the device)
+            for pos in (0, 127, 128, L - 129, L - 1):
+                scale = max(np.abs(want[:, pos]).max(), 0.05 * np.abs(want).max())
+                err = np.abs(got_n[:, pos].astype(np.float64) - want[:, pos]).max()
+                assert err <= 4e-2 * scale, f"{name}[:, {pos}] of unit {(b, h)}: {err / scale:.3e}"
 
 
 @pytest.mark.parametrize("dtype,E,H,Lq,Lkv,B,kind", [

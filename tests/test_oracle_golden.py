@@ -218,3 +218,66 @@ def test_gradient_oracle_against_finite_differences(with_mask, with_drop):
     np.testing.assert_allclose(dk, _fd(lambda t: f(q, t, v, bias), k), atol=1e-6, rtol=1e-6)
     np.testing.assert_allclose(dv, _fd(lambda t: f(q, k, t, bias), v), atol=1e-6, rtol=1e-6)
     np.testing.assert_allclose(db, _fd(lambda t: f(q, k, v, t), bias), atol=1e-6, rtol=1e-6)
+
+
+def test_config1_on_the_oracle():
+    """BASELINE config 1 exactly: Float32 q, k, v ~ N(0,1), E=512, nheads=8 (d=64), Lq=Lkv=128, batch=4, no
+    mask / bias, fdrop = identity; returns (x, α) with α of size (128, 128, 8, 4).  The Float32 oracle must
+    agree with its own Float64 row-restricted form and keep the reference's structural properties
+    (test/attention.jl:1-15: sizes, columns of α sum to 1)."""
+    rng = np.random.default_rng(1234)
+    E, H, L, B = 512, 8, 128, 4
+    q, k, v = (rng.standard_normal((E, L, B), dtype=np.float32) for _ in range(3))
+    x, a = O.dot_product_attention(q, k, v, nheads=H)
+    assert x.shape == (E, L, B) and a.shape == (L, L, H, B) and x.dtype == np.float32
+    np.testing.assert_allclose(a.sum(0), 1.0, atol=1e-5)
+    assert (a > 0).all()
+    rows = np.arange(L)
+    d = E // H
+    for (b, h) in [(0, 0), (3, 7), (1, 4)]:
+        xr, ar, _ = O.attention_rows(q, k, v, H, rows, b, h)
+        np.testing.assert_allclose(x[h * d:(h + 1) * d, :, b], xr, atol=1e-5)
+        np.testing.assert_allclose(a[:, :, h, b], ar, atol=1e-5)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_gradient_of_one_unit_matches_full_gradient(causal):
+    rng = np.random.default_rng(7)
+    E, H, L, B = 24, 3, 11, 2
+    q, k, v, dy = (rng.standard_normal((E, L, B)) for _ in range(4))
+    mask = O.make_causal_mask(q) if causal else None
+    gq, gk, gv, _ = O.dot_product_attention_grad(q, k, v, dy, mask=mask, nheads=H)
+    d = E // H
+    for b in range(B):
+        for h in range(H):
+            dq, dk, dv = O.attention_grad_unit(q, k, v, dy, H, b, h, causal=causal)
+            sl = slice(h * d, (h + 1) * d)
+            np.testing.assert_allclose(dq, gq[sl, :, b], atol=1e-12)
+            np.testing.assert_allclose(dk, gk[sl, :, b], atol=1e-12)
+            np.testing.assert_allclose(dv, gv[sl, :, b], atol=1e-12)
+
+
+def test_plus_inf_bias_is_always_attend_here():
+    """src/softmax.jl:73-75 reached through attention: a +Inf bias puts the whole weight of that query on
+    the +Inf keys in equal shares (masked keys excepted: the mask is applied after the bias,
+    src/attention.jl:122-123), a NaN logit makes the query's column NaN."""
+    rng = np.random.default_rng(8)
+    E, H, Lq, Lkv, B = 8, 2, 5, 6, 1
+    q, k, v = (rng.standard_normal((E, L, B)).astype(np.float32) for L in (Lq, Lkv, Lkv))
+    bias = np.zeros((Lkv, Lq, H, B), dtype=np.float32)
+    bias[2, 0] = np.inf                       # query 0: one-hot on key 2
+    bias[[1, 4], 1] = np.inf                  # query 1: halves on keys 1 and 4
+    bias[3, 2] = np.inf                       # query 2: +Inf on a key the mask removes
+    bias[0, 3] = np.nan                       # query 3: NaN
+    mask = np.ones((Lkv, Lq), dtype=bool)
+    mask[3, 2] = False
+    x, a = O.dot_product_attention(q, k, v, bias, mask=mask, nheads=H)
+    d = E // H
+    for h in range(H):
+        np.testing.assert_array_equal(a[:, 0, h, 0], np.eye(Lkv, dtype=np.float32)[2])
+        want = np.zeros(Lkv, dtype=np.float32); want[[1, 4]] = 0.5
+        np.testing.assert_array_equal(a[:, 1, h, 0], want)
+        assert a[3, 2, h, 0] == 0 and abs(a[:, 2, h, 0].sum() - 1) < 1e-6
+        assert np.isnan(a[:, 3, h, 0]).all() and np.isnan(x[h * d:(h + 1) * d, 3, 0]).all()
+        np.testing.assert_allclose(x[h * d:(h + 1) * d, 0, 0], v[h * d:(h + 1) * d, 2, 0], rtol=1e-6)
+        assert np.isfinite(a[:, 4, h, 0]).all()

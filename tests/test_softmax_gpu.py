@@ -54,6 +54,27 @@ def test_forward_and_pullbacks_match_the_oracle(dtype, shape, dims):
     np.testing.assert_allclose(nb.jl_to_numpy(dlx), want, atol=4 * tol * max(1.0, np.abs(want).max()), rtol=4 * tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,dims", [((300, 33), 1), ((70000, 3), 1), ((64, 50, 4), 2)])
+def test_in_place_forms(dtype, shape, dims):
+    """softmax!(x, x) and the pullbacks written over dy or y (src/softmax.jl:66, 98-101): the same values as
+    the out-of-place calls, for a warp per column, a block per column with re-read columns, and the
+    strided kernel."""
+    rng = np.random.default_rng(7)
+    x = _as_cm(_dev(_round(3.0 * rng.standard_normal(shape), dtype), dtype), dtype)
+    dy = _as_cm(_dev(_round(rng.standard_normal(shape), dtype), dtype), dtype)
+    for fwd, bwd in ((SM.softmax, SM.softmax_pullback), (SM.logsoftmax, SM.logsoftmax_pullback)):
+        y = fwd(x, dims=dims)
+        xc = x.clone()
+        assert fwd(xc, dims=dims, out=xc) is xc
+        assert torch.equal(xc, y)
+        dx = bwd(dy, y, dims=dims)
+        dyc, yc = dy.clone(), y.clone()
+        bwd(dyc, y, dims=dims, out=dyc)
+        bwd(dy, yc, dims=dims, out=yc)
+        assert torch.equal(dyc, dx) and torch.equal(yc, dx)
+
+
 def test_inf_nan_table_on_device():
     # test/softmax.jl:62-75 and the masked-input regression of test/ext_cuda/softmax.jl:34-78
     f, inf, nan = np.float32, np.inf, np.nan

@@ -23,6 +23,13 @@ from nnlib_jl_b200 import _lib
 DEV = "cuda:0"
 
 
+class _DeviceFloats:
+    """n float32 values at a raw device address, for torch.as_tensor."""
+
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
 def _params(q, k, v, x, alpha, H, causal):
     E, Lq, B = q.shape
     p = _lib.AttnParams()
@@ -59,6 +66,14 @@ def _both_ways(lib, dtype, E, H, Lq, Lkv, B, causal, seed):
     assert (x_new.float() - x_ref.float()).abs().max().item() <= tol
     assert (a_new.float() - a_ref.float()).abs().max().item() <= tol
     assert a_new.float().sum(0).sub(1).abs().max().item() <= 1e-2
+    # the log-sum-exp really went through the library's own array: its first Lq*H*B entries hold what the
+    # workspace of the other entry point holds (same kernels, same inputs)
+    ptr, nbytes = C.c_void_p(), C.c_size_t()
+    assert lib.nnlib_b200_static_scratch(C.byref(ptr), C.byref(nbytes)) == _lib.OK
+    assert nbytes.value == 4 * _lib.STATIC_MAX_QUERIES and ptr.value % 256 == 0
+    n = Lq * H * B
+    scratch = torch.as_tensor(_DeviceFloats(ptr.value, n), device=DEV)
+    assert torch.equal(scratch, ws.view(torch.float32)[:n])
 
 
 @pytest.mark.gpu
