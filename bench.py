@@ -20,7 +20,18 @@ every rank runs the same per-GPU work on its own batch slice (weak scaling; the
 * ``cpu_baseline``: the CPU restatement of the reference's operation sequence
   (the oracle), timed on this host's cores on a bounded sample.
 ``--impl reference`` times only that CPU path (NNlib.jl itself is Julia, which
-is not installed here) with all host threads.
+is not installed here) with all host threads; a step there is one bounded
+sample of the workload.
+
+Beside the line's own numbers (default workload only, ``--no-extras`` skips them):
+* ``strong_c5``: the long-context configuration (bf16 causal, L = 32768, 128
+  (batch, head) units) with its units partitioned over the N ranks
+  (``rank_rects``), per-rank time, aggregate TFLOP/s and, for N > 1, the time of
+  all 128 units on rank 0 alone measured in the same run.
+* ``sharded_driver`` (N > 1): the same 128 units through ``ShardedAttention`` —
+  ONE process, one host thread per device, inputs in pinned host memory.
+* ``host_copy_ceiling``: the end-to-end step's copies alone (same bytes, same
+  two copy streams, no kernels) on all ranks at once: what the host side allows.
 """
 from __future__ import annotations
 
@@ -42,7 +53,7 @@ METRIC = "attention TFLOP/s per B200 (bf16 causal, L=4096, d=128); % of dense TC
 WORKLOADS = {
     # name: dtype, E, H, Lq, Lkv, B(per GPU), causal, extras
     "c3": dict(desc="decoder causal self-attention (Llama-7B shape): bf16 E=4096 nheads=32 d=128 L=4096 batch=8, "
-                    "mask=make_causal_mask, x only",
+                    "mask=make_causal_mask(q), x only",
                dtype="bf16", E=4096, H=32, Lq=4096, Lkv=4096, B=8, causal=True),
     "c5": dict(desc="long-context causal: bf16 E=2048 nheads=16 d=128 L=32768 batch=8 (128 units)",
                dtype="bf16", E=2048, H=16, Lq=32768, Lkv=32768, B=8, causal=True),
@@ -90,6 +101,26 @@ def emit(obj):
     out = _json_out if _json_out is not None else sys.stdout
     out.write(json.dumps(obj) + "\n")
     out.flush()
+
+
+def config_of(args, w, world):
+    """The `config` object of the JSON line: the same for both arms."""
+    return {"workload": args.workload + ": " + w["desc"], "per_gpu_batch": w["B"], "global_batch": w["B"] * world,
+            "sharding": "batch slices per rank, no collective"}
+
+
+def profile_traffic(workload, w, esz):
+    """DRAM bytes of one launch of the dominant kernel from the ncu capture summarised under profiles/: the
+    read bytes of the (smaller) captured case scaled by the units processed, plus the algorithmic bytes of x
+    (part of x is still in L2 when a small capture ends, so its written figure undercounts)."""
+    p = ROOT / "profiles" / "traffic.json"
+    if not p.exists():
+        return None
+    t = json.loads(p.read_text()).get(workload)
+    if not t:
+        return None
+    x_bytes = w["E"] * w["Lq"] * w["B"] * esz
+    return t["dram_bytes_read"] * (w["B"] / t["capture_batch"]) + x_bytes
 
 
 def measured_peaks():
@@ -158,13 +189,41 @@ class ClockSampler:
 # --------------------------------------------------------------------------
 # CPU path (oracle) on a bounded sample
 # --------------------------------------------------------------------------
+def host_threads() -> int:
+    """Host cores this process may use."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
+
+
+def claim_host_threads():
+    """Give the BLAS behind numpy every core this process may use.  Launchers such as torchrun export
+    OMP_NUM_THREADS=1 to their children, which would silently turn the CPU arm into a one-thread run; must be
+    called before numpy is first imported."""
+    n = str(host_threads())
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = n
+
+
+def blas_threads_in_use() -> int:
+    """Threads the BLAS that numpy loaded really runs with (threadpoolctl), else the cores we may use."""
+    try:
+        from threadpoolctl import threadpool_info
+        counts = [int(i["num_threads"]) for i in threadpool_info() if i.get("user_api") == "blas"]
+        if counts:
+            return max(counts)
+    except Exception:
+        pass
+    return host_threads()
+
+
 def cpu_sample(w, budget_s: float = 20.0):
     """Time the CPU restatement of the reference's op sequence on a slice of the
     workload (whole heads of one batch element), sized from a one-head probe to
-    take roughly ``budget_s``.  Returns (TFLOP/s, cores, description)."""
+    take roughly ``budget_s``.  Returns (TFLOP/s, BLAS threads, description, seconds of the timed sample)."""
     import numpy as np
     from oracle import attention_oracle as O
-    cores = os.cpu_count() or 1
     d = w["E"] // w["H"]
     rng = np.random.default_rng(1234)
 
@@ -180,32 +239,38 @@ def cpu_sample(w, budget_s: float = 20.0):
     t1 = run(1)
     nh = int(max(1, min(w["H"], budget_s / max(t1, 1e-3))))
     t = run(nh) if nh > 1 else t1
+    cores = blas_threads_in_use()
     P = w["Lq"] * (w["Lq"] + 1) // 2 if w["causal"] else w["Lq"] * w["Lkv"]
     flops = 2.0 * (d + d) * P * nh
     return flops / t / 1e12, cores, (f"{nh} head(s) of one batch element of the workload "
-                                     f"({t:.2f} s, Float32, numpy/OpenBLAS, {cores} threads)")
+                                     f"({t:.2f} s, Float32, numpy/OpenBLAS, {cores} BLAS threads)"), t
 
 
 def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    vals = []
+    vals, secs = [], []
     desc = ""
-    cores = os.cpu_count() or 1
+    cores = host_threads()
     budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
     for it in range(args.warmup + args.steps):
-        v, cores, desc = cpu_sample(w, budget_s=budget)
+        v, cores, desc, t = cpu_sample(w, budget_s=budget)
         if it >= args.warmup:
             vals.append(v)
+            secs.append(t)
     value = statistics.mean(vals)
-    d = w["E"] // w["H"]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     out = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["desc"], "note": "NNlib.jl is Julia (not installed here): the CPU restatement of "
-                   "its operation sequence (oracle/attention_oracle.py) is timed instead"},
+        "steps": args.steps, "warmup": args.warmup,
+        # a step of this arm is one bounded sample of the workload (see `cpu_baseline.sample`); this is its time
+        "ms_per_step": 1e3 * statistics.mean(secs),
+        "ms_per_step_full_workload_extrapolated": 1e3 * algorithmic_flops(w) / (value * 1e12),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_of(args, w, world),
+        "note": "NNlib.jl is Julia (not installed here): the CPU restatement of its operation sequence "
+                "(oracle/attention_oracle.py) is timed instead, on rank 0 only, one bounded sample per step",
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -216,12 +281,59 @@ def run_reference(args, w):
 # --------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------
+def gpu_host_locality(torch, local):
+    """NUMA node and CPU list the kernel reports for GPU `local` (sysfs, read only), and how many NUMA nodes
+    this process can see.  Returns a dict for the JSON line; binds nothing."""
+    info = {"numa_nodes_visible": None, "gpu_numa_node": None, "gpu_local_cpus": None}
+    try:
+        nodes = [p for p in Path("/sys/devices/system/node").glob("node[0-9]*")]
+        info["numa_nodes_visible"] = len(nodes)
+    except OSError:
+        pass
+    try:
+        pr = torch.cuda.get_device_properties(local)
+        bus = "%04x:%02x:%02x.0" % (getattr(pr, "pci_domain_id", 0), pr.pci_bus_id, pr.pci_device_id)
+        base = Path("/sys/bus/pci/devices") / bus
+        info["gpu_numa_node"] = int((base / "numa_node").read_text().strip())
+        info["gpu_local_cpus"] = (base / "local_cpulist").read_text().strip()
+    except (OSError, ValueError, AttributeError):
+        pass
+    return info
+
+
+def parse_cpulist(text):
+    cpus = set()
+    for part in text.split(","):
+        part = part.strip()
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_near_gpu(info):
+    """Run this rank (and therefore place the pinned buffers it allocates from now on: first touch) on the
+    CPUs next to its GPU, when the machine has more than one NUMA node and says which CPUs those are."""
+    if not info.get("gpu_local_cpus") or (info.get("numa_nodes_visible") or 1) < 2:
+        return "not bound: one NUMA node visible" if (info.get("numa_nodes_visible") or 1) < 2 else "not bound"
+    try:
+        want = parse_cpulist(info["gpu_local_cpus"]) & os.sched_getaffinity(0)
+        if want:
+            os.sched_setaffinity(0, want)
+            return f"bound to {len(want)} CPUs of NUMA node {info['gpu_numa_node']}"
+    except (OSError, ValueError, AttributeError):
+        pass
+    return "not bound"
+
+
 def run_ours(args, w):
     import torch
     import torch.distributed as dist
 
     import nnlib_jl_b200 as nb
     from nnlib_jl_b200 import _lib
+    from nnlib_jl_b200.shard import ShardedAttention, rank_rects
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -231,6 +343,8 @@ def run_ours(args, w):
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    locality = gpu_host_locality(torch, local)
+    locality["binding"] = bind_near_gpu(locality)      # before any pinned allocation
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -246,7 +360,8 @@ def run_ours(args, w):
     kwargs = dict(nheads=H)
     bias = None
     if w.get("causal"):
-        kwargs["mask"] = nb.CausalMask()
+        # the reference's own call: the Bool matrix is built once, outside the timed region, and passed as mask=
+        kwargs["mask"] = nb.make_causal_mask(q)
     if w.get("padmask"):
         lens = torch.randint(Lkv // 2, Lkv + 1, (B,), generator=g, device=dev)
         m = (torch.arange(Lkv, device=dev)[None, :] < lens[:, None])            # (B, Lkv) row-major
@@ -351,38 +466,176 @@ def run_ours(args, w):
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     clocks = sampler.stop() if rank == 0 else None
+    nb.device_health(dev)
+
+    # ---- the same copies without the kernels: what the host side allows -------
+    ceiling = None
+    extras = (args.workload == "c3" and args.batch == 0 and not args.no_extras)
+    if extras:
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        xdev = nb.jl_empty((E, Lq, B), tdtype, dev)
+
+        def copies():
+            with torch.cuda.stream(s_in):
+                dq.permute(2, 1, 0).copy_(hq, non_blocking=True)
+                dk.permute(2, 1, 0).copy_(hk, non_blocking=True)
+                dv.permute(2, 1, 0).copy_(hv, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                hx.copy_(xdev.permute(2, 1, 0), non_blocking=True)
+
+        copies()
+        barrier()
+        cur = torch.cuda.current_stream()
+        c0.record(cur)
+        s_in.wait_event(c0); s_out.wait_event(c0)
+        for _ in range(5):
+            copies()
+        cur.wait_stream(s_in); cur.wait_stream(s_out)
+        c1.record(cur)
+        barrier()
+        ceiling = c0.elapsed_time(c1) / 5
+
+    # ---- north_star's multi-GPU split: the 128 units of the long-context configuration over the ranks ------
+    strong = None
+    sharded = None
+    if extras:
+        del dq, dk, dv
+        c5 = WORKLOADS["c5"]
+        E5, H5, L5, B5 = c5["E"], c5["H"], c5["Lq"], c5["B"]
+        d5 = E5 // H5
+        rects = rank_rects(B5, H5, rank, world)
+        unit_flops = 2.0 * (d5 + d5) * (L5 * (L5 + 1) // 2)
+        cm = nb.CausalMask()            # the Bool matrix would be 1 GiB at this length
+        probs = []
+        for r in rects:
+            gq = torch.Generator(device=dev).manual_seed(5000 + r.b0 * H5 + r.h0)
+            ts = [nb.jl_empty((r.nh * d5, L5, r.nb), tdtype, dev) for _ in range(3)]
+            for t in ts:
+                t.normal_(generator=gq)
+            probs.append((r, ts))
+
+        def strong_step():
+            for r, (tq, tk, tv) in probs:
+                nb.dot_product_attention(tq, tk, tv, mask=cm, nheads=r.nh)
+
+        for _ in range(2):
+            strong_step()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_strong = 5
+        barrier()
+        s0.record()
+        for _ in range(n_strong):
+            strong_step()
+        s1.record()
+        barrier()
+        strong_ms = s0.elapsed_time(s1) / n_strong
+        nb.device_health(dev)
+        del probs
+        t_all = torch.tensor([strong_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            gathered = [torch.zeros_like(t_all) for _ in range(world)]
+            dist.all_gather(gathered, t_all)
+            per_rank = [float(t.item()) for t in gathered]
+        else:
+            per_rank = [strong_ms]
+        strong = {"workload": "c5: " + c5["desc"], "units_total": B5 * H5,
+                  "units_per_rank": [sum(r.units for r in rank_rects(B5, H5, rr, world)) for rr in range(world)],
+                  "ms_per_step_per_rank": per_rank, "ms_per_step": max(per_rank),
+                  "tflops": unit_flops * B5 * H5 / (max(per_rank) * 1e-3) / 1e12, "scaling": "strong",
+                  "partition": "rank_rects(8, 16, rank, world): contiguous, balanced unit ranges; no collective"}
+
+        # all 128 units on rank 0 alone, and through the one-process driver, while the other ranks wait on the host
+        store = dist.distributed_c10d._get_default_store() if world > 1 else None
+        if world > 1 and rank != 0:
+            torch.cuda.synchronize()
+            store.wait(["bench_rank0_done"])
+        elif world > 1:
+            torch.cuda.synchronize()
+            try:
+                gq = torch.Generator(device=dev).manual_seed(5000)
+                tq, tk, tv = (nb.jl_empty((E5, L5, B5), tdtype, dev) for _ in range(3))
+                for t in (tq, tk, tv):
+                    t.normal_(generator=gq)
+                for _ in range(2):
+                    nb.dot_product_attention(tq, tk, tv, mask=cm, nheads=H5)
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for _ in range(3):
+                    nb.dot_product_attention(tq, tk, tv, mask=cm, nheads=H5)
+                a1.record()
+                torch.cuda.synchronize()
+                t1 = a0.elapsed_time(a1) / 3
+                strong["ms_per_step_one_gpu_same_run"] = t1
+                strong["efficiency_vs_one_gpu"] = t1 / (world * strong["ms_per_step"])
+                # one process, one host thread per device, inputs and output in pinned host memory
+                hq5, hk5, hv5 = (t.permute(2, 1, 0).cpu().pin_memory().permute(2, 1, 0) for t in (tq, tk, tv))
+                del tq, tk, tv
+                drv = ShardedAttention([f"cuda:{i}" for i in range(world)])
+                drv(hq5, hk5, hv5, mask=cm, nheads=H5)              # creates the contexts, warms the allocator
+                ts = []
+                for _ in range(3):
+                    t0 = time.perf_counter()
+                    drv(hq5, hk5, hv5, mask=cm, nheads=H5)          # returns after every device has synchronised
+                    ts.append(1e3 * (time.perf_counter() - t0))
+                h2d5 = 3 * E5 * L5 * B5 * 2
+                sharded = {"driver": "ShardedAttention: one process, one host thread per device, pinned host "
+                                     "inputs and output (copies inside the timed call)",
+                           "devices": world, "ms_per_call": min(ts), "ms_per_call_all": ts,
+                           "tflops": unit_flops * B5 * H5 / (min(ts) * 1e-3) / 1e12,
+                           "h2d_bytes_per_call": h2d5, "d2h_bytes_per_call": h2d5 // 3,
+                           "timing": "host clock around the call (it joins its threads after a device synchronise)"}
+            finally:
+                store.set("bench_rank0_done", "1")
+        if world > 1:
+            dist.barrier()
 
     # ---- max over ranks -----------------------------------------------------
-    times = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([ms_total, e2e_ms, ceiling if ceiling is not None else 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = times.tolist()
+    ms_total, e2e_ms, ceiling_ms = times.tolist()
     ms_step = ms_total / args.steps
     flops_gpu = algorithmic_flops(w)
     value = flops_gpu * world / (ms_step * 1e-3) / 1e12
     e2e_value = flops_gpu * world / (e2e_ms * 1e-3) / 1e12
     esz = torch.empty(0, dtype=tdtype).element_size()
+    h2d_bytes = (q.numel() + k.numel() + v.numel()) * esz
+    d2h_bytes = Lq * E * B * esz
 
     if rank == 0:
         peaks = measured_peaks()
         per_gpu = value / world
-        path = "tcgen05"
         out = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-            "config": {"workload": args.workload + ": " + w["desc"], "per_gpu_batch": B, "global_batch": B * world,
-                       "l2": "inputs (q,k,v = %.0f MB per GPU) larger than the 126 MB L2" %
-                             ((q.numel() + k.numel() + v.numel()) * esz / 1e6),
-                       "kernel_path": path, "sharding": "batch slices per rank, no collective"},
+            "config": config_of(args, w, world),
+            "notes": {"l2": "inputs (q,k,v = %.0f MB per GPU) larger than the 126 MB L2" % (h2d_bytes / 1e6),
+                      "kernel_path": "tcgen05",
+                      "mask": "make_causal_mask(q) built once before the timed region and passed as mask= "
+                              "(recognised as unmodified, never read)" if w.get("causal") else None},
             "per_gpu_tflops": per_gpu,
             "pct_of_dense_bf16_peak": 100.0 * per_gpu / peaks["bf16"],
             "clocks": clocks,
+            "ms_times_sm_mhz": (ms_step * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "path": e2e_path,
-                    "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * esz,
-                    "d2h_bytes_per_step": Lq * E * B * esz},
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                    "h2d_GBps_per_rank": h2d_bytes / (e2e_ms * 1e-3) / 1e9},
+            "host": locality,
             "gpu_launches": int(launches),
         }
+        if ceiling is not None:
+            out["host_copy_ceiling"] = {
+                "ms_per_step": ceiling_ms, "what": "the e2e step's copies alone (H2D q,k,v and D2H x on two streams, "
+                "no kernels), all ranks at once, max over ranks",
+                "h2d_GBps_per_rank": h2d_bytes / (ceiling_ms * 1e-3) / 1e9,
+                "aggregate_GBps": world * (h2d_bytes + d2h_bytes) / (ceiling_ms * 1e-3) / 1e9,
+                "e2e_over_ceiling": e2e_ms / ceiling_ms}
+        if strong is not None:
+            out["strong_c5"] = strong
+        if sharded is not None:
+            out["sharded_driver"] = sharded
         if w["causal"]:
             # long causal sequences: the fused kernel is bound by the tensor cores
             out["roofline"] = {
@@ -390,8 +643,9 @@ def run_ours(args, w):
                 "frac": per_gpu / peaks["bf16"], "peak_source": peaks["source"] + ", burst",
                 "frac_of_sustained": (per_gpu / peaks["bf16_sustained"]) if peaks["bf16_sustained"] else None,
                 "kernel": "attn_fwd_umma_kernel", "algorithmic_flops_per_launch": flops_gpu,
-                # dram__bytes_read+write of one launch (ncu, batch 2 scaled x4 by the units processed; see profiles/)
-                "traffic": 0.999e9 if args.workload == "c3" and B == 8 else None}
+                # dram__bytes_read + write of one launch, from the ncu capture listed in profiles/traffic.json
+                "traffic": profile_traffic(args.workload, w, esz),
+                "algorithmic_bytes_per_launch": algorithmic_bytes(w, esz)}
         else:
             # short sequences with bias / mask / scores returned: bound by HBM traffic (all launches of a step)
             nbytes = algorithmic_bytes(w, esz)
@@ -399,9 +653,10 @@ def run_ours(args, w):
             out["roofline"] = {
                 "bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
                 "peak_source": peaks["source"], "kernel": "attn_fwd_umma_kernel + attn_scores_umma_kernel"
-                if want_alpha else "attn_fwd_umma_kernel", "algorithmic_bytes_per_step": nbytes, "traffic": None}
+                if want_alpha else "attn_fwd_umma_kernel", "algorithmic_bytes_per_step": nbytes,
+                "traffic": profile_traffic(args.workload, w, esz)}
         if world == 1 and not args.no_cpu:
-            v_cpu, cores, desc = cpu_sample(w, budget_s=args.cpu_budget)
+            v_cpu, cores, desc, _ = cpu_sample(w, budget_s=args.cpu_budget)
             out["cpu_baseline"] = {"value": v_cpu, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
         emit(out)
     if world > 1:
@@ -455,6 +710,8 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip strong_c5 / sharded_driver / host_copy_ceiling (default workload only)")
     ap.add_argument("--backward", action="store_true", help="time the pullback (dq, dk, dv) of the workload instead")
     ap.add_argument("--softmax", action="store_true", help="time the stand-alone softmax kernels instead")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (smaller profiler captures)")
@@ -468,6 +725,7 @@ def main():
     if args.softmax:
         run_softmax(args)
     elif args.impl == "reference":
+        claim_host_threads()
         run_reference(args, w)
     else:
         run_ours(args, w)

@@ -24,8 +24,9 @@ class HostPipelinedAttention:
     pinned host memory.
 
     Host arrays are torch tensors of shape ``(B, L, E)`` (row-major: the memory
-    of Julia's column-major ``(E, L, B)``).  ``mask`` is ``None`` or
-    ``CausalMask()``.  Device staging buffers for two chunks (inputs, output, log-sum-exp) are allocated once
+    of Julia's column-major ``(E, L, B)``).  ``mask`` is ``None``,
+    ``CausalMask()`` or a Bool device array shared by all batch elements (such
+    as the result of ``make_causal_mask``).  Device staging buffers for two chunks (inputs, output, log-sum-exp) are allocated once
     in the constructor; :meth:`__call__` enqueues the whole pipeline and returns
     after the last result byte has been ordered on ``out_stream`` (call
     ``synchronize()`` or wait on :attr:`done` to read ``hx``).
@@ -34,7 +35,12 @@ class HostPipelinedAttention:
     def __init__(self, E: int, Ev: int, Lq: int, Lkv: int, B: int, dtype: torch.dtype, *, nheads: int,
                  mask=None, chunk: int = 1, device=None):
         if mask is not None and not isinstance(mask, CausalMask):
-            raise ArgumentError("HostPipelinedAttention: mask must be None or CausalMask()")
+            # a Bool array on the device that does not depend on the batch (what make_causal_mask returns, or
+            # any (Lkv, Lq[, H]) mask): every chunk uses it as it is
+            if not (isinstance(mask, torch.Tensor) and mask.dtype == torch.bool and mask.is_cuda
+                    and (mask.ndim <= 3 or mask.shape[3] == 1)):
+                raise ArgumentError("HostPipelinedAttention: mask must be None, CausalMask() or a Bool CUDA array "
+                                    "that is the same for every batch element")
         if chunk < 1 or B < 1:
             raise ArgumentError("HostPipelinedAttention: batch and chunk must be positive")
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
