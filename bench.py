@@ -572,11 +572,12 @@ def run_ours(args, w):
                 hq5, hk5, hv5 = (t.permute(2, 1, 0).cpu().pin_memory().permute(2, 1, 0) for t in (tq, tk, tv))
                 del tq, tk, tv
                 drv = ShardedAttention([f"cuda:{i}" for i in range(world)])
-                drv(hq5, hk5, hv5, mask=cm, nheads=H5)              # creates the contexts, warms the allocator
+                hx5 = torch.empty((B5, L5, E5), dtype=tdtype, pin_memory=True).permute(2, 1, 0)
+                drv(hq5, hk5, hv5, mask=cm, nheads=H5, out=hx5)     # creates the contexts, warms the allocator
                 ts = []
                 for _ in range(3):
                     t0 = time.perf_counter()
-                    drv(hq5, hk5, hv5, mask=cm, nheads=H5)          # returns after every device has synchronised
+                    drv(hq5, hk5, hv5, mask=cm, nheads=H5, out=hx5)  # returns after every device has synchronised
                     ts.append(1e3 * (time.perf_counter() - t0))
                 h2d5 = 3 * E5 * L5 * B5 * 2
                 sharded = {"driver": "ShardedAttention: one process, one host thread per device, pinned host "
@@ -701,6 +702,49 @@ def run_softmax(args):
           "hbm_peak_GBps": peaks["hbm"], "rows": rows})
 
 
+def run_batched_mul(args):
+    """Side measurement, not the bench line: batched_mul of BFloat16 arrays on the tcgen05 product kernel,
+    4096 x 4096 x 4096 x 8 (inputs 512 MB: larger than L2) in the four transpose combinations plus the two
+    products of the attention path at config-3 size; algorithmic FLOPs 2·M·N·K·batch against the measured
+    dense-bf16 peak."""
+    import torch
+
+    import nnlib_jl_b200 as nb
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    rows = []
+    dt = torch.bfloat16
+    cases = [("NN", 4096, 4096, 4096, 8), ("TN", 4096, 4096, 4096, 8), ("NT", 4096, 4096, 4096, 8),
+             ("TT", 4096, 4096, 4096, 8), ("NN", 8192, 8192, 8192, 1),
+             ("NN", 4096, 4096, 128, 64),      # logits = batched_mul(kt, qt) at L = 4096, d = 128 (64 units)
+             ("NN", 128, 4096, 4096, 64)]      # x = batched_mul(vt, alpha)
+    for tr, M, N, K, nbt in cases:
+        A = nb.jl_empty((M, K, nbt) if tr[0] == "N" else (K, M, nbt), dt, dev); A.normal_()
+        B = nb.jl_empty((K, N, nbt) if tr[1] == "N" else (N, K, nbt), dt, dev); B.normal_()
+        Cm = nb.jl_empty((M, N, nbt), dt, dev)
+        opA = A if tr[0] == "N" else nb.batched_transpose(A)
+        opB = B if tr[1] == "N" else nb.batched_transpose(B)
+        for _ in range(3):
+            nb.batched_mul_(Cm, opA, opB)
+        n = max(3, min(args.steps, 10))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            nb.batched_mul_(Cm, opA, opB)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        tf = 2.0 * M * N * K * nbt / (ms * 1e-3) / 1e12
+        rows.append({"trans": tr, "M": M, "N": N, "K": K, "batch": nbt, "ms": round(ms, 4), "tflops": round(tf, 1),
+                     "frac_of_bf16_peak": round(tf / peaks["bf16"], 3)})
+        del A, B, Cm
+    nb.device_health(dev)
+    emit({"note": "batched_mul on the tcgen05 product kernel (--batched-mul): not a bench line", "dtype": "bf16",
+          "bf16_peak_tflops": peaks["bf16"], "peak_source": peaks["source"] + ", burst", "rows": rows})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -714,6 +758,7 @@ def main():
                     help="skip strong_c5 / sharded_driver / host_copy_ceiling (default workload only)")
     ap.add_argument("--backward", action="store_true", help="time the pullback (dq, dk, dv) of the workload instead")
     ap.add_argument("--softmax", action="store_true", help="time the stand-alone softmax kernels instead")
+    ap.add_argument("--batched-mul", action="store_true", help="time batched_mul on the product kernel instead")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (smaller profiler captures)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
     args = ap.parse_args()
@@ -724,6 +769,8 @@ def main():
         w["desc"] += f" [batch overridden to {args.batch}]"
     if args.softmax:
         run_softmax(args)
+    elif args.batched_mul:
+        run_batched_mul(args)
     elif args.impl == "reference":
         claim_host_threads()
         run_reference(args, w)

@@ -256,6 +256,38 @@ typedef struct nnlib_b200_softmax_params {
 NNLIB_B200_API int nnlib_b200_softmax_fwd(const nnlib_b200_softmax_params* p, void* stream);
 NNLIB_B200_API int nnlib_b200_softmax_bwd(const nnlib_b200_softmax_params* p, void* stream);
 
+/* Strided-batched matrix product of column-major arrays,
+       C[:, :, b] = alpha * op(A[:, :, b]) * op(B[:, :, b]) + beta * C[:, :, b],   b = 0 .. batch-1,
+   the operation NNlib.batched_mul! reaches through NNlib._batched_gemm!(storage, transA, transB, alpha, A, B,
+   beta, C) (src/batched/batchedmul.jl:256-303; CPU kernel batched_gemm!, src/gemm.jl:89-188).  The reference's
+   CUDA method (ext/NNlibCUDAExt/batchedmul.jl:3-4) covers BlasFloat element types only; Float16 and BFloat16
+   arrays fall to the per-slice generic loop (src/batched/batchedmul.jl:306-325).  op(X) = X for trans = 0 and
+   the transpose of the stored matrix for trans = 1 (BLAS 'N' / 'T'); op(A) is M x K, op(B) is K x N.  Element
+   (i, j) of a stored matrix sits at X[i + ld*j + stride*b]; a batch stride of 0 for A or B uses one matrix for
+   every batch (size(A, 3) == 1 in the reference, src/gemm.jl:116-117).  beta = 0 never reads C.  Accumulation
+   is fp32.  16-bit element types with 16-byte aligned A and B and leading dimensions / batch strides that are
+   multiples of 8 elements run on the tensor cores (tcgen05), everything else (Float32 included) on a plain
+   CUDA-core kernel. */
+typedef struct nnlib_b200_gemm_params {
+  size_t struct_size;        /* = sizeof(nnlib_b200_gemm_params) */
+  int32_t dtype;             /* NNLIB_B200_F16 / BF16 / F32: element type of A, B and C */
+  int32_t transA, transB;    /* 0 = 'N', 1 = 'T' */
+  int32_t reserved;
+  int64_t M, N, K, batch;
+  const void* A;
+  int64_t lda, strideA;      /* elements; strideA = 0: A has no batch dimension */
+  const void* B;
+  int64_t ldb, strideB;
+  void* C;
+  int64_t ldc, strideC;
+  float alpha, beta;
+  int32_t* status;           /* optional device int32, as in nnlib_b200_attn_params */
+} nnlib_b200_gemm_params;
+
+NNLIB_B200_API int nnlib_b200_batched_gemm(const nnlib_b200_gemm_params* p, void* stream);
+/* NNLIB_B200_PATH_* that batched_gemm would take for p, or a negative error */
+NNLIB_B200_API int nnlib_b200_batched_gemm_path(const nnlib_b200_gemm_params* p);
+
 /* make_causal_mask (src/attention.jl:149-153): fill an (L, L) byte matrix
    with m[i + L*j] = (i <= j). */
 NNLIB_B200_API int nnlib_b200_causal_fill(uint8_t* mask, int64_t L, void* stream);

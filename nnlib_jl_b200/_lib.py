@@ -41,6 +41,8 @@ EXPORTS = (
     "nnlib_b200_static_scratch",
     "nnlib_b200_attn_bwd",
     "nnlib_b200_attn_bwd_path",
+    "nnlib_b200_batched_gemm",
+    "nnlib_b200_batched_gemm_path",
     "nnlib_b200_causal_fill",
     "nnlib_b200_causal_check",
     "nnlib_b200_attn_path",
@@ -105,6 +107,27 @@ class AttnGrads(C.Structure):
         self.struct_size = C.sizeof(AttnGrads)
 
 
+class GemmParams(C.Structure):
+    """Mirror of ``nnlib_b200_gemm_params``."""
+
+    _fields_ = [
+        ("struct_size", C.c_size_t),
+        ("dtype", C.c_int32), ("transA", C.c_int32), ("transB", C.c_int32), ("reserved", C.c_int32),
+        ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("batch", C.c_int64),
+        ("A", C.c_void_p), ("lda", C.c_int64), ("strideA", C.c_int64),
+        ("B", C.c_void_p), ("ldb", C.c_int64), ("strideB", C.c_int64),
+        ("C", C.c_void_p), ("ldc", C.c_int64), ("strideC", C.c_int64),
+        ("alpha", C.c_float), ("beta", C.c_float),
+        ("status", C.c_void_p),
+    ]
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.struct_size = C.sizeof(GemmParams)
+        if "alpha" not in kw:
+            self.alpha = 1.0
+
+
 class SoftmaxParams(C.Structure):
     """Mirror of ``nnlib_b200_softmax_params``."""
 
@@ -156,6 +179,10 @@ def load() -> C.CDLL:
     lib.nnlib_b200_attn_bwd_path.restype = C.c_int
     lib.nnlib_b200_workspace_bytes.argtypes = [P]
     lib.nnlib_b200_workspace_bytes.restype = C.c_size_t
+    lib.nnlib_b200_batched_gemm.argtypes = [C.POINTER(GemmParams), C.c_void_p]
+    lib.nnlib_b200_batched_gemm.restype = C.c_int
+    lib.nnlib_b200_batched_gemm_path.argtypes = [C.POINTER(GemmParams)]
+    lib.nnlib_b200_batched_gemm_path.restype = C.c_int
     lib.nnlib_b200_causal_fill.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     lib.nnlib_b200_causal_fill.restype = C.c_int
     lib.nnlib_b200_causal_check.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]

@@ -362,6 +362,69 @@ int nnlib_b200_softmax_bwd(const nnlib_b200_softmax_params* p, void* stream) {
   return finish(softmax_backward(p->dtype, p->log != 0, p->dy, p->x, p->out, p->inner, p->n, p->outer, (cudaStream_t)stream));
 }
 
+// validates the caller's struct and fills the kernels' argument block
+static int resolve_gemm(const nnlib_b200_gemm_params* p, GemmArgs* out) {
+  if (!p || p->struct_size != sizeof(nnlib_b200_gemm_params)) return NNLIB_B200_INVALID_ARG;
+  if (!dtype_ok(p->dtype)) return NNLIB_B200_INVALID_ARG;
+  if ((p->transA != 0 && p->transA != 1) || (p->transB != 0 && p->transB != 1)) return NNLIB_B200_INVALID_ARG;
+  if (p->M < 0 || p->N < 0 || p->K < 0 || p->batch < 0) return NNLIB_B200_INVALID_ARG;
+  if (p->M > 0x7fffffffLL || p->N > 0x7fffffffLL || p->K > 0x7fffffffLL || p->batch > 0x7fffffffLL)
+    return NNLIB_B200_INVALID_ARG;
+  if (!std::isfinite(p->alpha) || !std::isfinite(p->beta)) return NNLIB_B200_INVALID_ARG;
+  const bool empty = (p->M == 0 || p->N == 0 || p->batch == 0);
+  // stored shapes: A is (M, K) or, transposed, (K, M); B is (K, N) or (N, K); the leading dimension covers a column
+  const int64_t a_rows = p->transA ? p->K : p->M, b_rows = p->transB ? p->N : p->K;
+  if (p->lda < (a_rows > 1 ? a_rows : 1) || p->ldb < (b_rows > 1 ? b_rows : 1) || p->ldc < (p->M > 1 ? p->M : 1))
+    return NNLIB_B200_INVALID_ARG;
+  if (p->strideA < 0 || p->strideB < 0 || p->strideC < 0) return NNLIB_B200_INVALID_ARG;
+  if (!empty) {
+    if (!p->C || (p->K > 0 && (!p->A || !p->B))) return NNLIB_B200_INVALID_ARG;
+    if (p->batch > 1 && p->strideC < p->ldc * (p->N - 1) + p->M) return NNLIB_B200_INVALID_ARG;   // batches of C overlap
+  }
+  GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.A = p->A; g.B = p->B; g.C = p->C;
+  g.lda = p->lda; g.ldb = p->ldb; g.ldc = p->ldc;
+  g.strideA = p->strideA; g.strideB = p->strideB; g.strideC = p->strideC;
+  g.M = (int)p->M; g.N = (int)p->N; g.K = (int)p->K; g.batch = (int)p->batch;
+  g.transA = p->transA; g.transB = p->transB;
+  g.a_bcast = (p->strideA == 0) ? 1 : 0;
+  g.b_bcast = (p->strideB == 0) ? 1 : 0;
+  g.alpha = p->alpha; g.beta = p->beta;
+  g.status = p->status;
+  *out = g;
+  return NNLIB_B200_OK;
+}
+
+int nnlib_b200_batched_gemm(const nnlib_b200_gemm_params* p, void* stream) {
+  GemmArgs g;
+  const int rc = resolve_gemm(p, &g);
+  if (rc) return rc;
+  if (g.M == 0 || g.N == 0 || g.batch == 0) return NNLIB_B200_OK;
+  {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return NNLIB_B200_CUDA_ERROR; }
+    if (!on_current_device(g.C, dev) || !on_current_device(g.A, dev)) return NNLIB_B200_INVALID_ARG;
+    if (check_all_pointers() && !on_current_device(g.B, dev)) return NNLIB_B200_INVALID_ARG;
+  }
+  const char* why = force_simt() ? "NNLIB_B200_FORCE_SIMT is set" : gemm_umma_reject_reason(g, p->dtype);
+  if (log_calls()) {
+    static const char* const names[] = {"f16", "bf16", "f32"};
+    std::fprintf(stderr, "[nnlib_b200] batched_gemm %s %c%c M=%d N=%d K=%d batch=%d alpha=%g beta=%g -> %s%s%s\n",
+                 names[p->dtype], g.transA ? 'T' : 'N', g.transB ? 'T' : 'N', g.M, g.N, g.K, g.batch, (double)g.alpha,
+                 (double)g.beta, why ? "cuda-core" : "tcgen05", why ? ": " : "", why ? why : "");
+  }
+  if (!why) return finish(gemm_umma(g, p->dtype, (cudaStream_t)stream));
+  return finish(gemm_simt(g, p->dtype, (cudaStream_t)stream));
+}
+
+int nnlib_b200_batched_gemm_path(const nnlib_b200_gemm_params* p) {
+  GemmArgs g;
+  const int rc = resolve_gemm(p, &g);
+  if (rc) return rc;
+  return (!force_simt() && gemm_umma_reject_reason(g, p->dtype) == nullptr) ? NNLIB_B200_PATH_UMMA : NNLIB_B200_PATH_SIMT;
+}
+
 int nnlib_b200_causal_fill(uint8_t* mask, int64_t L, void* stream) {
   if (L < 0 || (L > 0 && !mask)) return NNLIB_B200_INVALID_ARG;
   return finish(causal_fill(mask, L, (cudaStream_t)stream));
@@ -382,11 +445,12 @@ int nnlib_b200_attn_path(const nnlib_b200_attn_params* p) {
 }
 
 int nnlib_b200_device_health(void* stream) {
-  int v = 0, w = 0;
+  int v = 0, w = 0, u = 0;
   cudaError_t e = umma_take_abort(&v, (cudaStream_t)stream);
   if (e == cudaSuccess) e = umma_bwd_take_abort(&w, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = gemm_take_abort(&u, (cudaStream_t)stream);
   if (e != cudaSuccess) return finish(e);
-  return (v || w) ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
+  return (v || w || u) ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
 }
 
 int nnlib_b200_selftest_wait_runout(uint64_t limit_ns, int32_t* status, void* stream) {

@@ -52,6 +52,23 @@ struct BwdArgs {
   float* delta;
 };
 
+// Kernel-side view of nnlib_b200_gemm_params: C = alpha * op(A) * op(B) + beta * C per batch, column-major.
+struct GemmArgs {
+  const void* A;
+  const void* B;
+  void* C;
+  long long lda, ldb, ldc;               // elements between successive columns of the stored matrices
+  long long strideA, strideB, strideC;   // elements between successive batches
+  int M, N, K, batch;
+  int transA, transB;                    // 1: the stored matrix is the transpose of the factor
+  int a_bcast, b_bcast;                  // 1: one matrix for every batch
+  float alpha, beta;
+  int c_vec;                             // 16-byte stores into C are possible
+  int tiles_m, tiles_n;
+  long long tiles;
+  int* status;
+};
+
 // ---- element types --------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<__half> {

@@ -37,6 +37,12 @@ bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype);
 cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_t st);
 cudaError_t umma_bwd_take_abort(int* out, cudaStream_t st);
 
+// strided-batched matrix product (gemm_umma.cu): tcgen05 kernel for 16-bit arrays, CUDA-core kernel for the rest
+const char* gemm_umma_reject_reason(const GemmArgs& g, int dtype);
+cudaError_t gemm_umma(const GemmArgs& g, int dtype, cudaStream_t st);
+cudaError_t gemm_simt(const GemmArgs& g, int dtype, cudaStream_t st);
+cudaError_t gemm_take_abort(int* out, cudaStream_t st);
+
 // softmax / logsoftmax over one dimension (softmax.cu)
 cudaError_t softmax_forward(int dtype, bool log, const void* x, void* y, long long inner, long long n, long long outer,
                             cudaStream_t st);

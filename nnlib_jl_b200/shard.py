@@ -126,7 +126,9 @@ class ShardedAttention:
     have joined, :class:`ShardError` reports per-device status.
 
     ``compute`` replaces the per-rectangle GPU call (tests inject host-side
-    failures and CPU stand-ins through it).
+    failures and CPU stand-ins through it).  ``out=`` in the call gives the
+    ``(Ev, Lq, B)`` array the shards write into (a caller that calls repeatedly
+    keeps one pinned array instead of paying for a new one each time).
     """
 
     def __init__(self, devices: Optional[Sequence[str]] = None, compute: Optional[Callable] = None,
@@ -139,7 +141,7 @@ class ShardedAttention:
         self.compute = compute or _cuda_compute
         self.out_device = out_device
 
-    def __call__(self, q, k, v, bias=None, *, fdrop=None, mask=None, nheads: int = 1):
+    def __call__(self, q, k, v, bias=None, *, fdrop=None, mask=None, nheads: int = 1, out=None):
         from .attention import ArgumentError, PhiloxDropout, _validate_3d, identity
         if q.ndim != 3:
             raise ArgumentError("ShardedAttention takes 3-d (features, length, batch) arrays")
@@ -154,10 +156,15 @@ class ShardedAttention:
         Ev = v.shape[0]
         H = nheads
         d, dv = E // H, Ev // H
-        x = jl_empty((Ev, Lq, B), q.dtype, self.out_device)
-        if self.out_device == "cpu" and torch.cuda.is_available():
-            x = jl_empty((Ev, Lq, B), q.dtype, "cpu")
-            x = x.permute(2, 1, 0).pin_memory().permute(2, 1, 0)
+        if out is not None:
+            if tuple(out.shape) != (Ev, Lq, B) or out.dtype != q.dtype:
+                raise ArgumentError(f"out must have size {(Ev, Lq, B)} and eltype {q.dtype}")
+            x = out
+        elif self.out_device == "cpu" and torch.cuda.is_available():
+            # pinned from the start (no pageable detour): the shards' device-to-host copies are asynchronous
+            x = torch.empty((B, Lq, Ev), dtype=q.dtype, pin_memory=True).permute(2, 1, 0)
+        else:
+            x = jl_empty((Ev, Lq, B), q.dtype, self.out_device)
         plan = partition_units(B, H, len(self.devices))
         results = [ShardResult(dev, rects) for dev, rects in zip(self.devices, plan)]
 
