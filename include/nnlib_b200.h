@@ -58,7 +58,7 @@
 extern "C" {
 #endif
 
-#define NNLIB_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+#define NNLIB_B200_VERSION 200 /* major*10000 + minor*100 + patch */
 
 #if defined(__GNUC__)
 #define NNLIB_B200_API __attribute__((visibility("default")))
@@ -86,7 +86,11 @@ enum {
 /* which kernel family a call would use (nnlib_b200_attn_path) */
 enum {
   NNLIB_B200_PATH_SIMT = 1,   /* CUDA-core kernel: any dtype, any d <= 1024, dv <= 512, any stride */
-  NNLIB_B200_PATH_UMMA = 2    /* tcgen05 + TMA kernel: f16/bf16, d = dv in {64,128}, 16-byte aligned rows */
+  NNLIB_B200_PATH_UMMA = 2,   /* tcgen05 + TMA kernel, two query tiles per CTA: f16/bf16, d = dv in {64,128},
+                                 16-byte aligned rows */
+  NNLIB_B200_PATH_TILE = 3    /* tcgen05 + TMA kernel, one query tile per CTA: f16/bf16 with d, dv any multiples
+                                 of 8 up to 128 (dv may differ from d); f32 with allow_tf32 and d, dv multiples
+                                 of 4 up to 128; 16-byte aligned rows */
 };
 
 typedef struct nnlib_b200_attn_params {
@@ -151,6 +155,14 @@ typedef struct nnlib_b200_attn_params {
 
   int32_t* status;             /* optional device int32: set to NNLIB_B200_TIMEOUT by a kernel whose
                                   bounded wait ran out (never happens in a correct run); else untouched */
+
+  int32_t allow_tf32;          /* Float32 arrays only.  0 (default): exact fp32 arithmetic on the CUDA-core
+                                  kernels, within 1e-5 of the reference's CPU result like the reference's own
+                                  GPU tests ask (test/ext_amdgpu/attention.jl:19-21).  1: both products run on
+                                  the tensor cores with TF32 operands (10-bit mantissa; max-abs error about
+                                  3e-3 on unit-variance inputs), what CUDA.jl's FAST_MATH math mode allows
+                                  cuBLAS to do for the reference's batched_mul */
+  int32_t reserved0;
 } nnlib_b200_attn_params;
 
 /* x = attention(q,k,v) and, when lse != NULL, lse.  Replaces the whole of

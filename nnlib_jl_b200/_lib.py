@@ -25,6 +25,7 @@ STATIC_MAX_QUERIES = 1 << 20
 
 PATH_SIMT = 1
 PATH_UMMA = 2
+PATH_TILE = 3
 
 LIB_NAME = "libnnlib_b200.so"
 LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
@@ -82,6 +83,7 @@ class AttnParams(C.Structure):
         ("lse", C.c_void_p), ("lse_stride_b", C.c_int64),
         ("alpha", C.c_void_p), ("alpha_stride_b", C.c_int64),
         ("status", C.c_void_p),
+        ("allow_tf32", C.c_int32), ("reserved0", C.c_int32),
     ]
 
     def __init__(self, **kw):

@@ -39,7 +39,29 @@ __all__ = [
     "identity",
     "device_health",
     "check_status",
+    "set_math_mode",
+    "math_mode",
 ]
+
+
+# Float32 arrays: exact fp32 arithmetic by default (the reference's GPU tests hold Float32 to 1e-5); in fast
+# math mode the two products run on the tensor cores with TF32 operands.  The Julia methods read
+# CUDA.math_mode() == CUDA.FAST_MATH, the switch CUDA.jl gives cuBLAS for the reference's own batched_mul.
+_fast_math = False
+
+
+def set_math_mode(mode: str) -> None:
+    """``"default"``: Float32 attention in exact fp32 on the CUDA cores.  ``"fast"``: Float32 attention on
+    the tensor cores with TF32 operands (max-abs error about 3e-3 on unit-variance inputs).  16-bit element
+    types are not affected."""
+    global _fast_math
+    if mode not in ("default", "fast"):
+        raise ValueError("math mode must be 'default' or 'fast'")
+    _fast_math = (mode == "fast")
+
+
+def math_mode() -> str:
+    return "fast" if _fast_math else "default"
 
 
 class ArgumentError(ValueError):
@@ -192,6 +214,7 @@ class _Problem:
                 self.keep.append(m8)
         p.causal = 1 if causal else 0
         p.nan_on_fully_masked = 1
+        p.allow_tf32 = 1 if (_fast_math and q.dtype == torch.float32) else 0
         p.scale = 0.0
         if dropout is not None and dropout.p > 0.0:
             p.dropout_p = dropout.p

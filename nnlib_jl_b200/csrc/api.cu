@@ -138,6 +138,7 @@ int resolve(const nnlib_b200_attn_params* p, unsigned need, AttnArgs* out, bool 
   }
   a.causal = p->causal ? 1 : 0;
   a.nan_fm = p->nan_on_fully_masked ? 1 : 0;
+  a.allow_tf32 = p->allow_tf32 ? 1 : 0;
   if (!(p->scale >= 0.f) || std::isinf(p->scale)) return NNLIB_B200_INVALID_ARG;
   a.scale = (p->scale == 0.f) ? (float)(1.0 / std::sqrt((double)p->d)) : p->scale;
   if (!(p->dropout_p >= 0.f && p->dropout_p < 1.f)) return NNLIB_B200_INVALID_ARG;
@@ -177,9 +178,14 @@ bool use_umma(const AttnArgs& a, int dtype, bool need_v) {
   return !force_simt() && umma_reject_reason(a, dtype, need_v) == nullptr;
 }
 
+// the one-tile tensor-core kernels: other head sizes, dv != d, Float32 on the TF32 path
+bool use_tile(const AttnArgs& a, int dtype, bool need_v) {
+  return !force_simt() && tile_reject_reason(a, dtype, need_v, a.allow_tf32 != 0) == nullptr;
+}
+
 // why a call does not run on the tensor-core kernels (for the log)
 const char* simt_reason(const AttnArgs& a, int dtype, bool need_v) {
-  return force_simt() ? "NNLIB_B200_FORCE_SIMT is set" : umma_reject_reason(a, dtype, need_v);
+  return force_simt() ? "NNLIB_B200_FORCE_SIMT is set" : tile_reject_reason(a, dtype, need_v, a.allow_tf32 != 0);
 }
 
 }  // namespace
@@ -191,8 +197,8 @@ int attention_validate(const nnlib_b200_attn_params* p) {
   const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN | NEED_ALPHA, &a);
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
-  const bool fwd_ok = use_umma(a, p->dtype, true) || simt_supports(a.d, a.dv);
-  const bool sc_ok = use_umma(a, p->dtype, false) || simt_supports(a.d, 1);
+  const bool fwd_ok = use_umma(a, p->dtype, true) || use_tile(a, p->dtype, true) || simt_supports(a.d, a.dv);
+  const bool sc_ok = use_umma(a, p->dtype, false) || use_tile(a, p->dtype, false) || simt_supports(a.d, 1);
   return (fwd_ok && sc_ok) ? NNLIB_B200_OK : NNLIB_B200_UNSUPPORTED_SHAPE;
 }
 
@@ -212,6 +218,10 @@ int nnlib_b200_attn_fwd(const nnlib_b200_attn_params* p, void* stream) {
     log_call("attn_fwd", p, a, "tcgen05", nullptr);
     return finish(umma_fwd(a, p->dtype, false, st));
   }
+  if (use_tile(a, p->dtype, true)) {
+    log_call("attn_fwd", p, a, "tcgen05 (one query tile per CTA)", umma_reject_reason(a, p->dtype, true));
+    return finish(tile_fwd(a, p->dtype, st));
+  }
   if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   log_call("attn_fwd", p, a, "cuda-core", simt_reason(a, p->dtype, true));
   return finish(simt_fwd(a, p->dtype, st));
@@ -227,6 +237,10 @@ int nnlib_b200_attn_stats(const nnlib_b200_attn_params* p, void* stream) {
     log_call("attn_stats", p, a, "tcgen05", nullptr);
     return finish(umma_fwd(a, p->dtype, true, st));
   }
+  if (use_tile(a, p->dtype, false)) {
+    log_call("attn_stats", p, a, "tcgen05 (one query tile per CTA)", umma_reject_reason(a, p->dtype, false));
+    return finish(tile_stats(a, p->dtype, st));
+  }
   if (!simt_supports(a.d, 1)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   log_call("attn_stats", p, a, "cuda-core", simt_reason(a, p->dtype, false));
   return finish(simt_stats(a, p->dtype, st));
@@ -241,6 +255,10 @@ int nnlib_b200_attn_scores(const nnlib_b200_attn_params* p, void* stream) {
   if (use_umma(a, p->dtype, false)) {
     log_call("attn_scores", p, a, "tcgen05", nullptr);
     return finish(umma_scores(a, p->dtype, st));
+  }
+  if (use_tile(a, p->dtype, false)) {
+    log_call("attn_scores", p, a, "tcgen05 (one query tile per CTA)", umma_reject_reason(a, p->dtype, false));
+    return finish(tile_scores(a, p->dtype, st));
   }
   if (!simt_supports(a.d, 1)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   log_call("attn_scores", p, a, "cuda-core", simt_reason(a, p->dtype, false));
@@ -440,17 +458,19 @@ int nnlib_b200_attn_path(const nnlib_b200_attn_params* p) {
   const int rc = resolve(p, NEED_QK | NEED_V, &a, false);
   if (rc) return rc;
   if (use_umma(a, p->dtype, true)) return NNLIB_B200_PATH_UMMA;
+  if (use_tile(a, p->dtype, true)) return NNLIB_B200_PATH_TILE;
   if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   return NNLIB_B200_PATH_SIMT;
 }
 
 int nnlib_b200_device_health(void* stream) {
-  int v = 0, w = 0, u = 0;
+  int v = 0, w = 0, u = 0, t = 0;
   cudaError_t e = umma_take_abort(&v, (cudaStream_t)stream);
   if (e == cudaSuccess) e = umma_bwd_take_abort(&w, (cudaStream_t)stream);
   if (e == cudaSuccess) e = gemm_take_abort(&u, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = tile_take_abort(&t, (cudaStream_t)stream);
   if (e != cudaSuccess) return finish(e);
-  return (v || w || u) ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
+  return (v || w || u || t) ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
 }
 
 int nnlib_b200_selftest_wait_runout(uint64_t limit_ns, int32_t* status, void* stream) {

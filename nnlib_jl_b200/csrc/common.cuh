@@ -37,6 +37,7 @@ struct AttnArgs {
   float scale;               // multiplies q·k (natural units)
   int bias_dtype;
   int causal, nan_fm;
+  int allow_tf32;            // Float32 arrays may run their products on the TF32 tensor-core path
   int d, dv, H, Lq, Lkv, B;
 };
 

@@ -32,6 +32,13 @@ cudaError_t umma_apply(const AttnArgs& a, int dtype, cudaStream_t st);
 cudaError_t umma_take_abort(int* out, cudaStream_t st);
 cudaError_t umma_wait_runout(unsigned long long limit_ns, int* status, cudaStream_t st);
 
+// tcgen05 + TMA kernels for other head sizes and for Float32 arrays on the TF32 path (attn_tile.cu)
+const char* tile_reject_reason(const AttnArgs& a, int dtype, bool need_v, bool allow_tf32);
+cudaError_t tile_fwd(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t tile_stats(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t tile_scores(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t tile_take_abort(int* out, cudaStream_t st);
+
 // tcgen05 backward kernels (attn_bwd_umma.cu)
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype);
 cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_t st);

@@ -227,6 +227,21 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
+// The same descriptor for an MN-major operand of 32-bit elements (TF32): such operands exist in one layout
+// only, the 128-byte swizzle whose unit is 32 bytes (layout type 1; the copy engine writes it with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B).  Rows of 128 bytes = 32 elements along M/N, one row per K index, four
+// K rows form a 512-byte group: SBO = distance between 4-K groups, LBO = distance between successive
+// 32-wide M/N blocks.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128_32b(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 1ull << 61;
+  return d;
+}
+
 // 32-bit instruction descriptor of tcgen05.mma.kind::f16 with fp32
 // accumulation: [4,6) D format (1 = f32), [7,10) A format, [10,13) B format
 // (0 = f16, 1 = bf16), bit 15 / 16: A / B is MN-major, [17,23) N >> 3,
@@ -291,6 +306,48 @@ __device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, u
       : "memory");
 }
 
+// The same two forms with the operand kind as a template flag: kind::f16 (Float16 / BFloat16 operands) or
+// kind::tf32 (Float32 operands read with a 10-bit mantissa; K = 8 per instruction instead of 16).
+template <bool TF32>
+__device__ __forceinline__ void umma_ss_kind(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  if (TF32) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    umma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+  }
+}
+template <bool TF32>
+__device__ __forceinline__ void umma_ts_kind(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  if (TF32) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+  }
+}
+
+// Instruction descriptor with the operand format given as a number (0 = f16, 1 = bf16, 2 = tf32); the
+// fields are those of make_idesc_f16.
+__host__ __device__ constexpr uint32_t make_idesc_fmt(uint32_t fmt, int M, int N, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 // The mbarrier receives one arrival when every tcgen05 operation this thread
 // issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -305,6 +362,13 @@ __device__ __forceinline__ void setmaxnreg_inc() {
 template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// fp32 -> tf32 (10-bit mantissa) rounded to nearest, as the bits of an fp32
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t y;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {

@@ -43,7 +43,7 @@ def test_struct_layout_matches_header(tmp_path):
 
 
 def test_version_and_strerror(lib):
-    assert lib.nnlib_b200_version() == 100
+    assert lib.nnlib_b200_version() == 200
     assert _lib.strerror(0) == "ok"
     for code in (-1, -2, -3, -4, -5, -99):
         assert _lib.strerror(code)

@@ -249,7 +249,8 @@ def _run_case(dtype, E, nheads, Lq, Lkv, B, *, causal=False, mask=None, bias=Non
     vn = _round_to(rng.standard_normal((Ev, Lkv, B)), dtype)
     q, k, v = _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype)
     if expect_umma is not None:
-        assert _path(q, k, v, nheads) == (_lib.PATH_UMMA if expect_umma else _lib.PATH_SIMT)
+        want_path = {True: _lib.PATH_UMMA, False: _lib.PATH_SIMT}.get(expect_umma, expect_umma)
+        assert _path(q, k, v, nheads) == want_path
     mask_np = None
     mask_arg = None
     if causal:
@@ -332,9 +333,136 @@ def test_umma_random_mask_and_bias():
 def test_simt_matches_oracle_for_other_shapes():
     # shapes the tensor-core kernels do not take run on the CUDA-core kernels
     _run_case(torch.float32, 96, 3, 70, 90, 2, seed=26, expect_umma=False)
-    _run_case(torch.bfloat16, 96, 2, 70, 90, 2, seed=27, expect_umma=False)       # d = 48
-    _run_case(torch.float16, 64, 1, 33, 65, 1, Ev=32, seed=28, expect_umma=False)  # dv != d
+    _run_case(torch.bfloat16, 84, 2, 70, 90, 2, seed=27, expect_umma=False)       # d = 42: not a multiple of 8
+    _run_case(torch.float16, 64, 1, 33, 65, 1, Ev=20, seed=28, expect_umma=False)  # dv = 20
     _run_case(torch.float32, 64, 2, 50, 50, 1, causal=True, seed=29, expect_umma=False)
+    _run_case(torch.bfloat16, 512, 2, 40, 70, 1, seed=29, expect_umma=False)      # d = 256: beyond the tensor-core kernels
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d,dv,H,Lq,Lkv,B", [
+    (32, 32, 2, 200, 264, 2),      # half a swizzle row of features
+    (96, 96, 2, 130, 70, 1),       # one and a half
+    (8, 8, 3, 64, 64, 1),          # smallest head the 16-byte rule allows
+    (120, 40, 1, 257, 129, 2),     # dv != d, neither a power of two
+    (64, 128, 2, 300, 500, 1),     # dv != d with the fused kernel's own sizes
+    (128, 64, 2, 100, 1000, 1),
+    (48, 72, 2, 1, 700, 2),        # decode-like
+])
+def test_tile_kernel_other_head_sizes(dtype, d, dv, H, Lq, Lkv, B):
+    """Head sizes other than 64 / 128 and value heads of another size than the query heads
+    (src/attention.jl:21-23, docstring example :36, test/attention.jl:61-68) on the tensor cores: the
+    one-tile kernels, forward and lazily rebuilt scores."""
+    _run_case(dtype, d * H, H, Lq, Lkv, B, Ev=dv * H, seed=70 + d, expect_umma=_lib.PATH_TILE)
+
+
+@pytest.mark.parametrize("dtype,d,dv", [(torch.bfloat16, 96, 96), (torch.float16, 40, 72)])
+def test_tile_kernel_masks_bias_dropout(dtype, d, dv):
+    """Every option of the call on the one-tile kernels: causal, key-padding and full masks, bias in
+    broadcast forms, Philox dropout (mask compared bit for bit), and the scores-only entry."""
+    rng = np.random.default_rng(71)
+    H, Lq, Lkv, B = 2, 150, 150, 2
+    _run_case(dtype, d * H, H, Lq, Lq, B, Ev=dv * H, causal=True, seed=72, expect_umma=_lib.PATH_TILE)
+    keypad = rng.random((Lkv, 1, 1, B)) > 0.3
+    keypad[0] = True
+    _run_case(dtype, d * H, H, Lq, Lkv, B, Ev=dv * H, mask=keypad, seed=73, expect_umma=_lib.PATH_TILE)
+    full = rng.random((Lkv, Lq, H, B)) > 0.3
+    full[0] = True
+    _run_case(dtype, d * H, H, Lq, Lkv, B, Ev=dv * H, mask=full, bias=0.5 * rng.standard_normal((Lkv, Lq, H, B)),
+              seed=74, expect_umma=_lib.PATH_TILE)
+    _run_case(dtype, d * H, H, Lq, Lkv, B, Ev=dv * H, bias=0.5 * rng.standard_normal((Lkv, 1, H)), seed=75,
+              expect_umma=_lib.PATH_TILE)
+    # dropout: exact mask, then values
+    p = 0.25
+    qn = _round_to(rng.standard_normal((d * H, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((d * H, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((dv * H, Lkv, B)), dtype)
+    fd = nb.PhiloxDropout(p, seed=77, offset=3)
+    y, a = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), nheads=H, fdrop=fd)
+    keep = P.keep_mask((Lkv, Lq, H, B), p, 77, 3)
+    yo, ao = O.dot_product_attention(qn, kn, vn, nheads=H, fdrop=lambda al: al * keep / np.float32(1 - p))
+    an = np.asarray(a)
+    assert ((an > 0) == (keep & (ao > 0))).mean() > 0.9999
+    _close(nb.jl_to_numpy(y), yo, dtype, "x with dropout")
+    _close(an, ao, dtype, "alpha with dropout")
+    # scores-only entry: statistics kernel + scores kernel
+    q4, k4 = (nb.jl_reshape(_dev(t, dtype), (d, H, t.shape[1], B)) for t in (qn, kn))
+    a2 = nb.jl_to_numpy(nb.dot_product_attention_scores(q4, k4, mask=nb.jl_from_numpy(keypad, device=DEV)))
+    ao2 = O.dot_product_attention_scores(O.split_heads(qn, H), O.split_heads(kn, H), mask=keypad)
+    _close(a2, ao2, dtype, "alpha (scores entry)")
+
+
+TF32_TOL = (3e-3, 1e-3)     # max-abs, mean-rel against the Float32 oracle: 10-bit mantissa operands
+
+
+def _close_tf32(got, want, what):
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert np.isfinite(got).all(), what
+    assert err.max() <= TF32_TOL[0], f"{what}: max-abs {err.max():.3e}"
+    assert err.mean() / np.abs(want).mean() <= TF32_TOL[1], f"{what}: mean-rel {err.mean() / np.abs(want).mean():.3e}"
+
+
+@pytest.fixture
+def fast_math():
+    nb.set_math_mode("fast")
+    yield
+    nb.set_math_mode("default")
+
+
+def test_tf32_path_config1_and_options(fast_math):
+    """Float32 arrays in fast math mode run both products on the tensor cores with TF32 operands: BASELINE
+    config 1 (E=512, nheads=8, L=128, batch=4, α returned) and a masked / biased / dropped-out case, inside
+    max-abs 3e-3 and mean-rel 1e-3 of the Float32 oracle; without the switch the same call stays on the
+    exact CUDA-core kernels."""
+    rng = np.random.default_rng(1234)
+    E, H, L, B = 512, 8, 128, 4
+    qn, kn, vn = (rng.standard_normal((E, L, B), dtype=np.float32) for _ in range(3))
+    q, k, v = (_dev(t, torch.float32) for t in (qn, kn, vn))
+    p = _lib.AttnParams()
+    p.dtype, p.d, p.dv, p.H, p.Lq, p.Lkv, p.B = _lib.F32, E // H, E // H, H, L, L, B
+    x = nb.jl_empty((E, L, B), torch.float32, DEV)
+    p.q, p.k, p.v, p.x = q.data_ptr(), k.data_ptr(), v.data_ptr(), x.data_ptr()
+    assert _lib.load().nnlib_b200_attn_path(p) == _lib.PATH_SIMT
+    p.allow_tf32 = 1
+    assert _lib.load().nnlib_b200_attn_path(p) == _lib.PATH_TILE
+    y, a = nb.dot_product_attention(q, k, v, nheads=H)
+    yo, ao = O.dot_product_attention(qn, kn, vn, nheads=H)
+    _close_tf32(nb.jl_to_numpy(y), yo, "x")
+    _close_tf32(np.asarray(a), ao, "alpha")
+    # options: d = 40, dv = 24, ragged lengths, full mask, bias, dropout
+    d, dv, H, Lq, Lkv, B, pd = 40, 24, 2, 150, 200, 2, 0.2
+    qn = rng.standard_normal((d * H, Lq, B), dtype=np.float32)
+    kn = rng.standard_normal((d * H, Lkv, B), dtype=np.float32)
+    vn = rng.standard_normal((dv * H, Lkv, B), dtype=np.float32)
+    bn = (0.5 * rng.standard_normal((Lkv, Lq, H, B))).astype(np.float32)
+    mask = rng.random((Lkv, Lq, 1, B)) > 0.3
+    mask[0] = True
+    keep = P.keep_mask((Lkv, Lq, H, B), pd, 9, 1)
+    y, a = nb.dot_product_attention(_dev(qn, torch.float32), _dev(kn, torch.float32), _dev(vn, torch.float32),
+                                    _dev(bn, torch.float32), mask=nb.jl_from_numpy(mask, device=DEV), nheads=H,
+                                    fdrop=nb.PhiloxDropout(pd, seed=9, offset=1))
+    yo, ao = O.dot_product_attention(qn, kn, vn, bn, mask=mask, nheads=H, fdrop=lambda al: al * keep / np.float32(1 - pd))
+    _close_tf32(nb.jl_to_numpy(y), yo, "x with options")
+    _close_tf32(np.asarray(a), ao, "alpha with options")
+
+
+def test_tf32_path_config3_shape_row_sampled(fast_math):
+    """A Float32 case of config 3's shape (E=4096, nheads=32, d=128, L=4096, causal; one batch element) on the
+    TF32 path against the row-sampled Float64 oracle."""
+    E, H, L, B = 4096, 32, 4096, 1
+    g = torch.Generator(device=DEV).manual_seed(45)
+    q, k, v = (nb.jl_empty((E, L, B), torch.float32, DEV) for _ in range(3))
+    for t in (q, k, v):
+        t.normal_(generator=g)
+    y, a = nb.dot_product_attention(q, k, v, mask=nb.make_causal_mask(q), nheads=H)
+    lse = a._problem.lse.cpu().numpy()
+    qn, kn, vn, yn = (nb.jl_to_numpy(t) for t in (q, k, v, y))
+    d = E // H
+    rows = _sample_rows(L)
+    for (b, h) in [(0, 0), (0, 31)]:
+        xr, ar, lr = O.attention_rows(qn, kn, vn, H, rows, b, h, causal=True)
+        _close_tf32(yn[h * d:(h + 1) * d][:, rows, b], xr.astype(np.float32), f"x rows of unit {(b, h)}")
+        np.testing.assert_allclose(lse[rows, h, b], lr, atol=5e-3)
 
 
 def test_nd_batch_and_lazy_alpha():
