@@ -745,6 +745,59 @@ def run_batched_mul(args):
           "bf16_peak_tflops": peaks["bf16"], "peak_source": peaks["source"] + ", burst", "rows": rows})
 
 
+def run_decode(args):
+    """Side measurement, not the bench line: few queries against a long key / value history (bf16, d = 128,
+    CausalMask(offset = Lkv - Lq)): the split-key forward against the ordinary forward on the same call.  The
+    work is the one pass over K and V: algorithmic bytes = 2 bytes x (d + dv) x Lkv x H x B, against the
+    measured HBM peak."""
+    import ctypes as C
+
+    import torch
+
+    import nnlib_jl_b200 as nb
+    from nnlib_jl_b200 import _lib
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    lib = _lib.load()
+    peaks = measured_peaks()
+    rows = []
+    dt = torch.bfloat16
+    for (Lq, Lkv, H, B) in [(1, 32768, 32, 1), (1, 32768, 8, 1), (1, 8192, 32, 8), (8, 32768, 16, 1), (16, 131072, 8, 1)]:
+        d = 128
+        q = nb.jl_empty((H * d, Lq, B), dt, dev); q.normal_()
+        k = nb.jl_empty((H * d, Lkv, B), dt, dev); k.normal_()
+        v = nb.jl_empty((H * d, Lkv, B), dt, dev); v.normal_()
+        pr = nb.attention._Problem(q, k, v, None, nb.CausalMask(Lkv - Lq), H, None, need_v=True)
+        pr.alloc_x(); pr.alloc_lse()
+        need = lib.nnlib_b200_attn_decode_workspace_bytes(C.byref(pr.p))
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        st = torch.cuda.current_stream().cuda_stream
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            ts = []
+            for _ in range(max(5, args.steps)):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return statistics.median(ts)
+
+        t_fwd = timed(lambda: lib.nnlib_b200_attn_fwd(C.byref(pr.p), st))
+        t_dec = timed(lambda: lib.nnlib_b200_attn_decode(C.byref(pr.p), ws.data_ptr(), need, st))
+        nbytes = 2.0 * (d + d) * Lkv * H * B
+        rows.append({"Lq": Lq, "Lkv": Lkv, "H": H, "B": B, "workspace_bytes": int(need),
+                     "attn_fwd_us": round(t_fwd * 1e3, 1), "attn_decode_us": round(t_dec * 1e3, 1),
+                     "decode_GBps": round(nbytes / t_dec / 1e6, 1),
+                     "decode_frac_of_hbm_peak": round(nbytes / t_dec / 1e6 / peaks["hbm"], 3)})
+        del q, k, v, pr, ws
+    nb.device_health(dev)
+    emit({"note": "split-key forward for few queries (--decode): not a bench line; L2 flushed between launches",
+          "dtype": "bf16", "hbm_peak_GBps": peaks["hbm"], "rows": rows})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -759,6 +812,7 @@ def main():
     ap.add_argument("--backward", action="store_true", help="time the pullback (dq, dk, dv) of the workload instead")
     ap.add_argument("--softmax", action="store_true", help="time the stand-alone softmax kernels instead")
     ap.add_argument("--batched-mul", action="store_true", help="time batched_mul on the product kernel instead")
+    ap.add_argument("--decode", action="store_true", help="time the split-key forward for few queries instead")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (smaller profiler captures)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
     args = ap.parse_args()
@@ -771,6 +825,8 @@ def main():
         run_softmax(args)
     elif args.batched_mul:
         run_batched_mul(args)
+    elif args.decode:
+        run_decode(args)
     elif args.impl == "reference":
         claim_host_threads()
         run_reference(args, w)

@@ -129,7 +129,8 @@ typedef struct nnlib_b200_attn_params {
   const uint8_t* mask;
   int64_t mask_stride[4];
 
-  int32_t causal;              /* 1: additionally keep only j <= i (make_causal_mask, src/attention.jl:149-153) */
+  int32_t causal;              /* 1: additionally keep only j <= i + causal_offset (make_causal_mask,
+                                  src/attention.jl:149-153, is the case causal_offset = 0) */
   int32_t nan_on_fully_masked; /* 1 (reference behaviour, src/softmax.jl:71-76): a query with nothing to
                                   attend to yields NaN in x and alpha; 0: zeros */
 
@@ -163,12 +164,29 @@ typedef struct nnlib_b200_attn_params {
                                   3e-3 on unit-variance inputs), what CUDA.jl's FAST_MATH math mode allows
                                   cuBLAS to do for the reference's batched_mul */
   int32_t reserved0;
+
+  int64_t causal_offset;       /* with causal = 1: query i keeps the keys j <= i + causal_offset.  0 is
+                                  make_causal_mask's square pattern; Lkv - Lq aligns the last query with the
+                                  last key (new queries against a longer key / value history).  A query that
+                                  keeps no key at all is one with nothing to attend to. */
 } nnlib_b200_attn_params;
 
 /* x = attention(q,k,v) and, when lse != NULL, lse.  Replaces the whole of
    dot_product_attention's arithmetic (src/attention.jl:86-101,112-127 and the
    softmax of src/softmax.jl:69-79) without materialising alpha. */
 NNLIB_B200_API int nnlib_b200_attn_fwd(const nnlib_b200_attn_params* p, void* stream);
+
+/* The same result as nnlib_b200_attn_fwd for a call with few queries against many keys (Lq <= 128; typically
+   one new token, or a handful, against a long key / value history, with causal_offset = Lkv - Lq).  attn_fwd
+   gives such a call one CTA per (head, batch) unit, which leaves most of the GPU idle when H*B is small; here
+   the key tiles of a unit are dealt to several CTAs and a second kernel merges their running maxima, sums and
+   partial outputs.  The partial results live in `workspace` (device memory, 16-byte aligned, at least
+   nnlib_b200_attn_decode_workspace_bytes(p)); when that function returns 0 the call gains nothing from
+   splitting (or its shape is outside the tensor-core kernels) and is simply forwarded to attn_fwd.
+   The reference has no counterpart: make_causal_mask is square only (src/attention.jl:149-153). */
+NNLIB_B200_API size_t nnlib_b200_attn_decode_workspace_bytes(const nnlib_b200_attn_params* p);
+NNLIB_B200_API int nnlib_b200_attn_decode(const nnlib_b200_attn_params* p, void* workspace, size_t workspace_bytes,
+                                          void* stream);
 
 /* lse only: the first half of dot_product_attention_scores
    (src/attention.jl:117-125) reduced to one float per query. */

@@ -33,6 +33,8 @@ LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
 # every symbol include/nnlib_b200.h declares
 EXPORTS = (
     "nnlib_b200_attn_fwd",
+    "nnlib_b200_attn_decode",
+    "nnlib_b200_attn_decode_workspace_bytes",
     "nnlib_b200_attn_stats",
     "nnlib_b200_attn_scores",
     "nnlib_b200_attn_apply",
@@ -84,6 +86,7 @@ class AttnParams(C.Structure):
         ("alpha", C.c_void_p), ("alpha_stride_b", C.c_int64),
         ("status", C.c_void_p),
         ("allow_tf32", C.c_int32), ("reserved0", C.c_int32),
+        ("causal_offset", C.c_int64),
     ]
 
     def __init__(self, **kw):
@@ -167,6 +170,10 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [P, C.c_void_p]
         fn.restype = C.c_int
+    lib.nnlib_b200_attn_decode.argtypes = [P, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.nnlib_b200_attn_decode.restype = C.c_int
+    lib.nnlib_b200_attn_decode_workspace_bytes.argtypes = [P]
+    lib.nnlib_b200_attn_decode_workspace_bytes.restype = C.c_size_t
     lib.nnlib_b200_attention.argtypes = [P, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.nnlib_b200_attention.restype = C.c_int
     lib.nnlib_b200_attention_static.argtypes = [P, C.c_void_p]

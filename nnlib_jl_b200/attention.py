@@ -69,12 +69,18 @@ class ArgumentError(ValueError):
 
 
 class CausalMask:
-    """Sentinel accepted as ``mask=``: the causal pattern ``kv <= query``
-    without materialising the ``(L, L)`` Bool matrix ``make_causal_mask``
-    returns (1 GiB at L = 32768)."""
+    """Sentinel accepted as ``mask=``: the causal pattern ``kv <= query + offset``
+    without materialising the Bool matrix.  ``offset = 0`` is what
+    ``make_causal_mask`` returns (1 GiB at L = 32768); ``offset = kv_len - q_len``
+    aligns the last query with the last key — new queries against a longer
+    key / value history, which the reference can only express with a
+    hand-built Bool mask (``make_causal_mask`` is square)."""
+
+    def __init__(self, offset: int = 0):
+        self.offset = int(offset)
 
     def __repr__(self):
-        return "CausalMask()"
+        return "CausalMask()" if self.offset == 0 else f"CausalMask(offset={self.offset})"
 
 
 def identity(x):
@@ -201,6 +207,7 @@ class _Problem:
         causal = False
         if isinstance(mask, CausalMask):
             causal = True
+            p.causal_offset = mask.offset
         elif mask is not None:
             if not isinstance(mask, torch.Tensor) or not mask.is_cuda or mask.dtype != torch.bool:
                 raise TypeError("mask must be a Bool CUDA tensor, a CausalMask() or None")
@@ -418,8 +425,16 @@ def _fused(q, k, v, bias, mask, nheads, dropout):
     x = pr.alloc_x()
     pr.alloc_lse()
     if pr.Lq > 0 and pr.B > 0:
+        lib = _lib.load()
         with torch.cuda.device(pr.dev):
-            _check(_lib.load().nnlib_b200_attn_fwd(C.byref(pr.p), _stream()), "attn_fwd")
+            # few queries against many keys: the library splits the keys of a unit over several CTAs when that
+            # pays and tells how much scratch memory the partial results need (0: the ordinary forward)
+            need = lib.nnlib_b200_attn_decode_workspace_bytes(C.byref(pr.p)) if pr.Lq <= 128 else 0
+            if need:
+                ws = torch.empty(need, dtype=torch.uint8, device=pr.dev)
+                _check(lib.nnlib_b200_attn_decode(C.byref(pr.p), ws.data_ptr(), need, _stream()), "attn_decode")
+            else:
+                _check(lib.nnlib_b200_attn_fwd(C.byref(pr.p), _stream()), "attn_fwd")
     return x, LazyAttnScores(pr, (pr.Lkv, pr.Lq, pr.H, pr.B))
 
 

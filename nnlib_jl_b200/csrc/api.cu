@@ -137,6 +137,8 @@ int resolve(const nnlib_b200_attn_params* p, unsigned need, AttnArgs* out, bool 
     a.mask_s[i] = p->mask_stride[i];
   }
   a.causal = p->causal ? 1 : 0;
+  if (p->causal_offset > 0x3fffffffLL || p->causal_offset < -0x3fffffffLL) return NNLIB_B200_INVALID_ARG;
+  a.coff = a.causal ? (int)p->causal_offset : 0;
   a.nan_fm = p->nan_on_fully_masked ? 1 : 0;
   a.allow_tf32 = p->allow_tf32 ? 1 : 0;
   if (!(p->scale >= 0.f) || std::isinf(p->scale)) return NNLIB_B200_INVALID_ARG;
@@ -225,6 +227,39 @@ int nnlib_b200_attn_fwd(const nnlib_b200_attn_params* p, void* stream) {
   if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   log_call("attn_fwd", p, a, "cuda-core", simt_reason(a, p->dtype, true));
   return finish(simt_fwd(a, p->dtype, st));
+}
+
+// does the split-key forward apply to this call, and is it worth it (a long key sequence, too few units to
+// fill the GPU otherwise)?
+static bool use_split(const AttnArgs& a, int dtype) {
+  if (a.Lq > 128 || force_simt()) return false;
+  if (tile_reject_reason(a, dtype, true, a.allow_tf32 != 0) != nullptr) return false;
+  return tile_split_count(a) > 1;
+}
+
+size_t nnlib_b200_attn_decode_workspace_bytes(const nnlib_b200_attn_params* p) {
+  AttnArgs a;
+  if (resolve(p, NEED_QK | NEED_V, &a, false) != NNLIB_B200_OK) return 0;
+  if (a.Lq == 0 || a.B == 0 || !use_split(a, p->dtype)) return 0;
+  return tile_split_workspace_bytes(a);
+}
+
+int nnlib_b200_attn_decode(const nnlib_b200_attn_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  AttnArgs a;
+  const int rc = resolve(p, NEED_QK | NEED_V, &a);
+  if (rc) return rc;
+  if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
+  if (!use_split(a, p->dtype)) return nnlib_b200_attn_fwd(p, stream);
+  const size_t need = tile_split_workspace_bytes(a);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0)
+    return NNLIB_B200_WORKSPACE_TOO_SMALL;
+  a.ws = static_cast<float*>(workspace);
+  if (log_calls()) {
+    char what[96];
+    std::snprintf(what, sizeof(what), "tcgen05 (keys split over %d CTAs per unit)", tile_split_count(a));
+    log_call("attn_decode", p, a, what, nullptr);
+  }
+  return finish(tile_split(a, p->dtype, (cudaStream_t)stream));
 }
 
 int nnlib_b200_attn_stats(const nnlib_b200_attn_params* p, void* stream) {

@@ -834,6 +834,7 @@ bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype) {
   if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
   if (!(a.d == 64 || a.d == 128) || a.dv != a.d) return false;
   if (g.dbias && !a.bias) return false;
+  if (a.causal && a.coff != 0) return false;      // the tile skipping here assumes the square causal pattern
   if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1 || !a.lse || !g.delta) return false;
   const void* ptrs[] = {a.q, a.k, a.v, a.x, g.dx, g.dq, g.dk, g.dv};
   for (const void* p : ptrs)

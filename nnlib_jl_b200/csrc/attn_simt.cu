@@ -31,7 +31,7 @@ __device__ __forceinline__ float logit_at(const AttnArgs& a, const float* qs, in
     s += load_bias(a.bias, j * a.bias_s[0] + i * a.bias_s[1] + h * a.bias_s[2] + b * a.bias_s[3], a.bias_dtype);
   }
   bool keep = true;
-  if (a.causal) keep = (j <= i);
+  if (a.causal) keep = (j <= i + a.coff);
   if (a.mask) keep = keep && (a.mask[j * a.mask_s[0] + i * a.mask_s[1] + h * a.mask_s[2] + b * a.mask_s[3]] != 0);
   return keep ? s : neg_inf();
 }

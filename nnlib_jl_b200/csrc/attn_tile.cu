@@ -21,7 +21,13 @@
 //              src/attention.jl:129-131, masks :133-138, dropout src/dropout.jl:77-87 on P after the row sum)
 //   TM_STATS   the log-sum-exp only
 //   TM_SCORES  alpha (after dropout) from a given log-sum-exp, written straight to the (Lkv, Lq, H, B) array
+//   TM_SPLIT   few queries (Lq <= 128: one query tile) against many keys: the key tiles of a unit are dealt to
+//              `n_splits` CTAs, each leaving its running maximum, its sum and its unnormalised O in a
+//              workspace; attn_split_reduce_kernel merges them into x and the log-sum-exp.  This is what
+//              keeps every SM busy when H*B is small (one new token against a long key / value history).
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 #include "extras.cuh"
@@ -35,7 +41,7 @@ __device__ int g_tile_abort = 0;  // sticky: a bounded wait of these kernels ran
 
 namespace {
 
-enum : int { TM_FWD = 0, TM_STATS = 1, TM_SCORES = 2 };
+enum : int { TM_FWD = 0, TM_STATS = 1, TM_SCORES = 2, TM_SPLIT = 3 };
 constexpr int kTThreads = 192;
 constexpr int kTBM = 128;          // queries per CTA
 constexpr int kTBN = 64;           // keys per tile
@@ -72,18 +78,78 @@ struct TBarriers {
 };
 static_assert(sizeof(TBarriers) <= 256, "barrier block");
 
+// Workspace of the split-key forward, in floats: (maximum, sum) per (unit, split, query), rounded up so that
+// the O rows behind them start on a 16-byte boundary, then dv floats of unnormalised O per (unit, split, query).
+__host__ __device__ inline long long split_ml_floats(const AttnArgs& a, int n_splits) {
+  return (((long long)a.H * a.B * n_splits * a.Lq * 2) + 3) & ~3LL;
+}
+__host__ __device__ inline long long split_ws_floats(const AttnArgs& a, int n_splits) {
+  return split_ml_floats(a, n_splits) + (long long)a.H * a.B * n_splits * a.Lq * a.dv;
+}
+
+// Second stage of the split-key forward: one block per (unit, query) merges the partial results of the
+// splits, x = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s, and writes the query's log-sum-exp.
+template <typename T>
+__global__ void __launch_bounds__(128) attn_split_reduce_kernel(const AttnArgs a, const int n_splits) {
+  const long long row = blockIdx.x;              // unit * Lq + i
+  const int i = (int)(row % a.Lq);
+  const int unit = (int)(row / a.Lq);
+  const int h = unit % a.H, b = unit / a.H;
+  const float* ml = a.ws + ((long long)unit * n_splits * a.Lq + i) * 2;
+  const float* o = a.ws + split_ml_floats(a, n_splits) + ((long long)unit * n_splits * a.Lq + i) * a.dv;
+  const long long sstride = a.Lq;                // splits of one unit are Lq slots apart
+  float M = __int_as_float(0xff800000);
+  bool any_nan = false;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = ml[s * sstride * 2], l = ml[s * sstride * 2 + 1];
+    if (l != l) any_nan = true;
+    if (l > 0.f) M = fmaxf(M, m);
+  }
+  const bool inf_row = (M == __int_as_float(0x7f800000));
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = ml[s * sstride * 2], l = ml[s * sstride * 2 + 1];
+    if (!(l > 0.f)) continue;
+    const float w = inf_row ? (m == M ? 1.f : 0.f) : exp2f(m - M);
+    L += w * l;
+  }
+  const bool dead = !(L > 0.f) && !any_nan;
+  const float nanv = __int_as_float(0x7fc00000);
+  if (threadIdx.x == 0 && a.lse) {
+    float lse = dead ? __int_as_float(0xff800000) : (M + log2f(L)) * 0.6931471805599453f;
+    if (inf_row && !dead) lse = lse_inf_rows(L);
+    if (any_nan) lse = nanv;
+    a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = lse;
+  }
+  T* xrow = reinterpret_cast<T*>(a.x) + (long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * a.dv;
+  for (int e = threadIdx.x; e < a.dv; e += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = ml[s * sstride * 2], l = ml[s * sstride * 2 + 1];
+      if (!(l > 0.f)) continue;
+      const float w = inf_row ? (m == M ? 1.f : 0.f) : exp2f(m - M);
+      acc = fmaf(w, o[(long long)s * sstride * a.dv + e], acc);
+    }
+    float out = acc * (a.inv_keep / L);
+    if (dead) out = a.nan_fm ? nanv : 0.f;
+    if (any_nan) out = nanv;
+    xrow[e] = Elem<T>::from_f(out);
+  }
+}
+
 template <typename T> struct Fmt;
 template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
 template <> struct Fmt<float> { static constexpr uint32_t v = 2; };
 
 template <typename T, int DQ, int DV, int MODE>
-__global__ void __launch_bounds__(kTThreads, (MODE == TM_FWD) ? 1 : TCfg<T, DQ, DV>::kCtasPerSm)   // the forward needs > 168 registers
+__global__ void __launch_bounds__(kTThreads, (MODE == TM_FWD || MODE == TM_SPLIT) ? 1 : TCfg<T, DQ, DV>::kCtasPerSm)   // the forward needs > 168 registers
 attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qtiles) {
+                 const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qtiles, const int n_splits) {
   using C = TCfg<T, DQ, DV>;
   constexpr bool TF32 = (sizeof(T) == 4);
   constexpr bool BF16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr bool PV = (MODE == TM_FWD || MODE == TM_SPLIT);     // the modes that form O = P V
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   TBarriers* bars = reinterpret_cast<TBarriers*>(smem + C::kBarOff);
@@ -91,12 +157,20 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // block -> (unit, query tile); within a unit the longest causal rows come first
-  const int unit = blockIdx.x / n_qtiles;
-  const int qt = n_qtiles - 1 - (blockIdx.x % n_qtiles);
+  // (TM_SPLIT: block -> (unit, split); there is one query tile)
+  const int unit = (MODE == TM_SPLIT) ? blockIdx.x / n_splits : blockIdx.x / n_qtiles;
+  const int split = (MODE == TM_SPLIT) ? blockIdx.x % n_splits : 0;
+  const int qt = (MODE == TM_SPLIT) ? 0 : n_qtiles - 1 - (blockIdx.x % n_qtiles);
   const int h = unit % a.H, b = unit / a.H;
   const int q0 = qt * kTBM;
   const int n_total = (a.Lkv + kTBN - 1) / kTBN;
-  const int nt = a.causal ? min(n_total, (min(a.Lkv, q0 + kTBM) + kTBN - 1) / kTBN) : n_total;   // tiles with live keys
+  // tiles with live keys; causal: query i sees keys j <= i + coff, and a tile whose rows see none still walks
+  // one (fully masked) key tile so that its rows come out as queries with nothing to attend to
+  const int nt_all = a.causal ? min(n_total, (min(a.Lkv, max(q0 + kTBM + a.coff, 1)) + kTBN - 1) / kTBN) : n_total;
+  // this CTA's share of them: tiles t0 .. t0 + nt - 1 (all of them unless the keys are split)
+  const int per_split = (nt_all + n_splits - 1) / n_splits;
+  const int t0 = (MODE == TM_SPLIT) ? split * per_split : 0;
+  const int nt = (MODE == TM_SPLIT) ? max(0, min(nt_all, t0 + per_split) - t0) : nt_all;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -129,7 +203,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (lane == 0 && nt > 0) {
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
-      if (MODE == TM_FWD) prefetch_tensormap(&tm_v);
+      if (PV) prefetch_tensormap(&tm_v);
       mbar_arrive_expect_tx(&bars->q_full, C::kQBytes);
 #pragma unroll
       for (int c = 0; c < C::kQChunks; ++c)
@@ -144,15 +218,15 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
         for (int c = 0; c < C::kQChunks; ++c)
           tma_load_4d(smem + C::kKOff + s * C::kKBytes + c * C::kKChunkBytes, &tm_k, &bars->k_full[s], c * C::kEpc, h,
-                      j * kTBN, b);
-        if (MODE == TM_FWD) {
+                      (t0 + j) * kTBN, b);
+        if (PV) {
           if (j >= kTStages) ok = mbar_wait(&bars->v_empty[s], ((j / kTStages) - 1) & 1, abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars->v_full[s], C::kVBytes);
 #pragma unroll
           for (int c = 0; c < C::kVChunks; ++c)
             tma_load_4d(smem + C::kVOff + s * C::kVBytes + c * C::kKChunkBytes, &tm_v, &bars->v_full[s], c * C::kEpc, h,
-                        j * kTBN, b);
+                        (t0 + j) * kTBN, b);
         }
       }
       if (*abort_flag) {
@@ -160,7 +234,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mbar_wait_drain(&bars->q_full, 0, kDrainNs);
         for (int jj = max(0, j - kTStages); jj < j; ++jj) {
           mbar_wait_drain(&bars->k_full[jj % kTStages], (jj / kTStages) & 1, kDrainNs);
-          if (MODE == TM_FWD) mbar_wait_drain(&bars->v_full[jj % kTStages], (jj / kTStages) & 1, kDrainNs);
+          if (PV) mbar_wait_drain(&bars->v_full[jj % kTStages], (jj / kTStages) & 1, kDrainNs);
         }
       }
     }
@@ -193,11 +267,11 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (ok) issue_qk(0);
       if (ok && nt > 1) issue_qk(1);
       for (int j = 0; j < nt && ok; ++j) {
-        // P(j) is in tensor memory (TM_FWD) / S(j) has been read (the other modes)
+        // P(j) is in tensor memory (the modes that form P V) / S(j) has been read (the other modes)
         ok = mbar_wait(&bars->p_ready[j & 1], (j >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        if (MODE == TM_FWD) {
+        if (PV) {
           const int s = j % kTStages;
           ok = mbar_wait(&bars->v_full[s], (j / kTStages) & 1, abort_flag);
           if (!ok) break;
@@ -223,7 +297,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
     const uint32_t tO = lane_base + 2 * kTBN;
     const float c2 = a.scale * kLog2e;
-    const int lim = a.causal ? min(i, a.Lkv - 1) : a.Lkv - 1;   // last key this row attends to
+    const int lim = a.causal ? min(i + a.coff, a.Lkv - 1) : a.Lkv - 1;   // last key this row attends to (< 0: none)
     const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
     const bool drop = a.dropout_p > 0.f;
     RowSide rs = make_row_side(a, i, h, b, row_ok);
@@ -247,7 +321,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     for (int j = 0; j < nt; ++j) {
       const int sb = j & 1;
-      const int j0 = j * kTBN;
+      const int j0 = (t0 + j) * kTBN;
       uint4 bq[2][4], mq[2][2];
       side_issue<true>(rs, j0, a.Lkv, bq[0], mq[0]);
       side_issue<true>(rs, j0 + 32, a.Lkv, bq[1], mq[1]);
@@ -263,7 +337,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tmem_ld32(lane_base + sb * kTBN, sr[0]);
       tmem_ld32(lane_base + sb * kTBN + 32, sr[1]);
       tmem_wait_ld();
-      if (MODE != TM_FWD) {
+      if (!PV) {
         // the scores are in registers: the issuer may refill this buffer
         tc_fence_before();
         __syncwarp();
@@ -330,7 +404,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (__any_sync(0xffffffffu, raise)) {
         const float f = (raise && j > 0) ? ex2_approx(m_used - m_new) : 1.f;   // exp2(-inf) = 0: nothing gathered yet
         l *= f;
-        if (MODE == TM_FWD && j > 0) {
+        if (PV && j > 0) {
           // O still receives P(j-1) V(j-1): wait for that product before touching the accumulator
           ok = mbar_wait_warp(&bars->o_ready, (j - 1) & 1, abort_flag);
           if (!ok) break;
@@ -363,7 +437,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           sr[c][e] = ((kb[c] >> e) & 1u) ? (TF32 ? to_tf32(p) : __float_as_uint(p)) : 0u;
         }
       l += sum;
-      if (MODE == TM_FWD) {
+      if (PV) {
         if (TF32) {
           tmem_st32(lane_base + sb * kTBN, sr[0]);
           tmem_st32(lane_base + sb * kTBN + 32, sr[1]);
@@ -389,7 +463,30 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const T z = Elem<T>::from_f(row_const ? const_val : 0.f);
       for (int jj = nt * kTBN; jj < a.Lkv; ++jj) arow[jj] = z;
     }
-    if (ok && MODE != TM_SCORES) {
+    if (ok && MODE == TM_SPLIT) {
+      // partial result of this split: running maximum, sum, unnormalised O (first dv columns), fp32
+      const long long slot = ((long long)unit * n_splits + split) * a.Lq + i;
+      float* ml = a.ws + slot * 2;
+      float* orow = a.ws + split_ml_floats(a, n_splits) + slot * a.dv;
+      if (row_ok) { ml[0] = m_used; ml[1] = l; }
+      ok = mbar_wait_warp(&bars->o_ready, (nt - 1) & 1, abort_flag);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
+          tmem_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              if (c * 32 + e < a.dv)
+                *reinterpret_cast<uint4*>(orow + c * 32 + e) = make_uint4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+          }
+        }
+      }
+    }
+    if (ok && MODE != TM_SCORES && MODE != TM_SPLIT) {
       const bool dead = !(l > 0.f);
       if (a.lse && row_ok) {
         float lse_v = (l != l) ? __int_as_float(0x7fc00000) : dead ? neg_inf() : (m_used + log2f(l)) * kLn2;
@@ -487,48 +584,55 @@ bool tile_stride_ok(long long s, int esz) { return s > 0 && (s * esz) % 16 == 0 
 
 template <typename T, int DQ, int DV, int MODE>
 cudaError_t launch_tile(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
-                        cudaStream_t st) {
+                        cudaStream_t st, int n_splits = 1) {
   using C = TCfg<T, DQ, DV>;
   auto kern = attn_tile_kernel<T, DQ, DV, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int n_qtiles = (a.Lq + kTBM - 1) / kTBM;
-  const long long blocks = (long long)n_qtiles * a.H * a.B;
+  const long long blocks = (long long)((MODE == TM_SPLIT) ? n_splits : n_qtiles) * a.H * a.B;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kTThreads, C::kSmemBytes, st>>>(mq, mk, mv, a, n_qtiles);
+  kern<<<(unsigned)blocks, kTThreads, C::kSmemBytes, st>>>(mq, mk, mv, a, n_qtiles, n_splits);
   count_launch();
+  if (MODE == TM_SPLIT) {
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const long long rows = (long long)a.Lq * a.H * a.B;
+    attn_split_reduce_kernel<T><<<(unsigned)rows, 128, 0, st>>>(a, n_splits);
+    count_launch();
+  }
   return cudaGetLastError();
 }
 
 template <typename T, int MODE>
 cudaError_t launch_tile_dims(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
-                             cudaStream_t st) {
+                             cudaStream_t st, int n_splits) {
   const bool q128 = a.d > 64;
-  if (MODE != TM_FWD) {   // the value heads play no part: one instantiation per query-head size
-    if (q128) return launch_tile<T, 128, 64, MODE>(mq, mk, mv, a, st);
-    return launch_tile<T, 64, 64, MODE>(mq, mk, mv, a, st);
+  if (MODE != TM_FWD && MODE != TM_SPLIT) {   // the value heads play no part: one instantiation per query-head size
+    if (q128) return launch_tile<T, 128, 64, MODE>(mq, mk, mv, a, st, n_splits);
+    return launch_tile<T, 64, 64, MODE>(mq, mk, mv, a, st, n_splits);
   }
   const bool v128 = a.dv > 64;
-  if (q128 && v128) return launch_tile<T, 128, 128, MODE>(mq, mk, mv, a, st);
-  if (q128) return launch_tile<T, 128, 64, MODE>(mq, mk, mv, a, st);
-  if (v128) return launch_tile<T, 64, 128, MODE>(mq, mk, mv, a, st);
-  return launch_tile<T, 64, 64, MODE>(mq, mk, mv, a, st);
+  if (q128 && v128) return launch_tile<T, 128, 128, MODE>(mq, mk, mv, a, st, n_splits);
+  if (q128) return launch_tile<T, 128, 64, MODE>(mq, mk, mv, a, st, n_splits);
+  if (v128) return launch_tile<T, 64, 128, MODE>(mq, mk, mv, a, st, n_splits);
+  return launch_tile<T, 64, 64, MODE>(mq, mk, mv, a, st, n_splits);
 }
 
 template <int MODE>
-cudaError_t tile_run(const AttnArgs& a, int dtype, cudaStream_t st) {
+cudaError_t tile_run(const AttnArgs& a, int dtype, cudaStream_t st, int n_splits = 1) {
   CUtensorMap mq, mk, mv;
   if (!make_head_map(&mq, a.q, dtype, a.d, a.H, a.Lq, a.B, a.q_sl, a.q_sb, kTBM)) return cudaErrorInvalidValue;
   if (!make_head_map(&mk, a.k, dtype, a.d, a.H, a.Lkv, a.B, a.k_sl, a.k_sb, kTBN)) return cudaErrorInvalidValue;
-  if (MODE == TM_FWD) {
+  if (MODE == TM_FWD || MODE == TM_SPLIT) {
     if (!make_head_map(&mv, a.v, dtype, a.dv, a.H, a.Lkv, a.B, a.v_sl, a.v_sb, kTBN, true)) return cudaErrorInvalidValue;
   } else {
     mv = mk;
   }
   switch (dtype) {
-    case NNLIB_B200_F16:  return launch_tile_dims<__half, MODE>(mq, mk, mv, a, st);
-    case NNLIB_B200_BF16: return launch_tile_dims<__nv_bfloat16, MODE>(mq, mk, mv, a, st);
-    default:              return launch_tile_dims<float, MODE>(mq, mk, mv, a, st);
+    case NNLIB_B200_F16:  return launch_tile_dims<__half, MODE>(mq, mk, mv, a, st, n_splits);
+    case NNLIB_B200_BF16: return launch_tile_dims<__nv_bfloat16, MODE>(mq, mk, mv, a, st, n_splits);
+    default:              return launch_tile_dims<float, MODE>(mq, mk, mv, a, st, n_splits);
   }
 }
 
@@ -562,6 +666,30 @@ const char* tile_reject_reason(const AttnArgs& a, int dtype, bool need_v, bool a
 cudaError_t tile_fwd(const AttnArgs& a, int dtype, cudaStream_t st) { return tile_run<TM_FWD>(a, dtype, st); }
 cudaError_t tile_stats(const AttnArgs& a, int dtype, cudaStream_t st) { return tile_run<TM_STATS>(a, dtype, st); }
 cudaError_t tile_scores(const AttnArgs& a, int dtype, cudaStream_t st) { return tile_run<TM_SCORES>(a, dtype, st); }
+
+// Split-key forward for few queries (Lq <= 128).  How many CTAs share the key tiles of one unit: enough to
+// give every SM about two CTAs, at least four 64-key tiles each, never an empty share.
+int tile_split_count(const AttnArgs& a) {
+  if (a.Lq < 1 || a.Lq > kTBM || a.Lkv < 1) return 0;
+  const int n_total = (a.Lkv + kTBN - 1) / kTBN;
+  const int nt = a.causal ? std::min(n_total, (std::min(a.Lkv, std::max(kTBM + a.coff, 1)) + kTBN - 1) / kTBN) : n_total;
+  const long long units = (long long)a.H * a.B;
+  // with a CTA for at least half of the SMs already, the two-tile kernel (one CTA per unit walking all the
+  // keys) moves the keys faster than these kernels would with the keys split
+  if (units * 2 > 148) return 1;
+  long long want = (2LL * 148 + units - 1) / units;
+  want = std::min<long long>(want, std::max(1, nt / 4));
+  want = std::max<long long>(want, 1);
+  const int per = (int)((nt + want - 1) / want);
+  return (nt + per - 1) / per;
+}
+size_t tile_split_workspace_bytes(const AttnArgs& a) {
+  const int n = tile_split_count(a);
+  return n > 0 ? (size_t)split_ws_floats(a, n) * sizeof(float) : 0;
+}
+cudaError_t tile_split(const AttnArgs& a, int dtype, cudaStream_t st) {
+  return tile_run<TM_SPLIT>(a, dtype, st, tile_split_count(a));
+}
 
 // Reads and clears the sticky "a bounded wait ran out" flag of these kernels on the current device.
 cudaError_t tile_take_abort(int* out, cudaStream_t st) {

@@ -119,7 +119,12 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   int n_t0, n_t1;
   {
     int kv_end0 = a.Lkv, kv_end1 = a.Lkv;
-    if (a.causal) { kv_end0 = min(kv_end0, q0 + kBM); kv_end1 = min(kv_end1, q0 + 2 * kBM); }
+    // causal: query i sees keys j <= i + coff; a tile whose rows see no key at all still walks one key tile
+    // (everything masked), so that its rows come out as queries with nothing to attend to
+    if (a.causal) {
+      kv_end0 = min(kv_end0, max(q0 + kBM + a.coff, 1));
+      kv_end1 = min(kv_end1, max(q0 + 2 * kBM + a.coff, 1));
+    }
     n_t0 = (q0 < a.Lq) ? (kv_end0 + kBN - 1) / kBN : 0;
     n_t1 = (q0 + kBM < a.Lq) ? (kv_end1 + kBN - 1) / kBN : 0;
   }
@@ -340,7 +345,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t tS = lane_base + t * kBN;
       const uint32_t tO = lane_base + kQT * kBN + t * D;
       const float c2 = a.scale * kLog2e;
-      const int lim = a.causal ? min(i, a.Lkv - 1) : a.Lkv - 1;  // last kv index this row attends to
+      const int lim = a.causal ? min(i + a.coff, a.Lkv - 1) : a.Lkv - 1;  // last kv index this row attends to (< 0: none)
       const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
 
       float m_used = neg_inf();  // running maximum (scaled, base 2) the stored exponentials refer to
@@ -661,7 +666,7 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   const int h = unit % a.H, b = unit / a.H;
   const int q0 = qt * kBM;
   const int n_total = (a.Lkv + kBN - 1) / kBN;
-  const int n_live = a.causal ? min(n_total, (min(a.Lkv, q0 + kBM) + kBN - 1) / kBN) : n_total;
+  const int n_live = a.causal ? min(n_total, (min(a.Lkv, max(q0 + kBM + a.coff, 1)) + kBN - 1) / kBN) : n_total;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -758,7 +763,7 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     const bool row_ok = i < a.Lq;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
     const float c2 = a.scale * kLog2e;
-    const int lim = a.causal ? min(i, a.Lkv - 1) : a.Lkv - 1;
+    const int lim = a.causal ? min(i + a.coff, a.Lkv - 1) : a.Lkv - 1;
     const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
     const float lse_nat = row_ok ? a.lse[i + (long long)a.Lq * h + a.lse_sb * b] : 0.f;
     // rows that need a constant instead of an exponential: nothing to attend to (NaN like the reference,

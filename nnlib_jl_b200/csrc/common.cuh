@@ -29,6 +29,7 @@ struct AttnArgs {
   void* alpha;
   long long alpha_sb;
   int* status;
+  float* ws;                 // split-key forward: per-split partial results (see attn_tile.cu)
   long long rng_h0, rng_b0, rng_H;
   unsigned int key0, key1, off_lo, off_hi;
   unsigned int drop_thresh;  // floor(p * 2^16): a score is dropped iff its 16-bit lane is below it
@@ -37,6 +38,7 @@ struct AttnArgs {
   float scale;               // multiplies q·k (natural units)
   int bias_dtype;
   int causal, nan_fm;
+  int coff;                  // causal: key j is kept iff j <= i + coff (0: the square make_causal_mask pattern)
   int allow_tf32;            // Float32 arrays may run their products on the TF32 tensor-core path
   int d, dv, H, Lq, Lkv, B;
 };

@@ -38,6 +38,9 @@ cudaError_t tile_fwd(const AttnArgs& a, int dtype, cudaStream_t st);
 cudaError_t tile_stats(const AttnArgs& a, int dtype, cudaStream_t st);
 cudaError_t tile_scores(const AttnArgs& a, int dtype, cudaStream_t st);
 cudaError_t tile_take_abort(int* out, cudaStream_t st);
+int tile_split_count(const AttnArgs& a);                 // 0: the split-key forward does not apply (Lq > 128)
+size_t tile_split_workspace_bytes(const AttnArgs& a);
+cudaError_t tile_split(const AttnArgs& a, int dtype, cudaStream_t st);   // a.ws holds the workspace
 
 // tcgen05 backward kernels (attn_bwd_umma.cu)
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype);

@@ -392,6 +392,76 @@ def test_tile_kernel_masks_bias_dropout(dtype, d, dv):
     _close(a2, ao2, dtype, "alpha (scores entry)")
 
 
+def _offset_mask(Lkv, Lq, off):
+    """the Bool matrix the reference would be handed for `key <= query + off`"""
+    return np.arange(Lkv)[:, None] <= (np.arange(Lq)[None, :] + off)
+
+
+@pytest.mark.parametrize("dtype,d,Lq,Lkv,off", [
+    (torch.bfloat16, 128, 300, 500, 200),     # two-tile fused kernel; last query sees the last key
+    (torch.float16, 64, 300, 500, 37),
+    (torch.bfloat16, 128, 260, 400, -140),    # negative: the first 140 queries see no key at all (NaN like the reference)
+    (torch.bfloat16, 96, 200, 333, 133),      # one-tile kernels
+    (torch.float32, 48, 70, 100, 30),         # CUDA-core kernels
+])
+def test_causal_offset_matches_an_explicit_mask(dtype, d, Lq, Lkv, off):
+    """CausalMask(offset) — key j visible to query i iff j <= i + offset — against the oracle fed the same
+    pattern as a Bool matrix, x and α, on every forward kernel family."""
+    rng = np.random.default_rng(80 + d)
+    H, B = 2, 2
+    qn = _round_to(rng.standard_normal((d * H, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((d * H, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((d * H, Lkv, B)), dtype)
+    mask = _offset_mask(Lkv, Lq, off)
+    y, a = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), mask=nb.CausalMask(off), nheads=H)
+    with np.errstate(invalid="ignore"):
+        yo, ao = O.dot_product_attention(qn, kn, vn, mask=mask, nheads=H)
+    yn, an = nb.jl_to_numpy(y), np.asarray(a)
+    live = mask.any(axis=0)
+    assert np.isnan(yn[:, ~live]).all() and np.isnan(an[:, ~live]).all()       # nothing to attend to
+    _close(yn[:, live], yo[:, live], dtype, "x")
+    _close(an[:, live], ao[:, live], dtype, "alpha")
+    assert (an[:, live][~mask[:, live]] == 0).all()
+
+
+@pytest.mark.parametrize("dtype,d,dv,H,B,Lq,Lkv", [
+    (torch.bfloat16, 128, 128, 2, 1, 1, 5000),      # one new token, two units: 148 SMs would see two CTAs
+    (torch.float16, 64, 64, 4, 1, 5, 3000),
+    (torch.bfloat16, 128, 128, 1, 2, 16, 4100),
+    (torch.bfloat16, 96, 40, 2, 1, 128, 2500),      # a full query tile, other head sizes
+])
+def test_split_key_forward_for_few_queries(dtype, d, dv, H, B, Lq, Lkv):
+    """Few queries against a long key / value history, aligned at the end (offset = Lkv - Lq): the keys of a
+    unit are split over several CTAs and merged; x, the log-sum-exp (through α) and the options agree with
+    the oracle."""
+    rng = np.random.default_rng(90 + Lq)
+    off = Lkv - Lq
+    qn = _round_to(rng.standard_normal((d * H, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((d * H, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((dv * H, Lkv, B)), dtype)
+    q, k, v = _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype)
+    pr = nb.attention._Problem(q, k, v, None, nb.CausalMask(off), H, None, need_v=True)
+    pr.alloc_x()
+    assert _lib.load().nnlib_b200_attn_decode_workspace_bytes(pr.p) > 0
+    mask = _offset_mask(Lkv, Lq, off)
+    y, a = nb.dot_product_attention(q, k, v, mask=nb.CausalMask(off), nheads=H)
+    yo, ao = O.dot_product_attention(qn, kn, vn, mask=mask, nheads=H)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x")
+    _close(np.asarray(a), ao, dtype, "alpha")
+    # with a key-padding mask, a bias and dropout on top
+    keypad = rng.random((Lkv, 1, 1, B)) > 0.2
+    keypad[-1] = True
+    bn = _round_to(0.5 * rng.standard_normal((Lkv, Lq, H, 1)), dtype)
+    pd = 0.2
+    keep = P.keep_mask((Lkv, Lq, H, B), pd, 11, 2)
+    y, a = nb.dot_product_attention(q, k, v, _dev(bn, dtype), mask=nb.jl_from_numpy(keypad, device=DEV), nheads=H,
+                                    fdrop=nb.PhiloxDropout(pd, seed=11, offset=2))
+    yo, ao = O.dot_product_attention(qn, kn, vn, bn, mask=keypad, nheads=H,
+                                     fdrop=lambda al: al * keep / np.float32(1 - pd))
+    _close(nb.jl_to_numpy(y), yo, dtype, "x with options")
+    _close(np.asarray(a), ao, dtype, "alpha with options")
+
+
 TF32_TOL = (3e-3, 1e-3)     # max-abs, mean-rel against the Float32 oracle: 10-bit mantissa operands
 
 
