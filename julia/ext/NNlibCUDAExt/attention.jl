@@ -57,7 +57,38 @@ Base.@kwdef struct B200AttnParams
     alpha::CuPtr{Cvoid} = CU_NULL
     alpha_stride_b::Int64 = 0
     status::CuPtr{Int32} = CU_NULL
+    allow_tf32::Int32 = 0
+    reserved0::Int32 = 0
+    causal_offset::Int64 = 0
 end
+
+# One Int32 per device that every launch reports to: a kernel that gave up on a bounded wait, and every launch
+# the library skipped on that device afterwards, writes NNLIB_B200_TIMEOUT there (include/nnlib_b200.h,
+# "fail-stop behaviour").  Looked at where this file synchronises anyway (`Array(α)`), and by `b200_check_status`.
+const _status_words = Dict{Int,CuArray{Int32,1}}()
+const _status_lock = ReentrantLock()
+function _status_word()
+    id = CUDA.deviceid(device())
+    lock(_status_lock) do
+        get!(() -> CUDA.zeros(Int32, 1), _status_words, id)
+    end
+end
+"Throw if a kernel launched through these methods on the current device gave up on a bounded wait."
+function b200_check_status()
+    w = lock(() -> get(_status_words, CUDA.deviceid(device()), nothing), _status_lock)
+    w === nothing && return nothing
+    v = Array(w)[1]
+    if v != 0
+        fill!(w, 0)
+        _b200_check(Cint(v), "a kernel of an earlier call")
+    end
+    nothing
+end
+
+# Float32 arrays: exact fp32 arithmetic unless CUDA.jl's math mode allows reduced precision — the switch that
+# lets cuBLAS use TF32 for the reference's own batched_mul.
+_allow_tf32(::Type{Float32}) = CUDA.math_mode() == CUDA.FAST_MATH
+_allow_tf32(::Type) = false
 
 function _b200_check(rc::Cint, where::String)
     rc == 0 && return nothing
@@ -71,6 +102,20 @@ for name in (:attn_fwd, :attn_stats, :attn_scores, :attn_apply)
     @eval function $fn(p::B200AttnParams)
         rc = ccall(($sym, libnnlib_b200[]), Cint, (Ref{B200AttnParams}, Ptr{Cvoid}), p, stream().handle)
         _b200_check(rc, $(string(name)))
+    end
+end
+
+# x and lse.  Few queries against many keys: the library splits the keys of a unit over several CTAs when that
+# pays and tells how much scratch memory the partial results need (0: the ordinary forward).
+function _b200_forward(p::B200AttnParams)
+    need = p.Lq <= 128 ? ccall((:nnlib_b200_attn_decode_workspace_bytes, libnnlib_b200[]), Csize_t,
+                               (Ref{B200AttnParams},), p) : Csize_t(0)
+    need == 0 && return _b200_attn_fwd(p)
+    ws = CuArray{UInt8}(undef, need)
+    GC.@preserve ws begin
+        rc = ccall((:nnlib_b200_attn_decode, libnnlib_b200[]), Cint,
+                   (Ref{B200AttnParams}, CuPtr{Cvoid}, Csize_t, Ptr{Cvoid}), p, pointer(ws), need, stream().handle)
+        _b200_check(rc, "attn_decode")
     end
 end
 
@@ -93,8 +138,17 @@ mutable struct PhiloxDropout
 end
 _take_offset!(d::PhiloxDropout) = (o = d.offset; d.offset += 1; o)
 
-"Sentinel for `mask=`: the causal pattern `kv <= query` without the `(L, L)` Bool matrix."
-struct CausalMask end
+"""
+    CausalMask(offset=0)
+
+Sentinel for `mask=`: the causal pattern `kv <= query + offset` without the Bool matrix.  `offset = 0` is
+`make_causal_mask`'s square pattern; `offset = kv_len - q_len` aligns the last query with the last key (new
+queries against a longer key / value history).
+"""
+struct CausalMask
+    offset::Int
+end
+CausalMask() = CausalMask(0)
 
 # Julia arrays carry no modification counter, so a matrix cannot be proven untouched after
 # `make_causal_mask` returned it (`m[1, 3] = true` must change the result).  Every square Bool matrix is
@@ -135,9 +189,11 @@ function _b200_params(q::DenseCuArray{T,3}, k::DenseCuArray{T,3}, v, bias, mask,
     Ev = v === nothing ? E : size(v, 1)
     full = (Lkv, Lq, H, B)
     causal = false
+    coff = 0
     mptr = CuPtr{UInt8}(0); mstr = (0, 0, 0, 0)
     if mask isa CausalMask
         causal = true
+        coff = mask.offset
     elseif mask !== nothing
         eltype(mask) === Bool || throw(ArgumentError("mask must be a Bool array"))
         if _is_causal_matrix(mask, Lq, Lkv)
@@ -161,8 +217,9 @@ function _b200_params(q::DenseCuArray{T,3}, k::DenseCuArray{T,3}, v, bias, mask,
         d=E ÷ H, dv=Ev ÷ H, H, Lq, Lkv, B,
         q=reinterpret(CuPtr{Cvoid}, pointer(q)), k=reinterpret(CuPtr{Cvoid}, pointer(k)),
         v=v === nothing ? CuPtr{Cvoid}(0) : reinterpret(CuPtr{Cvoid}, pointer(v)),
-        bias=bptr, bias_stride=bstr, mask=mptr, mask_stride=mstr, causal=Int32(causal),
-        dropout_p=p, philox_seed=seed, philox_offset=off, rng_h0=h0, rng_b0=b0, rng_H=Htot)
+        bias=bptr, bias_stride=bstr, mask=mptr, mask_stride=mstr, causal=Int32(causal), causal_offset=coff,
+        dropout_p=p, philox_seed=seed, philox_offset=off, rng_h0=h0, rng_b0=b0, rng_H=Htot,
+        status=pointer(_status_word()), allow_tf32=Int32(_allow_tf32(T)))
 end
 
 _with(p::B200AttnParams; kw...) = B200AttnParams(; (f => getfield(p, f) for f in fieldnames(B200AttnParams))..., kw...)
@@ -195,7 +252,7 @@ end
 Base.reshape(a::LazyAttnScores{T}, dims::Dims{N}) where {T,N} =
     (prod(dims) == prod(a.dims) || throw(DimensionMismatch()); LazyAttnScores{T,N}(dims, a.params, (a.keep, a), a.value))
 Base.getindex(a::LazyAttnScores, I...) = CUDA.@allowscalar materialize!(a)[I...]
-Base.Array(a::LazyAttnScores) = Array(materialize!(a))
+Base.Array(a::LazyAttnScores) = (h = Array(materialize!(a)); b200_check_status(); h)   # the copy synchronised anyway
 Base.collect(a::LazyAttnScores) = Array(a)
 CUDA.CuArray(a::LazyAttnScores) = materialize!(a)
 Base.Broadcast.broadcastable(a::LazyAttnScores) = materialize!(a)
@@ -234,7 +291,7 @@ function dot_product_attention(q::DenseCuArray{T,3}, k::DenseCuArray{T,3}, v::De
     if fdrop === identity || fdrop isa PhiloxDropout
         p = _b200_params(q, k, v, bias, mask, nheads, fdrop isa PhiloxDropout ? fdrop : nothing)
         p = _with(p; x=reinterpret(CuPtr{Cvoid}, pointer(x)), lse=pointer(lse))
-        GC.@preserve q k v x lse bias mask (Lq > 0 && B > 0 && _b200_attn_fwd(p))
+        GC.@preserve q k v x lse bias mask (Lq > 0 && B > 0 && _b200_forward(p))
         α = LazyAttnScores{T,4}((Lkv, Lq, nheads, B), p, (q, k, bias, mask, lse), nothing)
         return x, α
     else
