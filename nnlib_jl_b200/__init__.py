@@ -8,7 +8,7 @@ independent (batch, head) units of one call over the GPUs of a box.
 """
 from .attention import (ArgumentError, CausalMask, LazyAttnScores, PhiloxDropout, check_status, device_health,
                         dot_product_attention, dot_product_attention_pullback, dot_product_attention_scores, identity,
-                        make_causal_mask, math_mode, set_math_mode)
+                        make_causal_mask, math_mode, scores_mode, set_math_mode, set_scores_mode)
 from . import batched  # batched_mul / batched_mul! on the library's strided-batched product
 from .batched import batched_adjoint, batched_mul, batched_mul_, batched_transpose
 from . import softmax  # softmax / logsoftmax and pullbacks: nnlib_jl_b200.softmax.softmax(x, dims=...)
@@ -18,7 +18,7 @@ from .layout import (as_column_major, is_column_major, jl_empty, jl_from_numpy, 
 
 __all__ = [
     "ArgumentError", "CausalMask", "HostPipelinedAttention", "LazyAttnScores", "PhiloxDropout", "check_status", "device_health",
-    "dot_product_attention", "dot_product_attention_pullback", "dot_product_attention_scores", "identity", "make_causal_mask", "math_mode", "set_math_mode",
+    "dot_product_attention", "dot_product_attention_pullback", "dot_product_attention_scores", "identity", "make_causal_mask", "math_mode", "scores_mode", "set_math_mode", "set_scores_mode",
     "batched_adjoint", "batched_mul", "batched_mul_", "batched_transpose",
     "as_column_major", "is_column_major", "jl_empty", "jl_from_numpy", "jl_reshape", "jl_to_numpy", "jl_zeros",
 ]

@@ -41,6 +41,8 @@ __all__ = [
     "check_status",
     "set_math_mode",
     "math_mode",
+    "set_scores_mode",
+    "scores_mode",
 ]
 
 
@@ -62,6 +64,26 @@ def set_math_mode(mode: str) -> None:
 
 def math_mode() -> str:
     return "fast" if _fast_math else "default"
+
+
+# The reference returns the scores eagerly; here they are rebuilt on first use by default, so that
+# ``x, _ = dot_product_attention(...)`` never pays for them.  A caller that always reads α can ask for the eager
+# form: one library call produces x and α together, and for short key sequences (every query's score row in
+# tensor memory: kv_len <= 512 at d = 64, <= 256 at d = 128) that is one kernel instead of two.
+_eager_scores = False
+
+
+def set_scores_mode(mode: str) -> None:
+    """``"lazy"`` (default): α is a :class:`LazyAttnScores`.  ``"eager"``: α is computed with x and returned
+    as an ordinary array, like the reference does."""
+    global _eager_scores
+    if mode not in ("lazy", "eager"):
+        raise ValueError("scores mode must be 'lazy' or 'eager'")
+    _eager_scores = (mode == "eager")
+
+
+def scores_mode() -> str:
+    return "eager" if _eager_scores else "lazy"
 
 
 class ArgumentError(ValueError):
@@ -424,6 +446,12 @@ def _fused(q, k, v, bias, mask, nheads, dropout):
     pr = _Problem(q, k, v, bias, mask, nheads, dropout, need_v=True)
     x = pr.alloc_x()
     pr.alloc_lse()
+    if _eager_scores:
+        alpha = pr.alloc_alpha()
+        if pr.Lq > 0 and pr.B > 0 and pr.Lkv > 0:
+            with torch.cuda.device(pr.dev):
+                _check(_lib.load().nnlib_b200_attention(C.byref(pr.p), None, 0, _stream()), "attention")
+        return x, alpha
     if pr.Lq > 0 and pr.B > 0:
         lib = _lib.load()
         with torch.cuda.device(pr.dev):

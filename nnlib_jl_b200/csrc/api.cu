@@ -204,6 +204,21 @@ int attention_validate(const nnlib_b200_attn_params* p) {
   return (fwd_ok && sc_ok) ? NNLIB_B200_OK : NNLIB_B200_UNSUPPORTED_SHAPE;
 }
 
+// x and alpha for validated arguments (lse given): one kernel when a query's whole score row fits in tensor
+// memory, else the fused forward followed by the score-rebuild kernel
+int attention_both(const nnlib_b200_attn_params* p, void* stream) {
+  AttnArgs a;
+  int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN | NEED_ALPHA, &a, false);
+  if (rc) return rc;
+  if (a.Lq > 0 && a.B > 0 && a.Lkv > 0 && !force_simt() && short_supports(a, p->dtype)) {
+    log_call("attention", p, a, "tcgen05 (x and alpha in one pass)", nullptr);
+    return finish(short_attention(a, p->dtype, (cudaStream_t)stream));
+  }
+  rc = nnlib_b200_attn_fwd(p, stream);
+  if (rc) return rc;
+  return nnlib_b200_attn_scores(p, stream);
+}
+
 }  // namespace nb200
 
 using namespace nb200;
@@ -388,9 +403,7 @@ int nnlib_b200_attention(const nnlib_b200_attn_params* p, void* workspace, size_
   // every argument of both halves is checked before the first kernel is enqueued
   int rc = attention_validate(&q);
   if (rc) return rc;
-  rc = nnlib_b200_attn_fwd(&q, stream);
-  if (rc) return rc;
-  return nnlib_b200_attn_scores(&q, stream);
+  return attention_both(&q, stream);
 }
 
 static int check_softmax(const nnlib_b200_softmax_params* p, bool backward) {
@@ -499,13 +512,15 @@ int nnlib_b200_attn_path(const nnlib_b200_attn_params* p) {
 }
 
 int nnlib_b200_device_health(void* stream) {
-  int v = 0, w = 0, u = 0, t = 0;
-  cudaError_t e = umma_take_abort(&v, (cudaStream_t)stream);
+  int v = 0, w = 0, u = 0, t = 0, s = 0;
+  cudaError_t e = short_take_abort(&s, (cudaStream_t)stream);
+  v = 0;
+  if (e == cudaSuccess) e = umma_take_abort(&v, (cudaStream_t)stream);
   if (e == cudaSuccess) e = umma_bwd_take_abort(&w, (cudaStream_t)stream);
   if (e == cudaSuccess) e = gemm_take_abort(&u, (cudaStream_t)stream);
   if (e == cudaSuccess) e = tile_take_abort(&t, (cudaStream_t)stream);
   if (e != cudaSuccess) return finish(e);
-  return (v || w || u || t) ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
+  return (v || w || u || t || s) ? NNLIB_B200_TIMEOUT : NNLIB_B200_OK;
 }
 
 int nnlib_b200_selftest_wait_runout(uint64_t limit_ns, int32_t* status, void* stream) {

@@ -98,7 +98,5 @@ extern "C" int nnlib_b200_attention_static(const nnlib_b200_attn_params* p, void
   q.lse_stride_b = 0;   // dense (Lq, H, B)
   const int rc_args = nb200::attention_validate(&q);   // both halves, before anything is enqueued
   if (rc_args != NNLIB_B200_OK) return rc_args;
-  const int rc_fwd = nnlib_b200_attn_fwd(&q, stream);
-  if (rc_fwd != NNLIB_B200_OK) return rc_fwd;
-  return nnlib_b200_attn_scores(&q, stream);
+  return nb200::attention_both(&q, stream);
 }

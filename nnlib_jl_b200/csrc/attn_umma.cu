@@ -1099,20 +1099,6 @@ cudaError_t launch_scores(const CUtensorMap& mq, const CUtensorMap& mk, const CU
   return cudaGetLastError();
 }
 
-// (Lkv, Lq, H, B) score array with 128-byte-swizzled boxes of 64 keys x 128 queries
-bool make_alpha_map(CUtensorMap* m, const AttnArgs& a, int dtype) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[4] = {(cuuint64_t)a.Lkv, (cuuint64_t)a.Lq, (cuuint64_t)a.H, (cuuint64_t)a.B};
-  const cuuint64_t strides[3] = {(cuuint64_t)a.Lkv * 2, (cuuint64_t)a.Lkv * a.Lq * 2, (cuuint64_t)a.alpha_sb * 2};
-  const cuuint32_t box[4] = {64, 128, 1, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = fn(m, dtype == NNLIB_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                        4, a.alpha, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
 // Tensor map over the bias array as (Lkv, Lq, H or 1, B or 1) with 64-key x 128-query boxes, for the
 // staged-bias forward.  Possible when the bias has 16-bit elements, key stride 1, query / head / batch
 // strides that are multiples of 8 elements (0 = broadcast for head and batch) and a 16-byte aligned base.

@@ -8,6 +8,7 @@ namespace nb200 {
 
 // argument check of the x + alpha composites (api.cu): everything attn_fwd and attn_scores would reject
 int attention_validate(const nnlib_b200_attn_params* p);
+int attention_both(const nnlib_b200_attn_params* p, void* stream);
 
 // CUDA-core kernels (attn_simt.cu)
 bool simt_supports(int d, int dv);
@@ -41,6 +42,11 @@ cudaError_t tile_take_abort(int* out, cudaStream_t st);
 int tile_split_count(const AttnArgs& a);                 // 0: the split-key forward does not apply (Lq > 128)
 size_t tile_split_workspace_bytes(const AttnArgs& a);
 cudaError_t tile_split(const AttnArgs& a, int dtype, cudaStream_t st);   // a.ws holds the workspace
+
+// x and alpha in one pass when a query's whole score row fits in tensor memory (attn_short.cu)
+bool short_supports(const AttnArgs& a, int dtype);
+cudaError_t short_attention(const AttnArgs& a, int dtype, cudaStream_t st);
+cudaError_t short_take_abort(int* out, cudaStream_t st);
 
 // tcgen05 backward kernels (attn_bwd_umma.cu)
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype);

@@ -432,6 +432,10 @@ cudaError_t launch_softmax(const void* x, const void* dy, void* out, long long i
       if (n > 2048) NB_SM_LAUNCH(256, false, 0); else NB_SM_LAUNCH(32, false, 0);
     } else if (np <= 32ll * 8) {
       NB_SM_LAUNCH(32, true, 8);
+    } else if (sizeof(T) == 2 && FWD && np <= 32ll * 16) {
+      // 16-bit columns of up to 4096 elements still fit a warp's registers (16 packets per lane): no block-wide
+      // barrier between the passes, sixteen independent loads in flight per lane
+      NB_SM_LAUNCH(32, true, 16);
     } else if (np <= 256ll * 8) {
       NB_SM_LAUNCH(256, true, 8);
     } else if (np <= 1024ll * kBig) {

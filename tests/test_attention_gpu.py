@@ -392,6 +392,81 @@ def test_tile_kernel_masks_bias_dropout(dtype, d, dv):
     _close(a2, ao2, dtype, "alpha (scores entry)")
 
 
+@pytest.fixture
+def eager_scores():
+    nb.set_scores_mode("eager")
+    yield
+    nb.set_scores_mode("lazy")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d,H,Lq,Lkv,B,kind", [
+    (64, 3, 512, 512, 2, "keypad"),     # config 2's shape class: four key tiles in tensor memory
+    (64, 2, 300, 264, 1, "plain"),      # ragged: a partial last key tile, a partial query tile
+    (64, 2, 384, 384, 2, "causal"),     # key tiles above the diagonal are written as zeros
+    (128, 2, 200, 256, 1, "plain"),     # d = 128: two key tiles
+    (128, 1, 256, 256, 2, "causal"),
+    (64, 2, 130, 512, 1, "bias"),       # bias, full mask and dropout
+    (64, 1, 64, 8, 1, "plain"),         # a single short tile
+])
+def test_short_sequence_kernel_x_and_alpha_in_one_pass(eager_scores, dtype, d, H, Lq, Lkv, B, kind):
+    """Eager scores for key sequences that fit one CTA's tensor memory: one kernel writes x and α
+    (src/attention.jl:83 returns both), checked against the oracle with every option."""
+    rng = np.random.default_rng(100 + Lq + Lkv)
+    E = d * H
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    q, k, v = _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype)
+    lib = _lib.load()
+    mask_np = bias_np = None
+    mask_arg = bias_arg = None
+    fdrop, fdrop_o = nb.identity, (lambda al: al)
+    if kind == "keypad":
+        lens = rng.integers(Lkv // 2, Lkv + 1, size=B)
+        mask_np = (np.arange(Lkv)[:, None, None, None] < lens[None, None, None, :])
+        mask_arg = nb.jl_from_numpy(mask_np, device=DEV)
+    elif kind == "causal":
+        mask_np = O.make_causal_mask(qn)
+        mask_arg = nb.make_causal_mask(q)
+    elif kind == "bias":
+        bias_np = _round_to(0.5 * rng.standard_normal((Lkv, Lq, H, B)), dtype)
+        bias_arg = _dev(bias_np, dtype)
+        mask_np = rng.random((Lkv, Lq, 1, B)) > 0.25
+        mask_np[0] = True
+        mask_arg = nb.jl_from_numpy(mask_np, device=DEV)
+        keep = P.keep_mask((Lkv, Lq, H, B), 0.2, 21, 4)
+        fdrop = nb.PhiloxDropout(0.2, seed=21, offset=4)
+        fdrop_o = lambda al: al * keep / np.float32(0.8)
+    n0 = lib.nnlib_b200_launch_count()
+    y, a = nb.dot_product_attention(q, k, v, bias_arg, mask=mask_arg, nheads=H, fdrop=fdrop)
+    assert lib.nnlib_b200_launch_count() - n0 == 1, "x and alpha must come from one kernel"
+    assert isinstance(a, torch.Tensor) and tuple(a.shape) == (Lkv, Lq, H, B)
+    yo, ao = O.dot_product_attention(qn, kn, vn, bias_np, mask=mask_np, nheads=H, fdrop=fdrop_o)
+    an = nb.jl_to_numpy(a)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x")
+    _close(an, ao, dtype, "alpha")
+    if mask_np is not None:
+        keepm = np.broadcast_to(O._bcast_to_scores(mask_np), ao.shape)
+        assert (an[~keepm] == 0).all(), "masked scores must be exactly 0"
+    if kind != "bias":
+        np.testing.assert_allclose(an.sum(0), 1.0, atol=1e-2)
+
+
+def test_eager_scores_on_longer_sequences_use_the_two_kernels(eager_scores):
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(101)
+    E, H, Lq, Lkv, B = 128, 2, 100, 700, 1
+    qn, kn, vn = (_round_to(rng.standard_normal((E, L, B)), dtype) for L in (Lq, Lkv, Lkv))
+    lib = _lib.load()
+    n0 = lib.nnlib_b200_launch_count()
+    y, a = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), nheads=H)
+    assert lib.nnlib_b200_launch_count() - n0 == 2
+    yo, ao = O.dot_product_attention(qn, kn, vn, nheads=H)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x")
+    _close(nb.jl_to_numpy(a), ao, dtype, "alpha")
+
+
 def _offset_mask(Lkv, Lq, off):
     """the Bool matrix the reference would be handed for `key <= query + off`"""
     return np.arange(Lkv)[:, None] <= (np.arange(Lq)[None, :] + off)
