@@ -6,18 +6,21 @@
 // Lkv <= 512 (d = 64) or <= 256 (d = 128) one CTA can hold the 128 x Lkv score block of its 128 queries in the
 // 512 TMEM columns, so the exact two-pass softmax of the reference (src/softmax.jl:69-79) needs no online
 // rescaling and no log-sum-exp round trip, and every exponential is taken once:
-//   warp 4     allocates tensor memory; TMA: Q, all K tiles, all V tiles (no ring: everything is resident)
-//   warp 5     tcgen05.mma: S_t = Q K_t^T for every key tile, later O = sum_t P_t V_t
-//   warps 0-3  thread r owns query row r:
+//   warp 8     allocates tensor memory; TMA: Q, all K tiles, all V tiles (no ring: everything is resident)
+//   warp 9     tcgen05.mma: S_t = Q K_t^T for every key tile, later O = sum_t P_t V_t
+//   warps 0-7  two threads per query row r (TMEM lane r): warps 0-3 own the first half of the key tiles,
+//              warps 4-7 the second half; the halves of a row meet through shared memory at two barriers
 //                pass 1  logits -> scale, bias (src/attention.jl:129-131), masks (:133-138) -> row maximum;
 //                        the prepared logits go back to their TMEM columns
 //                pass 2  p = exp2(s - m), row sum, dropout (src/dropout.jl:77-87); the 16-bit probabilities
-//                        are packed into the low half of the score columns (chunk g of 32 scores moves from
-//                        columns [32g, 32g+32) to [16g, 16g+16): always behind the reader)
+//                        are packed into the low half of their own tile's columns (chunk c of tile t moves
+//                        from [128t + 32c, +32) to [128t + 16c, +16): always behind the reader)
 //                pass 3  alpha' = P / l / (1-p) into 128-byte swizzled staging boxes (64 keys x 128 queries)
-//                epilogue x = O / l / (1-p)
-//   warp 6     ships every filled staging box with one cp.async.bulk.tensor store into the (Lkv, Lq, H, B) array
-// O lives in the columns the packing freed.  Bound by the HBM write of alpha.
+//                epilogue x = O / l / (1-p), each half writing half of the features
+//   warps 10, 11  one per half: ship every filled staging box with one cp.async.bulk.tensor store into the
+//              (Lkv, Lq, H, B) array
+// O lives in columns the packing freed (d = 64: the upper half of tile 0) or behind the scores (d = 128).
+// Bound by the HBM write of alpha.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -32,42 +35,56 @@ __device__ int g_short_abort = 0;  // sticky: a bounded wait of this kernel ran 
 
 namespace {
 
-constexpr int kShThreads = 224;
+constexpr int kShThreads = 384;
 constexpr int kShStageBytes = 128 * 128;   // staging box of the TMA store: 128 queries x 64 scores
 
 template <int D>
 struct ShCfg {
   static constexpr int kMaxTiles = (D == 64) ? 4 : 2;          // key tiles of 128 the CTA can hold
+  static constexpr int kTilesPerPart = kMaxTiles / 2;          // key tiles of one half of the softmax warps
   static constexpr int kChunks = D / 64;
   static constexpr int kTileBytes = kChunks * kChunkBytes;     // 128 rows x D features
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kTileBytes;
   static constexpr int kVOff = kKOff + kMaxTiles * kTileBytes;
-  static constexpr int kStOff = kVOff + kMaxTiles * kTileBytes;
-  static constexpr int kBarOff = kStOff + 2 * kShStageBytes;
+  static constexpr int kStOff = kVOff + kMaxTiles * kTileBytes;   // 2 halves x 2 staging boxes
+  static constexpr int kXOff = kKOff;      // row maxima and sums of the two halves: over K, which is done with by then
+  static constexpr int kBarOff = kStOff + 4 * kShStageBytes;
   static constexpr int kSmemBytes = kBarOff + 256 + 1024;
-  static constexpr int kTmemCols = kMaxTiles * 128;            // 512 / 256
-  static constexpr int kOCol = kMaxTiles * 64;                 // first column behind the packed probabilities
+  static constexpr int kTmemCols = 512;
+  static constexpr int kOCol = (D == 64) ? 64 : 256;
 };
 static_assert(ShCfg<64>::kSmemBytes <= 232448 && ShCfg<128>::kSmemBytes <= 232448, "shared memory budget");
-static_assert(ShCfg<64>::kOCol + 64 <= ShCfg<64>::kTmemCols && ShCfg<128>::kOCol + 128 <= ShCfg<128>::kTmemCols, "O fits");
 
 struct ShBarriers {
-  uint64_t qk_full, v_full, s_full, p_ready, o_full;
-  uint64_t stage_full[2], stage_free[2];
+  uint64_t qk_full, v_full, s_full[2], p_ready, o_full;
+  uint64_t stage_full[2][2], stage_free[2][2];
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(ShBarriers) <= 256, "barrier block");
 
-template <int D, bool BF16>
+// all 256 softmax threads (and nobody else)
+__device__ __forceinline__ void softmax_threads_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// XM = side + 3*drop as in the fused forward (attn_umma.cu): side 0 = no side input (optionally causal),
+// 1 = Bool mask array, 2 = bias (and mask); drop: dropout code compiled in.  The passes are bound by
+// instruction issue, so what a call does not use must not be in its loop.
+template <int D, bool BF16, int XM>
 __global__ void __launch_bounds__(kShThreads, 1)
 attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a, const AttnArgs a,
                   const int n_qtiles) {
   using C = ShCfg<D>;
+  constexpr int TPP = C::kTilesPerPart;
+  constexpr bool EXTRAS = (XM % 3) != 0;
+  constexpr bool XBIAS = (XM % 3) == 2;
+  constexpr bool DROP = XM >= 3;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   ShBarriers* bars = reinterpret_cast<ShBarriers*>(smem + C::kBarOff);
+  // [2 (max, sum)][2 halves][128 rows]; written only after ALL scores are complete, i.e. after the last read of K
+  float* xstat = reinterpret_cast<float*>(smem + C::kXOff);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -81,17 +98,19 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(&bars->qk_full, 1);
     mbar_init(&bars->v_full, 1);
-    mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->p_ready, 4);
+    mbar_init(&bars->s_full[0], 1);
+    mbar_init(&bars->s_full[1], 1);
+    mbar_init(&bars->p_ready, 8);
     mbar_init(&bars->o_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->stage_full[s], 4);
-      mbar_init(&bars->stage_free[s], 1);
-    }
+    for (int p = 0; p < 2; ++p)
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(&bars->stage_full[p][s], 4);
+        mbar_init(&bars->stage_free[p][s], 1);
+      }
     bars->abort_flag = *reinterpret_cast<volatile int*>(&g_short_abort);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(&bars->tmem_base, C::kTmemCols);
     tmem_relinquish();
   }
@@ -101,7 +120,7 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem = bars->tmem_base;
   const bool start_ok = (*abort_flag == 0);
 
-  if (start_ok && warp == 4) {
+  if (start_ok && warp == 8) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       prefetch_tensormap(&tm_q);
@@ -123,7 +142,7 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (!mbar_wait(&bars->qk_full, 0, abort_flag)) mbar_wait_drain(&bars->qk_full, 0, kDrainNs);
       if (!mbar_wait(&bars->v_full, 0, abort_flag)) mbar_wait_drain(&bars->v_full, 0, kDrainNs);
     }
-  } else if (start_ok && warp == 5) {
+  } else if (start_ok && warp == 9) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(BF16, kBM, kBN, false, false);
@@ -132,16 +151,18 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       bool ok = mbar_wait(&bars->qk_full, 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        for (int t = 0; t < n_live; ++t) {
-          const uint32_t ka = smem_u32(smem + C::kKOff + t * C::kTileBytes);
+        for (int t = 0; t < C::kMaxTiles; ++t) {
+          if (t < n_live) {
+            const uint32_t ka = smem_u32(smem + C::kKOff + t * C::kTileBytes);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
-            umma_ss(tmem + t * kBN, make_smem_desc_sw128(qa + off, 16, 1024), make_smem_desc_sw128(ka + off, 16, 1024),
-                    idesc_qk, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
+              umma_ss(tmem + t * kBN, make_smem_desc_sw128(qa + off, 16, 1024), make_smem_desc_sw128(ka + off, 16, 1024),
+                      idesc_qk, kk > 0 ? 1u : 0u);
+            }
           }
+          if ((t + 1) % TPP == 0) umma_commit(&bars->s_full[t / TPP]);   // the scores of one half of the warps
         }
-        umma_commit(&bars->s_full);
         // every row's probabilities are packed (and every score column has been read): O may be written
         ok = mbar_wait(&bars->p_ready, 0, abort_flag);
         if (ok) ok = mbar_wait(&bars->v_full, 0, abort_flag);
@@ -151,124 +172,173 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const uint32_t va = smem_u32(smem + C::kVOff + t * C::kTileBytes);
 #pragma unroll
             for (int kk = 0; kk < kBN / 16; ++kk)
-              umma_ts(tmem + C::kOCol, tmem + t * 64 + kk * 8, make_smem_desc_sw128(va + kk * 2048, kChunkBytes, 1024),
+              umma_ts(tmem + C::kOCol, tmem + t * kBN + kk * 8, make_smem_desc_sw128(va + kk * 2048, kChunkBytes, 1024),
                       idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(&bars->o_full);
         }
       }
     }
-  } else if (start_ok && warp == 6) {
-    // ---- store thread: each filled staging box (128 queries x 64 scores) goes out as one TMA store
+  } else if (start_ok && warp >= 10) {
+    // ---- store threads, one per half: each filled staging box (128 queries x 64 scores) goes out as one TMA store
     if (lane == 0) {
+      const int part = warp - 10;
       prefetch_tensormap(&tm_a);
       bool ok = true;
-      const int n_half = 2 * n_total;
-      for (int n = 0; n < n_half && ok; ++n) {
-        ok = mbar_wait(&bars->stage_full[n & 1], (n >> 1) & 1, abort_flag);
+      const int n_first = 2 * TPP * part;
+      const int n_mine = max(0, min(2 * n_total, 2 * TPP * (part + 1)) - n_first);
+      for (int k = 0; k < n_mine && ok; ++k) {
+        ok = mbar_wait(&bars->stage_full[part][k & 1], (k >> 1) & 1, abort_flag);
         if (!ok) break;
-        tma_store_4d(&tm_a, smem + C::kStOff + (n & 1) * kShStageBytes, n * 64, q0, h, b);
+        tma_store_4d(&tm_a, smem + C::kStOff + (part * 2 + (k & 1)) * kShStageBytes, (n_first + k) * 64, q0, h, b);
         tma_store_commit();
-        if (n >= 1) {
+        if (k >= 1) {
           tma_store_wait_read<1>();                 // the previous box has been read out of shared memory
-          mbar_arrive(&bars->stage_free[(n - 1) & 1]);
+          mbar_arrive(&bars->stage_free[part][(k - 1) & 1]);
         }
       }
       tma_store_wait_read<0>();                     // shared memory must stay valid until the last read
     }
-  } else if (start_ok && warp < 4) {
+  } else if (start_ok && warp < 8) {
     // ----------------------------------------------------------- softmax warps
-    const int r = warp * 32 + lane;
+    const int part = warp >> 2;                       // which half of the key tiles
+    const int r = (warp & 3) * 32 + lane;             // row inside the tile = TMEM lane
     const int i = q0 + r;
     const bool row_ok = i < a.Lq;
-    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float c2 = a.scale * kLog2e;
     const int lim = a.causal ? min(i + a.coff, a.Lkv - 1) : a.Lkv - 1;   // last key this row attends to (< 0: none)
     const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
-    const bool drop = a.dropout_p > 0.f;
-    RowSide rs = make_row_side(a, i, h, b, row_ok);
-    const int n_chunks = n_live * 4;     // chunks of 32 keys
+    RowSide rs;
+    if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
+    // EXTRAS: the prepared logits are already scaled; plain logits get scale*log2(e) inside the exponential's FMA
+    const float cs = EXTRAS ? 1.f : c2;
+    const int t_first = part * TPP;
+    const int t_end = min(n_live, t_first + TPP);     // this thread's live tiles: [t_first, t_end)
 
-    bool ok = mbar_wait_warp(&bars->s_full, 0, abort_flag);
+    // Every softmax thread goes through both exchange barriers whatever happens, so that a wait that ran out
+    // in one warp cannot leave the others at a barrier; the results of an aborted CTA are discarded anyway.
+    bool ok = mbar_wait_warp(&bars->s_full[part], 0, abort_flag);
     float m = neg_inf();
-    float l = 0.f;
-    if (ok) {
+    if (ok && t_end > t_first) {
       tc_fence_after();
       // ---- pass 1: prepared logits (scaled base 2, bias added, masked keys -inf) and the row maximum
       // (two chunks per turn, so that the bias / mask words of the next chunk are in flight while one is worked on)
+      // Two chunks per turn: the bias / mask words of the next chunk and its scores (the other register
+      // buffer) are in flight while one chunk is worked on.
       uint4 bq0[4], bq1[4], mq0[2], mq1[2];
-      auto prepare = [&](int g, const uint4 (&bq)[4], const uint4 (&mq)[2]) {
-        uint32_t s[32];
-        tmem_ld32(lane_base + g * 32, s);
-        tmem_wait_ld();
-        side_apply<true>(rs, s, bq, mq, g * 32, a.Lkv, lim, row_ok, c2);
+      uint32_t s0[32], s1[32];
+      auto prepare = [&](int g, uint32_t (&s)[32], const uint4 (&bq)[4], const uint4 (&mq)[2]) {
+        if (EXTRAS) {
+          side_apply<XBIAS>(rs, s, bq, mq, g * 32, a.Lkv, lim, row_ok, c2);
+        } else if (__any_sync(0xffffffffu, g * 32 + 31 > lim)) {
+          // the causal diagonal or the end of the keys runs through this chunk
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (g * 32 + e > lim) s[e] = 0xff800000u;
+        } else {
+          // plain chunk: the raw scores stay where they are
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
+          return;
+        }
 #pragma unroll
         for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
-        __syncwarp();                     // the bias / mask code above branches per row
+        __syncwarp();                     // the code above branches per row
         tmem_st32(lane_base + g * 32, s);
       };
-      side_issue<true>(rs, 0, a.Lkv, bq0, mq0);
+      const int g_end = t_end * 4;
+      if (EXTRAS) side_issue<XBIAS>(rs, t_first * kBN, a.Lkv, bq0, mq0);
+      tmem_ld32(lane_base + t_first * kBN, s0);
 #pragma unroll 1
-      for (int g = 0; g < n_chunks; g += 2) {
-        side_issue<true>(rs, (g + 1) * 32, a.Lkv, bq1, mq1);
-        prepare(g, bq0, mq0);
-        if (g + 2 < n_chunks) side_issue<true>(rs, (g + 2) * 32, a.Lkv, bq0, mq0);
-        prepare(g + 1, bq1, mq1);
+      for (int g = t_first * 4; g < g_end; g += 2) {
+        if (EXTRAS) side_issue<XBIAS>(rs, (g + 1) * 32, a.Lkv, bq1, mq1);
+        tmem_wait_ld();
+        tmem_ld32(lane_base + (g + 1) * 32, s1);
+        prepare(g, s0, bq0, mq0);
+        if (EXTRAS && g + 2 < g_end) side_issue<XBIAS>(rs, (g + 2) * 32, a.Lkv, bq0, mq0);
+        tmem_wait_ld();
+        if (g + 2 < g_end) tmem_ld32(lane_base + (g + 2) * 32, s0);
+        prepare(g + 1, s1, bq1, mq1);
       }
       tmem_wait_st();
+    }
+    if (part == 0) mbar_wait_warp(&bars->s_full[1], 0, abort_flag);   // the other half's products still read K until then
+    xstat[part * 128 + r] = m * cs;                   // in scaled base-2 units from here on (scale > 0)
+    softmax_threads_sync();
+    m = fmaxf(xstat[r], xstat[128 + r]);              // fmaxf drops a NaN: a NaN logit shows up in the sum instead
+
+    float l = 0.f;
+    if (ok && t_end > t_first) {
       // ---- pass 2: exponentials, row sum, dropout, packed probabilities
-      const bool row_inf = (m == pos_inf());          // a +Inf bias: equal shares on the +Inf keys (src/softmax.jl:73-75)
-      const float m_sub = (m == neg_inf()) ? 0.f : m;
-#pragma unroll 1
-      for (int g = 0; g < n_chunks; ++g) {
+      const bool row_inf = XBIAS && (m == pos_inf());  // a +Inf bias: equal shares on the +Inf keys (src/softmax.jl:73-75)
+      const float m_neg = (m == neg_inf()) ? 0.f : -m;
+      uint32_t s0[32], s1[32];
+      auto exps = [&](int g, const uint32_t (&s)[32]) {
         unsigned int kb = 0xffffffffu;
-        if (drop) kb = dropout_keep32(a, srow, (unsigned int)g);
-        uint32_t s[32];
-        tmem_ld32(lane_base + g * 32, s);
-        tmem_wait_ld();
+        if (DROP) kb = dropout_keep32(a, srow, (unsigned int)g);
         uint32_t pk[16];
-        float sum = 0.f;
+        float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = ex2_approx(__uint_as_float(s[e]) - m_sub);
-          float p1 = ex2_approx(__uint_as_float(s[e + 1]) - m_sub);
-          if (row_inf) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(s[e]), cs, m_neg));
+          float p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), cs, m_neg));
+          if (XBIAS && row_inf) {
             p0 = (s[e] == 0x7f800000u) ? 1.f : 0.f;
             p1 = (s[e + 1] == 0x7f800000u) ? 1.f : 0.f;
           }
-          sum += p0 + p1;                 // dropout follows the softmax: the row sum keeps the dropped scores
-          if (!((kb >> e) & 1u)) p0 = 0.f;
-          if (!((kb >> (e + 1)) & 1u)) p1 = 0.f;
+          sum0 += p0;                     // dropout follows the softmax: the row sum keeps the dropped scores
+          sum1 += p1;
           pk[e >> 1] = pack2<BF16>(p0, p1);
+          if (DROP) pk[e >> 1] &= (((kb >> e) & 1u) ? 0x0000ffffu : 0u) | (((kb >> (e + 1)) & 1u) ? 0xffff0000u : 0u);
         }
-        l += sum;
-        tmem_st16(lane_base + g * 16, pk);
+        l += sum0 + sum1;
+        tmem_st16(lane_base + (g >> 2) * kBN + (g & 3) * 16, pk);   // chunk c of tile t -> [128 t + 16 c, +16)
+      };
+      // the next chunk's scores are fetched while one chunk is turned into probabilities; the packed
+      // probabilities of chunk g land in columns chunk g / 2 of the same tile has already left
+      const int g_end = t_end * 4;
+      tmem_ld32(lane_base + t_first * kBN, s0);
+#pragma unroll 1
+      for (int g = t_first * 4; g < g_end; g += 2) {
+        tmem_wait_ld();
+        tmem_ld32(lane_base + (g + 1) * 32, s1);
+        exps(g, s0);
+        tmem_wait_ld();
+        if (g + 2 < g_end) tmem_ld32(lane_base + (g + 2) * 32, s0);
+        exps(g + 1, s1);
       }
       tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_ready);
     }
+    tc_fence_before();
+    __syncwarp();
+    if (ok && lane == 0) mbar_arrive(&bars->p_ready);
+    xstat[256 + part * 128 + r] = l;
+    softmax_threads_sync();
+    l = xstat[256 + r] + xstat[256 + 128 + r];
 
     // ---- pass 3: alpha' = P / l / (1-p), box by box
-    bool okst = ok;
     if (ok) {
       const bool dead = !(l > 0.f);
       const float nanv = __int_as_float(0x7fc00000);
       const float scale = dead ? 0.f : a.inv_keep / l;
       const float dead_val = (a.nan_fm || l != l) ? nanv : 0.f;
-      if (a.lse && row_ok) {
+      if (part == 0 && a.lse && row_ok) {
         float lse_v = (l != l) ? nanv : dead ? neg_inf() : (m + log2f(l)) * kLn2;
         if (m == pos_inf() && !dead) lse_v = lse_inf_rows(l);
         a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = lse_v;
       }
-      const int n_half = 2 * n_total;
-#pragma unroll 1
-      for (int n = 0; n < n_half; ++n) {
-        uint32_t pk[32];
+      const int n_first = 2 * TPP * part;
+      const int n_mine = max(0, min(2 * n_total, 2 * TPP * (part + 1)) - n_first);
+      const bool any_dead = __any_sync(0xffffffffu, dead);
+      bool okst = true;
+      // packed probabilities of box n (keys [64 n, 64 n + 64)) of this row: fetched one box ahead
+      auto fetch = [&](int n, uint32_t (&pk)[32]) {
+        if (n < 2 * n_live) tmem_ld32(lane_base + (n >> 1) * kBN + (n & 1) * 32, pk);
+      };
+      auto emit = [&](int k, uint32_t (&pk)[32]) {
+        const int n = n_first + k;
         if (n < 2 * n_live) {
-          tmem_ld32(lane_base + n * 32, pk);          // 64 packed probabilities of this row
-          tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             float lo, hi;
@@ -279,9 +349,13 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pk[e]));
               lo = f.x; hi = f.y;
             }
-            lo *= scale; hi *= scale;
-            if (dead) { lo = dead_val; hi = dead_val; }
-            pk[e] = pack2<BF16>(lo, hi);
+            pk[e] = pack2<BF16>(lo * scale, hi * scale);
+          }
+          if (any_dead) {                 // rows with nothing to attend to (or a NaN logit): a constant
+            const uint32_t z = pack2<BF16>(dead_val, dead_val);
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (dead) pk[e] = z;
           }
         } else {
           // key tiles entirely above the causal diagonal
@@ -289,21 +363,33 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 32; ++e) pk[e] = z;
         }
-        if (n >= 2) {
-          okst = mbar_wait_warp(&bars->stage_free[n & 1], ((n >> 1) - 1) & 1, abort_flag);
-          if (!okst) break;
+        if (k >= 2) {
+          okst = mbar_wait_warp(&bars->stage_free[part][k & 1], ((k >> 1) - 1) & 1, abort_flag);
+          if (!okst) return;
         }
-        uint8_t* row = smem + C::kStOff + (n & 1) * kShStageBytes + r * 128;
+        uint8_t* row = smem + C::kStOff + (part * 2 + (k & 1)) * kShStageBytes + r * 128;
 #pragma unroll
         for (int v = 0; v < 8; ++v)
           *reinterpret_cast<uint4*>(row + ((v ^ (r & 7)) << 4)) =
               make_uint4(pk[v * 4], pk[v * 4 + 1], pk[v * 4 + 2], pk[v * 4 + 3]);
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->stage_full[n & 1]);
+        if (lane == 0) mbar_arrive(&bars->stage_full[part][k & 1]);
+      };
+      uint32_t pk0[32], pk1[32];
+      if (n_mine > 0) fetch(n_first, pk0);
+#pragma unroll 1
+      for (int k = 0; k < n_mine && okst; k += 2) {
+        tmem_wait_ld();
+        if (k + 1 < n_mine) fetch(n_first + k + 1, pk1);
+        emit(k, pk0);
+        if (!okst || k + 1 >= n_mine) break;
+        tmem_wait_ld();
+        if (k + 2 < n_mine) fetch(n_first + k + 2, pk0);
+        emit(k + 1, pk1);
       }
 
-      // ---- epilogue: x = O / l / (1-p)
+      // ---- epilogue: x = O / l / (1-p); each half of the warps writes half of the features
       if (okst) {
         ok = mbar_wait_warp(&bars->o_full, 0, abort_flag);
         if (ok) {
@@ -311,7 +397,8 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
                           2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * D);
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
+          for (int cc = 0; cc < D / 64; ++cc) {
+            const int c = part * (D / 64) + cc;       // 32-column chunk of O
             uint32_t o[32];
             tmem_ld32(lane_base + C::kOCol + c * 32, o);
             tmem_wait_ld();
@@ -338,7 +425,7 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, C::kTmemCols);
   }
@@ -348,10 +435,10 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, int XM>
 cudaError_t launch_short(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma,
                          const AttnArgs& a, cudaStream_t st) {
-  auto kern = attn_short_kernel<D, BF16>;
+  auto kern = attn_short_kernel<D, BF16, XM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ShCfg<D>::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int n_qtiles = (a.Lq + kBM - 1) / kBM;
@@ -383,8 +470,23 @@ cudaError_t short_attention(const AttnArgs& a, int dtype, cudaStream_t st) {
   if (!make_map(&mv, a.v, dtype, E, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
   if (!make_alpha_map(&ma, a, dtype)) return cudaErrorInvalidValue;
   const bool bf16 = dtype == NNLIB_B200_BF16;
-  if (a.d == 128) return bf16 ? launch_short<128, true>(mq, mk, mv, ma, a, st) : launch_short<128, false>(mq, mk, mv, ma, a, st);
-  return bf16 ? launch_short<64, true>(mq, mk, mv, ma, a, st) : launch_short<64, false>(mq, mk, mv, ma, a, st);
+  const int side = a.bias != nullptr ? 2 : (a.mask != nullptr ? 1 : 0);
+  const int xm = side + (a.dropout_p > 0.f ? 3 : 0);
+#define NB_SH(DD, BF)                                                           \
+  do {                                                                          \
+    switch (xm) {                                                               \
+      case 0: return launch_short<DD, BF, 0>(mq, mk, mv, ma, a, st);            \
+      case 1: return launch_short<DD, BF, 1>(mq, mk, mv, ma, a, st);            \
+      case 2: return launch_short<DD, BF, 2>(mq, mk, mv, ma, a, st);            \
+      case 3: return launch_short<DD, BF, 3>(mq, mk, mv, ma, a, st);            \
+      case 4: return launch_short<DD, BF, 4>(mq, mk, mv, ma, a, st);            \
+      default: return launch_short<DD, BF, 5>(mq, mk, mv, ma, a, st);           \
+    }                                                                           \
+  } while (0)
+  if (a.d == 128) { if (bf16) NB_SH(128, true); NB_SH(128, false); }
+  if (bf16) NB_SH(64, true);
+  NB_SH(64, false);
+#undef NB_SH
 }
 
 // Reads and clears the sticky "a bounded wait ran out" flag of this kernel on the current device.
