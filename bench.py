@@ -60,6 +60,9 @@ WORKLOADS = {
     "c2": dict(desc="encoder self-attention (BERT-base shape): bf16 E=768 nheads=12 d=64 L=512 batch=32, "
                     "key-padding mask, scores returned",
                dtype="bf16", E=768, H=12, Lq=512, Lkv=512, B=32, causal=False, padmask=True, alpha=True),
+    "c3f32": dict(desc="config 3's shape in Float32 on the TF32 tensor-core path (set_math_mode('fast')): E=4096 nheads=32 "
+                       "d=128 L=4096 batch=2, causal, x only",
+                  dtype="f32", E=4096, H=32, Lq=4096, Lkv=4096, B=2, causal=True, fast_math=True),
     "c4": dict(desc="cross-attention with additive bias: fp16 q(1024,256,16) kv(1024,2048,16) nheads=16 d=64, "
                     "bias f16 (Lkv,Lq,H,B), dropout 0.1",
                dtype="f16", E=1024, H=16, Lq=256, Lkv=2048, B=16, causal=False, bias=True, dropout=0.1),
@@ -368,6 +371,8 @@ def run_ours(args, w):
         kwargs["mask"] = m.reshape(B, 1, 1, Lkv).permute(3, 2, 1, 0)            # (Lkv,1,1,B) column-major
     if w.get("bias"):
         bias = nb.jl_empty((Lkv, Lq, H, B), tdtype, dev); bias.normal_(0.0, 0.5, generator=g)
+    if w.get("fast_math"):
+        nb.set_math_mode("fast")
     want_alpha = bool(w.get("alpha"))
     if want_alpha:
         # the workload returns the scores: ask for them with x (one library call) instead of rebuilding them lazily

@@ -35,13 +35,6 @@ namespace nb200 {
 
 __device__ int g_bwd_abort = 0;  // sticky: a bounded wait of a backward kernel ran out
 
-#ifdef NB200_TRACE
-// Development aid: per-phase clock stamps of one CTA, read back by a test harness.  Not compiled into
-// the shipped library.
-__device__ long long g_trace_bwd[4][64][8];
-#define NB_TRACE(role, j, slot) \
-  do { if (blockIdx.x == NB200_TRACE_BLOCK && (j) < 64) g_trace_bwd[role][j][slot] = clock64(); } while (0)
-#endif
 
 namespace {
 
@@ -146,14 +139,6 @@ __device__ __forceinline__ float bias16_value(unsigned int word, int odd, int dt
   return __half2float(__ushort_as_half((unsigned short)h));
 }
 
-#ifdef NB200_TRACE
-#ifndef NB200_TRACE_DKV
-#define NB200_TRACE_DKV 0
-#endif
-#define BW_TRACE(role, j, slot) do { if (DKV == (NB200_TRACE_DKV != 0)) NB_TRACE(role, j, slot); } while (0)
-#else
-#define BW_TRACE(role, j, slot) do { } while (0)
-#endif
 
 // score row held as raw TMEM words: element e lives in su[e / 32][e % 32]
 #define NB_SR(e) __uint_as_float(su[(e) >> 5][(e) & 31])
@@ -257,7 +242,6 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         const int s = it % C::kStagesA;
         if (it >= C::kStagesA) ok = mbar_wait(&bars->a_empty[s], ((it / C::kStagesA) - 1) & 1, abort_flag);
         if (!ok) break;
-        BW_TRACE(3, it, 0);
         mbar_arrive_expect_tx(&bars->a_full[s], C::kTile);
         for (int c = 0; c < D / 64; ++c)
           tma_load_3d(smem + C::kAOff + s * C::kTile + c * kChunkBytes, &tm_ra, &bars->a_full[s], h * D + c * 64,
@@ -279,7 +263,6 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         const int s = it % C::kStagesB;
         if (it >= C::kStagesB) ok = mbar_wait(&bars->b_empty[s], ((it / C::kStagesB) - 1) & 1, abort_flag);
         if (!ok) break;
-        BW_TRACE(3, it, 1);
         mbar_arrive_expect_tx(&bars->b_full[s], C::kTile);
         for (int c = 0; c < D / 64; ++c)
           tma_load_3d(smem + C::kBOff + s * C::kTile + c * kChunkBytes, &tm_rb, &bars->b_full[s], h * D + c * 64,
@@ -356,15 +339,12 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       for (int it = 0; it < n && ok; ++it) {
         const uint32_t par = it & 1;
         const bool more = it + 1 < n;
-        BW_TRACE(2, it, 0);
         if (more) {
           ok = mbar_wait(&bars->a_full[(it + 1) % C::kStagesA], ((it + 1) / C::kStagesA) & 1, abort_flag);
           if (ok) ok = mbar_wait(&bars->s_read, par, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          BW_TRACE(2, it, 1);
           issue_s(it + 1);
-          BW_TRACE(2, it, 2);
         }
         if (!DKV) {
           if (more) {
@@ -372,30 +352,24 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
             if (ok) ok = mbar_wait(&bars->dp_read, par, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            BW_TRACE(2, it, 3);
             issue_dp(it + 1);
           }
           ok = mbar_wait(&bars->ds_ready, par, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          BW_TRACE(2, it, 4);
           issue_ds_acc(it);
-          BW_TRACE(2, it, 5);
         } else {
           ok = mbar_wait(&bars->ds_ready, par, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          BW_TRACE(2, it, 3);
           issue_ds_acc(it);
           if (more) {
             ok = mbar_wait(&bars->b_full[(it + 1) % C::kStagesB], ((it + 1) / C::kStagesB) & 1, abort_flag);
             if (!ok) break;
             issue_dp(it + 1);   // overwrites dS: ordered behind the dK products above
           }
-          BW_TRACE(2, it, 4);
           ok = mbar_wait(&bars->pt_ready, par, abort_flag);
           if (!ok) break;
-          BW_TRACE(2, it, 5);
           issue_dv(it);
         }
       }
@@ -541,12 +515,10 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
           }
         }
       }
-      if (threadIdx.x == 0) BW_TRACE(0, it, 0);
       ok = mbar_wait(&bars->s_full, par, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (threadIdx.x == 0) BW_TRACE(0, it, 1);
       uint32_t su[2][32];
       tmem_ld32(tS, su[0]);
       tmem_ld32(tS + 32, su[1]);
@@ -554,7 +526,6 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_read);
-      if (threadIdx.x == 0) BW_TRACE(0, it, 2);
 
       if (!DKV) {
         const int lim = row_ok ? (a.causal ? min(row, a.Lkv - 1) : a.Lkv - 1) : -1;  // last key of this row
@@ -631,12 +602,10 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         }
       }
 
-      if (threadIdx.x == 0) BW_TRACE(0, it, 3);
       ok = mbar_wait(&bars->dp_full, par, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (threadIdx.x == 0) BW_TRACE(0, it, 4);
 
       // dS = P (dP - D), rounded to the element type: the A operand of the dQ / dK product
       uint32_t pk[32];
@@ -698,7 +667,6 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_ready);
-      if (threadIdx.x == 0) BW_TRACE(0, it, 5);
 
       if (BIAS && !DKV && dbias_p) {
         // gradient of the bias = dS in fp32 (masked and dropped-out positions included: they are zero /
@@ -751,7 +719,6 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         if (lane == 0) mbar_arrive(&bars->pt_ready);
         if (it + 1 < n) col_store(it + 1, col_next);
       }
-      if (threadIdx.x == 0) BW_TRACE(0, it, 6);
     }
 
     // ---------------------------------------------------------------- epilogue
@@ -807,7 +774,6 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
   }
 }
 
-#undef BW_TRACE
 #undef NB_SR
 #undef NB_SR_SET
 
@@ -880,11 +846,6 @@ cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_
   return e;
 }
 
-#ifdef NB200_TRACE
-extern "C" __attribute__((visibility("default"))) int nnlib_b200_trace_dump_bwd(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_trace_bwd, sizeof(long long) * 4 * 64 * 8);
-}
-#endif
 
 // Reads and clears the backward kernels' sticky "a bounded wait ran out" flag of the current device.
 // Synchronises the stream.

@@ -38,15 +38,6 @@ namespace nb200 {
 
 __device__ int g_umma_abort = 0;  // sticky: a bounded wait ran out somewhere
 
-#ifdef NB200_TRACE
-// Development aid: per-phase clock stamps of one CTA (block 0), read back by a
-// test harness.  Not compiled into the shipped library.
-__device__ long long g_trace[4][64][8];
-#define NB_TRACE(role, j, slot) \
-  do { if (blockIdx.x == NB200_TRACE_BLOCK && (j) < 64) g_trace[role][j][slot] = clock64(); } while (0)
-#else
-#define NB_TRACE(role, j, slot) do { } while (0)
-#endif
 
 namespace {
 
@@ -290,11 +281,8 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t par = j & 1;
         // operand tiles first: they land long before the probabilities are ready, so these two
         // waits cost nothing on the softmax -> MMA -> softmax chain
-        NB_TRACE(3, j, 0);
         if (!STATS) ok = mbar_wait(&bars->v_full[sv], (j / C::kStagesV) & 1, abort_flag);
-        NB_TRACE(3, j, 1);
         if (ok && j + 1 < n_kv) ok = mbar_wait(&bars->k_full[sk], ((j + 1) / C::kStagesK) & 1, abort_flag);
-        NB_TRACE(3, j, 2);
 #pragma unroll
         for (int t = 0; t < kQT; ++t) {
           const int nt = (t == 0) ? n_t0 : n_t1;
@@ -303,14 +291,11 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           ok = mbar_wait(&bars->p_half[t][0], par, abort_flag);
           if (!ok) continue;
           tc_fence_after();
-          NB_TRACE(2, j, t * 4 + 0);
           if (!STATS) {
             NB_ISSUE_PV(t, sv, 0, kBN / 32, j == 0);
-            NB_TRACE(2, j, t * 4 + 1);
             ok = mbar_wait(&bars->p_half[t][1], par, abort_flag);
             if (!ok) continue;
             tc_fence_after();
-            NB_TRACE(2, j, t * 4 + 2);
             NB_ISSUE_PV(t, sv, kBN / 32, kBN / 16, false);
           }
           if (j + 1 < nt) {
@@ -319,14 +304,10 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           } else if (!STATS) {
             umma_commit(&bars->o_full[t]);
           }
-          NB_TRACE(2, j, t * 4 + 3);
         }
         if (!ok) break;
-        NB_TRACE(3, j, 3);
         if (!STATS) umma_commit(&bars->v_empty[sv]);
-        NB_TRACE(3, j, 4);
         if (j + 1 < n_kv) umma_commit(&bars->k_empty[sk]);
-        NB_TRACE(3, j, 5);
       }
 #undef NB_ISSUE_QK
 #undef NB_ISSUE_PV
@@ -355,7 +336,6 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
 
       for (int j = 0; j < nt; ++j) {
-        if (r == 0) NB_TRACE(t, j, 0);
         // bias / mask of the first 64 keys of this tile: in flight while the scores are awaited
         uint4 bq[2][4], mq[2][2];
         if (EXTRAS) {
@@ -373,12 +353,10 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        if (r == 0) NB_TRACE(t, j, 1);
         uint32_t sr[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
         tmem_wait_ld();
-        if (r == 0) NB_TRACE(t, j, 2);
 
         const int j0 = j * kBN;
         if (STATS) {
@@ -498,7 +476,6 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
             NB_EXP_HALF_W(0, (m_used == neg_inf()) ? 0.f : m_used);
           }
-          if (r == 0) NB_TRACE(t, j, 3);
           const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
@@ -522,7 +499,6 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->p_half[t][hf]);
-            if (r == 0) NB_TRACE(t, j, 4 + hf);
           }
         } else {
           // statistics only: running maximum and sum
@@ -537,7 +513,6 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #undef NB_EXP_HALF_W
 #undef NB_EXP_HALF
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        if (r == 0) NB_TRACE(t, j, 6);
       }
 
       // ---------------------------------------------------------- epilogue
@@ -1255,11 +1230,6 @@ cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st) {
   return cudaErrorInvalidValue;
 }
 
-#ifdef NB200_TRACE
-extern "C" __attribute__((visibility("default"))) int nnlib_b200_trace_dump(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 4 * 64 * 8);
-}
-#endif
 
 // Self-test of the bounded wait: one CTA waits, with the same mbar_wait every kernel here uses, on a
 // barrier that nobody ever arrives at.  The wait gives up after `limit_ns`, the CTA leaves through the

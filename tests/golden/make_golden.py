@@ -2,15 +2,15 @@
 
 NNlib.jl is Julia and cannot run where these tests run, but its test-suite
 carries literal known-answer vectors for the attention path.  This script reads
-those test files AS TEXT from a checkout of the reference (default
-``/root/reference``) and writes ``nnlib_attention_golden.json`` next to itself:
+those test files AS TEXT from a checkout of the reference (its path is the one argument)
+and writes ``nnlib_attention_golden.json`` next to itself:
 
 * ``test/attention.jl`` "specific results": ``ytrue`` (12 values) and ``αtrue``
   (18 values) for ``q = k = v = reshape(1:12, 4, 3, 1) ./ 12, nheads = 2``;
 * ``test/softmax.jl`` "softmax with Inf, NaN": the 2x2 input/output tables;
 * ``test/softmax.jl`` first tests: ``softmax([0, 0])`` and the -100000 pair.
 
-Run:  python tests/golden/make_golden.py [path-to-reference]
+Run:  python tests/golden/make_golden.py <path-to-an-NNlib.jl-checkout>
 """
 from __future__ import annotations
 
@@ -81,4 +81,6 @@ def main(ref: Path) -> None:
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    if len(sys.argv) != 2:
+        sys.exit("usage: python make_golden.py <path of an NNlib.jl checkout>")
+    main(Path(sys.argv[1]))
