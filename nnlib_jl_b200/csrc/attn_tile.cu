@@ -45,7 +45,7 @@ enum : int { TM_FWD = 0, TM_STATS = 1, TM_SCORES = 2, TM_SPLIT = 3 };
 constexpr int kTThreads = 192;
 constexpr int kTBM = 128;          // queries per CTA
 constexpr int kTBN = 64;           // keys per tile
-constexpr int kTStages = 2;
+constexpr int kTMaxStages = 4;
 constexpr float kTRescaleGap = 8.0f;
 
 template <typename T, int DQ, int DV>
@@ -59,10 +59,14 @@ struct TCfg {
   static constexpr int kQBytes = kQChunks * kQChunkBytes;
   static constexpr int kKBytes = kQChunks * kKChunkBytes;
   static constexpr int kVBytes = kVChunks * kKChunkBytes;
+  // ring depth: a 64-key tile is little work, so the copies of several tiles must be in flight to cover the
+  // latency of a load that misses L2 (two stages left the tensor core waiting: 6.6 k cycles per tile measured)
+  static constexpr int kStagesFit = (200 * 1024 - kQBytes) / (kKBytes + kVBytes);
+  static constexpr int kStages = kStagesFit >= kTMaxStages ? kTMaxStages : (kStagesFit < 2 ? 2 : kStagesFit);
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQBytes;
-  static constexpr int kVOff = kKOff + kTStages * kKBytes;
-  static constexpr int kBarOff = kVOff + kTStages * kVBytes;
+  static constexpr int kVOff = kKOff + kStages * kKBytes;
+  static constexpr int kBarOff = kVOff + kStages * kVBytes;
   static constexpr int kSmemBytes = kBarOff + 256 + 1024;
   static constexpr int kKStep = 32 / kEsz;                   // K elements of one tcgen05.mma (32 bytes)
   static constexpr int kCtasPerSm = (kSmemBytes <= 110 * 1024) ? 2 : 1;
@@ -71,7 +75,7 @@ static_assert(TCfg<float, 128, 128>::kSmemBytes <= 232448, "shared memory budget
 
 struct TBarriers {
   uint64_t q_full;
-  uint64_t k_full[kTStages], k_empty[kTStages], v_full[kTStages], v_empty[kTStages];
+  uint64_t k_full[kTMaxStages], k_empty[kTMaxStages], v_full[kTMaxStages], v_empty[kTMaxStages];
   uint64_t s_full[2], p_ready[2], o_ready;
   uint32_t tmem_base;
   int abort_flag;
@@ -142,8 +146,11 @@ template <> struct Fmt<__half> { static constexpr uint32_t v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t v = 1; };
 template <> struct Fmt<float> { static constexpr uint32_t v = 2; };
 
-template <typename T, int DQ, int DV, int MODE>
-__global__ void __launch_bounds__(kTThreads, (MODE == TM_FWD || MODE == TM_SPLIT) ? 1 : TCfg<T, DQ, DV>::kCtasPerSm)   // the forward needs > 168 registers
+// SIDE: bias / Bool mask arrays are handled (through the per-row helpers of extras.cuh, chosen at run time);
+// without it the loop holds no trace of them — the generic helpers cost 1.6 k of a tile's 3.7 k cycles even
+// when a call has neither.
+template <typename T, int DQ, int DV, int MODE, bool SIDE>
+__global__ void __launch_bounds__(kTThreads, TCfg<T, DQ, DV>::kCtasPerSm)
 attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qtiles, const int n_splits) {
   using C = TCfg<T, DQ, DV>;
@@ -174,7 +181,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
-    for (int s = 0; s < kTStages; ++s) {
+    for (int s = 0; s < kTMaxStages; ++s) {
       mbar_init(&bars->k_full[s], 1);
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_full[s], 1);
@@ -211,8 +218,8 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bool ok = true;
       int j = 0;
       for (; j < nt; ++j) {
-        const int s = j % kTStages;
-        if (j >= kTStages) ok = mbar_wait(&bars->k_empty[s], ((j / kTStages) - 1) & 1, abort_flag);
+        const int s = j % C::kStages;
+        if (j >= C::kStages) ok = mbar_wait(&bars->k_empty[s], ((j / C::kStages) - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->k_full[s], C::kKBytes);
 #pragma unroll
@@ -220,7 +227,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tma_load_4d(smem + C::kKOff + s * C::kKBytes + c * C::kKChunkBytes, &tm_k, &bars->k_full[s], c * C::kEpc, h,
                       (t0 + j) * kTBN, b);
         if (PV) {
-          if (j >= kTStages) ok = mbar_wait(&bars->v_empty[s], ((j / kTStages) - 1) & 1, abort_flag);
+          if (j >= C::kStages) ok = mbar_wait(&bars->v_empty[s], ((j / C::kStages) - 1) & 1, abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars->v_full[s], C::kVBytes);
 #pragma unroll
@@ -232,9 +239,9 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (*abort_flag) {
         // give copies still in flight a bounded chance to land before the CTA leaves
         mbar_wait_drain(&bars->q_full, 0, kDrainNs);
-        for (int jj = max(0, j - kTStages); jj < j; ++jj) {
-          mbar_wait_drain(&bars->k_full[jj % kTStages], (jj / kTStages) & 1, kDrainNs);
-          if (PV) mbar_wait_drain(&bars->v_full[jj % kTStages], (jj / kTStages) & 1, kDrainNs);
+        for (int jj = max(0, j - C::kStages); jj < j; ++jj) {
+          mbar_wait_drain(&bars->k_full[jj % C::kStages], (jj / C::kStages) & 1, kDrainNs);
+          if (PV) mbar_wait_drain(&bars->v_full[jj % C::kStages], (jj / C::kStages) & 1, kDrainNs);
         }
       }
     }
@@ -248,8 +255,8 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
       // S(j) = Q K_j^T into score buffer j & 1
       auto issue_qk = [&](int j) {
-        const int s = j % kTStages;
-        ok = mbar_wait(&bars->k_full[s], (j / kTStages) & 1, abort_flag);
+        const int s = j % C::kStages;
+        ok = mbar_wait(&bars->k_full[s], (j / C::kStages) & 1, abort_flag);
         if (!ok) return;
         tc_fence_after();
         const uint32_t ka = smem_u32(smem + C::kKOff + s * C::kKBytes);
@@ -272,8 +279,8 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         if (PV) {
-          const int s = j % kTStages;
-          ok = mbar_wait(&bars->v_full[s], (j / kTStages) & 1, abort_flag);
+          const int s = j % C::kStages;
+          ok = mbar_wait(&bars->v_full[s], (j / C::kStages) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
           const uint32_t va = smem_u32(smem + C::kVOff + s * C::kVBytes);
@@ -300,7 +307,10 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int lim = a.causal ? min(i + a.coff, a.Lkv - 1) : a.Lkv - 1;   // last key this row attends to (< 0: none)
     const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
     const bool drop = a.dropout_p > 0.f;
-    RowSide rs = make_row_side(a, i, h, b, row_ok);
+    RowSide rs;
+    if (SIDE) rs = make_row_side(a, i, h, b, row_ok);
+    // SIDE: the prepared logits are already scaled; plain logits get scale*log2(e) inside the exponential's FMA
+    const float cs = SIDE ? 1.f : c2;
 
     float m_used = neg_inf();   // running maximum (scaled, base 2) the stored exponentials refer to
     float l = 0.f;
@@ -322,9 +332,10 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     for (int j = 0; j < nt; ++j) {
       const int sb = j & 1;
       const int j0 = (t0 + j) * kTBN;
-      uint4 bq[2][4], mq[2][2];
-      side_issue<true>(rs, j0, a.Lkv, bq[0], mq[0]);
-      side_issue<true>(rs, j0 + 32, a.Lkv, bq[1], mq[1]);
+      // (one set of bias / mask words: the second chunk's are fetched once the first chunk's have been used, so
+      // that the forward modes fit two CTAs on an SM)
+      uint4 bq[4], mq[2];
+      if (SIDE) side_issue<true>(rs, j0, a.Lkv, bq, mq);
       unsigned int kb[2] = {0xffffffffu, 0xffffffffu};
       if (MODE != TM_STATS && drop) {
 #pragma unroll
@@ -344,15 +355,25 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (lane == 0) mbar_arrive(&bars->p_ready[sb]);
       }
       // scaled base-2 logits with bias, masks, causal limit and the end of the keys applied
+      if (SIDE) {
+        side_apply<true>(rs, sr[0], bq, mq, j0, a.Lkv, lim, row_ok, c2);
+        side_issue<true>(rs, j0 + 32, a.Lkv, bq, mq);
+        side_apply<true>(rs, sr[1], bq, mq, j0 + 32, a.Lkv, lim, row_ok, c2);
+      } else if (__any_sync(0xffffffffu, j0 + kTBN - 1 > lim || !row_ok)) {
+        // the causal diagonal, the end of the keys or the end of the queries runs through this tile
 #pragma unroll
-      for (int c = 0; c < 2; ++c) side_apply<true>(rs, sr[c], bq[c], mq[c], j0 + c * 32, a.Lkv, lim, row_ok, c2);
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (j0 + c * 32 + e > lim || !row_ok) sr[c][e] = 0xff800000u;
+      }
 
       if (MODE == TM_SCORES) {
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            float al = ex2_approx(__uint_as_float(sr[c][e]) - lse2);       // -inf (masked) gives 0
+            float al = ex2_approx(fmaf(__uint_as_float(sr[c][e]), cs, -lse2));   // -inf (masked) gives 0
             if (rinf) al = (sr[c][e] == 0x7f800000u) ? inf_share : 0.f;
             if (row_const) al = const_val;
             if (drop) al = ((kb[c] >> e) & 1u) ? al * a.inv_keep : 0.f;
@@ -399,7 +420,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
-      const float m_new = fmaxf(m_used, mx);
+      const float m_new = fmaxf(m_used, mx * cs);
       const bool raise = m_new > m_used + kTRescaleGap;        // also true for m_used = -inf < m_new
       if (__any_sync(0xffffffffu, raise)) {
         const float f = (raise && j > 0) ? ex2_approx(m_used - m_new) : 1.f;   // exp2(-inf) = 0: nothing gathered yet
@@ -430,8 +451,8 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          float p = ex2_approx(__uint_as_float(sr[c][e]) - m_sub);
-          if (row_inf) p = (sr[c][e] == 0x7f800000u) ? 1.f : 0.f;
+          float p = ex2_approx(fmaf(__uint_as_float(sr[c][e]), cs, -m_sub));
+          if (SIDE && row_inf) p = (sr[c][e] == 0x7f800000u) ? 1.f : 0.f;
           sum += p;
           // dropout follows the softmax: the row sum keeps the dropped scores
           sr[c][e] = ((kb[c] >> e) & 1u) ? (TF32 ? to_tf32(p) : __float_as_uint(p)) : 0u;
@@ -442,13 +463,13 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tmem_st32(lane_base + sb * kTBN, sr[0]);
           tmem_st32(lane_base + sb * kTBN + 32, sr[1]);
         } else {
-          uint32_t pk[32];
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
+          for (int c = 0; c < 2; ++c) {
+            uint32_t pk[16];
 #pragma unroll
-            for (int e = 0; e < 32; e += 2)
-              pk[c * 16 + (e >> 1)] = pack2<BF16>(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
-          tmem_st32(lane_base + sb * kTBN, pk);
+            for (int e = 0; e < 32; e += 2) pk[e >> 1] = pack2<BF16>(__uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
+            tmem_st16(lane_base + sb * kTBN + c * 16, pk);
+          }
         }
         tmem_wait_st();
         tc_fence_before();
@@ -582,11 +603,11 @@ bool make_head_map(CUtensorMap* m, const void* base, int dtype, long long dhead,
 
 bool tile_stride_ok(long long s, int esz) { return s > 0 && (s * esz) % 16 == 0 && s * esz < (1ll << 40); }
 
-template <typename T, int DQ, int DV, int MODE>
-cudaError_t launch_tile(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
-                        cudaStream_t st, int n_splits = 1) {
+template <typename T, int DQ, int DV, int MODE, bool SIDE>
+cudaError_t launch_tile_side(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
+                             cudaStream_t st, int n_splits) {
   using C = TCfg<T, DQ, DV>;
-  auto kern = attn_tile_kernel<T, DQ, DV, MODE>;
+  auto kern = attn_tile_kernel<T, DQ, DV, MODE, SIDE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int n_qtiles = (a.Lq + kTBM - 1) / kTBM;
@@ -602,6 +623,13 @@ cudaError_t launch_tile(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     count_launch();
   }
   return cudaGetLastError();
+}
+
+template <typename T, int DQ, int DV, int MODE>
+cudaError_t launch_tile(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
+                        cudaStream_t st, int n_splits = 1) {
+  if (a.bias != nullptr || a.mask != nullptr) return launch_tile_side<T, DQ, DV, MODE, true>(mq, mk, mv, a, st, n_splits);
+  return launch_tile_side<T, DQ, DV, MODE, false>(mq, mk, mv, a, st, n_splits);
 }
 
 template <typename T, int MODE>
