@@ -194,9 +194,9 @@ const char* simt_reason(const AttnArgs& a, int dtype, bool need_v) {
 
 // Arguments of the x + alpha composite (attn_fwd followed by attn_scores), checked as a whole so that a
 // bad alpha cannot surface after x and lse were already written.  Not exported.
-int attention_validate(const nnlib_b200_attn_params* p) {
+int attention_validate(const nnlib_b200_attn_params* p, bool launching) {
   AttnArgs a;
-  const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN | NEED_ALPHA, &a);
+  const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN | NEED_ALPHA, &a, launching);
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
   const bool fwd_ok = use_umma(a, p->dtype, true) || use_tile(a, p->dtype, true) || simt_supports(a.d, a.dv);

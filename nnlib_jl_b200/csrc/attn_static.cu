@@ -90,13 +90,18 @@ extern "C" int nnlib_b200_attention_static(const nnlib_b200_attn_params* p, void
   const unsigned long long lq = (unsigned long long)p->Lq, hh = (unsigned long long)p->H, bb = (unsigned long long)p->B;
   if (lq > kMaxQueries || hh > kMaxQueries || bb > kMaxQueries || lq * hh > kMaxQueries || lq * hh * bb > kMaxQueries)
     return NNLIB_B200_WORKSPACE_TOO_SMALL;
-  float* lse = nullptr;
-  const int rc = static_lse_address(&lse);
-  if (rc != NNLIB_B200_OK) return rc;
   nnlib_b200_attn_params q = *p;
-  q.lse = lse;          // any lse pointer of the caller is ignored: this variant owns the buffer
   q.lse_stride_b = 0;   // dense (Lq, H, B)
-  const int rc_args = nb200::attention_validate(&q);   // both halves, before anything is enqueued
-  if (rc_args != NNLIB_B200_OK) return rc_args;
+  // argument errors are reported before the device is touched: check everything but the pointers' devices
+  // with a stand-in for the scratch address, which is looked up only for a call that can run
+  q.lse = reinterpret_cast<float*>(uintptr_t(256));
+  int rc = nb200::attention_validate(&q, false);
+  if (rc != NNLIB_B200_OK) return rc;
+  float* lse = nullptr;
+  rc = static_lse_address(&lse);
+  if (rc != NNLIB_B200_OK) return rc;
+  q.lse = lse;          // any lse pointer of the caller is ignored: this variant owns the buffer
+  rc = nb200::attention_validate(&q, true);   // both halves, before anything is enqueued
+  if (rc != NNLIB_B200_OK) return rc;
   return nb200::attention_both(&q, stream);
 }

@@ -7,7 +7,7 @@
 namespace nb200 {
 
 // argument check of the x + alpha composites (api.cu): everything attn_fwd and attn_scores would reject
-int attention_validate(const nnlib_b200_attn_params* p);
+int attention_validate(const nnlib_b200_attn_params* p, bool launching = true);
 int attention_both(const nnlib_b200_attn_params* p, void* stream);
 
 // CUDA-core kernels (attn_simt.cu)

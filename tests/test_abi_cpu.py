@@ -159,3 +159,70 @@ def test_path_selection_is_pure_host_logic(lib):
     assert lib.nnlib_b200_attn_path(C.byref(_params(d=48, dv=48))) == _lib.PATH_SIMT
     assert lib.nnlib_b200_attn_path(C.byref(_params(d=2048, dv=2048))) == _lib.UNSUPPORTED_SHAPE
     assert lib.nnlib_b200_attn_path(C.byref(_params(q=0x1004))) == _lib.PATH_SIMT          # unaligned rows
+
+
+def test_composites_check_both_halves_before_anything_is_enqueued(lib):
+    # x + alpha in one call: a missing alpha (checked by the second half only) must be reported before the first
+    # half runs, i.e. without a CUDA call — this box has no GPU, so anything else would answer CUDA_ERROR
+    before = lib.nnlib_b200_launch_count()
+    p = _params(lse=0x2000)                       # alpha missing
+    assert lib.nnlib_b200_attention(C.byref(p), None, 0, None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attention_static(C.byref(_params()), None) == _lib.INVALID_ARG
+    p = _params(lse=0x2000, alpha=0x3000, alpha_stride_b=1)      # batches of alpha would overlap
+    assert lib.nnlib_b200_attention(C.byref(p), None, 0, None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_launch_count() == before
+
+
+def test_backward_wants_dk_dv_whenever_there_are_keys(lib):
+    # no queries but keys: dk and dv are still written (zeros), so they must be given
+    p = _params(lse=0x2000, Lq=0)
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), C.byref(_grads(dk=None)), None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_bwd(C.byref(p), C.byref(_grads(dv=None)), None) == _lib.INVALID_ARG
+    # no keys at all: nothing to write
+    assert lib.nnlib_b200_attn_bwd(C.byref(_params(lse=0x2000, Lq=0, Lkv=0)), C.byref(_grads(dk=None, dv=None)), None) == _lib.OK
+
+
+def _gemm(**kw):
+    g = _lib.GemmParams()
+    g.dtype = _lib.BF16
+    g.M, g.N, g.K, g.batch = 64, 32, 16, 2
+    g.A = g.B = g.C = 0x5000
+    g.lda, g.ldb, g.ldc = 64, 16, 64
+    g.strideA, g.strideB, g.strideC = 64 * 16, 16 * 32, 64 * 32
+    for k, v in kw.items():
+        setattr(g, k, v)
+    return g
+
+
+def test_batched_gemm_argument_checks_and_path_without_a_gpu(lib):
+    assert lib.nnlib_b200_batched_gemm(None, None) == _lib.INVALID_ARG
+    for bad in (dict(struct_size=8), dict(dtype=9), dict(transA=2), dict(M=-1), dict(lda=63), dict(ldb=15), dict(ldc=63),
+                dict(A=None), dict(C=None), dict(strideC=100), dict(alpha=float("nan")), dict(strideA=-1),
+                dict(transA=1, lda=15)):
+        assert lib.nnlib_b200_batched_gemm(C.byref(_gemm(**bad)), None) == _lib.INVALID_ARG, bad
+    # the path is pure host logic: aligned 16-bit operands take the tensor cores (when the driver is there),
+    # Float32 and unaligned leading dimensions the CUDA-core kernel
+    assert lib.nnlib_b200_batched_gemm_path(C.byref(_gemm())) in (_lib.PATH_UMMA, _lib.PATH_SIMT)
+    assert lib.nnlib_b200_batched_gemm_path(C.byref(_gemm(dtype=_lib.F32))) == _lib.PATH_SIMT
+    assert lib.nnlib_b200_batched_gemm_path(C.byref(_gemm(lda=65))) == _lib.PATH_SIMT
+    assert lib.nnlib_b200_batched_gemm_path(C.byref(_gemm(A=0x5004))) == _lib.PATH_SIMT
+    # empty products enqueue nothing
+    before = lib.nnlib_b200_launch_count()
+    assert lib.nnlib_b200_batched_gemm(C.byref(_gemm(batch=0)), None) == _lib.OK
+    assert lib.nnlib_b200_batched_gemm(C.byref(_gemm(M=0, lda=1, ldc=1)), None) == _lib.OK
+    assert lib.nnlib_b200_launch_count() == before
+
+
+def test_decode_entry_and_new_fields_without_a_gpu(lib):
+    assert lib.nnlib_b200_attn_decode(None, None, 0, None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_attn_decode_workspace_bytes(None) == 0
+    assert lib.nnlib_b200_attn_decode(C.byref(_params(Lq=0)), None, 0, None) == _lib.OK        # empty: nothing to do
+    assert lib.nnlib_b200_attn_fwd(C.byref(_params(causal=1, causal_offset=2 ** 40)), None) == _lib.INVALID_ARG
+    # more than one query tile never splits; neither does a short key sequence
+    assert lib.nnlib_b200_attn_decode_workspace_bytes(C.byref(_params(Lq=129, Lkv=100000))) == 0
+    assert lib.nnlib_b200_attn_decode_workspace_bytes(C.byref(_params(Lq=1, Lkv=128))) == 0
+    # Float32 takes the tensor cores only when the caller allows TF32
+    assert lib.nnlib_b200_attn_path(C.byref(_params(dtype=_lib.F32))) == _lib.PATH_SIMT
+    assert lib.nnlib_b200_attn_path(C.byref(_params(dtype=_lib.F32, allow_tf32=1))) in (_lib.PATH_TILE, _lib.PATH_SIMT)
+    assert lib.nnlib_b200_selftest_wait_runout(0, None, None) == _lib.INVALID_ARG
+    assert lib.nnlib_b200_static_scratch(None, None) == _lib.INVALID_ARG
