@@ -152,6 +152,10 @@ int resolve(const nnlib_b200_attn_params* p, unsigned need, AttnArgs* out, bool 
   }
   a.key0 = (unsigned int)(p->philox_seed & 0xffffffffull);
   a.key1 = (unsigned int)(p->philox_seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    a.rkey[2 * r] = a.key0 + (unsigned int)r * kPhiloxW0;
+    a.rkey[2 * r + 1] = a.key1 + (unsigned int)r * kPhiloxW1;
+  }
   a.off_lo = (unsigned int)(p->philox_offset & 0xffffffffull);
   a.off_hi = (unsigned int)(p->philox_offset >> 32);
   if (p->rng_h0 < 0 || p->rng_b0 < 0 || p->rng_H < 0) return NNLIB_B200_INVALID_ARG;

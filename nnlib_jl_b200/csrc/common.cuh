@@ -32,6 +32,7 @@ struct AttnArgs {
   float* ws;                 // split-key forward: per-split partial results (see attn_tile.cu)
   long long rng_h0, rng_b0, rng_H;
   unsigned int key0, key1, off_lo, off_hi;
+  unsigned int rkey[20];   // the ten round keys of Philox4x32-10 (key0 + r*W0, key1 + r*W1), bumped once on the host
   unsigned int drop_thresh;  // floor(p * 2^16): a score is dropped iff its 16-bit lane is below it
   float inv_keep;            // 1/(1-p)
   float dropout_p;
@@ -95,6 +96,7 @@ __device__ __forceinline__ float load_bias(const void* p, long long idx, int dty
 }
 
 // ---- Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11) ----
+constexpr unsigned int kPhiloxW0 = 0x9E3779B9u, kPhiloxW1 = 0xBB67AE85u;
 __host__ __device__ __forceinline__ void philox4x32_10(unsigned int& c0, unsigned int& c1, unsigned int& c2,
                                                        unsigned int& c3, unsigned int k0, unsigned int k1) {
 #pragma unroll
@@ -106,8 +108,23 @@ __host__ __device__ __forceinline__ void philox4x32_10(unsigned int& c0, unsigne
     const unsigned int n2 = (unsigned int)(p0 >> 32) ^ c3 ^ k1;
     const unsigned int n3 = (unsigned int)p0;
     c0 = n0; c1 = n1; c2 = n2; c3 = n3;
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
+    k0 += kPhiloxW0;
+    k1 += kPhiloxW1;
+  }
+}
+// The same ten rounds with the round keys read from a table (kernel arguments: they are operands from the
+// constant bank, so a round is two wide multiplies and two three-input XORs, no key arithmetic).
+__device__ __forceinline__ void philox4x32_10_keyed(unsigned int& c0, unsigned int& c1, unsigned int& c2,
+                                                    unsigned int& c3, const unsigned int (&rk)[20]) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const unsigned long long p0 = 0xD2511F53ull * c0;
+    const unsigned long long p1 = 0xCD9E8D57ull * c2;
+    const unsigned int n0 = (unsigned int)(p1 >> 32) ^ c1 ^ rk[2 * r];
+    const unsigned int n1 = (unsigned int)p1;
+    const unsigned int n2 = (unsigned int)(p0 >> 32) ^ c3 ^ rk[2 * r + 1];
+    const unsigned int n3 = (unsigned int)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
   }
 }
 
@@ -115,7 +132,7 @@ __host__ __device__ __forceinline__ void philox4x32_10(unsigned int& c0, unsigne
 __device__ __forceinline__ void dropout_words(const AttnArgs& a, unsigned long long r, unsigned int j8,
                                               unsigned int w[4]) {
   unsigned int c0 = j8, c1 = (unsigned int)r, c2 = (unsigned int)(r >> 32) + a.off_hi, c3 = a.off_lo;
-  philox4x32_10(c0, c1, c2, c3, a.key0, a.key1);
+  philox4x32_10_keyed(c0, c1, c2, c3, a.rkey);
   w[0] = c0; w[1] = c1; w[2] = c2; w[3] = c3;
 }
 

@@ -109,13 +109,25 @@ __device__ __forceinline__ uint4 repack<__half>(const float (&f)[8]) {
   for (int u = 0; u < 4; ++u) e[u] = __floats2half2_rn(f[2 * u], f[2 * u + 1]);
   return q;
 }
-template <typename T>
-// plain (coherent) load: the output may be the input array itself (softmax!(x, x) of the reference), and a
-// column longer than a thread's register share is read a second time after other threads may have
-// written theirs, so the non-coherent path and `__restrict__` are both out
-__device__ __forceinline__ uint4 load_raw(const T* p) { return *reinterpret_cast<const uint4*>(p); }
-template <typename T>
-__device__ __forceinline__ void load_pack(const T* p, float (&f)[Pack<T>::V]) { unpack<T>(load_raw<T>(p), f); }
+// Every kernel exists twice.  NA (no alias: the host saw that the output overlaps neither input) takes
+// `__restrict__` pointers and loads through the non-coherent path, which lets the compiler start the next
+// column's loads before this column's stores.  The other variant serves the in-place forms (softmax!(x, x) of the
+// reference, a pullback written over dy): plain coherent loads, no promise about aliasing — a column longer than a
+// thread's register share is read a second time after other threads may have written theirs.
+template <typename T, bool NA> struct Ptrs { using In = const T*; using Out = T*; };
+template <typename T> struct Ptrs<T, true> { using In = const T* __restrict__; using Out = T* __restrict__; };
+template <typename T, bool NA>
+__device__ __forceinline__ uint4 load_raw(const T* p) {
+  if constexpr (NA) return __ldg(reinterpret_cast<const uint4*>(p));
+  else return *reinterpret_cast<const uint4*>(p);
+}
+template <typename T, bool NA>
+__device__ __forceinline__ T load_elem(const T* p) {
+  if constexpr (NA) return __ldg(p);
+  else return *p;
+}
+template <typename T, bool NA>
+__device__ __forceinline__ void load_pack(const T* p, float (&f)[Pack<T>::V]) { unpack<T>(load_raw<T, NA>(p), f); }
 template <typename T>
 __device__ __forceinline__ void store_pack(T* p, const float (&f)[Pack<T>::V]) {
   *reinterpret_cast<uint4*>(p) = repack<T>(f);
@@ -170,8 +182,9 @@ __device__ __forceinline__ void fwd_pack(const ColStat& c, float inv_s, float lo
 // VECT: columns are whole 16-byte packets (n a multiple of the packet, arrays 16-byte aligned).
 // KP > 0 (with VECT): a thread's packets (at most KP, as raw 16-byte words) stay in registers between
 // the two passes, so the column is read from memory once.
-template <typename T, int MODE, int G, bool VECT, int KP>
-__global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const T* x, const T* dy, T* out, long long n, long long cols) {
+template <typename T, int MODE, int G, bool VECT, int KP, bool NA>
+__global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(typename Ptrs<T, NA>::In x, typename Ptrs<T, NA>::In dy,
+                                                                            typename Ptrs<T, NA>::Out out, long long n, long long cols) {
   constexpr int kBlock = G > 256 ? G : 256;
   constexpr int kPerBlock = kBlock / G;
   constexpr int kWarps = kBlock / 32;
@@ -198,8 +211,8 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
       for (int k = 0; k < (CACHE ? KP : 1); ++k) {
         const long long jp = t + (long long)k * G;
         if (jp < np) {
-          cx[k] = load_raw<T>(xc + jp * V);
-          if (!FWD) cd[k] = load_raw<T>(dc + jp * V);
+          cx[k] = load_raw<T, NA>(xc + jp * V);
+          if (!FWD) cd[k] = load_raw<T, NA>(dc + jp * V);
         }
       }
 #pragma unroll
@@ -222,11 +235,11 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
     } else if (VECT) {
       for (long long jp = t; jp < np; jp += G) {
         float f[V], d[V];
-        load_pack<T>(xc + jp * V, f);
+        load_pack<T, NA>(xc + jp * V, f);
         if (FWD) {
           stat_add_pack<V>(c, f);
         } else {
-          load_pack<T>(dc + jp * V, d);
+          load_pack<T, NA>(dc + jp * V, d);
 #pragma unroll
           for (int u = 0; u < V; ++u) acc += (MODE == SM_BWD) ? d[u] * f[u] : d[u];
         }
@@ -353,12 +366,12 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
     } else if (VECT) {
       for (long long jp = t; jp < np; jp += G) {
         float f[V], d[V];
-        load_pack<T>(xc + jp * V, f);
+        load_pack<T, NA>(xc + jp * V, f);
         if (FWD) {
           fwd_pack<MODE, V>(c, inv_s, log_s, f);
           store_pack<T>(oc + jp * V, f);
         } else {
-          load_pack<T>(dc + jp * V, d);
+          load_pack<T, NA>(dc + jp * V, d);
 #pragma unroll
           for (int u = 0; u < V; ++u) d[u] = (MODE == SM_BWD) ? f[u] * (d[u] - acc) : d[u] - __expf(f[u]) * acc;
           store_pack<T>(oc + jp * V, d);
@@ -378,8 +391,9 @@ __global__ void __launch_bounds__((G > 256 ? G : 256)) softmax_cols_kernel(const
 }
 
 // ---- reduction dimension strided (inner > 1): one thread per (i, o), neighbours along i coalesce ----
-template <typename T, int MODE>
-__global__ void __launch_bounds__(256) softmax_strided_kernel(const T* x, const T* dy, T* out, long long inner, long long n,
+template <typename T, int MODE, bool NA>
+__global__ void __launch_bounds__(256) softmax_strided_kernel(typename Ptrs<T, NA>::In x, typename Ptrs<T, NA>::In dy,
+                                                              typename Ptrs<T, NA>::Out out, long long inner, long long n,
                                                               long long outer) {
   const long long total = inner * outer;
   for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += (long long)gridDim.x * blockDim.x) {
@@ -411,6 +425,13 @@ cudaError_t launch_softmax(const void* x, const void* dy, void* out, long long i
   const T* xp = static_cast<const T*>(x);
   const T* dp = static_cast<const T*>(dy);
   T* op = static_cast<T*>(out);
+  // does the output overlap an input?  (the in-place forms of the reference: the same array, same extent)
+  const uintptr_t bytes = (uintptr_t)(inner * n * outer) * sizeof(T);
+  auto overlaps = [bytes](const void* a, const void* b) {
+    const uintptr_t pa = reinterpret_cast<uintptr_t>(a), pb = reinterpret_cast<uintptr_t>(b);
+    return a != nullptr && b != nullptr && pa < pb + bytes && pb < pa + bytes;
+  };
+  const bool no_alias = !overlaps(x, out) && !overlaps(dy, out);
   if (inner == 1) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool vect = (n % Pack<T>::V) == 0 && al16(x) && al16(out) && (dy == nullptr || al16(dy));
@@ -426,10 +447,19 @@ cudaError_t launch_softmax(const void* x, const void* dy, void* out, long long i
     constexpr int kBlock = (GG) > 256 ? (GG) : 256;                                                    \
     const long long need = (outer + (kBlock / (GG)) - 1) / (kBlock / (GG));                            \
     const long long blocks = need < cap ? need : cap;                                                  \
-    softmax_cols_kernel<T, MODE, GG, VV, KK><<<(unsigned)blocks, kBlock, 0, st>>>(xp, dp, op, n, outer); \
+    if (no_alias)                                                                                      \
+      softmax_cols_kernel<T, MODE, GG, VV, KK, true><<<(unsigned)blocks, kBlock, 0, st>>>(xp, dp, op, n, outer);  \
+    else                                                                                               \
+      softmax_cols_kernel<T, MODE, GG, VV, KK, false><<<(unsigned)blocks, kBlock, 0, st>>>(xp, dp, op, n, outer); \
   } while (0)
     if (!vect) {
       if (n > 2048) NB_SM_LAUNCH(256, false, 0); else NB_SM_LAUNCH(32, false, 0);
+    } else if (np <= 32ll * 2) {
+      // short columns (attention-sized rows of scores): two packets per lane, few registers, so that enough
+      // warps are resident to keep the memory system busy with so little in flight per warp
+      NB_SM_LAUNCH(32, true, 2);
+    } else if (np <= 32ll * 4) {
+      NB_SM_LAUNCH(32, true, 4);
     } else if (np <= 32ll * 8) {
       NB_SM_LAUNCH(32, true, 8);
     } else if (sizeof(T) == 2 && FWD && np <= 32ll * 16) {
@@ -447,7 +477,10 @@ cudaError_t launch_softmax(const void* x, const void* dy, void* out, long long i
   } else {
     const long long need = (inner * outer + 255) / 256;
     const long long blocks = need < 148ll * 32 ? need : 148ll * 32;
-    softmax_strided_kernel<T, MODE><<<(unsigned)blocks, 256, 0, st>>>(xp, dp, op, inner, n, outer);
+    if (no_alias)
+      softmax_strided_kernel<T, MODE, true><<<(unsigned)blocks, 256, 0, st>>>(xp, dp, op, inner, n, outer);
+    else
+      softmax_strided_kernel<T, MODE, false><<<(unsigned)blocks, 256, 0, st>>>(xp, dp, op, inner, n, outer);
   }
   count_launch();
   return cudaGetLastError();
