@@ -76,7 +76,7 @@ static_assert(TCfg<float, 128, 128>::kSmemBytes <= 232448, "shared memory budget
 struct TBarriers {
   uint64_t q_full;
   uint64_t k_full[kTMaxStages], k_empty[kTMaxStages], v_full[kTMaxStages], v_empty[kTMaxStages];
-  uint64_t s_full[2], p_ready[2], o_ready;
+  uint64_t s_full[2], p_ready[2], o_ready, o_final;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -192,6 +192,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(&bars->p_ready[s], 4);
     }
     mbar_init(&bars->o_ready, 1);
+    mbar_init(&bars->o_final, 1);
     bars->abort_flag = *reinterpret_cast<volatile int*>(&g_tile_abort);
     fence_mbar_init();
   }
@@ -292,6 +293,9 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
           umma_commit(&bars->v_empty[s]);
           umma_commit(&bars->o_ready);
+          // The epilogue has a barrier of its own: a warp that is done early knows only that P(nt-3) V(nt-3) has
+          // completed, and a parity wait on o_ready cannot tell phase nt - 1 from phase nt - 3.
+          if (j == nt - 1) umma_commit(&bars->o_final);
         }
         if (j + 2 < nt) issue_qk(j + 2);
       }
@@ -490,7 +494,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       float* ml = a.ws + slot * 2;
       float* orow = a.ws + split_ml_floats(a, n_splits) + slot * a.dv;
       if (row_ok) { ml[0] = m_used; ml[1] = l; }
-      ok = mbar_wait_warp(&bars->o_ready, (nt - 1) & 1, abort_flag);
+      ok = mbar_wait_warp(&bars->o_final, 0, abort_flag);
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -515,7 +519,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = lse_v;
       }
       if (MODE == TM_FWD) {
-        ok = mbar_wait_warp(&bars->o_ready, (nt - 1) & 1, abort_flag);
+        ok = mbar_wait_warp(&bars->o_final, 0, abort_flag);
         if (ok) {
           tc_fence_after();
           const float inv = dead ? (a.nan_fm ? __int_as_float(0x7fc00000) : 0.f) : a.inv_keep / l;

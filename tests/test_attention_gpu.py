@@ -467,6 +467,77 @@ def test_eager_scores_on_longer_sequences_use_the_two_kernels(eager_scores):
     _close(nb.jl_to_numpy(a), ao, dtype, "alpha")
 
 
+@pytest.mark.parametrize("seed", range(80))
+def test_random_configurations_match_the_oracle(seed):
+    """Seeded random draws over everything the public call accepts — element type, head size (any, not only
+    the tensor-core ones), dv != d, heads, ragged lengths, batch, mask form (none / causal matrix / offset /
+    key padding / random Bool array with any broadcast shape), bias broadcast shape, Philox dropout, lazy or
+    eager scores — whichever kernel family the library picks.  x and alpha against the oracle."""
+    rng = np.random.default_rng(7000 + seed)
+    dtype = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
+    d = int(rng.choice([8, 16, 24, 40, 64, 64, 72, 96, 128, 128, 20, 33]))
+    dv = d if rng.random() < 0.6 else int(rng.choice([8, 32, 64, 128, 48]))
+    H = int(rng.integers(1, 5))
+    lmax = 330 if seed < 48 else 900                       # the later seeds walk the copy rings around several times
+    Lq, Lkv = int(rng.integers(1, lmax)), int(rng.integers(1, lmax))
+    if rng.random() < 0.25:
+        Lkv = int(rng.choice([64, 128, 256, 264]))        # sizes the short-sequence kernel takes
+    B = int(rng.integers(1, 4))
+    E, Ev = d * H, dv * H
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((Ev, Lkv, B)), dtype)
+    q, k, v = _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype)
+
+    mask_np = mask_arg = None
+    kind = str(rng.choice(["none", "causal", "offset", "keypad", "random", "random"]))
+    if kind == "causal" and Lq == Lkv:
+        mask_np, mask_arg = O.make_causal_mask(qn), nb.make_causal_mask(q)
+    elif kind in ("causal", "offset"):
+        off = int(rng.integers(0, max(1, Lkv)))            # key 0 stays visible to every query
+        mask_np, mask_arg = _offset_mask(Lkv, Lq, off), nb.CausalMask(off)
+    elif kind == "keypad":
+        lens = rng.integers(1, Lkv + 1, size=B)
+        mask_np = np.arange(Lkv)[:, None, None, None] < lens[None, None, None, :]
+        mask_arg = nb.jl_from_numpy(mask_np, device=DEV)
+    elif kind == "random":
+        shape = [(Lkv, Lq), (Lkv, Lq, 1, B), (Lkv, Lq, H, B), (Lkv, 1, H, 1), (Lkv, Lq, H)][int(rng.integers(0, 5))]
+        mask_np = rng.random(shape) > 0.3
+        mask_np[0] = True                                   # nobody is left without a key
+        mask_arg = nb.jl_from_numpy(mask_np, device=DEV)
+
+    bias_np = bias_arg = None
+    if rng.random() < 0.4:
+        shape = [(Lkv, Lq, H, B), (Lkv, Lq), (Lkv, 1, 1, B), (1, Lq, H, 1), (Lkv, Lq, H)][int(rng.integers(0, 5))]
+        bias_np = _round_to(0.5 * rng.standard_normal(shape), dtype)
+        bias_arg = _dev(bias_np, dtype)
+
+    fdrop, fdrop_o, p_drop = nb.identity, (lambda al: al), 0.0
+    if rng.random() < 0.3:
+        p_drop, dseed, doff = float(rng.choice([0.1, 0.25, 0.5])), int(rng.integers(0, 2 ** 31)), int(rng.integers(0, 1000))
+        keep = P.keep_mask((Lkv, Lq, H, B), p_drop, dseed, doff)
+        fdrop = nb.PhiloxDropout(p_drop, seed=dseed, offset=doff)
+        fdrop_o = lambda al: al * keep / np.float32(1.0 - p_drop)
+
+    eager = rng.random() < 0.5
+    nb.set_scores_mode("eager" if eager else "lazy")
+    try:
+        y, a = nb.dot_product_attention(q, k, v, bias_arg, mask=mask_arg, nheads=H, fdrop=fdrop)
+        an = nb.jl_to_numpy(a) if isinstance(a, torch.Tensor) else np.asarray(a)
+    finally:
+        nb.set_scores_mode("lazy")
+    yo, ao = O.dot_product_attention(qn, kn, vn, bias_np, mask=mask_np, nheads=H, fdrop=fdrop_o)
+    what = f"seed {seed}: {dtype} d={d} dv={dv} H={H} Lq={Lq} Lkv={Lkv} B={B} mask={kind} bias={None if bias_np is None else bias_np.shape} p={p_drop} eager={eager}"
+    assert tuple(y.shape) == (Ev, Lq, B) and an.shape == (Lkv, Lq, H, B), what
+    _close(nb.jl_to_numpy(y), yo, dtype, "x, " + what)
+    _close(an, ao, dtype, "alpha, " + what)
+    if mask_np is not None:
+        keepm = np.broadcast_to(O._bcast_to_scores(mask_np), ao.shape)
+        assert (an[~keepm] == 0).all(), "masked scores must be exactly 0, " + what
+    if p_drop == 0.0:
+        np.testing.assert_allclose(an.sum(0), 1.0, atol=1e-2, err_msg=what)
+
+
 def _offset_mask(Lkv, Lq, off):
     """the Bool matrix the reference would be handed for `key <= query + off`"""
     return np.arange(Lkv)[:, None] <= (np.arange(Lq)[None, :] + off)
@@ -1099,6 +1170,70 @@ def test_pullback_on_tensor_cores(dtype, E, H, Lq, Lkv, B, causal):
     _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq")
     _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk")
     _grad_close(nb.jl_to_numpy(dv), gv, dtype, "dv")
+
+
+@pytest.mark.parametrize("seed", range(32))
+def test_random_configurations_of_the_pullback_match_the_gradient_oracle(seed):
+    """Seeded random draws for the backward: element type, head size (tensor-core sizes and others), dv != d,
+    ragged lengths with several key / query tiles, mask form, bias broadcast shape (dbias has the bias's own
+    shape), Philox dropout replayed from the forward — whichever backward the library picks."""
+    rng = np.random.default_rng(9000 + seed)
+    dtype = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
+    d = int(rng.choice([64, 128, 64, 128, 32, 48, 8, 20]))
+    dv = d if rng.random() < 0.7 else int(rng.choice([16, 64, 128]))
+    H = int(rng.integers(1, 4))
+    Lq, Lkv = int(rng.integers(1, 420)), int(rng.integers(1, 420))
+    if dtype == torch.float32:
+        Lq, Lkv = min(Lq, 90), min(Lkv, 90)                # the Float32 kernels are the slow exact ones
+    B = int(rng.integers(1, 3))
+    E, Ev = d * H, dv * H
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((Ev, Lkv, B)), dtype)
+    dyn = _round_to(rng.standard_normal((Ev, Lq, B)), dtype)
+    q, k, v = _dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype)
+
+    mask_np = mask_arg = None
+    kind = str(rng.choice(["none", "causal", "offset", "keypad", "random"]))
+    if kind == "causal" and Lq == Lkv:
+        mask_np, mask_arg = O.make_causal_mask(qn), nb.make_causal_mask(q)
+    elif kind in ("causal", "offset"):
+        off = int(rng.integers(0, max(1, Lkv)))
+        mask_np, mask_arg = _offset_mask(Lkv, Lq, off), nb.CausalMask(off)
+    elif kind == "keypad":
+        lens = rng.integers(1, Lkv + 1, size=B)
+        mask_np = np.arange(Lkv)[:, None, None, None] < lens[None, None, None, :]
+        mask_arg = nb.jl_from_numpy(mask_np, device=DEV)
+    elif kind == "random":
+        shape = [(Lkv, Lq), (Lkv, Lq, 1, B), (Lkv, Lq, H, B)][int(rng.integers(0, 3))]
+        mask_np = rng.random(shape) > 0.3
+        mask_np[0] = True
+        mask_arg = nb.jl_from_numpy(mask_np, device=DEV)
+
+    bias_np = bias_arg = None
+    if rng.random() < 0.4:
+        shape = [(Lkv, Lq, H, B), (Lkv, Lq), (Lkv, 1, 1, B), (Lkv, Lq, H)][int(rng.integers(0, 4))]
+        bias_np = _round_to(0.5 * rng.standard_normal(shape), dtype)
+        bias_arg = _dev(bias_np, dtype)
+
+    fdrop, keep, p_drop = nb.identity, None, 0.0
+    if rng.random() < 0.3:
+        p_drop, dseed, doff = float(rng.choice([0.1, 0.25])), int(rng.integers(0, 2 ** 31)), int(rng.integers(0, 1000))
+        keep = P.keep_mask((Lkv, Lq, H, B), p_drop, dseed, doff)
+        fdrop = nb.PhiloxDropout(p_drop, seed=dseed, offset=doff)
+
+    what = f"seed {seed}: {dtype} d={d} dv={dv} H={H} Lq={Lq} Lkv={Lkv} B={B} mask={kind} bias={None if bias_np is None else bias_np.shape} p={p_drop}"
+    x, a, back = nb.dot_product_attention_pullback(q, k, v, bias_arg, mask=mask_arg, nheads=H, fdrop=fdrop)
+    dq, dk, dv_, db = back(_dev(dyn, dtype))
+    gq, gk, gv, gb = O.dot_product_attention_grad(qn, kn, vn, dyn, bias_np, mask=mask_np, nheads=H, keep=keep, p=p_drop)
+    _grad_close(nb.jl_to_numpy(dq), gq, dtype, "dq, " + what)
+    _grad_close(nb.jl_to_numpy(dk), gk, dtype, "dk, " + what)
+    _grad_close(nb.jl_to_numpy(dv_), gv, dtype, "dv, " + what)
+    if bias_np is None:
+        assert db is None, what
+    else:
+        assert tuple(db.shape) == bias_np.shape, what
+        _grad_close(nb.jl_to_numpy(db), gb, dtype, "dbias, " + what)
 
 
 def test_pullback_at_config3_size_unit_sampled():
