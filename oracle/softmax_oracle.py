@@ -40,7 +40,9 @@ def _softmax(x, dims):
         m = np.max(x, axis=ax, keepdims=True)                       # fast_maximum (:118): NaN propagates
         finite = np.exp(x - m)
         out = np.where(np.isposinf(m), np.where(np.isposinf(x), 1.0, 0.0), finite).astype(x.dtype)
-        return out / np.sum(out, axis=ax, keepdims=True)
+        # (the sum is accumulated in Float64: numpy adds one by one over several axes at once, which costs a
+        # Float32 sum of 10^4 terms five digits; the reference's sum! is pairwise)
+        return out / np.sum(out, axis=ax, keepdims=True, dtype=np.float64).astype(x.dtype)
 
 
 def logsoftmax(x, dims=1):
@@ -54,17 +56,17 @@ def _logsoftmax(x, dims):
     with np.errstate(invalid="ignore", over="ignore", divide="ignore"):
         m = np.max(x, axis=ax, keepdims=True)
         out = np.where(np.isposinf(m), np.where(np.isposinf(x), 0.0, -np.inf), x - m).astype(x.dtype)
-        return out - np.log(np.sum(np.exp(out), axis=ax, keepdims=True))
+        return out - np.log(np.sum(np.exp(out), axis=ax, keepdims=True, dtype=np.float64)).astype(x.dtype)
 
 
 def softmax_pullback(dy, y, dims=1):
     (y, shape), (dy, _) = _pad(y, dims), _pad(dy, dims)
     ax = _axis(y, dims)
     dx = dy * y
-    return (dx - y * np.sum(dx, axis=ax, keepdims=True)).reshape(shape)
+    return (dx - y * np.sum(dx, axis=ax, keepdims=True, dtype=np.float64).astype(dx.dtype)).reshape(shape)
 
 
 def logsoftmax_pullback(dy, y, dims=1):
     (y, shape), (dy, _) = _pad(y, dims), _pad(dy, dims)
     ax = _axis(y, dims)
-    return (dy - np.sum(dy, axis=ax, keepdims=True) * np.exp(y)).reshape(shape)
+    return (dy - np.sum(dy, axis=ax, keepdims=True, dtype=np.float64).astype(dy.dtype) * np.exp(y)).reshape(shape)

@@ -520,17 +520,24 @@ def test_random_configurations_match_the_oracle(seed):
         fdrop_o = lambda al: al * keep / np.float32(1.0 - p_drop)
 
     eager = rng.random() < 0.5
+    fast = dtype == torch.float32 and rng.random() < 0.5       # Float32 on the tensor cores (TF32 operands)
     nb.set_scores_mode("eager" if eager else "lazy")
+    nb.set_math_mode("fast" if fast else "default")
     try:
         y, a = nb.dot_product_attention(q, k, v, bias_arg, mask=mask_arg, nheads=H, fdrop=fdrop)
         an = nb.jl_to_numpy(a) if isinstance(a, torch.Tensor) else np.asarray(a)
     finally:
         nb.set_scores_mode("lazy")
+        nb.set_math_mode("default")
     yo, ao = O.dot_product_attention(qn, kn, vn, bias_np, mask=mask_np, nheads=H, fdrop=fdrop_o)
-    what = f"seed {seed}: {dtype} d={d} dv={dv} H={H} Lq={Lq} Lkv={Lkv} B={B} mask={kind} bias={None if bias_np is None else bias_np.shape} p={p_drop} eager={eager}"
+    what = f"seed {seed}: {dtype} d={d} dv={dv} H={H} Lq={Lq} Lkv={Lkv} B={B} mask={kind} bias={None if bias_np is None else bias_np.shape} p={p_drop} eager={eager} tf32={fast}"
     assert tuple(y.shape) == (Ev, Lq, B) and an.shape == (Lkv, Lq, H, B), what
-    _close(nb.jl_to_numpy(y), yo, dtype, "x, " + what)
-    _close(an, ao, dtype, "alpha, " + what)
+    if fast:
+        _close_tf32(nb.jl_to_numpy(y), yo, "x, " + what)
+        _close_tf32(an, ao, "alpha, " + what)
+    else:
+        _close(nb.jl_to_numpy(y), yo, dtype, "x, " + what)
+        _close(an, ao, dtype, "alpha, " + what)
     if mask_np is not None:
         keepm = np.broadcast_to(O._bcast_to_scores(mask_np), ao.shape)
         assert (an[~keepm] == 0).all(), "masked scores must be exactly 0, " + what

@@ -154,3 +154,38 @@ def test_large_product_against_float32():
     got = nb.jl_to_numpy(nb.batched_mul(nb.batched_transpose(_dev(np.transpose(An, (1, 0, 2)), dtype)),
                                         nb.batched_transpose(_dev(np.transpose(Bn, (1, 0, 2)), dtype))))
     _close(got, BO.batched_mul(An, Bn), dtype, "large TT")
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_products_match_the_oracle(seed):
+    """Seeded random draws: element type, transposes, sizes from a few elements to several tiles (multiples of 8
+    or not — the second kind takes the CUDA-core kernel), batch count, a batch of one on either side, alpha / beta,
+    padded leading dimensions."""
+    rng = np.random.default_rng(11000 + seed)
+    dtype = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
+    ta, tb = str(rng.choice(["N", "T"])), str(rng.choice(["N", "T"]))
+    if rng.random() < 0.6:
+        M, N, K = (int(8 * rng.integers(1, 70)) for _ in range(3))
+    else:
+        M, N, K = (int(rng.integers(1, 300)) for _ in range(3))
+    if dtype == torch.float32:
+        M, N, K = min(M, 200), min(N, 200), min(K, 200)
+    nbatch = int(rng.integers(1, 5))
+    ba = 1 if rng.random() < 0.2 else nbatch                  # size(A, 3) == 1: the same matrix for every batch
+    bb = 1 if rng.random() < 0.2 else nbatch
+    pad_a = int(rng.choice([0, 0, 8, 3]))                     # rows of padding under each column of A's storage
+    sa = (M, K) if ta == "N" else (K, M)
+    sb = (K, N) if tb == "N" else (N, K)
+    Abig = _round_to(rng.standard_normal((sa[0] + pad_a, sa[1], ba)), dtype)
+    Bn = _round_to(rng.standard_normal((sb[0], sb[1], bb)), dtype)
+    Cn = _round_to(rng.standard_normal((M, N, nbatch)), dtype)
+    An = Abig[:sa[0]]
+    A = _dev(Abig, dtype)[:sa[0]]
+    B, Cd = _dev(Bn, dtype), _dev(Cn, dtype)
+    opA = A if ta == "N" else nb.batched_transpose(A)
+    opB = B if tb == "N" else nb.batched_transpose(B)
+    alpha, beta = (1.0, 0.0) if rng.random() < 0.5 else (float(rng.choice([0.5, -1.5, 2.0])), float(rng.choice([0.0, 1.0, -0.5])))
+    what = f"seed {seed}: {dtype} {ta}{tb} {M}x{N}x{K} batches {ba}/{bb}/{nbatch} pad {pad_a} alpha {alpha} beta {beta}"
+    nb.batched_mul_(Cd, opA, opB, alpha, beta)
+    want = BO.batched_gemm(ta, tb, np.float32(alpha), An, Bn, np.float32(beta), Cn)
+    _close(nb.jl_to_numpy(Cd), want, dtype, what)

@@ -107,3 +107,40 @@ def test_argument_checks():
     with pytest.raises(TypeError):
         SM.softmax(torch.zeros(3, 3))
     assert tuple(SM.softmax(nb.jl_zeros((0, 5), torch.float32, DEV)).shape) == (0, 5)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_shapes_and_dims_match_the_oracle(seed):
+    """Seeded random draws: element type, rank 1 to 4, sizes that land on every kernel variant (a warp, a block
+    or a large block per column, cached or re-read columns, the strided kernel), any run of consecutive dims,
+    forward / log forward and both pullbacks, out of place and in place."""
+    rng = np.random.default_rng(12000 + seed)
+    dtype = [torch.float32, torch.float16, torch.bfloat16][seed % 3]
+    rank = int(rng.integers(1, 5))
+    first = int(rng.choice([1, 3, 8, 33, 64, 257, 512, 1000, 2048, 4100, 9000, 20000]))
+    rest = [int(rng.integers(1, 7)) for _ in range(rank - 1)]
+    shape = tuple([min(first, max(1, 600000 // int(np.prod(rest)))) if rest else first] + rest)
+    lo = int(rng.integers(1, rank + 1)); hi = int(rng.integers(lo, rank + 1))
+    dims = lo if lo == hi else tuple(range(lo, hi + 1))
+    xn = _round(3.0 * rng.standard_normal(shape), dtype)
+    dyn = _round(rng.standard_normal(shape), dtype)
+    x, dy = _as_cm(_dev(xn, dtype), dtype), _as_cm(_dev(dyn, dtype), dtype)
+    tol = TOL[dtype]
+    what = f"seed {seed}: {dtype} shape {shape} dims {dims}"
+    y, ly = SM.softmax(x, dims=dims), SM.logsoftmax(x, dims=dims)
+    yo, lyo = S.softmax(xn, dims), S.logsoftmax(xn, dims)
+    np.testing.assert_allclose(nb.jl_to_numpy(y), yo, atol=tol, rtol=tol, err_msg=what)
+    np.testing.assert_allclose(nb.jl_to_numpy(ly), lyo, atol=tol * max(1.0, np.abs(lyo).max()), rtol=tol, err_msg=what)
+    yr, lyr = nb.jl_to_numpy(y), nb.jl_to_numpy(ly)
+    dx = SM.softmax_pullback(dy, y, dims=dims)
+    np.testing.assert_allclose(nb.jl_to_numpy(dx), S.softmax_pullback(dyn, yr, dims), atol=4 * tol, rtol=4 * tol, err_msg=what)
+    dlx = SM.logsoftmax_pullback(dy, ly, dims=dims)
+    want = S.logsoftmax_pullback(dyn, lyr, dims)
+    np.testing.assert_allclose(nb.jl_to_numpy(dlx), want, atol=4 * tol * max(1.0, np.abs(want).max()), rtol=4 * tol, err_msg=what)
+    # in place: the same values as out of place, bit for bit
+    x2 = _as_cm(_dev(xn, dtype), dtype)
+    SM.softmax(x2, dims=dims, out=x2)
+    assert torch.equal(x2, y), what
+    dy2 = _as_cm(_dev(dyn, dtype), dtype)
+    SM.softmax_pullback(dy2, y, dims=dims, out=dy2)
+    assert torch.equal(dy2, dx), what
