@@ -69,9 +69,12 @@ struct TCfg {
   static constexpr int kBarOff = kVOff + kStages * kVBytes;
   static constexpr int kSmemBytes = kBarOff + 256 + 1024;
   static constexpr int kKStep = 32 / kEsz;                   // K elements of one tcgen05.mma (32 bytes)
-  static constexpr int kCtasPerSm = (kSmemBytes <= 110 * 1024) ? 2 : 1;
+  // tensor memory: two 64-column score buffers and DV columns of O, rounded up to a power of two
+  static constexpr int kTmemCols = (2 * kTBN + DV <= 256) ? 256 : 512;
+  static constexpr int kCtasPerSm = (kSmemBytes <= 110 * 1024 && kTmemCols <= 256) ? 2 : 1;
 };
 static_assert(TCfg<float, 128, 128>::kSmemBytes <= 232448, "shared memory budget");
+static_assert(TCfg<__half, 256, 256>::kSmemBytes <= 232448 && TCfg<__half, 256, 256>::kStages >= 2, "shared memory budget (d = 256)");
 
 struct TBarriers {
   uint64_t q_full;
@@ -197,7 +200,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     fence_mbar_init();
   }
   if (warp == 4) {
-    tmem_alloc(&bars->tmem_base, 256);
+    tmem_alloc(&bars->tmem_base, C::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -573,7 +576,7 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   if (warp == 4) {
     tc_fence_after();
-    tmem_dealloc(tmem, 256);
+    tmem_dealloc(tmem, C::kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag) {
     atomicExch(&g_tile_abort, 1);
@@ -639,6 +642,13 @@ cudaError_t launch_tile(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
 template <typename T, int MODE>
 cudaError_t launch_tile_dims(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
                              cudaStream_t st, int n_splits) {
+  // head sizes are padded (with zeros, by the copy engine) to 64, 128 or — 16-bit element types only — 256
+  if constexpr (sizeof(T) == 2 && (MODE == TM_FWD || MODE == TM_SPLIT)) {
+    if (a.dv > 128) return launch_tile<T, 256, 256, MODE>(mq, mk, mv, a, st, n_splits);
+    if (a.d > 128) return launch_tile<T, 256, 128, MODE>(mq, mk, mv, a, st, n_splits);
+  } else if constexpr (sizeof(T) == 2) {
+    if (a.d > 128) return launch_tile<T, 256, 64, MODE>(mq, mk, mv, a, st, n_splits);
+  }
   const bool q128 = a.d > 64;
   if (MODE != TM_FWD && MODE != TM_SPLIT) {   // the value heads play no part: one instantiation per query-head size
     if (q128) return launch_tile<T, 128, 64, MODE>(mq, mk, mv, a, st, n_splits);
@@ -676,9 +686,11 @@ const char* tile_reject_reason(const AttnArgs& a, int dtype, bool need_v, bool a
   if (dtype == NNLIB_B200_F32 && !allow_tf32) return "Float32 arrays without allow_tf32 (exact CUDA-core arithmetic)";
   const int esz = (dtype == NNLIB_B200_F32) ? 4 : 2;
   const int vec = 16 / esz;
-  if (a.d < 1 || a.d > 128 || a.d % vec != 0) return "head size d is not a multiple of 16 bytes of elements up to 128";
-  if (need_v && (a.dv < 1 || a.dv > 128 || a.dv % vec != 0))
-    return "head size dv is not a multiple of 16 bytes of elements up to 128";
+  const int dmax = (esz == 2) ? 256 : 128;   // a 128-query tile of Float32 heads of 256 would not leave room for the key ring
+  if (a.d < 1 || a.d > dmax || a.d % vec != 0)
+    return "head size d is not a multiple of 16 bytes of elements up to 256 (16-bit types) / 128 (Float32)";
+  if (need_v && (a.dv < 1 || a.dv > dmax || a.dv % vec != 0))
+    return "head size dv is not a multiple of 16 bytes of elements up to 256 (16-bit types) / 128 (Float32)";
   if (!(a.scale > 0.f)) return "scale is not positive";
   if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1) return "empty problem";
   if (!aligned16(a.q) || !aligned16(a.k)) return "q or k is not 16-byte aligned";

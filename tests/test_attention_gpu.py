@@ -348,6 +348,11 @@ def test_simt_matches_oracle_for_other_shapes():
     (64, 128, 2, 300, 500, 1),     # dv != d with the fused kernel's own sizes
     (128, 64, 2, 100, 1000, 1),
     (48, 72, 2, 1, 700, 2),        # decode-like
+    (256, 256, 2, 200, 330, 1),    # the largest heads the tensor-core path takes (16-bit types)
+    (192, 128, 2, 130, 260, 2),    # query / key heads wider than the value heads
+    (160, 256, 1, 257, 129, 1),
+    (64, 200, 2, 100, 300, 1),     # only the value heads are wide
+    (256, 256, 2, 4, 2000, 1),     # few queries against many keys: the keys are split
 ])
 def test_tile_kernel_other_head_sizes(dtype, d, dv, H, Lq, Lkv, B):
     """Head sizes other than 64 / 128 and value heads of another size than the query heads
@@ -475,8 +480,8 @@ def test_random_configurations_match_the_oracle(seed):
     eager scores — whichever kernel family the library picks.  x and alpha against the oracle."""
     rng = np.random.default_rng(7000 + seed)
     dtype = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
-    d = int(rng.choice([8, 16, 24, 40, 64, 64, 72, 96, 128, 128, 20, 33]))
-    dv = d if rng.random() < 0.6 else int(rng.choice([8, 32, 64, 128, 48]))
+    d = int(rng.choice([8, 16, 24, 40, 64, 64, 72, 96, 128, 128, 20, 33, 192, 256]))
+    dv = d if rng.random() < 0.6 else int(rng.choice([8, 32, 64, 128, 48, 256, 160]))
     H = int(rng.integers(1, 5))
     lmax = 330 if seed < 48 else 900                       # the later seeds walk the copy rings around several times
     Lq, Lkv = int(rng.integers(1, lmax)), int(rng.integers(1, lmax))
