@@ -336,7 +336,7 @@ def test_simt_matches_oracle_for_other_shapes():
     _run_case(torch.bfloat16, 84, 2, 70, 90, 2, seed=27, expect_umma=False)       # d = 42: not a multiple of 8
     _run_case(torch.float16, 64, 1, 33, 65, 1, Ev=20, seed=28, expect_umma=False)  # dv = 20
     _run_case(torch.float32, 64, 2, 50, 50, 1, causal=True, seed=29, expect_umma=False)
-    _run_case(torch.bfloat16, 512, 2, 40, 70, 1, seed=29, expect_umma=False)      # d = 256: beyond the tensor-core kernels
+    _run_case(torch.bfloat16, 528, 2, 40, 70, 1, seed=29, expect_umma=False)      # d = 264: beyond the tensor-core kernels
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
