@@ -403,23 +403,37 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const float cs = EXTRAS ? 1.f : c2;
 
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        unsigned long long sum2[2] = {0ull, 0ull};   // the plain variants: two pairs of partial row sums (packed fp32 adds)
+        const unsigned long long cs2 = pair_of(cs);
         uint32_t pk[32];
-        // exponentials of 64 keys (chunks 2*HF, 2*HF+1) relative to REF, packed into pk, summed into sum4
+        // exponentials of 64 keys (chunks 2*HF, 2*HF+1) relative to REF, packed into pk, summed into sum2
         // SEL (a literal): rows whose reference is +Inf put weight 1 on their +Inf logits and 0 elsewhere
         // (the slow branch of the reference's softmax, src/softmax.jl:73-75) instead of exp2(Inf - Inf)
 #define NB_EXP_HALF(HF, REF, SEL)                                                                  \
   do {                                                                                             \
     const float ref_ = (REF);                                                                      \
     const float nref_ = -ref_;                                                                     \
+    const unsigned long long nref2_ = pair_of(nref_);                                              \
     _Pragma("unroll") for (int cc = 0; cc < 2; ++cc) {                                             \
       _Pragma("unroll") for (int e = 0; e < 32; e += 2) {                                          \
-        float p0 = ex2_approx(fmaf(__uint_as_float(sr[(HF) * 2 + cc][e]), cs, nref_));             \
-        float p1 = ex2_approx(fmaf(__uint_as_float(sr[(HF) * 2 + cc][e + 1]), cs, nref_));         \
-        if ((SEL) && ref_ == pos_inf()) {                                                          \
-          p0 = (sr[(HF) * 2 + cc][e] == 0x7f800000u) ? 1.f : 0.f;                                  \
-          p1 = (sr[(HF) * 2 + cc][e + 1] == 0x7f800000u) ? 1.f : 0.f;                              \
+        float p0, p1;                                                                              \
+        if (EXTRAS) {                                                                              \
+          /* the variants with side inputs measured slower with the packed forms */               \
+          p0 = ex2_approx(fmaf(__uint_as_float(sr[(HF) * 2 + cc][e]), cs, nref_));                 \
+          p1 = ex2_approx(fmaf(__uint_as_float(sr[(HF) * 2 + cc][e + 1]), cs, nref_));             \
+          if ((SEL) && ref_ == pos_inf()) {                                                        \
+            p0 = (sr[(HF) * 2 + cc][e] == 0x7f800000u) ? 1.f : 0.f;                                \
+            p1 = (sr[(HF) * 2 + cc][e + 1] == 0x7f800000u) ? 1.f : 0.f;                            \
+          }                                                                                        \
+          sum4[(e >> 1) & 3] += p0 + p1;                                                           \
+        } else {                                                                                   \
+          /* two logits per instruction: scale and subtract the reference, add to the row sum */  \
+          float x0, x1;                                                                            \
+          fma2(x0, x1, __uint_as_float(sr[(HF) * 2 + cc][e]), __uint_as_float(sr[(HF) * 2 + cc][e + 1]), cs2, nref2_); \
+          p0 = ex2_approx(x0);                                                                     \
+          p1 = ex2_approx(x1);                                                                     \
+          add2(sum2[(e >> 1) & 1], p0, p1);                                                        \
         }                                                                                          \
-        sum4[(e >> 1) & 3] += p0 + p1;                                                             \
         pk[cc * 16 + (e >> 1)] = pack2<BF16>(p0, p1);                                              \
       }                                                                                            \
     }                                                                                              \
@@ -474,6 +488,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             if (raise) m_used = m_new;
             sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
+            sum2[0] = sum2[1] = 0ull;
             NB_EXP_HALF_W(0, (m_used == neg_inf()) ? 0.f : m_used);
           }
           const float m_sub = (m_used == neg_inf()) ? 0.f : m_used;
@@ -512,7 +527,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
 #undef NB_EXP_HALF_W
 #undef NB_EXP_HALF
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        l += EXTRAS ? (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]) : pair_sum(sum2[0]) + pair_sum(sum2[1]);
       }
 
       // ---------------------------------------------------------- epilogue

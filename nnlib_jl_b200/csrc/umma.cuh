@@ -381,6 +381,38 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
   return y;
 }
 
+// Two fp32 operations per instruction (sm_100 packed forms): d = a * b + c and d += a on pairs of floats.
+// `b2`, `c2` hold the same value twice (pair_of).  Same rounding as the scalar forms.
+__device__ __forceinline__ unsigned long long pair_of(float x) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, unsigned long long b2, unsigned long long c2) {
+  asm("{\n\t"
+      ".reg .b64 ra, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "fma.rn.f32x2 rd, ra, %4, %5;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "l"(b2), "l"(c2));
+}
+__device__ __forceinline__ void add2(unsigned long long& acc, float a0, float a1) {
+  asm("{\n\t"
+      ".reg .b64 ra;\n\t"
+      "mov.b64 ra, {%1, %2};\n\t"
+      "add.rn.f32x2 %0, %0, ra;\n\t"
+      "}"
+      : "+l"(acc)
+      : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ float pair_sum(unsigned long long v) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+  return lo + hi;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
