@@ -183,6 +183,10 @@ int finish(cudaError_t e) {
 bool use_umma(const AttnArgs& a, int dtype, bool need_v) {
   return !force_simt() && umma_reject_reason(a, dtype, need_v) == nullptr;
 }
+// the fused forward and its statistics-only form take any d = dv <= 128 that is a multiple of 8
+bool use_umma_fwd(const AttnArgs& a, int dtype, bool need_v) {
+  return !force_simt() && umma_fwd_reject_reason(a, dtype, need_v) == nullptr;
+}
 
 // the one-tile tensor-core kernels: other head sizes, dv != d, Float32 on the TF32 path
 bool use_tile(const AttnArgs& a, int dtype, bool need_v) {
@@ -203,7 +207,7 @@ int attention_validate(const nnlib_b200_attn_params* p, bool launching) {
   const int rc = resolve(p, NEED_QK | NEED_V | NEED_LSE_IN | NEED_ALPHA, &a, launching);
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
-  const bool fwd_ok = use_umma(a, p->dtype, true) || use_tile(a, p->dtype, true) || simt_supports(a.d, a.dv);
+  const bool fwd_ok = use_umma_fwd(a, p->dtype, true) || use_tile(a, p->dtype, true) || simt_supports(a.d, a.dv);
   const bool sc_ok = use_umma(a, p->dtype, false) || use_tile(a, p->dtype, false) || simt_supports(a.d, 1);
   return (fwd_ok && sc_ok) ? NNLIB_B200_OK : NNLIB_B200_UNSUPPORTED_SHAPE;
 }
@@ -235,12 +239,12 @@ int nnlib_b200_attn_fwd(const nnlib_b200_attn_params* p, void* stream) {
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_umma(a, p->dtype, true)) {
+  if (use_umma_fwd(a, p->dtype, true)) {
     log_call("attn_fwd", p, a, "tcgen05", nullptr);
     return finish(umma_fwd(a, p->dtype, false, st));
   }
   if (use_tile(a, p->dtype, true)) {
-    log_call("attn_fwd", p, a, "tcgen05 (one query tile per CTA)", umma_reject_reason(a, p->dtype, true));
+    log_call("attn_fwd", p, a, "tcgen05 (one query tile per CTA)", umma_fwd_reject_reason(a, p->dtype, true));
     return finish(tile_fwd(a, p->dtype, st));
   }
   if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
@@ -287,12 +291,12 @@ int nnlib_b200_attn_stats(const nnlib_b200_attn_params* p, void* stream) {
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_umma(a, p->dtype, false)) {
+  if (use_umma_fwd(a, p->dtype, false)) {
     log_call("attn_stats", p, a, "tcgen05", nullptr);
     return finish(umma_fwd(a, p->dtype, true, st));
   }
   if (use_tile(a, p->dtype, false)) {
-    log_call("attn_stats", p, a, "tcgen05 (one query tile per CTA)", umma_reject_reason(a, p->dtype, false));
+    log_call("attn_stats", p, a, "tcgen05 (one query tile per CTA)", umma_fwd_reject_reason(a, p->dtype, false));
     return finish(tile_stats(a, p->dtype, st));
   }
   if (!simt_supports(a.d, 1)) return NNLIB_B200_UNSUPPORTED_SHAPE;
@@ -509,7 +513,7 @@ int nnlib_b200_attn_path(const nnlib_b200_attn_params* p) {
   AttnArgs a;
   const int rc = resolve(p, NEED_QK | NEED_V, &a, false);
   if (rc) return rc;
-  if (use_umma(a, p->dtype, true)) return NNLIB_B200_PATH_UMMA;
+  if (use_umma_fwd(a, p->dtype, true)) return NNLIB_B200_PATH_UMMA;
   if (use_tile(a, p->dtype, true)) return NNLIB_B200_PATH_TILE;
   if (!simt_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   return NNLIB_B200_PATH_SIMT;

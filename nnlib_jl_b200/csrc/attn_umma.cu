@@ -1,7 +1,11 @@
 // Fused attention forward on the sm_100a tensor cores.
 //
 // One CTA owns 256 consecutive queries (two 128-row tiles) of one (head,
-// batch) unit and walks over the keys/values in 128-row tiles:
+// batch) unit and walks over the keys/values in 128-row tiles.  Heads are
+// addressed through 4-d tensor maps (features of a head, heads, positions,
+// batch), so a head narrower than the padded size D (64 or 128) arrives with
+// zeros behind its own features and any d = dv <= 128 that is a multiple of 8
+// runs here:
 //
 //   warp 0      TMA producer of Q (once) and of the ring of K tiles
 //   warp 3      TMA producer of the ring of V tiles
@@ -165,8 +169,8 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if ((t == 0 ? n_t0 : n_t1) == 0) continue;
         mbar_arrive_expect_tx(&bars->q_full[t], C::kTileBytes);
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_3d(smem + C::kQOff + t * C::kTileBytes + c * kChunkBytes, &tm_q, &bars->q_full[t],
-                      h * D + c * 64, q0 + t * kBM, b);
+          tma_load_4d(smem + C::kQOff + t * C::kTileBytes + c * kChunkBytes, &tm_q, &bars->q_full[t],
+                      c * 64, h, q0 + t * kBM, b);
       }
       bool ok = true;
       int j = 0;
@@ -176,8 +180,8 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->k_full[s], C::kTileBytes);
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_3d(smem + C::kKOff + s * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->k_full[s],
-                      h * D + c * 64, j * kBN, b);
+          tma_load_4d(smem + C::kKOff + s * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->k_full[s],
+                      c * 64, h, j * kBN, b);
       }
       if (*abort_flag) {
         // give copies still in flight a bounded chance to land before the CTA leaves
@@ -196,8 +200,8 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->v_full[s], C::kTileBytes);
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_3d(smem + C::kVOff + s * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full[s],
-                      h * D + c * 64, j * kBN, b);
+          tma_load_4d(smem + C::kVOff + s * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full[s],
+                      c * 64, h, j * kBN, b);
       }
       if (*abort_flag) {
         for (int jj = max(0, j - C::kStagesV); jj < j; ++jj)
@@ -545,7 +549,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             tc_fence_after();
             const float inv = dead ? (a.nan_fm ? __int_as_float(0x7fc00000) : 0.f) : a.inv_keep / l;
             uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
-                            2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * D);
+                            2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * a.dv);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t o[32];
@@ -554,6 +558,7 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
               if (row_ok) {
 #pragma unroll
                 for (int e = 0; e < 32; e += 8) {
+                  if (c * 32 + e >= a.dv) continue;   // a head narrower than the padded size: the rest is padding
                   float f[8];
 #pragma unroll
                   for (int u = 0; u < 8; ++u) f[u] = dead ? inv : __uint_as_float(o[e + u]) * inv;
@@ -1141,14 +1146,44 @@ const char* umma_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
 
 bool umma_supports(const AttnArgs& a, int dtype, bool need_v) { return umma_reject_reason(a, dtype, need_v) == nullptr; }
 
+// The fused forward (and its statistics-only form) takes more head sizes than the other kernels of this file:
+// any d = dv <= 128 that is a multiple of 8, padded to 64 or 128 by the copy engine.
+const char* umma_fwd_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
+  if (a.d == 64 || a.d == 128) return umma_reject_reason(a, dtype, need_v);
+  if (a.d < 8 || a.d > 128 || a.d % 8 != 0) return "head size d is not a multiple of 8 up to 128";
+  AttnArgs b = a;
+  b.d = 128;                      // every other condition is that of the 64 / 128 sizes
+  if (need_v) {
+    if (a.dv != a.d) return "dv differs from d";
+    b.dv = 128;
+  }
+  return umma_reject_reason(b, dtype, need_v);
+}
+
+// (features of one head, heads, positions, batch) view of q, k or v with 128-byte-swizzled boxes of 64 features x
+// 128 positions of one head; features beyond the head's own are filled with zeros by the copy
+static bool make_head_map(CUtensorMap* m, const void* base, int dtype, long long dhead, long long H, long long len,
+                          long long batch, long long stride_l, long long stride_b) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)dhead, (cuuint64_t)H, (cuuint64_t)len, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)dhead * 2, (cuuint64_t)stride_l * 2, (cuuint64_t)stride_b * 2};
+  const cuuint32_t box[4] = {64, 1, 128, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(m, dtype == NNLIB_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
-  const long long E = (long long)a.H * a.d;
-  if (!make_map(&mq, a.q, dtype, E, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
-  if (!make_map(&mk, a.k, dtype, E, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mq, a.q, dtype, a.d, a.H, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mk, a.k, dtype, a.d, a.H, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
   if (stats_only) {
     mv = mk;
-  } else if (!make_map(&mv, a.v, dtype, (long long)a.H * a.dv, a.Lkv, a.B, a.v_sl, a.v_sb)) {
+  } else if (!make_head_map(&mv, a.v, dtype, a.dv, a.H, a.Lkv, a.B, a.v_sl, a.v_sb)) {
     return cudaErrorInvalidValue;
   }
   const bool bf16 = dtype == NNLIB_B200_BF16;
@@ -1179,7 +1214,7 @@ cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t
   } while (0)
 #define NB_FWD_BF(DD) \
   do { if (bf16) NB_FWD_EX(DD, true); else NB_FWD_EX(DD, false); } while (0)
-  if (a.d == 128) NB_FWD_BF(128); else NB_FWD_BF(64);
+  if (a.d > 64) NB_FWD_BF(128); else NB_FWD_BF(64);
 #undef NB_FWD_BF
 #undef NB_FWD_EX
 #undef NB_FWD

@@ -358,10 +358,12 @@ def test_tile_kernel_other_head_sizes(dtype, d, dv, H, Lq, Lkv, B):
     """Head sizes other than 64 / 128 and value heads of another size than the query heads
     (src/attention.jl:21-23, docstring example :36, test/attention.jl:61-68) on the tensor cores: the
     one-tile kernels, forward and lazily rebuilt scores."""
-    _run_case(dtype, d * H, H, Lq, Lkv, B, Ev=dv * H, seed=70 + d, expect_umma=_lib.PATH_TILE)
+    # d = dv up to 128 runs on the fused two-tile kernel (padded to 64 / 128), everything else here on the one-tile ones
+    want = _lib.PATH_UMMA if (d == dv and d <= 128) else _lib.PATH_TILE
+    _run_case(dtype, d * H, H, Lq, Lkv, B, Ev=dv * H, seed=70 + d, expect_umma=want)
 
 
-@pytest.mark.parametrize("dtype,d,dv", [(torch.bfloat16, 96, 96), (torch.float16, 40, 72)])
+@pytest.mark.parametrize("dtype,d,dv", [(torch.bfloat16, 96, 32), (torch.float16, 40, 72)])
 def test_tile_kernel_masks_bias_dropout(dtype, d, dv):
     """Every option of the call on the one-tile kernels: causal, key-padding and full masks, bias in
     broadcast forms, Philox dropout (mask compared bit for bit), and the scores-only entry."""
