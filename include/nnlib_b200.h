@@ -87,7 +87,7 @@ enum {
 enum {
   NNLIB_B200_PATH_SIMT = 1,   /* CUDA-core kernel: any dtype, any d <= 1024, dv <= 512, any stride */
   NNLIB_B200_PATH_UMMA = 2,   /* tcgen05 + TMA kernel, two query tiles per CTA: f16/bf16, d = dv any multiple
-                                 of 8 up to 128 (scores / apply / backward: 64 or 128), 16-byte aligned rows */
+                                 of 8 up to 128 (scores / apply: 64 or 128), 16-byte aligned rows */
   NNLIB_B200_PATH_TILE = 3    /* tcgen05 + TMA kernel, one query tile per CTA: f16/bf16 with d, dv any multiples
                                  of 8 up to 256 (dv may differ from d); f32 with allow_tf32 and d, dv multiples
                                  of 4 up to 128; 16-byte aligned rows */
@@ -260,7 +260,7 @@ NNLIB_B200_API int nnlib_b200_attn_bwd(const nnlib_b200_attn_params* p, const nn
                                        void* stream);
 
 /* NNLIB_B200_PATH_* that attn_bwd would take for (p, g), or a negative error.  The tensor-core
-   backward covers 16-bit element types with d = dv in {64, 128} and every option of the forward
+   backward covers 16-bit element types with d = dv any multiple of 8 up to 128 and every option of the forward
    (causal flag, Bool mask arrays, dropout, bias with dbias); Float32 arrays and other head sizes
    run on the CUDA-core kernels. */
 NNLIB_B200_API int nnlib_b200_attn_bwd_path(const nnlib_b200_attn_params* p, const nnlib_b200_attn_grads* g);

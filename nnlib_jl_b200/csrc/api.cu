@@ -378,7 +378,7 @@ int nnlib_b200_attn_bwd(const nnlib_b200_attn_params* p, const nnlib_b200_attn_g
   }
   if (!simt_bwd_supports(a.d, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   log_call("attn_bwd", p, a, "cuda-core", force_simt() ? "NNLIB_B200_FORCE_SIMT is set"
-                                                       : "16-bit arrays with d = dv in {64,128} and 16-byte aligned rows only");
+                                                       : "16-bit arrays with d = dv a multiple of 8 up to 128 and 16-byte aligned rows only");
   return finish(simt_bwd(a, b, p->dtype, (cudaStream_t)stream));
 }
 

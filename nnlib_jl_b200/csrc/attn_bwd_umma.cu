@@ -233,8 +233,8 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       prefetch_tensormap(&tm_ra);
       mbar_arrive_expect_tx(&bars->fix_full, 2 * C::kTile);
       for (int c = 0; c < D / 64; ++c) {
-        tma_load_3d(smem + C::kFixOff + c * kChunkBytes, &tm_fa, &bars->fix_full, h * D + c * 64, t0, b);
-        tma_load_3d(smem + C::kFixOff + C::kTile + c * kChunkBytes, &tm_fb, &bars->fix_full, h * D + c * 64, t0, b);
+        tma_load_4d(smem + C::kFixOff + c * kChunkBytes, &tm_fa, &bars->fix_full, c * 64, h, t0, b);
+        tma_load_4d(smem + C::kFixOff + C::kTile + c * kChunkBytes, &tm_fb, &bars->fix_full, c * 64, h, t0, b);
       }
       bool ok = true;
       int it = 0;
@@ -244,7 +244,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->a_full[s], C::kTile);
         for (int c = 0; c < D / 64; ++c)
-          tma_load_3d(smem + C::kAOff + s * C::kTile + c * kChunkBytes, &tm_ra, &bars->a_full[s], h * D + c * 64,
+          tma_load_4d(smem + C::kAOff + s * C::kTile + c * kChunkBytes, &tm_ra, &bars->a_full[s], c * 64, h,
                       (r_first + it) * 128, b);
       }
       if (*abort_flag) {
@@ -265,7 +265,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->b_full[s], C::kTile);
         for (int c = 0; c < D / 64; ++c)
-          tma_load_3d(smem + C::kBOff + s * C::kTile + c * kChunkBytes, &tm_rb, &bars->b_full[s], h * D + c * 64,
+          tma_load_4d(smem + C::kBOff + s * C::kTile + c * kChunkBytes, &tm_rb, &bars->b_full[s], c * 64, h,
                       (r_first + it) * 128, b);
       }
       if (*abort_flag)
@@ -403,11 +403,12 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
       const bool dead = lse_nat == neg_inf();
       lse2_row = dead ? pos_inf : lse_nat * kLog2e;
       const uint4* dxr = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(g.dx) +
-                         2ll * ((long long)row * g.dx_sl + (long long)b * g.dx_sb + (long long)h * D));
+                         2ll * ((long long)row * g.dx_sl + (long long)b * g.dx_sb + (long long)h * a.d));
       const uint4* xr = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.x) +
-                        2ll * ((long long)row * a.x_sl + (long long)b * a.x_sb + (long long)h * D));
+                        2ll * ((long long)row * a.x_sl + (long long)b * a.x_sb + (long long)h * a.d));
 #pragma unroll
-      for (int e = 0; e < D / 8; ++e) dl_row = dot8<BF16>(__ldg(dxr + e), __ldg(xr + e), dl_row);
+      for (int e = 0; e < D / 8; ++e)
+        if (e * 8 < a.d) dl_row = dot8<BF16>(__ldg(dxr + e), __ldg(xr + e), dl_row);   // the head's own features
       if (dead) dl_row = 0.f;   // its x is NaN (or 0)
       if (half == 0) delta_u[row] = dl_row;
     }
@@ -730,7 +731,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
     if (ok) {
       // dq half: the two column groups share dQ's 32-column chunks; dk/dv half: group 0 stores dV, group 1 dK
       const long long Lrow = DKV ? a.Lkv : a.Lq;
-      const long long dense = 2ll * (((long long)row + Lrow * b) * ((long long)a.H * D) + (long long)h * D);
+      const long long dense = 2ll * (((long long)row + Lrow * b) * ((long long)a.H * a.d) + (long long)h * a.d);
       uint8_t* out = reinterpret_cast<uint8_t*>(DKV ? (half == 0 ? g.dv : g.dk) : g.dq) + dense;
       const float mul = (DKV && half == 0) ? 1.f : a.scale;
       const uint32_t col = (DKV && half == 1) ? kColAcc1 : kColAcc0;
@@ -749,6 +750,7 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
         if (row_ok) {
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
+            if (c * 32 + e >= a.d) continue;   // a head narrower than the padded size: the rest is padding
             uint4 v;
             v.x = pack2<BF16>(__uint_as_float(o[e]) * mul, __uint_as_float(o[e + 1]) * mul);
             v.y = pack2<BF16>(__uint_as_float(o[e + 2]) * mul, __uint_as_float(o[e + 3]) * mul);
@@ -794,11 +796,12 @@ cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const 
 
 }  // namespace
 
-// The tensor-core backward covers half-precision arrays with d = dv in {64, 128} and every feature of the
+// The tensor-core backward covers half-precision arrays with d = dv any multiple of 8 up to 128 (heads are
+// addressed through 4-d tensor maps and padded with zeros to 64 / 128) and every feature of the
 // forward: causal flag, Bool mask arrays, Philox dropout and bias (any element type and strides).
 bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype) {
   if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
-  if (!(a.d == 64 || a.d == 128) || a.dv != a.d) return false;
+  if (a.d < 8 || a.d > 128 || a.d % 8 != 0 || a.dv != a.d) return false;   // padded to 64 / 128 by the copy engine
   if (g.dbias && !a.bias) return false;
   if (a.causal && a.coff != 0) return false;      // the tile skipping here assumes the square causal pattern
   if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1 || !a.lse || !g.delta) return false;
@@ -813,11 +816,10 @@ bool umma_bwd_supports(const AttnArgs& a, const BwdArgs& g, int dtype) {
 
 cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mdx;
-  const long long E = (long long)a.H * a.d;
-  if (!make_map(&mq, a.q, dtype, E, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
-  if (!make_map(&mk, a.k, dtype, E, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
-  if (!make_map(&mv, a.v, dtype, E, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
-  if (!make_map(&mdx, g.dx, dtype, E, a.Lq, a.B, g.dx_sl, g.dx_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mq, a.q, dtype, a.d, a.H, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mk, a.k, dtype, a.d, a.H, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mv, a.v, dtype, a.d, a.H, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mdx, g.dx, dtype, a.d, a.H, a.Lq, a.B, g.dx_sl, g.dx_sb)) return cudaErrorInvalidValue;
   const bool bf16 = dtype == NNLIB_B200_BF16;
   cudaError_t e;
 #define NB_BW2(DD, BF, FT)                                                                       \
@@ -839,7 +841,7 @@ cudaError_t umma_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_
     }                                                                                            \
   } while (0)
   const int feat = (a.mask ? 1 : 0) | (a.dropout_p > 0.f ? 2 : 0) | (a.bias ? 4 : 0);
-  if (a.d == 128) { if (bf16) NB_BW(128, true); else NB_BW(128, false); }
+  if (a.d > 64) { if (bf16) NB_BW(128, true); else NB_BW(128, false); }
   else            { if (bf16) NB_BW(64, true);  else NB_BW(64, false); }
 #undef NB_BW
 #undef NB_BW2

@@ -1160,23 +1160,6 @@ const char* umma_fwd_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
   return umma_reject_reason(b, dtype, need_v);
 }
 
-// (features of one head, heads, positions, batch) view of q, k or v with 128-byte-swizzled boxes of 64 features x
-// 128 positions of one head; features beyond the head's own are filled with zeros by the copy
-static bool make_head_map(CUtensorMap* m, const void* base, int dtype, long long dhead, long long H, long long len,
-                          long long batch, long long stride_l, long long stride_b) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[4] = {(cuuint64_t)dhead, (cuuint64_t)H, (cuuint64_t)len, (cuuint64_t)batch};
-  const cuuint64_t strides[3] = {(cuuint64_t)dhead * 2, (cuuint64_t)stride_l * 2, (cuuint64_t)stride_b * 2};
-  const cuuint32_t box[4] = {64, 1, 128, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = fn(m, dtype == NNLIB_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                        4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
 cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   if (!make_head_map(&mq, a.q, dtype, a.d, a.H, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
