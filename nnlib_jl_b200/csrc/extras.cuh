@@ -96,18 +96,19 @@ __device__ __forceinline__ void side_apply(const RowSide& rs, unsigned int (&s)[
         s[e + 1] = __float_as_uint(fmaf(__uint_as_float(s[e + 1]), c2, f.y * kLog2eF));
       }
     }
+  } else if (WITH_BIAS && rs.bias_row) {   // any stride / element type: one load per key
+    // (the same expression as the vector form above, so that a row gives the same bits whichever form its
+    // alignment selects: a shard of an array and the array itself must agree exactly)
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      float bv = 0.f;
+      if (e <= lim_e) bv = load_bias(rs.bias_row, (jj0 + e) * rs.bias_s0, rs.bias_dtype) * kLog2eF;
+      s[e] = __float_as_uint(fmaf(__uint_as_float(s[e]), c2, bv));
+      asm volatile("" ::: "memory");   // one load at a time: this path must not cost registers
+    }
   } else {
 #pragma unroll
     for (int e = 0; e < 32; ++e) s[e] = __float_as_uint(__uint_as_float(s[e]) * c2);
-    if (WITH_BIAS && rs.bias_row) {   // any stride / element type: one load per key
-#pragma unroll
-      for (int e = 0; e < 32; ++e)
-        if (e <= lim_e) {
-          s[e] = __float_as_uint(fmaf(load_bias(rs.bias_row, (jj0 + e) * rs.bias_s0, rs.bias_dtype), kLog2eF,
-                                      __uint_as_float(s[e])));
-          asm volatile("" ::: "memory");   // one load at a time: this path must not cost registers
-        }
-    }
   }
   // ---- range and mask
   if (rs.mask_row && rs.mask_vec && inside) {

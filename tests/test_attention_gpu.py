@@ -1075,6 +1075,49 @@ def test_sharded_driver_on_device_matches_single_call():
     _close(nb.jl_to_numpy(x), yo, dtype, "sharded x")
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shard_partitions_match_the_single_call(seed):
+    """Seeded random draws of (heads, batch, shard count, head size, options): the driver cuts the unit grid into
+    head-range rectangles and each shard addresses its slice of the parent arrays through pointer offsets and
+    the parent's strides — bit-identical x to the unsharded call, whatever the cut."""
+    from nnlib_jl_b200.shard import ShardedAttention
+    rng = np.random.default_rng(13000 + seed)
+    ndev = torch.cuda.device_count()
+    nshards = int(rng.integers(1, 6))
+    devices = [f"cuda:{i % ndev}" for i in range(nshards)]
+    dtype = [torch.bfloat16, torch.float16][seed % 2]
+    d = int(rng.choice([64, 128, 96, 40, 72]))
+    H, B = int(rng.integers(1, 6)), int(rng.integers(1, 4))
+    Lq, Lkv = int(rng.integers(1, 300)), int(rng.integers(1, 400))
+    E = d * H
+    qn = _round_to(rng.standard_normal((E, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((E, Lkv, B)), dtype)
+    kind = str(rng.choice(["none", "causal", "keypad", "full"]))
+    mask_np = None
+    mask_host = None
+    if kind == "causal":
+        mask_host = nb.CausalMask(int(rng.integers(0, max(1, Lkv))))
+    elif kind == "keypad":
+        mask_np = rng.random((Lkv, 1, 1, B)) > 0.3
+    elif kind == "full":
+        mask_np = rng.random((Lkv, Lq, H, B)) > 0.3
+    if mask_np is not None:
+        mask_np[0] = True
+        mask_host = nb.jl_from_numpy(mask_np)
+    bias_host = None
+    if rng.random() < 0.4:
+        shape = [(Lkv, Lq, H, B), (Lkv, 1, H, 1), (Lkv, Lq)][int(rng.integers(0, 3))]
+        bias_host = nb.jl_from_numpy(_round_to(0.5 * rng.standard_normal(shape), dtype), dtype=dtype)
+    fd = (lambda: nb.PhiloxDropout(0.2, seed=7 + seed, offset=seed)) if rng.random() < 0.4 else (lambda: nb.identity)
+    q, k, v = (nb.jl_from_numpy(a, dtype=dtype) for a in (qn, kn, vn))           # host arrays
+    what = f"seed {seed}: {dtype} d={d} H={H} B={B} Lq={Lq} Lkv={Lkv} shards={nshards} mask={kind} bias={None if bias_host is None else tuple(bias_host.shape)}"
+    x = ShardedAttention(devices)(q, k, v, bias_host, mask=mask_host, nheads=H, fdrop=fd())
+    to_dev = lambda t: t if (t is None or isinstance(t, nb.CausalMask)) else t.to(DEV)
+    y, _ = nb.dot_product_attention(q.to(DEV), k.to(DEV), v.to(DEV), to_dev(bias_host), mask=to_dev(mask_host), nheads=H, fdrop=fd())
+    assert torch.equal(x, y.cpu()), what
+
+
 @pytest.mark.parametrize("B,chunk,causal", [(5, 2, True), (3, 1, False), (2, 4, True)])
 def test_host_pipelined_attention_matches_device_call(B, chunk, causal):
     """q, k, v in pinned host memory, batch cut into chunks whose copies and kernels overlap: the same
