@@ -1523,3 +1523,34 @@ def test_opaque_fdrop_on_tensor_cores(dtype, E, H, Lq, Lkv, B):
     _close(nb.jl_to_numpy(y), O.join_heads(np.transpose(x4, (0, 2, 1, 3))), dtype, "x = V·alpha'")
     yo, _ = O.dot_product_attention(qn, kn, vn, nheads=H, fdrop=lambda al: al * keep_np / np.float32(0.7))
     _close(nb.jl_to_numpy(y), yo, dtype, "x vs oracle")
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_configurations_with_an_opaque_fdrop(seed):
+    """fdrop as an arbitrary callable over seeded random shapes and options: statistics -> scores -> fdrop -> x = V alpha'
+    (src/attention.jl:91-98), whichever kernels the shapes select for the three steps."""
+    rng = np.random.default_rng(14000 + seed)
+    dtype = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
+    d = int(rng.choice([64, 128, 96, 40, 8, 20, 256]))
+    dv = d if rng.random() < 0.7 else int(rng.choice([32, 64, 128]))
+    H, B = int(rng.integers(1, 4)), int(rng.integers(1, 3))
+    Lq, Lkv = int(rng.integers(1, 260)), int(rng.integers(1, 330))
+    if rng.random() < 0.5:
+        Lkv = int(8 * rng.integers(1, 40))          # 16-byte aligned score rows: the tensor-core apply kernel
+    qn = _round_to(rng.standard_normal((d * H, Lq, B)), dtype)
+    kn = _round_to(rng.standard_normal((d * H, Lkv, B)), dtype)
+    vn = _round_to(rng.standard_normal((dv * H, Lkv, B)), dtype)
+    mask_np = mask_arg = None
+    if rng.random() < 0.5:
+        mask_np = rng.random((Lkv, Lq, 1, B)) > 0.3
+        mask_np[0] = True
+        mask_arg = nb.jl_from_numpy(mask_np, device=DEV)
+    keep_np = rng.random((Lkv, Lq, H, B)) > 0.3
+    keep = nb.jl_from_numpy(keep_np, device=DEV)
+    what = f"seed {seed}: {dtype} d={d} dv={dv} H={H} B={B} Lq={Lq} Lkv={Lkv} mask={mask_np is not None}"
+    y, a = nb.dot_product_attention(_dev(qn, dtype), _dev(kn, dtype), _dev(vn, dtype), mask=mask_arg, nheads=H,
+                                    fdrop=lambda al: al * keep / 0.7)
+    an = nb.jl_to_numpy(a)
+    yo, ao = O.dot_product_attention(qn, kn, vn, mask=mask_np, nheads=H, fdrop=lambda al: al * keep_np / np.float32(0.7))
+    _close(an, ao, dtype, "alpha', " + what)
+    _close(nb.jl_to_numpy(y), yo, dtype, "x, " + what)
