@@ -87,7 +87,7 @@ enum {
 enum {
   NNLIB_B200_PATH_SIMT = 1,   /* CUDA-core kernel: any dtype, any d <= 1024, dv <= 512, any stride */
   NNLIB_B200_PATH_UMMA = 2,   /* tcgen05 + TMA kernel, two query tiles per CTA: f16/bf16, d = dv any multiple
-                                 of 8 up to 128 (scores / apply: 64 or 128), 16-byte aligned rows */
+                                 of 8 up to 128, 16-byte aligned rows */
   NNLIB_B200_PATH_TILE = 3    /* tcgen05 + TMA kernel, one query tile per CTA: f16/bf16 with d, dv any multiples
                                  of 8 up to 256 (dv may differ from d); f32 with allow_tf32 and d, dv multiples
                                  of 4 up to 128; 16-byte aligned rows */

@@ -208,7 +208,7 @@ int attention_validate(const nnlib_b200_attn_params* p, bool launching) {
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0) return NNLIB_B200_OK;
   const bool fwd_ok = use_umma_fwd(a, p->dtype, true) || use_tile(a, p->dtype, true) || simt_supports(a.d, a.dv);
-  const bool sc_ok = use_umma(a, p->dtype, false) || use_tile(a, p->dtype, false) || simt_supports(a.d, 1);
+  const bool sc_ok = use_umma_fwd(a, p->dtype, false) || use_tile(a, p->dtype, false) || simt_supports(a.d, 1);
   return (fwd_ok && sc_ok) ? NNLIB_B200_OK : NNLIB_B200_UNSUPPORTED_SHAPE;
 }
 
@@ -310,12 +310,12 @@ int nnlib_b200_attn_scores(const nnlib_b200_attn_params* p, void* stream) {
   if (rc) return rc;
   if (a.Lq == 0 || a.B == 0 || a.Lkv == 0) return NNLIB_B200_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_umma(a, p->dtype, false)) {
+  if (use_umma_fwd(a, p->dtype, false)) {
     log_call("attn_scores", p, a, "tcgen05", nullptr);
     return finish(umma_scores(a, p->dtype, st));
   }
   if (use_tile(a, p->dtype, false)) {
-    log_call("attn_scores", p, a, "tcgen05 (one query tile per CTA)", umma_reject_reason(a, p->dtype, false));
+    log_call("attn_scores", p, a, "tcgen05 (one query tile per CTA)", umma_fwd_reject_reason(a, p->dtype, false));
     return finish(tile_scores(a, p->dtype, st));
   }
   if (!simt_supports(a.d, 1)) return NNLIB_B200_UNSUPPORTED_SHAPE;
@@ -334,7 +334,7 @@ int nnlib_b200_attn_apply(const nnlib_b200_attn_params* p, void* stream) {
   }
   if (!simt_supports(1, a.dv)) return NNLIB_B200_UNSUPPORTED_SHAPE;
   log_call("attn_apply", p, a, "cuda-core", force_simt() ? "NNLIB_B200_FORCE_SIMT is set"
-                                                         : "16-bit arrays with dv in {64,128}, Lkv % 8 == 0 and "
+                                                         : "16-bit arrays with dv a multiple of 8 up to 128, Lkv % 8 == 0 and "
                                                            "16-byte aligned rows only");
   return finish(simt_apply(a, p->dtype, (cudaStream_t)stream));
 }

@@ -694,7 +694,7 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       prefetch_tensormap(&tm_k);
       mbar_arrive_expect_tx(&bars->q_full, C::kTileBytes);
       for (int c = 0; c < C::kChunks; ++c)
-        tma_load_3d(smem + C::kQOff + c * kChunkBytes, &tm_q, &bars->q_full, h * D + c * 64, q0, b);
+        tma_load_4d(smem + C::kQOff + c * kChunkBytes, &tm_q, &bars->q_full, c * 64, h, q0, b);
       bool ok = true;
       int j = 0;
       for (; j < n_live; ++j) {
@@ -703,8 +703,8 @@ attn_scores_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->k_full[s], C::kTileBytes);
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_3d(smem + C::kKOff + s * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->k_full[s],
-                      h * D + c * 64, j * kBN, b);
+          tma_load_4d(smem + C::kKOff + s * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->k_full[s],
+                      c * 64, h, j * kBN, b);
       }
       if (*abort_flag) {
         mbar_wait_drain(&bars->q_full, 0, kDrainNs);
@@ -974,7 +974,7 @@ attn_apply_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
         for (int c = 0; c < 2; ++c)
           tma_load_4d(st + c * kChunkBytes, &tm_a, &bars->full[s], j * kBN + c * 64, q0, h, b);
         for (int c = 0; c < D / 64; ++c)
-          tma_load_3d(st + C::kATile + c * kChunkBytes, &tm_v, &bars->full[s], h * D + c * 64, j * kBN, b);
+          tma_load_4d(st + C::kATile + c * kChunkBytes, &tm_v, &bars->full[s], c * 64, h, j * kBN, b);
       }
       if (*abort_flag)
         for (int jj = max(0, j - C::kStages); jj < j; ++jj)
@@ -1007,7 +1007,7 @@ attn_apply_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     const int i = q0 + warp * 32 + lane;
     const bool row_ok = i < a.Lq;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-    uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) + 2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * D);
+    uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) + 2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * a.dv);
     bool ok = true;
     if (n_kv > 0) {
       ok = mbar_wait(&bars->o_full, 0, abort_flag);
@@ -1028,6 +1028,7 @@ attn_apply_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
         if (row_ok) {
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
+            if (c * 32 + e >= a.dv) continue;   // a head narrower than the padded size: the rest is padding
             uint4 v;
             v.x = pack2<BF16>(__uint_as_float(o[e]), __uint_as_float(o[e + 1]));
             v.y = pack2<BF16>(__uint_as_float(o[e + 2]), __uint_as_float(o[e + 3]));
@@ -1146,8 +1147,8 @@ const char* umma_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
 
 bool umma_supports(const AttnArgs& a, int dtype, bool need_v) { return umma_reject_reason(a, dtype, need_v) == nullptr; }
 
-// The fused forward (and its statistics-only form) takes more head sizes than the other kernels of this file:
-// any d = dv <= 128 that is a multiple of 8, padded to 64 or 128 by the copy engine.
+// The fused forward, its statistics-only form and the score-rebuild kernel take any d = dv <= 128 that is a
+// multiple of 8, padded to 64 or 128 by the copy engine (the short-sequence kernel keeps 64 / 128).
 const char* umma_fwd_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
   if (a.d == 64 || a.d == 128) return umma_reject_reason(a, dtype, need_v);
   if (a.d < 8 || a.d > 128 || a.d % 8 != 0) return "head size d is not a multiple of 8 up to 128";
@@ -1206,7 +1207,7 @@ cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t
 
 bool umma_apply_supports(const AttnArgs& a, int dtype) {
   if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return false;
-  if (!(a.dv == 64 || a.dv == 128)) return false;
+  if (a.dv < 8 || a.dv > 128 || a.dv % 8 != 0) return false;   // padded to 64 / 128 by the copy engine
   if (a.Lq < 1 || a.Lkv < 1 || a.H < 1 || a.B < 1) return false;
   if (a.Lkv % 8 != 0 || !aligned16(a.alpha) || a.alpha_sb % 8 != 0) return false;
   if ((long long)a.Lkv * a.Lq * 2 >= (1ll << 40)) return false;
@@ -1219,7 +1220,7 @@ bool umma_apply_supports(const AttnArgs& a, int dtype) {
 cudaError_t umma_apply(const AttnArgs& a, int dtype, cudaStream_t st) {
   CUtensorMap ma, mv;
   if (!make_alpha_map(&ma, a, dtype)) return cudaErrorInvalidValue;
-  if (!make_map(&mv, a.v, dtype, (long long)a.H * a.dv, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mv, a.v, dtype, a.dv, a.H, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
   const int n_qtiles = (a.Lq + kBM - 1) / kBM;
   const long long blocks = (long long)n_qtiles * a.H * a.B;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
@@ -1231,7 +1232,7 @@ cudaError_t umma_apply(const AttnArgs& a, int dtype, cudaStream_t st) {
     if (e != cudaSuccess) return e;                                                                          \
     kern<<<(unsigned)blocks, kApThreads, ApCfg<DD>::kSmemBytes, st>>>(ma, mv, a, n_qtiles);                  \
   } while (0)
-  if (a.dv == 128) { if (bf16) NB_AP(128, true); else NB_AP(128, false); }
+  if (a.dv > 64) { if (bf16) NB_AP(128, true); else NB_AP(128, false); }
   else             { if (bf16) NB_AP(64, true);  else NB_AP(64, false); }
 #undef NB_AP
   count_launch();
@@ -1240,9 +1241,8 @@ cudaError_t umma_apply(const AttnArgs& a, int dtype, cudaStream_t st) {
 
 cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st) {
   CUtensorMap mq, mk;
-  const long long E = (long long)a.H * a.d;
-  if (!make_map(&mq, a.q, dtype, E, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
-  if (!make_map(&mk, a.k, dtype, E, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mq, a.q, dtype, a.d, a.H, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mk, a.k, dtype, a.d, a.H, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
   const bool bf16 = dtype == NNLIB_B200_BF16;
   const int xm = (a.bias != nullptr || a.dropout_p > 0.f) ? 2 : (a.mask != nullptr ? 1 : 0);
   // the staged TMA store needs 16-byte aligned score rows
@@ -1256,7 +1256,7 @@ cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st) {
   do { if (xm == 2) NB_SC(DD, BF, 2); else if (xm == 1) NB_SC(DD, BF, 1); else NB_SC(DD, BF, 0); } while (0)
 #define NB_SC_BF(DD) \
   do { if (bf16) NB_SC_EX(DD, true); else NB_SC_EX(DD, false); } while (0)
-  if (a.d == 128) NB_SC_BF(128); else NB_SC_BF(64);
+  if (a.d > 64) NB_SC_BF(128); else NB_SC_BF(64);
 #undef NB_SC_BF
 #undef NB_SC_EX
 #undef NB_SC
