@@ -180,10 +180,7 @@ int finish(cudaError_t e) {
   return NNLIB_B200_CUDA_ERROR;
 }
 
-bool use_umma(const AttnArgs& a, int dtype, bool need_v) {
-  return !force_simt() && umma_reject_reason(a, dtype, need_v) == nullptr;
-}
-// the fused forward and its statistics-only form take any d = dv <= 128 that is a multiple of 8
+// the two-tile tensor-core kernels: 16-bit arrays with d = dv <= 128 a multiple of 8
 bool use_umma_fwd(const AttnArgs& a, int dtype, bool need_v) {
   return !force_simt() && umma_fwd_reject_reason(a, dtype, need_v) == nullptr;
 }
