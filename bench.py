@@ -445,7 +445,8 @@ def run_ours(args, w):
     if bias is None and not w.get("padmask") and not w.get("dropout") and not want_alpha:
         # plain / causal: the library's host-buffer pipeline (batch chunks; H2D, kernels and D2H overlap)
         pipe = nb.HostPipelinedAttention(E, E, Lq, Lkv, B, tdtype, nheads=H, mask=kwargs.get("mask"), chunk=1, device=dev)
-        e2e_path = "HostPipelinedAttention: batch chunks of 1, H2D / kernels / D2H overlapped"
+        e2e_path = ("HostPipelinedAttention: batch chunks of 1, the last one in 4 query ranges; H2D / kernels / D2H "
+                    "overlapped")
 
         def e2e_step():
             pipe(hq, hk, hv, hx)

@@ -292,6 +292,16 @@ def _is_causal_matrix(mask: torch.Tensor, Lq: int, Lkv: int) -> bool:
     return bool(flag.item())
 
 
+def _known_causal_matrix(mask, Lq: int, Lkv: int) -> bool:
+    """The part of :func:`_is_causal_matrix` that needs no device work: ``mask`` is a matrix that
+    :func:`make_causal_mask` returned for this length and that has not been written to since."""
+    if not isinstance(mask, torch.Tensor) or mask.ndim != 2 or Lq != Lkv or tuple(mask.shape) != (Lkv, Lq):
+        return False
+    with _made_causal_lock:
+        hit = _made_causal.get(id(mask))
+    return hit is not None and hit[0]() is mask and hit[1] == mask._version and hit[2] == Lq
+
+
 class LazyAttnScores:
     """The ``α`` of ``(x, α) = dot_product_attention(...)``, materialised on
     first use.  The fused kernel keeps one log-sum-exp per query; the

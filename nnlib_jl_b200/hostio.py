@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-from .attention import ArgumentError, CausalMask, _fused_into, check_status
+from .attention import ArgumentError, CausalMask, _fused_into, _known_causal_matrix, check_status
 from .layout import jl_empty
 
 __all__ = ["HostPipelinedAttention"]
@@ -30,10 +30,16 @@ class HostPipelinedAttention:
     in the constructor; :meth:`__call__` enqueues the whole pipeline and returns
     after the last result byte has been ordered on ``out_stream`` (call
     ``synchronize()`` or wait on :attr:`done` to read ``hx``).
+
+    What is left exposed at the end of the step is the last kernel and the last copy back, so the queries of
+    the last batch element are taken in ``tail_split`` ranges (a range of queries is a contiguous block of q
+    and of x, and needs nothing but its own rows of q beside the element's k and v): its kernels and copies
+    back run while the rest of its q is still arriving, and only a ``tail_split``-th of a result follows the
+    last input byte.
     """
 
     def __init__(self, E: int, Ev: int, Lq: int, Lkv: int, B: int, dtype: torch.dtype, *, nheads: int,
-                 mask=None, chunk: int = 1, device=None):
+                 mask=None, chunk: int = 1, device=None, tail_split: int = 4):
         if mask is not None and not isinstance(mask, CausalMask):
             # a Bool array on the device that does not depend on the batch (what make_causal_mask returns, or
             # any (Lkv, Lq[, H]) mask): every chunk uses it as it is
@@ -47,6 +53,7 @@ class HostPipelinedAttention:
         self.E, self.Ev, self.Lq, self.Lkv, self.B = int(E), int(Ev), int(Lq), int(Lkv), int(B)
         self.dtype, self.nheads, self.mask = dtype, int(nheads), mask
         self.chunk = min(int(chunk), self.B)
+        self.tail_split = max(1, min(int(tail_split), self.Lq // 256)) if self.Lq >= 512 else 1
         c = self.chunk
         # two staging sets: one is being filled while the other is in the kernels
         self.dq = [jl_empty((E, Lq, c), dtype, self.dev) for _ in range(2)]
@@ -62,6 +69,8 @@ class HostPipelinedAttention:
             self.drained = [torch.cuda.Event() for _ in range(2)]     # x of staging set s has left the device
             self.consumed = [torch.cuda.Event() for _ in range(2)]    # the kernels no longer read staging set s
             self.done = torch.cuda.Event()
+            self.piece_loaded = [torch.cuda.Event() for _ in range(self.tail_split)]
+            self.piece_computed = [torch.cuda.Event() for _ in range(self.tail_split)]
 
     @staticmethod
     def _check_host(name, t, shape, dtype):
@@ -88,28 +97,61 @@ class HostPipelinedAttention:
                 s = i & 1
                 b0, b1 = i * c, min(B, (i + 1) * c)
                 w = b1 - b0
+                tail = (i == n - 1) and self.tail_split > 1
                 # ---- host -> device (copy engine 1)
                 if i >= 2:
                     self.in_stream.wait_event(self.consumed[s])       # chunk i-2 no longer needs this set
                 with torch.cuda.stream(self.in_stream):
-                    self.dq[s].permute(2, 1, 0)[:w].copy_(hq[b0:b1], non_blocking=True)
                     self.dk[s].permute(2, 1, 0)[:w].copy_(hk[b0:b1], non_blocking=True)
                     self.dv[s].permute(2, 1, 0)[:w].copy_(hv[b0:b1], non_blocking=True)
+                    if not tail:
+                        self.dq[s].permute(2, 1, 0)[:w].copy_(hq[b0:b1], non_blocking=True)
+                    elif w > 1:
+                        self.dq[s].permute(2, 1, 0)[:w - 1].copy_(hq[b0:b1 - 1], non_blocking=True)
                     self.loaded[s].record(self.in_stream)
                 # ---- kernels (caller's stream)
                 comp.wait_event(self.loaded[s])
                 if i >= 2:
                     comp.wait_event(self.drained[s])                  # x of chunk i-2 has been copied out
                 q, k, v, x = self.dq[s], self.dk[s], self.dv[s], self.dx[s]
-                if w != c:
-                    q, k, v, x = q[:, :, :w], k[:, :, :w], v[:, :, :w], x[:, :, :w]
-                _fused_into(q, k, v, self.mask, self.nheads, x, self.lse[s])
+                wf = w - 1 if tail else w                              # batch elements handled whole
+                if wf > 0:
+                    qf, kf, vf, xf = (q, k, v, x) if wf == c else (q[:, :, :wf], k[:, :, :wf], v[:, :, :wf], x[:, :, :wf])
+                    _fused_into(qf, kf, vf, self.mask, self.nheads, xf, self.lse[s])
+                    self.computed[s].record(comp)
+                    self.out_stream.wait_event(self.computed[s])
+                    with torch.cuda.stream(self.out_stream):
+                        hx[b0:b0 + wf].copy_(xf.permute(2, 1, 0), non_blocking=True)
+                if tail:
+                    # the last batch element, one range of queries after the other
+                    e = w - 1
+                    causal_matrix = _known_causal_matrix(self.mask, self.Lq, self.Lkv)
+                    step = -(-self.Lq // self.tail_split)
+                    lse_off = wf * self.Lq * self.nheads
+                    for pz in range(self.tail_split):
+                        l0, l1 = pz * step, min(self.Lq, (pz + 1) * step)
+                        if l0 >= l1:
+                            break
+                        with torch.cuda.stream(self.in_stream):
+                            q.permute(2, 1, 0)[e, l0:l1].copy_(hq[b1 - 1, l0:l1], non_blocking=True)
+                            self.piece_loaded[pz].record(self.in_stream)
+                        comp.wait_event(self.piece_loaded[pz])
+                        if self.mask is None:
+                            m = None
+                        elif isinstance(self.mask, CausalMask):
+                            m = CausalMask(self.mask.offset + l0)
+                        elif causal_matrix:
+                            m = CausalMask(l0)             # the same pattern for queries l0 .. l1 - 1, nothing to read
+                        else:
+                            m = self.mask[:, l0:l1]
+                        _fused_into(q[:, l0:l1, e:e + 1], k[:, :, e:e + 1], v[:, :, e:e + 1], m, self.nheads,
+                                    x[:, l0:l1, e:e + 1], self.lse[s][lse_off + l0 * self.nheads:])
+                        self.piece_computed[pz].record(comp)
+                        self.out_stream.wait_event(self.piece_computed[pz])
+                        with torch.cuda.stream(self.out_stream):
+                            hx[b1 - 1, l0:l1].copy_(x.permute(2, 1, 0)[e, l0:l1], non_blocking=True)
                 self.consumed[s].record(comp)
-                self.computed[s].record(comp)
-                # ---- device -> host (copy engine 2)
-                self.out_stream.wait_event(self.computed[s])
                 with torch.cuda.stream(self.out_stream):
-                    hx[b0:b1].copy_(x.permute(2, 1, 0), non_blocking=True)
                     self.drained[s].record(self.out_stream)
             self.done.record(self.out_stream)
             comp.wait_event(self.done)             # later work on the caller's stream sees hx complete

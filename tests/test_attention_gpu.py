@@ -1139,6 +1139,48 @@ def test_host_pipelined_attention_matches_device_call(B, chunk, causal):
         pipe(hq.clone(), hk, hv, hx)        # not pinned
 
 
+@pytest.mark.parametrize("B,chunk,kind,tail_split", [
+    (3, 1, "causal_matrix", 4), (2, 2, "sentinel", 3), (1, 1, "none", 4), (3, 2, "bool", 4), (2, 1, "bool3", 2),
+    (2, 1, "offset", 4),
+])
+def test_host_pipeline_takes_the_last_batch_element_in_query_ranges(B, chunk, kind, tail_split):
+    """The queries of the last batch element go through the pipeline in ranges (their kernels and copies
+    back overlap the rest of the input): bit-identical to one device call for every form of mask — the
+    causal matrix (recognised, replaced by the pattern with the range's offset), the sentinel with and
+    without an offset, and Bool arrays (column ranges of them)."""
+    dtype, E, H, L = torch.bfloat16, 256, 2, 1100
+    g = torch.Generator().manual_seed(56)
+    hq, hk, hv = (torch.randn((B, L, E), generator=g).to(dtype).pin_memory() for _ in range(3))
+    hx = torch.zeros((B, L, E), dtype=dtype).pin_memory()
+    probe = nb.jl_empty((E, L, 1), dtype, DEV)
+    if kind == "causal_matrix":
+        mask = nb.make_causal_mask(probe)
+    elif kind == "sentinel":
+        mask = nb.CausalMask()
+    elif kind == "offset":
+        mask = nb.CausalMask(37)
+    elif kind == "bool":
+        m = torch.rand((L, L), generator=g) > 0.3
+        m[0] = True
+        mask = nb.jl_from_numpy(m.numpy().T.copy().T, device=DEV)
+    elif kind == "bool3":
+        m = torch.rand((L, L, H), generator=g) > 0.3
+        m[0] = True
+        mask = nb.jl_from_numpy(m.numpy(), device=DEV)
+    else:
+        mask = None
+    pipe = nb.HostPipelinedAttention(E, E, L, L, B, dtype, nheads=H, mask=mask, chunk=chunk, device=DEV,
+                                     tail_split=tail_split)
+    assert pipe.tail_split == tail_split
+    for _ in range(2):
+        pipe(hq, hk, hv, hx)
+    pipe.synchronize()
+    q, k, v = (t.to(DEV).permute(2, 1, 0) for t in (hq, hk, hv))
+    y, _ = nb.dot_product_attention(q, k, v, mask=mask, nheads=H)
+    torch.cuda.synchronize()
+    assert torch.equal(hx, y.permute(2, 1, 0).cpu())
+
+
 # --------------------------------------------------------------------------
 # backward (pullback) against the gradient oracle
 # --------------------------------------------------------------------------
