@@ -140,6 +140,36 @@ class ShardedAttention:
         self.devices = [str(d) for d in devices]
         self.compute = compute or _cuda_compute
         self.out_device = out_device
+        self._pipes = {}      # per-device pipelines for shards whose arrays cross the bus (see _pipelined)
+
+    def _pipelined(self, slot, dev, rect, q, k, v, x, bias, mask, dropout, H) -> bool:
+        """A rectangle of whole batch elements whose inputs and output sit in pinned host memory goes through
+        a per-device :class:`HostPipelinedAttention` (one batch element at a time, so that the copy of the
+        next element, the kernels of this one and the copy back of the previous one overlap).  Returns False
+        when the rectangle does not qualify (a head range, bias, dropout, a mask array, device-resident or pageable arrays, an injected ``compute``) — the caller then takes the plain route."""
+        from .attention import CausalMask
+        from .hostio import HostPipelinedAttention
+        if self.compute is not _cuda_compute or not str(dev).startswith("cuda"):
+            return False
+        if rect.h0 != 0 or rect.nh != H or bias is not None or dropout is not None or rect.nb < 2:
+            return False
+        if not (mask is None or isinstance(mask, CausalMask)):
+            return False                                       # mask arrays take the plain route
+        hosts = [t.permute(2, 1, 0) for t in (q, k, v, x)]      # (B, L, E) views of the column-major arrays
+        if any(t.is_cuda or not t.is_contiguous() or not t.is_pinned() for t in hosts):
+            return False
+        E, Lq, _ = q.shape
+        Ev, Lkv = v.shape[0], k.shape[1]
+        # one pipeline per worker thread (`slot`): two shards may share a device, never staging buffers
+        key = (slot, str(dev), E, Ev, Lq, Lkv, rect.nb, q.dtype, H, repr(mask))
+        pipe = self._pipes.get(key)
+        if pipe is None:
+            pipe = HostPipelinedAttention(E, Ev, Lq, Lkv, rect.nb, q.dtype, nheads=H, mask=mask, chunk=1, device=dev)
+            self._pipes[key] = pipe
+        bs = slice(rect.b0, rect.b0 + rect.nb)
+        with torch.cuda.device(dev):
+            pipe(hosts[0][bs], hosts[1][bs], hosts[2][bs], hosts[3][bs])
+        return True
 
     def __call__(self, q, k, v, bias=None, *, fdrop=None, mask=None, nheads: int = 1, out=None):
         from .attention import ArgumentError, PhiloxDropout, _validate_3d, identity
@@ -172,6 +202,8 @@ class ShardedAttention:
             try:
                 for rect in res.rects:
                     bs = slice(rect.b0, rect.b0 + rect.nb)
+                    if self._pipelined(results.index(res), res.device, rect, q, k, v, x, bias, mask, dropout, H):
+                        continue
                     qs = q[rect.h0 * d:(rect.h0 + rect.nh) * d, :, bs]
                     ks = k[rect.h0 * d:(rect.h0 + rect.nh) * d, :, bs]
                     vs = v[rect.h0 * dv:(rect.h0 + rect.nh) * dv, :, bs]

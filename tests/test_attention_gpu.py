@@ -1075,6 +1075,27 @@ def test_sharded_driver_on_device_matches_single_call():
     _close(nb.jl_to_numpy(x), yo, dtype, "sharded x")
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_sharded_driver_pipelines_whole_batch_shards(causal):
+    """Shards that are ranges of whole batch elements, with inputs and output in pinned host memory and no side
+    input, go through a per-device pipeline (copies and kernels of neighbouring batch elements overlap): the
+    same bits as one device call."""
+    from nnlib_jl_b200.shard import ShardedAttention
+    ndev = torch.cuda.device_count()
+    devices = [f"cuda:{i % ndev}" for i in range(2)]
+    dtype, E, H, L, B = torch.bfloat16, 256, 2, 700, 6                     # 12 units over 2 shards: 3 batch elements each
+    g = torch.Generator().manual_seed(57)
+    hq, hk, hv = (torch.randn((B, L, E), generator=g).to(dtype).pin_memory().permute(2, 1, 0) for _ in range(3))
+    hx = torch.zeros((B, L, E), dtype=dtype).pin_memory().permute(2, 1, 0)
+    mask = nb.CausalMask() if causal else None
+    drv = ShardedAttention(devices)
+    for _ in range(2):
+        x = drv(hq, hk, hv, mask=mask, nheads=H, out=hx)
+    assert x is hx and len(drv._pipes) == len(devices)
+    y, _ = nb.dot_product_attention(hq.to(DEV), hk.to(DEV), hv.to(DEV), mask=mask, nheads=H)
+    assert torch.equal(hx, y.cpu())
+
+
 @pytest.mark.parametrize("seed", range(12))
 def test_random_shard_partitions_match_the_single_call(seed):
     """Seeded random draws of (heads, batch, shard count, head size, options): the driver cuts the unit grid into
