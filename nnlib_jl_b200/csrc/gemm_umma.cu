@@ -355,7 +355,9 @@ cudaError_t gemm_umma(const GemmArgs& g0, int dtype, cudaStream_t st) {
   g.c_vec = (aligned16(g.C) && g.ldc % 8 == 0 && (g.batch == 1 || g.strideC % 8 == 0)) ? 1 : 0;
   const bool bf16 = dtype == NNLIB_B200_BF16;
   // tile: 256 x 256 for large products, 128 n-rows for narrow ones, 128 m-columns for short ones
-  const int nh = (g.N > 128 && g.M > 128) ? 2 : 1;
+  // (a short K leaves the 256 x 256 tile, whose accumulator fills all of tensor memory, with nothing to overlap
+  // its epilogue with: 128 rows of n then, two accumulators in turn)
+  const int nh = (g.N > 128 && g.M > 128 && g.K > 512) ? 2 : 1;
   const int mt = (g.M > 128) ? 256 : 128;
 #define NB_G4(BF, NHH, MTT)                                                               \
   do {                                                                                    \
