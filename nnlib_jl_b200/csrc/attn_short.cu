@@ -128,16 +128,14 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       prefetch_tensormap(&tm_v);
       mbar_arrive_expect_tx(&bars->qk_full, (1 + n_live) * C::kTileBytes);
       for (int c = 0; c < C::kChunks; ++c)
-        tma_load_3d(smem + C::kQOff + c * kChunkBytes, &tm_q, &bars->qk_full, h * D + c * 64, q0, b);
+        tma_load_4d(smem + C::kQOff + c * kChunkBytes, &tm_q, &bars->qk_full, c * 64, h, q0, b);
       for (int t = 0; t < n_live; ++t)
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_3d(smem + C::kKOff + t * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->qk_full, h * D + c * 64,
-                      t * kBN, b);
+          tma_load_4d(smem + C::kKOff + t * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->qk_full, c * 64, h, t * kBN, b);
       mbar_arrive_expect_tx(&bars->v_full, n_live * C::kTileBytes);
       for (int t = 0; t < n_live; ++t)
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_3d(smem + C::kVOff + t * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full, h * D + c * 64,
-                      t * kBN, b);
+          tma_load_4d(smem + C::kVOff + t * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full, c * 64, h, t * kBN, b);
       // the copies land whatever happens to the rest of the CTA: wait for them on the way out of an abort
       if (!mbar_wait(&bars->qk_full, 0, abort_flag)) mbar_wait_drain(&bars->qk_full, 0, kDrainNs);
       if (!mbar_wait(&bars->v_full, 0, abort_flag)) mbar_wait_drain(&bars->v_full, 0, kDrainNs);
@@ -395,7 +393,7 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (ok) {
           tc_fence_after();
           uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
-                          2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * D);
+                          2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * a.dv);
 #pragma unroll
           for (int cc = 0; cc < D / 64; ++cc) {
             const int c = part * (D / 64) + cc;       // 32-column chunk of O
@@ -405,6 +403,7 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (row_ok) {
 #pragma unroll
               for (int e = 0; e < 32; e += 8) {
+                if (c * 32 + e >= a.dv) continue;   // a head narrower than the padded size: the rest is padding
                 float f[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) f[u] = dead ? dead_val : __uint_as_float(o[e + u]) * scale;
@@ -451,12 +450,12 @@ cudaError_t launch_short(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
 
 }  // namespace
 
-// x and alpha together for a short key sequence: the fused forward's shapes (16-bit, d = dv in {64, 128},
+// x and alpha together for a short key sequence: the fused forward's shapes (16-bit, d = dv <= 128 a multiple of 8,
 // 16-byte aligned rows), every key of a query within one CTA's tensor memory, and score rows the TMA store
 // can address.
 bool short_supports(const AttnArgs& a, int dtype) {
-  if (!umma_supports(a, dtype, true)) return false;
-  const int max_keys = (a.d == 64) ? 512 : 256;
+  if (umma_fwd_reject_reason(a, dtype, true) != nullptr) return false;   // any d = dv <= 128 that is a multiple of 8
+  const int max_keys = (a.d <= 64) ? 512 : 256;
   if (a.Lkv > max_keys) return false;
   if (!a.alpha || a.Lkv % 8 != 0 || !aligned16(a.alpha) || a.alpha_sb % 8 != 0) return false;
   return true;
@@ -464,10 +463,9 @@ bool short_supports(const AttnArgs& a, int dtype) {
 
 cudaError_t short_attention(const AttnArgs& a, int dtype, cudaStream_t st) {
   CUtensorMap mq, mk, mv, ma;
-  const long long E = (long long)a.H * a.d;
-  if (!make_map(&mq, a.q, dtype, E, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
-  if (!make_map(&mk, a.k, dtype, E, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
-  if (!make_map(&mv, a.v, dtype, E, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mq, a.q, dtype, a.d, a.H, a.Lq, a.B, a.q_sl, a.q_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mk, a.k, dtype, a.d, a.H, a.Lkv, a.B, a.k_sl, a.k_sb)) return cudaErrorInvalidValue;
+  if (!make_head_map(&mv, a.v, dtype, a.d, a.H, a.Lkv, a.B, a.v_sl, a.v_sb)) return cudaErrorInvalidValue;
   if (!make_alpha_map(&ma, a, dtype)) return cudaErrorInvalidValue;
   const bool bf16 = dtype == NNLIB_B200_BF16;
   const int side = a.bias != nullptr ? 2 : (a.mask != nullptr ? 1 : 0);
@@ -483,7 +481,7 @@ cudaError_t short_attention(const AttnArgs& a, int dtype, cudaStream_t st) {
       default: return launch_short<DD, BF, 5>(mq, mk, mv, ma, a, st);           \
     }                                                                           \
   } while (0)
-  if (a.d == 128) { if (bf16) NB_SH(128, true); NB_SH(128, false); }
+  if (a.d > 64) { if (bf16) NB_SH(128, true); NB_SH(128, false); }
   if (bf16) NB_SH(64, true);
   NB_SH(64, false);
 #undef NB_SH

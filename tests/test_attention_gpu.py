@@ -415,6 +415,10 @@ def eager_scores():
     (128, 1, 256, 256, 2, "causal"),
     (64, 2, 130, 512, 1, "bias"),       # bias, full mask and dropout
     (64, 1, 64, 8, 1, "plain"),         # a single short tile
+    (40, 3, 200, 328, 2, "keypad"),     # a head narrower than the 64-feature box: the copy engine pads it
+    (96, 2, 150, 256, 1, "causal"),     # between the two compiled sizes
+    (72, 2, 256, 200, 2, "bias"),
+    (8, 5, 130, 512, 1, "plain"),       # the smallest head
 ])
 def test_short_sequence_kernel_x_and_alpha_in_one_pass(eager_scores, dtype, d, H, Lq, Lkv, B, kind):
     """Eager scores for key sequences that fit one CTA's tensor memory: one kernel writes x and α
