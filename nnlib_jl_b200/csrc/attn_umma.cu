@@ -1126,8 +1126,8 @@ bool make_bias_map(CUtensorMap* m, const AttnArgs& a) {
 
 }  // namespace
 
-// nullptr when the tensor-core kernels take the call, else the reason they do not
-const char* umma_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
+// the rules of the two compiled head sizes: nullptr when the tensor-core kernels take the call, else the reason
+static const char* umma_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
   if (dtype != NNLIB_B200_F16 && dtype != NNLIB_B200_BF16) return "element type is not Float16 / BFloat16";
   if (!(a.d == 64 || a.d == 128)) return "head size d is not 64 or 128";
   if (need_v && a.dv != a.d) return "dv differs from d";
@@ -1145,10 +1145,8 @@ const char* umma_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
   return nullptr;
 }
 
-bool umma_supports(const AttnArgs& a, int dtype, bool need_v) { return umma_reject_reason(a, dtype, need_v) == nullptr; }
-
-// The fused forward, its statistics-only form and the score-rebuild kernel take any d = dv <= 128 that is a
-// multiple of 8, padded to 64 or 128 by the copy engine (the short-sequence kernel keeps 64 / 128).
+// The fused forward, its statistics-only form, the score-rebuild kernel and the short-sequence kernel take any
+// d = dv <= 128 that is a multiple of 8, padded to 64 or 128 by the copy engine.
 const char* umma_fwd_reject_reason(const AttnArgs& a, int dtype, bool need_v) {
   if (a.d == 64 || a.d == 128) return umma_reject_reason(a, dtype, need_v);
   if (a.d < 8 || a.d > 128 || a.d % 8 != 0) return "head size d is not a multiple of 8 up to 128";

@@ -24,9 +24,7 @@ bool simt_bwd_supports(int d, int dv);
 cudaError_t simt_bwd(const AttnArgs& a, const BwdArgs& g, int dtype, cudaStream_t st);
 
 // tcgen05 + TMA kernels (attn_umma.cu)
-bool umma_supports(const AttnArgs& a, int dtype, bool need_v);
 const char* umma_fwd_reject_reason(const AttnArgs& a, int dtype, bool need_v);
-const char* umma_reject_reason(const AttnArgs& a, int dtype, bool need_v);
 cudaError_t umma_fwd(const AttnArgs& a, int dtype, bool stats_only, cudaStream_t st);
 cudaError_t umma_scores(const AttnArgs& a, int dtype, cudaStream_t st);
 bool umma_apply_supports(const AttnArgs& a, int dtype);

@@ -416,7 +416,7 @@ def eager_scores():
     (64, 2, 130, 512, 1, "bias"),       # bias, full mask and dropout
     (64, 1, 64, 8, 1, "plain"),         # a single short tile
     (40, 3, 200, 328, 2, "keypad"),     # a head narrower than the 64-feature box: the copy engine pads it
-    (96, 2, 150, 256, 1, "causal"),     # between the two compiled sizes
+    (96, 2, 256, 256, 1, "causal"),     # between the two compiled sizes
     (72, 2, 256, 200, 2, "bias"),
     (8, 5, 130, 512, 1, "plain"),       # the smallest head
 ])
