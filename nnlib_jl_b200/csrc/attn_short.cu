@@ -50,6 +50,9 @@ struct ShCfg {
   static constexpr int kStOff = kVOff + kMaxTiles * kTileBytes;   // 2 halves x 2 staging boxes
   static constexpr int kXOff = kKOff;      // row maxima and sums of the two halves: over K, which is done with by then
   static constexpr int kBarOff = kStOff + 4 * kShStageBytes;
+  // keep bits of a mask array, [chunk of 32 keys][query row]: in the staging boxes, which pass 3 is the first to
+  // fill — every thread is through pass 1 (the last reader of the bits) by then
+  static constexpr int kKeepOff = kStOff;
   static constexpr int kSmemBytes = kBarOff + 256 + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kOCol = (D == 64) ? 64 : 256;
@@ -190,12 +193,11 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (!ok) break;
         tma_store_4d(&tm_a, smem + C::kStOff + (part * 2 + (k & 1)) * kShStageBytes, (n_first + k) * 64, q0, h, b);
         tma_store_commit();
-        if (k >= 1) {
-          tma_store_wait_read<1>();                 // the previous box has been read out of shared memory
-          mbar_arrive(&bars->stage_free[part][(k - 1) & 1]);
-        }
+        // this thread has nothing else to do: hand the box back the moment it has been read out of shared memory
+        // (the softmax warps fill the other box meanwhile), which also keeps shared memory valid until the last read
+        tma_store_wait_read<0>();
+        mbar_arrive(&bars->stage_free[part][k & 1]);
       }
-      tma_store_wait_read<0>();                     // shared memory must stay valid until the last read
     }
   } else if (start_ok && warp < 8) {
     // ----------------------------------------------------------- softmax warps
@@ -209,26 +211,62 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
     RowSide rs;
     if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
-    // EXTRAS: the prepared logits are already scaled; plain logits get scale*log2(e) inside the exponential's FMA
-    const float cs = EXTRAS ? 1.f : c2;
+    // with a bias the prepared logits are already scaled; otherwise (plain, or a mask array only) the scores stay
+    // raw and get scale*log2(e) inside the exponential's FMA
+    const float cs = XBIAS ? 1.f : c2;
     const int t_first = part * TPP;
     const int t_end = min(n_live, t_first + TPP);     // this thread's live tiles: [t_first, t_end)
 
     // Every softmax thread goes through both exchange barriers whatever happens, so that a wait that ran out
     // in one warp cannot leave the others at a barrier; the results of an aborted CTA are discarded anyway.
+    // A mask array without a bias: the keep bits of this thread's chunks are gathered while the loads and the
+    // score products are under way (the softmax threads have nothing to do until then), so that pass 1 has no
+    // global load in it.  Each thread reads back only what it wrote itself.
+    uint32_t* keepbits = reinterpret_cast<uint32_t*>(smem + C::kKeepOff);
+    if (EXTRAS && !XBIAS) {
+      // all the 16-byte loads first, so that their latencies overlap
+      uint4 mw[TPP * 4][2];
+      const bool vec = rs.mask_row != nullptr && rs.mask_vec;
+#pragma unroll
+      for (int c = 0; c < TPP * 4; ++c) {
+        const int g = t_first * 4 + c;
+        const bool in = vec && g < t_end * 4 && g * 32 + 32 <= a.Lkv;
+        const uint4* p = reinterpret_cast<const uint4*>(rs.mask_row + (in ? g * 32 : 0));
+        mw[c][0] = in ? __ldg(p) : make_uint4(0u, 0u, 0u, 0u);
+        mw[c][1] = in ? __ldg(p + 1) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int c = 0; c < TPP * 4; ++c) {
+        const int g = t_first * 4 + c;
+        if (g >= t_end * 4) continue;
+        const unsigned int range = range_keep_bits(g * 32, lim, row_ok);
+        const bool in = vec && g * 32 + 32 <= a.Lkv;
+        keepbits[g * 128 + r] = in ? (range & mask_word_bits(mw[c][0], mw[c][1])) : mask_keep_bits_bytes(rs, g * 32, range);
+      }
+    }
     bool ok = mbar_wait_warp(&bars->s_full[part], 0, abort_flag);
     float m = neg_inf();
     if (ok && t_end > t_first) {
       tc_fence_after();
       // ---- pass 1: prepared logits (scaled base 2, bias added, masked keys -inf) and the row maximum
-      // (two chunks per turn, so that the bias / mask words of the next chunk are in flight while one is worked on)
-      // Two chunks per turn: the bias / mask words of the next chunk and its scores (the other register
-      // buffer) are in flight while one chunk is worked on.
+      // Two chunks per turn: the bias words of the next chunk and its scores (the other register buffer) are in
+      // flight while one chunk is worked on.
       uint4 bq0[4], bq1[4], mq0[2], mq1[2];
       uint32_t s0[32], s1[32];
       auto prepare = [&](int g, uint32_t (&s)[32], const uint4 (&bq)[4], const uint4 (&mq)[2]) {
-        if (EXTRAS) {
-          side_apply<XBIAS>(rs, s, bq, mq, g * 32, a.Lkv, lim, row_ok, c2);
+        if (XBIAS) {
+          side_apply<true>(rs, s, bq, mq, g * 32, a.Lkv, lim, row_ok, c2);
+        } else if (EXTRAS) {
+          const unsigned int kb = keepbits[g * 128 + r];
+          if (!__any_sync(0xffffffffu, kb != 0xffffffffu)) {
+            // every key of the chunk is kept for every row of the warp: the raw scores stay where they are
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
+            return;
+          }
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (!((kb >> e) & 1u)) s[e] = 0xff800000u;
         } else if (__any_sync(0xffffffffu, g * 32 + 31 > lim)) {
           // the causal diagonal or the end of the keys runs through this chunk
 #pragma unroll
@@ -246,15 +284,15 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_st32(lane_base + g * 32, s);
       };
       const int g_end = t_end * 4;
-      if (EXTRAS) side_issue<XBIAS>(rs, t_first * kBN, a.Lkv, bq0, mq0);
+      if (XBIAS) side_issue<true>(rs, t_first * kBN, a.Lkv, bq0, mq0);
       tmem_ld32(lane_base + t_first * kBN, s0);
 #pragma unroll 1
       for (int g = t_first * 4; g < g_end; g += 2) {
-        if (EXTRAS) side_issue<XBIAS>(rs, (g + 1) * 32, a.Lkv, bq1, mq1);
+        if (XBIAS) side_issue<true>(rs, (g + 1) * 32, a.Lkv, bq1, mq1);
         tmem_wait_ld();
         tmem_ld32(lane_base + (g + 1) * 32, s1);
         prepare(g, s0, bq0, mq0);
-        if (EXTRAS && g + 2 < g_end) side_issue<XBIAS>(rs, (g + 2) * 32, a.Lkv, bq0, mq0);
+        if (XBIAS && g + 2 < g_end) side_issue<true>(rs, (g + 2) * 32, a.Lkv, bq0, mq0);
         tmem_wait_ld();
         if (g + 2 < g_end) tmem_ld32(lane_base + (g + 2) * 32, s0);
         prepare(g + 1, s1, bq1, mq1);
@@ -271,26 +309,38 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // ---- pass 2: exponentials, row sum, dropout, packed probabilities
       const bool row_inf = XBIAS && (m == pos_inf());  // a +Inf bias: equal shares on the +Inf keys (src/softmax.jl:73-75)
       const float m_neg = (m == neg_inf()) ? 0.f : -m;
+      const unsigned long long cs2 = pair_of(cs), mneg2 = pair_of(m_neg);
       uint32_t s0[32], s1[32];
       auto exps = [&](int g, const uint32_t (&s)[32]) {
         unsigned int kb = 0xffffffffu;
         if (DROP) kb = dropout_keep32(a, srow, (unsigned int)g);
         uint32_t pk[16];
         float sum0 = 0.f, sum1 = 0.f;
+        unsigned long long sum2[2] = {0ull, 0ull};
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(s[e]), cs, m_neg));
-          float p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), cs, m_neg));
-          if (XBIAS && row_inf) {
-            p0 = (s[e] == 0x7f800000u) ? 1.f : 0.f;
-            p1 = (s[e + 1] == 0x7f800000u) ? 1.f : 0.f;
+          float p0, p1;
+          if (XBIAS) {
+            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), cs, m_neg));
+            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), cs, m_neg));
+            if (row_inf) {
+              p0 = (s[e] == 0x7f800000u) ? 1.f : 0.f;
+              p1 = (s[e + 1] == 0x7f800000u) ? 1.f : 0.f;
+            }
+            sum0 += p0;                   // dropout follows the softmax: the row sum keeps the dropped scores
+            sum1 += p1;
+          } else {
+            // two logits per instruction (packed fp32): scale and subtract the maximum, add to the row sum
+            float x0, x1;
+            fma2(x0, x1, __uint_as_float(s[e]), __uint_as_float(s[e + 1]), cs2, mneg2);
+            p0 = ex2_approx(x0);
+            p1 = ex2_approx(x1);
+            add2(sum2[(e >> 1) & 1], p0, p1);
           }
-          sum0 += p0;                     // dropout follows the softmax: the row sum keeps the dropped scores
-          sum1 += p1;
           pk[e >> 1] = pack2<BF16>(p0, p1);
           if (DROP) pk[e >> 1] &= (((kb >> e) & 1u) ? 0x0000ffffu : 0u) | (((kb >> (e + 1)) & 1u) ? 0xffff0000u : 0u);
         }
-        l += sum0 + sum1;
+        l += XBIAS ? sum0 + sum1 : pair_sum(sum2[0]) + pair_sum(sum2[1]);
         tmem_st16(lane_base + (g >> 2) * kBN + (g & 3) * 16, pk);   // chunk c of tile t -> [128 t + 16 c, +16)
       };
       // the next chunk's scores are fetched while one chunk is turned into probabilities; the packed

@@ -68,6 +68,33 @@ __device__ __forceinline__ unsigned int u4_word(const uint4& q, int w) {
   return w == 0 ? q.x : (w == 1 ? q.y : (w == 2 ? q.z : q.w));
 }
 
+// the four "non-zero" flags of a word of mask bytes as bits 0..3
+__device__ __forceinline__ unsigned int nonzero_nibble(unsigned int w) {
+  return (((nonzero_bytes(w) >> 7) * 0x00204081u) >> 21) & 0xfu;
+}
+
+// bit e: mask byte e of the 32 bytes (lo, hi) is non-zero
+__device__ __forceinline__ unsigned int mask_word_bits(const uint4& lo, const uint4& hi) {
+  return nonzero_nibble(lo.x) | (nonzero_nibble(lo.y) << 4) | (nonzero_nibble(lo.z) << 8) |
+         (nonzero_nibble(lo.w) << 12) | (nonzero_nibble(hi.x) << 16) | (nonzero_nibble(hi.y) << 20) |
+         (nonzero_nibble(hi.z) << 24) | (nonzero_nibble(hi.w) << 28);
+}
+
+// bit e: key jj0+e lies inside the row's range (keys 0 .. lim; none when the row itself is out of range)
+__device__ __forceinline__ unsigned int range_keep_bits(int jj0, int lim, bool row_ok) {
+  const int lim_e = row_ok ? lim - jj0 : -1;
+  return lim_e >= 31 ? 0xffffffffu : (lim_e < 0 ? 0u : (0xffffffffu >> (31 - lim_e)));
+}
+
+// Keep bits of keys jj0 .. jj0+31 of a row whose mask cannot be fetched with 16-byte loads: one byte at a time.
+__device__ __forceinline__ unsigned int mask_keep_bits_bytes(const RowSide& rs, int jj0, unsigned int range) {
+  if (range == 0u || !rs.mask_row) return range;
+  unsigned int m = 0u;
+  for (int e = 0; e < 32; ++e)
+    if (((range >> e) & 1u) && rs.mask_row[(jj0 + e) * rs.mask_s0] != 0) m |= 1u << e;
+  return m;
+}
+
 // s[e] (raw q·k of keys jj0+e) -> scaled base-2 logit with bias added, or -inf where the key is
 // masked, beyond `lim` (causal / end of the keys) or the row is out of range.  Works in place.
 // BIAS_STAGED: bq was filled from a shared-memory copy of the bias tile (zero beyond the array), so the
