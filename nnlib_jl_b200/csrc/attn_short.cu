@@ -17,8 +17,10 @@
 //                        from [128t + 32c, +32) to [128t + 16c, +16): always behind the reader)
 //                pass 3  alpha' = P / l / (1-p) into 128-byte swizzled staging boxes (64 keys x 128 queries)
 //                epilogue x = O / l / (1-p), each half writing half of the features
-//   warps 10, 11  one per half: ship every filled staging box with one cp.async.bulk.tensor store into the
-//              (Lkv, Lq, H, B) array
+//   warp 10    ships every filled staging box with one cp.async.bulk.tensor store into the (Lkv, Lq, H, B) array
+//   warp 11    a mask array that does not depend on the query: its bytes -> keep bits, one item ahead
+// With d = 64 shared memory has room for the next work item's operands: one CTA per SM walks over the items and
+// the loads of the next one run under the passes of the current one.
 // O lives in columns the packing freed (d = 64: the upper half of tile 0) or behind the scores (d = 128).
 // Bound by the HBM write of alpha.
 #include <cuda.h>
@@ -48,27 +50,51 @@ struct ShCfg {
   static constexpr int kKOff = kTileBytes;
   static constexpr int kVOff = kKOff + kMaxTiles * kTileBytes;
   static constexpr int kStOff = kVOff + kMaxTiles * kTileBytes;   // 2 halves x 2 staging boxes
-  static constexpr int kXOff = kKOff;      // row maxima and sums of the two halves: over K, which is done with by then
   static constexpr int kBarOff = kStOff + 4 * kShStageBytes;
-  // keep bits of a mask array, [chunk of 32 keys][query row]: in the staging boxes, which pass 3 is the first to
-  // fill — every thread is through pass 1 (the last reader of the bits) by then
-  static constexpr int kKeepOff = kStOff;
-  static constexpr int kSmemBytes = kBarOff + 256 + 1024;
+  // d = 64 leaves room for a CTA that walks over several work items and loads the next item's Q, K, V while the
+  // current one is in its passes; nothing of one item may then share memory with the operands of the next.
+  // d = 128 fills shared memory: one work item per CTA, and the two small arrays below lie over memory that is
+  // idle when they are in use.
+  static constexpr bool kPersistent = (D == 64);
+  // row maxima and sums of the two halves.  One item per CTA: over K, which is done with by the time they are
+  // written (every score product has completed).
+  static constexpr int kXOff = kPersistent ? kBarOff + 512 : kKOff;
+  // keep bits of a mask array, [chunk of 32 keys][query row].  One item per CTA: in the staging boxes, which
+  // pass 3 is the first to fill — every thread is through pass 1 (the last reader of the bits) by then.
+  static constexpr int kKeepOff = kPersistent ? kXOff + 2048 : kStOff;
+  static constexpr int kSmemBytes = (kPersistent ? kKeepOff + kMaxTiles * 4 * 128 * 4 : kBarOff + 512) + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kOCol = (D == 64) ? 64 : 256;
 };
 static_assert(ShCfg<64>::kSmemBytes <= 232448 && ShCfg<128>::kSmemBytes <= 232448, "shared memory budget");
 
 struct ShBarriers {
-  uint64_t qk_full, v_full, s_full[2], p_ready, o_full;
+  uint64_t qk_full, v_full, s_full[2], p_ready, o_full, tmem_free;
   uint64_t stage_full[2][2], stage_free[2][2];
+  uint64_t bits_full[2], bits_free[2];   // keep bits of a row-invariant mask: two slots, used by alternate items
+  uint32_t maskbits[2][16];              // [slot][chunk of 32 keys]
   uint32_t tmem_base;
   int abort_flag;
 };
-static_assert(sizeof(ShBarriers) <= 256, "barrier block");
+static_assert(sizeof(ShBarriers) <= 512, "barrier block");
 
 // all 256 softmax threads (and nobody else)
 __device__ __forceinline__ void softmax_threads_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// the same barrier, which also tells every thread whether any of them brought `flag`
+__device__ __forceinline__ bool softmax_threads_sync_any(bool flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, 256, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}"
+      : "=r"(r)
+      : "r"(flag ? 1u : 0u)
+      : "memory");
+  return r != 0;
+}
 
 // XM = side + 3*drop as in the fused forward (attn_umma.cu): side 0 = no side input (optionally causal),
 // 1 = Bool mask array, 2 = bias (and mask); drop: dropout code compiled in.  The passes are bound by
@@ -77,12 +103,16 @@ template <int D, bool BF16, int XM>
 __global__ void __launch_bounds__(kShThreads, 1)
 attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a, const AttnArgs a,
-                  const int n_qtiles) {
+                  const int n_qtiles, const int n_work) {
   using C = ShCfg<D>;
   constexpr int TPP = C::kTilesPerPart;
   constexpr bool EXTRAS = (XM % 3) != 0;
   constexpr bool XBIAS = (XM % 3) == 2;
   constexpr bool DROP = XM >= 3;
+  constexpr bool MASK_ONLY = EXTRAS && !XBIAS;
+  // The walk over several items costs registers; the bias and dropout variants have none to spare and take one
+  // item per CTA.
+  constexpr bool LOOP = C::kPersistent && XM < 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   ShBarriers* bars = reinterpret_cast<ShBarriers*>(smem + C::kBarOff);
@@ -91,12 +121,23 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int unit = blockIdx.x / n_qtiles;
-  const int qt = n_qtiles - 1 - (blockIdx.x % n_qtiles);
-  const int h = unit % a.H, b = unit / a.H;
-  const int q0 = qt * kBM;
+  // Work item w = (128 queries, head, batch element).  This CTA takes items blockIdx.x, blockIdx.x + gridDim.x, ...;
+  // every role walks over them in the same order, `it` counting them, and every barrier completes one phase per
+  // item (the staging-box barriers: one per box), so a waiter is never more than one phase behind.
   const int n_total = (a.Lkv + kBN - 1) / kBN;                 // <= kMaxTiles (the host checked)
-  const int n_live = a.causal ? min(n_total, (min(a.Lkv, max(q0 + kBM + a.coff, 1)) + kBN - 1) / kBN) : n_total;
+  // A mask that does not depend on the query (key padding): one warp turns the mask bytes of the next item into
+  // bits while the current item is in its passes, instead of every thread fetching the same bytes for its own row.
+  const bool rowinv = MASK_ONLY && a.mask != nullptr && a.mask_s[1] == 0;
+  struct Work { int h, b, q0, n_live; };
+  auto work_of = [&](int w) {
+    Work k;
+    const int unit = w / n_qtiles;
+    k.h = unit % a.H;
+    k.b = unit / a.H;
+    k.q0 = (n_qtiles - 1 - (w % n_qtiles)) * kBM;
+    k.n_live = a.causal ? min(n_total, (min(a.Lkv, max(k.q0 + kBM + a.coff, 1)) + kBN - 1) / kBN) : n_total;
+    return k;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->qk_full, 1);
@@ -105,6 +146,11 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->p_ready, 8);
     mbar_init(&bars->o_full, 1);
+    mbar_init(&bars->tmem_free, 8);
+    for (int p = 0; p < 2; ++p) {
+      mbar_init(&bars->bits_full[p], 1);
+      mbar_init(&bars->bits_free[p], 8);
+    }
     for (int p = 0; p < 2; ++p)
       for (int s = 0; s < 2; ++s) {
         mbar_init(&bars->stage_full[p][s], 4);
@@ -129,19 +175,37 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
-      mbar_arrive_expect_tx(&bars->qk_full, (1 + n_live) * C::kTileBytes);
-      for (int c = 0; c < C::kChunks; ++c)
-        tma_load_4d(smem + C::kQOff + c * kChunkBytes, &tm_q, &bars->qk_full, c * 64, h, q0, b);
-      for (int t = 0; t < n_live; ++t)
+      int n_qk = 0, n_v = 0;                         // loads issued so far
+      bool ok = true;
+      for (int it = 0, w = blockIdx.x; (LOOP ? w < n_work : it < 1) && ok; w += gridDim.x, ++it) {
+        const Work wk = work_of(w);
+        // Q and K of the previous item have been read by its last score product
+        if (it > 0) ok = mbar_wait(&bars->s_full[1], (it - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars->qk_full, (1 + wk.n_live) * C::kTileBytes);
         for (int c = 0; c < C::kChunks; ++c)
-          tma_load_4d(smem + C::kKOff + t * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->qk_full, c * 64, h, t * kBN, b);
-      mbar_arrive_expect_tx(&bars->v_full, n_live * C::kTileBytes);
-      for (int t = 0; t < n_live; ++t)
-        for (int c = 0; c < C::kChunks; ++c)
-          tma_load_4d(smem + C::kVOff + t * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full, c * 64, h, t * kBN, b);
-      // the copies land whatever happens to the rest of the CTA: wait for them on the way out of an abort
-      if (!mbar_wait(&bars->qk_full, 0, abort_flag)) mbar_wait_drain(&bars->qk_full, 0, kDrainNs);
-      if (!mbar_wait(&bars->v_full, 0, abort_flag)) mbar_wait_drain(&bars->v_full, 0, kDrainNs);
+          tma_load_4d(smem + C::kQOff + c * kChunkBytes, &tm_q, &bars->qk_full, c * 64, wk.h, wk.q0, wk.b);
+        for (int t = 0; t < wk.n_live; ++t)
+          for (int c = 0; c < C::kChunks; ++c)
+            tma_load_4d(smem + C::kKOff + t * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->qk_full, c * 64, wk.h,
+                        t * kBN, wk.b);
+        ++n_qk;
+        // V of the previous item has been read by its last P V product
+        if (it > 0) ok = mbar_wait(&bars->o_full, (it - 1) & 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars->v_full, wk.n_live * C::kTileBytes);
+        for (int t = 0; t < wk.n_live; ++t)
+          for (int c = 0; c < C::kChunks; ++c)
+            tma_load_4d(smem + C::kVOff + t * C::kTileBytes + c * kChunkBytes, &tm_v, &bars->v_full, c * 64, wk.h,
+                        t * kBN, wk.b);
+        ++n_v;
+      }
+      // the copies land whatever happens to the rest of the CTA: wait for the last ones on the way out of an abort
+      // (the earlier ones were waited for by the products that freed their buffers)
+      if (n_qk > 0 && !mbar_wait(&bars->qk_full, (n_qk - 1) & 1, abort_flag))
+        mbar_wait_drain(&bars->qk_full, (n_qk - 1) & 1, kDrainNs);
+      if (n_v > 0 && !mbar_wait(&bars->v_full, (n_v - 1) & 1, abort_flag))
+        mbar_wait_drain(&bars->v_full, (n_v - 1) & 1, kDrainNs);
     }
   } else if (start_ok && warp == 9) {
     // -------------------------------------------------------------- MMA issuer
@@ -149,8 +213,14 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       constexpr uint32_t idesc_qk = make_idesc_f16(BF16, kBM, kBN, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(BF16, kBM, D, false, true);
       const uint32_t qa = smem_u32(smem + C::kQOff);
-      bool ok = mbar_wait(&bars->qk_full, 0, abort_flag);
-      if (ok) {
+      bool ok = true;
+      for (int it = 0, w = blockIdx.x; (LOOP ? w < n_work : it < 1) && ok; w += gridDim.x, ++it) {
+        const int n_live = work_of(w).n_live;
+        const uint32_t ph = it & 1;
+        ok = mbar_wait(&bars->qk_full, ph, abort_flag);
+        // every softmax warp has read the previous item's probabilities and O out of tensor memory
+        if (ok && it > 0) ok = mbar_wait(&bars->tmem_free, (it - 1) & 1, abort_flag);
+        if (!ok) break;
         tc_fence_after();
         for (int t = 0; t < C::kMaxTiles; ++t) {
           if (t < n_live) {
@@ -165,309 +235,374 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if ((t + 1) % TPP == 0) umma_commit(&bars->s_full[t / TPP]);   // the scores of one half of the warps
         }
         // every row's probabilities are packed (and every score column has been read): O may be written
-        ok = mbar_wait(&bars->p_ready, 0, abort_flag);
-        if (ok) ok = mbar_wait(&bars->v_full, 0, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          for (int t = 0; t < n_live; ++t) {
-            const uint32_t va = smem_u32(smem + C::kVOff + t * C::kTileBytes);
+        ok = mbar_wait(&bars->p_ready, ph, abort_flag);
+        if (ok) ok = mbar_wait(&bars->v_full, ph, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        for (int t = 0; t < n_live; ++t) {
+          const uint32_t va = smem_u32(smem + C::kVOff + t * C::kTileBytes);
 #pragma unroll
-            for (int kk = 0; kk < kBN / 16; ++kk)
-              umma_ts(tmem + C::kOCol, tmem + t * kBN + kk * 8, make_smem_desc_sw128(va + kk * 2048, kChunkBytes, 1024),
-                      idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kBN / 16; ++kk)
+            umma_ts(tmem + C::kOCol, tmem + t * kBN + kk * 8, make_smem_desc_sw128(va + kk * 2048, kChunkBytes, 1024),
+                    idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars->o_full);
+      }
+    }
+  } else if (start_ok && warp == 10) {
+    // ---- store thread: each filled staging box (128 queries x 64 scores) goes out as one TMA store.  The two
+    // halves of the softmax warps fill their k-th boxes at about the same time: both are sent, then handed back
+    // the moment the copy engine has read them (the softmax warps fill the other two boxes meanwhile).
+    if (lane == 0) {
+      prefetch_tensormap(&tm_a);
+      bool ok = true;
+      const int n_box = 2 * n_total;                  // boxes of 64 keys per item; half p owns [2 TPP p, 2 TPP (p + 1))
+      const int n0 = min(n_box, 2 * TPP), n1 = n_box - n0;
+      int cb0 = 0, cb1 = 0;                           // boxes of each half so far, over all items
+      for (int it = 0, w = blockIdx.x; (LOOP ? w < n_work : it < 1) && ok; w += gridDim.x, ++it) {
+        const Work wk = work_of(w);
+        for (int k = 0; k < n0 && ok; ++k) {
+          ok = mbar_wait(&bars->stage_full[0][cb0 & 1], (cb0 >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tma_store_4d(&tm_a, smem + C::kStOff + (cb0 & 1) * kShStageBytes, k * 64, wk.q0, wk.h, wk.b);
+          tma_store_commit();
+          const bool second = k < n1;
+          if (second) {
+            ok = mbar_wait(&bars->stage_full[1][cb1 & 1], (cb1 >> 1) & 1, abort_flag);
+            if (ok) {
+              tma_store_4d(&tm_a, smem + C::kStOff + (2 + (cb1 & 1)) * kShStageBytes, (2 * TPP + k) * 64, wk.q0, wk.h,
+                           wk.b);
+              tma_store_commit();
+            }
           }
-          umma_commit(&bars->o_full);
+          tma_store_wait_read<0>();                   // also keeps shared memory valid until the last read
+          mbar_arrive(&bars->stage_free[0][cb0 & 1]);
+          ++cb0;
+          if (second && ok) {
+            mbar_arrive(&bars->stage_free[1][cb1 & 1]);
+            ++cb1;
+          }
         }
       }
     }
-  } else if (start_ok && warp >= 10) {
-    // ---- store threads, one per half: each filled staging box (128 queries x 64 scores) goes out as one TMA store
-    if (lane == 0) {
-      const int part = warp - 10;
-      prefetch_tensormap(&tm_a);
+  } else if (start_ok && warp == 11) {
+    // ---- mask warp: lane c gathers the keep bits of keys [32 c, 32 c + 32) of the item's (head, batch element)
+    if (rowinv) {
       bool ok = true;
-      const int n_first = 2 * TPP * part;
-      const int n_mine = max(0, min(2 * n_total, 2 * TPP * (part + 1)) - n_first);
-      for (int k = 0; k < n_mine && ok; ++k) {
-        ok = mbar_wait(&bars->stage_full[part][k & 1], (k >> 1) & 1, abort_flag);
+      for (int it = 0, w = blockIdx.x; (LOOP ? w < n_work : it < 1) && ok; w += gridDim.x, ++it) {
+        const Work wk = work_of(w);
+        const int slot = it & 1;
+        // the slot's previous user (two items back) is through its pass 1
+        if (it >= 2) ok = mbar_wait_warp(&bars->bits_free[slot], ((it >> 1) - 1) & 1, abort_flag);
         if (!ok) break;
-        tma_store_4d(&tm_a, smem + C::kStOff + (part * 2 + (k & 1)) * kShStageBytes, (n_first + k) * 64, q0, h, b);
-        tma_store_commit();
-        // this thread has nothing else to do: hand the box back the moment it has been read out of shared memory
-        // (the softmax warps fill the other box meanwhile), which also keeps shared memory valid until the last read
-        tma_store_wait_read<0>();
-        mbar_arrive(&bars->stage_free[part][k & 1]);
+        if (lane < n_total * 4) {
+          const unsigned char* mrow = a.mask + (long long)wk.h * a.mask_s[2] + (long long)wk.b * a.mask_s[3];
+          const int jj0 = lane * 32;
+          unsigned int bits = 0u;
+          if (a.mask_s[0] == 1 && (reinterpret_cast<unsigned long long>(mrow) & 15ull) == 0 && jj0 + 32 <= a.Lkv) {
+            const uint4* p = reinterpret_cast<const uint4*>(mrow + jj0);
+            bits = mask_word_bits(__ldg(p), __ldg(p + 1));
+          } else {
+            for (int e = 0; e < 32; ++e)
+              if (jj0 + e < a.Lkv && mrow[(long long)(jj0 + e) * a.mask_s[0]] != 0) bits |= 1u << e;
+          }
+          bars->maskbits[slot][lane] = bits;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->bits_full[slot]);
       }
     }
   } else if (start_ok && warp < 8) {
     // ----------------------------------------------------------- softmax warps
     const int part = warp >> 2;                       // which half of the key tiles
     const int r = (warp & 3) * 32 + lane;             // row inside the tile = TMEM lane
-    const int i = q0 + r;
-    const bool row_ok = i < a.Lq;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float c2 = a.scale * kLog2e;
-    const int lim = a.causal ? min(i + a.coff, a.Lkv - 1) : a.Lkv - 1;   // last key this row attends to (< 0: none)
-    const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
-    RowSide rs;
-    if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
     // with a bias the prepared logits are already scaled; otherwise (plain, or a mask array only) the scores stay
     // raw and get scale*log2(e) inside the exponential's FMA
     const float cs = XBIAS ? 1.f : c2;
     const int t_first = part * TPP;
-    const int t_end = min(n_live, t_first + TPP);     // this thread's live tiles: [t_first, t_end)
+    int cb = 0;                                       // staging boxes of this half so far, over all items
+#pragma unroll 1
+    for (int it = 0, w = blockIdx.x; LOOP ? w < n_work : it < 1; w += gridDim.x, ++it) {
+      const Work wk = work_of(w);
+      const int h = wk.h, b = wk.b, q0 = wk.q0, n_live = wk.n_live;
+      const uint32_t ph = it & 1;                       // phase of the once-per-item barriers
+      const int i = q0 + r;
+      const bool row_ok = i < a.Lq;
+      const int lim = a.causal ? min(i + a.coff, a.Lkv - 1) : a.Lkv - 1;   // last key this row attends to (< 0: none)
+      const unsigned long long srow = score_row(a, row_ok ? i : 0, h, b);
+      RowSide rs;
+      if (EXTRAS) rs = make_row_side(a, i, h, b, row_ok);
+      const int t_end = min(n_live, t_first + TPP);     // this thread's live tiles: [t_first, t_end)
 
-    // Every softmax thread goes through both exchange barriers whatever happens, so that a wait that ran out
-    // in one warp cannot leave the others at a barrier; the results of an aborted CTA are discarded anyway.
-    // A mask array without a bias: the keep bits of this thread's chunks are gathered while the loads and the
-    // score products are under way (the softmax threads have nothing to do until then), so that pass 1 has no
-    // global load in it.  Each thread reads back only what it wrote itself.
-    uint32_t* keepbits = reinterpret_cast<uint32_t*>(smem + C::kKeepOff);
-    if (EXTRAS && !XBIAS) {
-      // all the 16-byte loads first, so that their latencies overlap
-      uint4 mw[TPP * 4][2];
-      const bool vec = rs.mask_row != nullptr && rs.mask_vec;
+      // Every softmax thread goes through both exchange barriers of an item whatever happens, and all of them leave
+      // the walk together (the second barrier tells each whether any wait ran out), so that a wait that ran out in
+      // one warp cannot leave the others at a barrier; the results of an aborted CTA are discarded anyway.
+      // A mask array without a bias: the keep bits of this thread's chunks are gathered while the loads and the
+      // score products are under way (the softmax threads have nothing to do until then), so that pass 1 has no
+      // global load in it.  Each thread reads back only what it wrote itself.
+      uint32_t* keepbits = reinterpret_cast<uint32_t*>(smem + C::kKeepOff);
+      if (MASK_ONLY && !rowinv) {
+        // all the 16-byte loads first, so that their latencies overlap
+        uint4 mw[TPP * 4][2];
+        const bool vec = rs.mask_row != nullptr && rs.mask_vec;
 #pragma unroll
-      for (int c = 0; c < TPP * 4; ++c) {
-        const int g = t_first * 4 + c;
-        const bool in = vec && g < t_end * 4 && g * 32 + 32 <= a.Lkv;
-        const uint4* p = reinterpret_cast<const uint4*>(rs.mask_row + (in ? g * 32 : 0));
-        mw[c][0] = in ? __ldg(p) : make_uint4(0u, 0u, 0u, 0u);
-        mw[c][1] = in ? __ldg(p + 1) : make_uint4(0u, 0u, 0u, 0u);
-      }
+        for (int c = 0; c < TPP * 4; ++c) {
+          const int g = t_first * 4 + c;
+          const bool in = vec && g < t_end * 4 && g * 32 + 32 <= a.Lkv;
+          const uint4* p = reinterpret_cast<const uint4*>(rs.mask_row + (in ? g * 32 : 0));
+          mw[c][0] = in ? __ldg(p) : make_uint4(0u, 0u, 0u, 0u);
+          mw[c][1] = in ? __ldg(p + 1) : make_uint4(0u, 0u, 0u, 0u);
+        }
 #pragma unroll
-      for (int c = 0; c < TPP * 4; ++c) {
-        const int g = t_first * 4 + c;
-        if (g >= t_end * 4) continue;
-        const unsigned int range = range_keep_bits(g * 32, lim, row_ok);
-        const bool in = vec && g * 32 + 32 <= a.Lkv;
-        keepbits[g * 128 + r] = in ? (range & mask_word_bits(mw[c][0], mw[c][1])) : mask_keep_bits_bytes(rs, g * 32, range);
+        for (int c = 0; c < TPP * 4; ++c) {
+          const int g = t_first * 4 + c;
+          if (g >= t_end * 4) continue;
+          const unsigned int range = range_keep_bits(g * 32, lim, row_ok);
+          const bool in = vec && g * 32 + 32 <= a.Lkv;
+          keepbits[g * 128 + r] = in ? (range & mask_word_bits(mw[c][0], mw[c][1])) : mask_keep_bits_bytes(rs, g * 32, range);
+        }
       }
-    }
-    bool ok = mbar_wait_warp(&bars->s_full[part], 0, abort_flag);
-    float m = neg_inf();
-    if (ok && t_end > t_first) {
-      tc_fence_after();
-      // ---- pass 1: prepared logits (scaled base 2, bias added, masked keys -inf) and the row maximum
-      // Two chunks per turn: the bias words of the next chunk and its scores (the other register buffer) are in
-      // flight while one chunk is worked on.
-      uint4 bq0[4], bq1[4], mq0[2], mq1[2];
-      uint32_t s0[32], s1[32];
-      auto prepare = [&](int g, uint32_t (&s)[32], const uint4 (&bq)[4], const uint4 (&mq)[2]) {
-        if (XBIAS) {
-          side_apply<true>(rs, s, bq, mq, g * 32, a.Lkv, lim, row_ok, c2);
-        } else if (EXTRAS) {
-          const unsigned int kb = keepbits[g * 128 + r];
-          if (!__any_sync(0xffffffffu, kb != 0xffffffffu)) {
-            // every key of the chunk is kept for every row of the warp: the raw scores stay where they are
+      bool okb = true;
+      if (rowinv) okb = mbar_wait_warp(&bars->bits_full[it & 1], (it >> 1) & 1, abort_flag);
+      bool ok = mbar_wait_warp(&bars->s_full[part], ph, abort_flag);
+      ok = ok && okb;
+      float m = neg_inf();
+      if (ok && t_end > t_first) {
+        tc_fence_after();
+        // ---- pass 1: prepared logits (scaled base 2, bias added, masked keys -inf) and the row maximum
+        // Two chunks per turn: the bias words of the next chunk and its scores (the other register buffer) are in
+        // flight while one chunk is worked on.
+        uint4 bq0[4], bq1[4], mq0[2], mq1[2];
+        uint32_t s0[32], s1[32];
+        auto prepare = [&](int g, uint32_t (&s)[32], const uint4 (&bq)[4], const uint4 (&mq)[2]) {
+          if (XBIAS) {
+            side_apply<true>(rs, s, bq, mq, g * 32, a.Lkv, lim, row_ok, c2);
+          } else if (EXTRAS) {
+            const unsigned int kb = rowinv ? (range_keep_bits(g * 32, lim, row_ok) & bars->maskbits[it & 1][g])
+                                           : keepbits[g * 128 + r];
+            if (!__any_sync(0xffffffffu, kb != 0xffffffffu)) {
+              // every key of the chunk is kept for every row of the warp: the raw scores stay where they are
+#pragma unroll
+              for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
+              return;
+            }
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (!((kb >> e) & 1u)) s[e] = 0xff800000u;
+          } else if (__any_sync(0xffffffffu, g * 32 + 31 > lim)) {
+            // the causal diagonal or the end of the keys runs through this chunk
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (g * 32 + e > lim) s[e] = 0xff800000u;
+          } else {
+            // plain chunk: the raw scores stay where they are
 #pragma unroll
             for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
             return;
           }
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (!((kb >> e) & 1u)) s[e] = 0xff800000u;
-        } else if (__any_sync(0xffffffffu, g * 32 + 31 > lim)) {
-          // the causal diagonal or the end of the keys runs through this chunk
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (g * 32 + e > lim) s[e] = 0xff800000u;
-        } else {
-          // plain chunk: the raw scores stay where they are
-#pragma unroll
           for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
-          return;
-        }
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
-        __syncwarp();                     // the code above branches per row
-        tmem_st32(lane_base + g * 32, s);
-      };
-      const int g_end = t_end * 4;
-      if (XBIAS) side_issue<true>(rs, t_first * kBN, a.Lkv, bq0, mq0);
-      tmem_ld32(lane_base + t_first * kBN, s0);
+          __syncwarp();                     // the code above branches per row
+          tmem_st32(lane_base + g * 32, s);
+        };
+        const int g_end = t_end * 4;
+        if (XBIAS) side_issue<true>(rs, t_first * kBN, a.Lkv, bq0, mq0);
+        tmem_ld32(lane_base + t_first * kBN, s0);
 #pragma unroll 1
-      for (int g = t_first * 4; g < g_end; g += 2) {
-        if (XBIAS) side_issue<true>(rs, (g + 1) * 32, a.Lkv, bq1, mq1);
-        tmem_wait_ld();
-        tmem_ld32(lane_base + (g + 1) * 32, s1);
-        prepare(g, s0, bq0, mq0);
-        if (XBIAS && g + 2 < g_end) side_issue<true>(rs, (g + 2) * 32, a.Lkv, bq0, mq0);
-        tmem_wait_ld();
-        if (g + 2 < g_end) tmem_ld32(lane_base + (g + 2) * 32, s0);
-        prepare(g + 1, s1, bq1, mq1);
-      }
-      tmem_wait_st();
-    }
-    if (part == 0) mbar_wait_warp(&bars->s_full[1], 0, abort_flag);   // the other half's products still read K until then
-    xstat[part * 128 + r] = m * cs;                   // in scaled base-2 units from here on (scale > 0)
-    softmax_threads_sync();
-    m = fmaxf(xstat[r], xstat[128 + r]);              // fmaxf drops a NaN: a NaN logit shows up in the sum instead
-
-    float l = 0.f;
-    if (ok && t_end > t_first) {
-      // ---- pass 2: exponentials, row sum, dropout, packed probabilities
-      const bool row_inf = XBIAS && (m == pos_inf());  // a +Inf bias: equal shares on the +Inf keys (src/softmax.jl:73-75)
-      const float m_neg = (m == neg_inf()) ? 0.f : -m;
-      const unsigned long long cs2 = pair_of(cs), mneg2 = pair_of(m_neg);
-      uint32_t s0[32], s1[32];
-      auto exps = [&](int g, const uint32_t (&s)[32]) {
-        unsigned int kb = 0xffffffffu;
-        if (DROP) kb = dropout_keep32(a, srow, (unsigned int)g);
-        uint32_t pk[16];
-        float sum0 = 0.f, sum1 = 0.f;
-        unsigned long long sum2[2] = {0ull, 0ull};
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0, p1;
-          if (XBIAS) {
-            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), cs, m_neg));
-            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), cs, m_neg));
-            if (row_inf) {
-              p0 = (s[e] == 0x7f800000u) ? 1.f : 0.f;
-              p1 = (s[e + 1] == 0x7f800000u) ? 1.f : 0.f;
-            }
-            sum0 += p0;                   // dropout follows the softmax: the row sum keeps the dropped scores
-            sum1 += p1;
-          } else {
-            // two logits per instruction (packed fp32): scale and subtract the maximum, add to the row sum
-            float x0, x1;
-            fma2(x0, x1, __uint_as_float(s[e]), __uint_as_float(s[e + 1]), cs2, mneg2);
-            p0 = ex2_approx(x0);
-            p1 = ex2_approx(x1);
-            add2(sum2[(e >> 1) & 1], p0, p1);
-          }
-          pk[e >> 1] = pack2<BF16>(p0, p1);
-          if (DROP) pk[e >> 1] &= (((kb >> e) & 1u) ? 0x0000ffffu : 0u) | (((kb >> (e + 1)) & 1u) ? 0xffff0000u : 0u);
+        for (int g = t_first * 4; g < g_end; g += 2) {
+          if (XBIAS) side_issue<true>(rs, (g + 1) * 32, a.Lkv, bq1, mq1);
+          tmem_wait_ld();
+          tmem_ld32(lane_base + (g + 1) * 32, s1);
+          prepare(g, s0, bq0, mq0);
+          if (XBIAS && g + 2 < g_end) side_issue<true>(rs, (g + 2) * 32, a.Lkv, bq0, mq0);
+          tmem_wait_ld();
+          if (g + 2 < g_end) tmem_ld32(lane_base + (g + 2) * 32, s0);
+          prepare(g + 1, s1, bq1, mq1);
         }
-        l += XBIAS ? sum0 + sum1 : pair_sum(sum2[0]) + pair_sum(sum2[1]);
-        tmem_st16(lane_base + (g >> 2) * kBN + (g & 3) * 16, pk);   // chunk c of tile t -> [128 t + 16 c, +16)
-      };
-      // the next chunk's scores are fetched while one chunk is turned into probabilities; the packed
-      // probabilities of chunk g land in columns chunk g / 2 of the same tile has already left
-      const int g_end = t_end * 4;
-      tmem_ld32(lane_base + t_first * kBN, s0);
-#pragma unroll 1
-      for (int g = t_first * 4; g < g_end; g += 2) {
-        tmem_wait_ld();
-        tmem_ld32(lane_base + (g + 1) * 32, s1);
-        exps(g, s0);
-        tmem_wait_ld();
-        if (g + 2 < g_end) tmem_ld32(lane_base + (g + 2) * 32, s0);
-        exps(g + 1, s1);
+        tmem_wait_st();
       }
-      tmem_wait_st();
-    }
-    tc_fence_before();
-    __syncwarp();
-    if (ok && lane == 0) mbar_arrive(&bars->p_ready);
-    xstat[256 + part * 128 + r] = l;
-    softmax_threads_sync();
-    l = xstat[256 + r] + xstat[256 + 128 + r];
-
-    // ---- pass 3: alpha' = P / l / (1-p), box by box
-    if (ok) {
-      const bool dead = !(l > 0.f);
-      const float nanv = __int_as_float(0x7fc00000);
-      const float scale = dead ? 0.f : a.inv_keep / l;
-      const float dead_val = (a.nan_fm || l != l) ? nanv : 0.f;
-      if (part == 0 && a.lse && row_ok) {
-        float lse_v = (l != l) ? nanv : dead ? neg_inf() : (m + log2f(l)) * kLn2;
-        if (m == pos_inf() && !dead) lse_v = lse_inf_rows(l);
-        a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = lse_v;
-      }
-      const int n_first = 2 * TPP * part;
-      const int n_mine = max(0, min(2 * n_total, 2 * TPP * (part + 1)) - n_first);
-      const bool any_dead = __any_sync(0xffffffffu, dead);
-      bool okst = true;
-      // packed probabilities of box n (keys [64 n, 64 n + 64)) of this row: fetched one box ahead
-      auto fetch = [&](int n, uint32_t (&pk)[32]) {
-        if (n < 2 * n_live) tmem_ld32(lane_base + (n >> 1) * kBN + (n & 1) * 32, pk);
-      };
-      auto emit = [&](int k, uint32_t (&pk)[32]) {
-        const int n = n_first + k;
-        if (n < 2 * n_live) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            float lo, hi;
-            if (BF16) {
-              lo = __uint_as_float(pk[e] << 16);
-              hi = __uint_as_float(pk[e] & 0xffff0000u);
-            } else {
-              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pk[e]));
-              lo = f.x; hi = f.y;
-            }
-            pk[e] = pack2<BF16>(lo * scale, hi * scale);
-          }
-          if (any_dead) {                 // rows with nothing to attend to (or a NaN logit): a constant
-            const uint32_t z = pack2<BF16>(dead_val, dead_val);
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (dead) pk[e] = z;
-          }
-        } else {
-          // key tiles entirely above the causal diagonal
-          const uint32_t z = dead ? pack2<BF16>(dead_val, dead_val) : 0u;
-#pragma unroll
-          for (int e = 0; e < 32; ++e) pk[e] = z;
-        }
-        if (k >= 2) {
-          okst = mbar_wait_warp(&bars->stage_free[part][k & 1], ((k >> 1) - 1) & 1, abort_flag);
-          if (!okst) return;
-        }
-        uint8_t* row = smem + C::kStOff + (part * 2 + (k & 1)) * kShStageBytes + r * 128;
-#pragma unroll
-        for (int v = 0; v < 8; ++v)
-          *reinterpret_cast<uint4*>(row + ((v ^ (r & 7)) << 4)) =
-              make_uint4(pk[v * 4], pk[v * 4 + 1], pk[v * 4 + 2], pk[v * 4 + 3]);
-        fence_proxy_async_smem();
+      if (rowinv) {                                     // this warp is done with the slot of mask bits
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->stage_full[part][k & 1]);
-      };
-      uint32_t pk0[32], pk1[32];
-      if (n_mine > 0) fetch(n_first, pk0);
-#pragma unroll 1
-      for (int k = 0; k < n_mine && okst; k += 2) {
-        tmem_wait_ld();
-        if (k + 1 < n_mine) fetch(n_first + k + 1, pk1);
-        emit(k, pk0);
-        if (!okst || k + 1 >= n_mine) break;
-        tmem_wait_ld();
-        if (k + 2 < n_mine) fetch(n_first + k + 2, pk0);
-        emit(k + 1, pk1);
+        if (lane == 0) mbar_arrive(&bars->bits_free[it & 1]);
       }
+      if (part == 0) mbar_wait_warp(&bars->s_full[1], ph, abort_flag);   // the other half's products still read K until then
+      xstat[part * 128 + r] = m * cs;                   // in scaled base-2 units from here on (scale > 0)
+      softmax_threads_sync();
+      m = fmaxf(xstat[r], xstat[128 + r]);              // fmaxf drops a NaN: a NaN logit shows up in the sum instead
 
-      // ---- epilogue: x = O / l / (1-p); each half of the warps writes half of the features
-      if (okst) {
-        ok = mbar_wait_warp(&bars->o_full, 0, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
-                          2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * a.dv);
+      float l = 0.f;
+      if (ok && t_end > t_first) {
+        // ---- pass 2: exponentials, row sum, dropout, packed probabilities
+        const bool row_inf = XBIAS && (m == pos_inf());  // a +Inf bias: equal shares on the +Inf keys (src/softmax.jl:73-75)
+        const float m_neg = (m == neg_inf()) ? 0.f : -m;
+        const unsigned long long cs2 = pair_of(cs), mneg2 = pair_of(m_neg);
+        uint32_t s0[32], s1[32];
+        auto exps = [&](int g, const uint32_t (&s)[32]) {
+          unsigned int kb = 0xffffffffu;
+          if (DROP) kb = dropout_keep32(a, srow, (unsigned int)g);
+          uint32_t pk[16];
+          float sum0 = 0.f, sum1 = 0.f;
+          unsigned long long sum2[2] = {0ull, 0ull};
 #pragma unroll
-          for (int cc = 0; cc < D / 64; ++cc) {
-            const int c = part * (D / 64) + cc;       // 32-column chunk of O
-            uint32_t o[32];
-            tmem_ld32(lane_base + C::kOCol + c * 32, o);
-            tmem_wait_ld();
-            if (row_ok) {
+          for (int e = 0; e < 32; e += 2) {
+            float p0, p1;
+            if (XBIAS) {
+              p0 = ex2_approx(fmaf(__uint_as_float(s[e]), cs, m_neg));
+              p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), cs, m_neg));
+              if (row_inf) {
+                p0 = (s[e] == 0x7f800000u) ? 1.f : 0.f;
+                p1 = (s[e + 1] == 0x7f800000u) ? 1.f : 0.f;
+              }
+              sum0 += p0;                   // dropout follows the softmax: the row sum keeps the dropped scores
+              sum1 += p1;
+            } else {
+              // two logits per instruction (packed fp32): scale and subtract the maximum, add to the row sum
+              float x0, x1;
+              fma2(x0, x1, __uint_as_float(s[e]), __uint_as_float(s[e + 1]), cs2, mneg2);
+              p0 = ex2_approx(x0);
+              p1 = ex2_approx(x1);
+              add2(sum2[(e >> 1) & 1], p0, p1);
+            }
+            pk[e >> 1] = pack2<BF16>(p0, p1);
+            if (DROP) pk[e >> 1] &= (((kb >> e) & 1u) ? 0x0000ffffu : 0u) | (((kb >> (e + 1)) & 1u) ? 0xffff0000u : 0u);
+          }
+          l += XBIAS ? sum0 + sum1 : pair_sum(sum2[0]) + pair_sum(sum2[1]);
+          tmem_st16(lane_base + (g >> 2) * kBN + (g & 3) * 16, pk);   // chunk c of tile t -> [128 t + 16 c, +16)
+        };
+        // the next chunk's scores are fetched while one chunk is turned into probabilities; the packed
+        // probabilities of chunk g land in columns chunk g / 2 of the same tile has already left
+        const int g_end = t_end * 4;
+        tmem_ld32(lane_base + t_first * kBN, s0);
+#pragma unroll 1
+        for (int g = t_first * 4; g < g_end; g += 2) {
+          tmem_wait_ld();
+          tmem_ld32(lane_base + (g + 1) * 32, s1);
+          exps(g, s0);
+          tmem_wait_ld();
+          if (g + 2 < g_end) tmem_ld32(lane_base + (g + 2) * 32, s0);
+          exps(g + 1, s1);
+        }
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(&bars->p_ready);
+      xstat[256 + part * 128 + r] = l;
+      if (softmax_threads_sync_any(!ok || *abort_flag != 0)) break;
+      l = xstat[256 + r] + xstat[256 + 128 + r];
+
+      // ---- pass 3: alpha' = P / l / (1-p), box by box
+      if (ok) {
+        const bool dead = !(l > 0.f);
+        const float nanv = __int_as_float(0x7fc00000);
+        const float scale = dead ? 0.f : a.inv_keep / l;
+        const float dead_val = (a.nan_fm || l != l) ? nanv : 0.f;
+        if (part == 0 && a.lse && row_ok) {
+          float lse_v = (l != l) ? nanv : dead ? neg_inf() : (m + log2f(l)) * kLn2;
+          if (m == pos_inf() && !dead) lse_v = lse_inf_rows(l);
+          a.lse[i + (long long)a.Lq * h + a.lse_sb * b] = lse_v;
+        }
+        const int n_first = 2 * TPP * part;
+        const int n_mine = max(0, min(2 * n_total, 2 * TPP * (part + 1)) - n_first);
+        const bool any_dead = __any_sync(0xffffffffu, dead);
+        bool okst = true;
+        // packed probabilities of box n (keys [64 n, 64 n + 64)) of this row: fetched one box ahead
+        auto fetch = [&](int n, uint32_t (&pk)[32]) {
+          if (n < 2 * n_live) tmem_ld32(lane_base + (n >> 1) * kBN + (n & 1) * 32, pk);
+        };
+        auto emit = [&](int k, uint32_t (&pk)[32]) {
+          const int n = n_first + k;
+          if (n < 2 * n_live) {
 #pragma unroll
-              for (int e = 0; e < 32; e += 8) {
-                if (c * 32 + e >= a.dv) continue;   // a head narrower than the padded size: the rest is padding
-                float f[8];
+            for (int e = 0; e < 32; ++e) {
+              float lo, hi;
+              if (BF16) {
+                lo = __uint_as_float(pk[e] << 16);
+                hi = __uint_as_float(pk[e] & 0xffff0000u);
+              } else {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pk[e]));
+                lo = f.x; hi = f.y;
+              }
+              pk[e] = pack2<BF16>(lo * scale, hi * scale);
+            }
+            if (any_dead) {                 // rows with nothing to attend to (or a NaN logit): a constant
+              const uint32_t z = pack2<BF16>(dead_val, dead_val);
 #pragma unroll
-                for (int u = 0; u < 8; ++u) f[u] = dead ? dead_val : __uint_as_float(o[e + u]) * scale;
-                uint4 v;
-                v.x = pack2<BF16>(f[0], f[1]);
-                v.y = pack2<BF16>(f[2], f[3]);
-                v.z = pack2<BF16>(f[4], f[5]);
-                v.w = pack2<BF16>(f[6], f[7]);
-                *reinterpret_cast<uint4*>(xrow + (c * 32 + e) * 2) = v;
+              for (int e = 0; e < 32; ++e)
+                if (dead) pk[e] = z;
+            }
+          } else {
+            // key tiles entirely above the causal diagonal
+            const uint32_t z = dead ? pack2<BF16>(dead_val, dead_val) : 0u;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) pk[e] = z;
+          }
+          const int ck = cb + k;            // box number over all items: slot ck & 1, its use number ck >> 1
+          if (ck >= 2) {
+            okst = mbar_wait_warp(&bars->stage_free[part][ck & 1], ((ck >> 1) - 1) & 1, abort_flag);
+            if (!okst) return;
+          }
+          uint8_t* row = smem + C::kStOff + (part * 2 + (ck & 1)) * kShStageBytes + r * 128;
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            *reinterpret_cast<uint4*>(row + ((v ^ (r & 7)) << 4)) =
+                make_uint4(pk[v * 4], pk[v * 4 + 1], pk[v * 4 + 2], pk[v * 4 + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->stage_full[part][ck & 1]);
+        };
+        uint32_t pk0[32], pk1[32];
+        if (n_mine > 0) fetch(n_first, pk0);
+#pragma unroll 1
+        for (int k = 0; k < n_mine && okst; k += 2) {
+          tmem_wait_ld();
+          if (k + 1 < n_mine) fetch(n_first + k + 1, pk1);
+          emit(k, pk0);
+          if (!okst || k + 1 >= n_mine) break;
+          tmem_wait_ld();
+          if (k + 2 < n_mine) fetch(n_first + k + 2, pk0);
+          emit(k + 1, pk1);
+        }
+
+        // ---- epilogue: x = O / l / (1-p); each half of the warps writes half of the features
+        if (okst) {
+          ok = mbar_wait_warp(&bars->o_full, ph, abort_flag);
+          if (ok) {
+            tc_fence_after();
+            uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
+                            2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * a.dv);
+#pragma unroll
+            for (int cc = 0; cc < D / 64; ++cc) {
+              const int c = part * (D / 64) + cc;       // 32-column chunk of O
+              uint32_t o[32];
+              tmem_ld32(lane_base + C::kOCol + c * 32, o);
+              tmem_wait_ld();
+              if (row_ok) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                  if (c * 32 + e >= a.dv) continue;   // a head narrower than the padded size: the rest is padding
+                  float f[8];
+#pragma unroll
+                  for (int u = 0; u < 8; ++u) f[u] = dead ? dead_val : __uint_as_float(o[e + u]) * scale;
+                  uint4 v;
+                  v.x = pack2<BF16>(f[0], f[1]);
+                  v.y = pack2<BF16>(f[2], f[3]);
+                  v.z = pack2<BF16>(f[4], f[5]);
+                  v.w = pack2<BF16>(f[6], f[7]);
+                  *reinterpret_cast<uint4*>(xrow + (c * 32 + e) * 2) = v;
+                }
               }
             }
           }
         }
       }
+      cb += max(0, min(2 * n_total, 2 * TPP * (part + 1)) - 2 * TPP * part);   // the boxes of this half per item
+      // this warp has read everything it needs out of tensor memory: the next item's scores may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_free);
     }
   }
 
@@ -484,6 +619,14 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
 }
 
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      n < 1)
+    n = 148;
+  return n;
+}
+
 template <int D, bool BF16, int XM>
 cudaError_t launch_short(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma,
                          const AttnArgs& a, cudaStream_t st) {
@@ -491,9 +634,12 @@ cudaError_t launch_short(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ShCfg<D>::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int n_qtiles = (a.Lq + kBM - 1) / kBM;
-  const long long blocks = (long long)n_qtiles * a.H * a.B;
-  if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kShThreads, ShCfg<D>::kSmemBytes, st>>>(mq, mk, mv, ma, a, n_qtiles);
+  const long long n_work = (long long)n_qtiles * a.H * a.B;
+  if (n_work > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+  // d = 64 without bias and dropout: one CTA per SM walks over the work items; otherwise one item per CTA
+  const bool loop = ShCfg<D>::kPersistent && XM < 2;   // as LOOP in the kernel
+  const long long blocks = loop ? (n_work < sm_count() ? n_work : sm_count()) : n_work;
+  kern<<<(unsigned)blocks, kShThreads, ShCfg<D>::kSmemBytes, st>>>(mq, mk, mv, ma, a, n_qtiles, (int)n_work);
   count_launch();
   return cudaGetLastError();
 }
