@@ -78,6 +78,22 @@ struct ShBarriers {
 };
 static_assert(sizeof(ShBarriers) <= 512, "barrier block");
 
+// d = a * b + c and d = a * b on pairs of 16-bit values, in the arrays' own type
+template <bool BF16>
+__device__ __forceinline__ uint32_t fma16x2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  if (BF16) asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  else asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t mul16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  if (BF16) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  else asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // all 256 softmax threads (and nobody else)
 __device__ __forceinline__ void softmax_threads_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 // the same barrier, which also tells every thread whether any of them brought `flag`
@@ -190,8 +206,8 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tma_load_4d(smem + C::kKOff + t * C::kTileBytes + c * kChunkBytes, &tm_k, &bars->qk_full, c * 64, wk.h,
                         t * kBN, wk.b);
         ++n_qk;
-        // V of the previous item has been read by its last P V product
-        if (it > 0) ok = mbar_wait(&bars->o_full, (it - 1) & 1, abort_flag);
+        // V's memory of the previous item: read by its last P V product, then used by the epilogue to stage x
+        if (it > 0) ok = mbar_wait(&bars->tmem_free, (it - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->v_full, wk.n_live * C::kTileBytes);
         for (int t = 0; t < wk.n_live; ++t)
@@ -499,6 +515,17 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const float nanv = __int_as_float(0x7fc00000);
         const float scale = dead ? 0.f : a.inv_keep / l;
         const float dead_val = (a.nan_fm || l != l) ? nanv : 0.f;
+        // alpha' = P * scale in the arrays' own 16-bit arithmetic: the scale as a leading 16-bit value plus a 16-bit
+        // remainder, so that the result is P * scale to within its final rounding (the remainder's rounding error
+        // is 2^-8 of a term that is itself 2^-8 of the result)
+        const uint32_t scale_hi2 = pack2<BF16>(scale, scale);
+        float scale_hi;
+        if (BF16) {
+          scale_hi = __uint_as_float(scale_hi2 << 16);
+        } else {
+          scale_hi = __half2float(__ushort_as_half(static_cast<unsigned short>(scale_hi2 & 0xffffu)));
+        }
+        const uint32_t scale_lo2 = pack2<BF16>(scale - scale_hi, scale - scale_hi);
         if (part == 0 && a.lse && row_ok) {
           float lse_v = (l != l) ? nanv : dead ? neg_inf() : (m + log2f(l)) * kLn2;
           if (m == pos_inf() && !dead) lse_v = lse_inf_rows(l);
@@ -515,18 +542,9 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         auto emit = [&](int k, uint32_t (&pk)[32]) {
           const int n = n_first + k;
           if (n < 2 * n_live) {
+            // two scores per instruction: P * scale_hi + (P * scale_lo), rounded once by the fused multiply-add
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              float lo, hi;
-              if (BF16) {
-                lo = __uint_as_float(pk[e] << 16);
-                hi = __uint_as_float(pk[e] & 0xffff0000u);
-              } else {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pk[e]));
-                lo = f.x; hi = f.y;
-              }
-              pk[e] = pack2<BF16>(lo * scale, hi * scale);
-            }
+            for (int e = 0; e < 32; ++e) pk[e] = fma16x2<BF16>(pk[e], scale_hi2, mul16x2<BF16>(pk[e], scale_lo2));
             if (any_dead) {                 // rows with nothing to attend to (or a NaN logit): a constant
               const uint32_t z = pack2<BF16>(dead_val, dead_val);
 #pragma unroll
@@ -566,35 +584,48 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           emit(k + 1, pk1);
         }
 
-        // ---- epilogue: x = O / l / (1-p); each half of the warps writes half of the features
+        // ---- epilogue: x = O / l / (1-p); each half of the warps handles half of the features.  A thread owns a
+        // row, and rows lie far apart in x: the rows go through shared memory (V's, which the last P V product has
+        // finished with; swizzled against bank conflicts) so that a warp writes whole runs of a row's features
+        // instead of 32 scattered 16-byte pieces per instruction.  A warp reads back only what it wrote itself.
         if (okst) {
           ok = mbar_wait_warp(&bars->o_full, ph, abort_flag);
           if (ok) {
             tc_fence_after();
-            uint8_t* xrow = reinterpret_cast<uint8_t*>(a.x) +
-                            2ll * ((long long)i * a.x_sl + (long long)b * a.x_sb + (long long)h * a.dv);
+            constexpr int PPR = D / 16;               // 16-byte pieces of a row per half of the warps
+            uint8_t* xst = smem + C::kVOff;           // [128 rows][D features], 16-byte pieces XOR-swizzled by row
 #pragma unroll
             for (int cc = 0; cc < D / 64; ++cc) {
-              const int c = part * (D / 64) + cc;       // 32-column chunk of O
+              const int c = part * (D / 64) + cc;     // 32-column chunk of O
               uint32_t o[32];
               tmem_ld32(lane_base + C::kOCol + c * 32, o);
               tmem_wait_ld();
-              if (row_ok) {
 #pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-                  if (c * 32 + e >= a.dv) continue;   // a head narrower than the padded size: the rest is padding
-                  float f[8];
+              for (int e = 0; e < 32; e += 8) {
+                float f[8];
 #pragma unroll
-                  for (int u = 0; u < 8; ++u) f[u] = dead ? dead_val : __uint_as_float(o[e + u]) * scale;
-                  uint4 v;
-                  v.x = pack2<BF16>(f[0], f[1]);
-                  v.y = pack2<BF16>(f[2], f[3]);
-                  v.z = pack2<BF16>(f[4], f[5]);
-                  v.w = pack2<BF16>(f[6], f[7]);
-                  *reinterpret_cast<uint4*>(xrow + (c * 32 + e) * 2) = v;
-                }
+                for (int u = 0; u < 8; ++u) f[u] = dead ? dead_val : __uint_as_float(o[e + u]) * scale;
+                uint4 v;
+                v.x = pack2<BF16>(f[0], f[1]);
+                v.y = pack2<BF16>(f[2], f[3]);
+                v.z = pack2<BF16>(f[4], f[5]);
+                v.w = pack2<BF16>(f[6], f[7]);
+                const int piece = c * 4 + (e >> 3);
+                *reinterpret_cast<uint4*>(xst + r * (D * 2) + ((piece ^ (r & 7)) << 4)) = v;
               }
             }
+            __syncwarp();
+            const int pc = part * PPR + (lane % PPR);   // this lane's piece of a row
+#pragma unroll
+            for (int g = 0; g < PPR; ++g) {
+              const int rr = (warp & 3) * 32 + g * (32 / PPR) + lane / PPR;
+              const uint4 v = *reinterpret_cast<const uint4*>(xst + rr * (D * 2) + ((pc ^ (rr & 7)) << 4));
+              if (q0 + rr < a.Lq && pc * 8 < a.dv)      // rows beyond Lq; a head narrower than the padded size
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.x) +
+                                          2ll * ((long long)(q0 + rr) * a.x_sl + (long long)b * a.x_sb +
+                                                 (long long)h * a.dv + pc * 8)) = v;
+            }
+            fence_proxy_async_smem();                   // the next item's V is written by the copy engine
           }
         }
       }
