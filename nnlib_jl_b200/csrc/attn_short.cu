@@ -395,9 +395,12 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         auto prepare = [&](int g, uint32_t (&s)[32], const uint4 (&bq)[4], const uint4 (&mq)[2]) {
           if (XBIAS) {
             side_apply<true>(rs, s, bq, mq, g * 32, a.Lkv, lim, row_ok, c2);
-          } else if (EXTRAS) {
-            const unsigned int kb = rowinv ? (range_keep_bits(g * 32, lim, row_ok) & bars->maskbits[it & 1][g])
-                                           : keepbits[g * 128 + r];
+          } else {
+            // keep bits of the chunk: the row's range (the causal diagonal, the end of the keys), and the mask array
+            unsigned int kb;
+            if (!EXTRAS) kb = range_keep_bits(g * 32, lim, true);
+            else if (rowinv) kb = range_keep_bits(g * 32, lim, row_ok) & bars->maskbits[it & 1][g];
+            else kb = keepbits[g * 128 + r];
             if (!__any_sync(0xffffffffu, kb != 0xffffffffu)) {
               // every key of the chunk is kept for every row of the warp: the raw scores stay where they are
 #pragma unroll
@@ -407,16 +410,6 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
             for (int e = 0; e < 32; ++e)
               if (!((kb >> e) & 1u)) s[e] = 0xff800000u;
-          } else if (__any_sync(0xffffffffu, g * 32 + 31 > lim)) {
-            // the causal diagonal or the end of the keys runs through this chunk
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (g * 32 + e > lim) s[e] = 0xff800000u;
-          } else {
-            // plain chunk: the raw scores stay where they are
-#pragma unroll
-            for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
-            return;
           }
 #pragma unroll
           for (int e = 0; e < 32; e += 2) m = max3(m, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
