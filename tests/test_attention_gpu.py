@@ -419,6 +419,10 @@ def eager_scores():
     (96, 2, 256, 256, 1, "causal"),     # between the two compiled sizes
     (72, 2, 256, 200, 2, "bias"),
     (8, 5, 130, 512, 1, "plain"),       # the smallest head
+    (64, 12, 384, 384, 12, "keypad"),   # 432 work items: every CTA walks over three or more of them
+    (64, 10, 320, 320, 16, "causal"),   # 480 items of unequal length
+    (64, 6, 300, 512, 16, "rowmask"),   # a mask that depends on the query, several items per CTA
+    (64, 4, 256, 128, 48, "dropout"),   # dropout alone: one item per CTA
 ])
 def test_short_sequence_kernel_x_and_alpha_in_one_pass(eager_scores, dtype, d, H, Lq, Lkv, B, kind):
     """Eager scores for key sequences that fit one CTA's tensor memory: one kernel writes x and α
@@ -440,6 +444,14 @@ def test_short_sequence_kernel_x_and_alpha_in_one_pass(eager_scores, dtype, d, H
     elif kind == "causal":
         mask_np = O.make_causal_mask(qn)
         mask_arg = nb.make_causal_mask(q)
+    elif kind == "rowmask":
+        mask_np = rng.random((Lkv, Lq, 1, B)) > 0.3
+        mask_np[0] = True
+        mask_arg = nb.jl_from_numpy(mask_np, device=DEV)
+    elif kind == "dropout":
+        keep = P.keep_mask((Lkv, Lq, H, B), 0.25, 9, 2)
+        fdrop = nb.PhiloxDropout(0.25, seed=9, offset=2)
+        fdrop_o = lambda al: al * keep / np.float32(0.75)
     elif kind == "bias":
         bias_np = _round_to(0.5 * rng.standard_normal((Lkv, Lq, H, B)), dtype)
         bias_arg = _dev(bias_np, dtype)
@@ -460,7 +472,7 @@ def test_short_sequence_kernel_x_and_alpha_in_one_pass(eager_scores, dtype, d, H
     if mask_np is not None:
         keepm = np.broadcast_to(O._bcast_to_scores(mask_np), ao.shape)
         assert (an[~keepm] == 0).all(), "masked scores must be exactly 0"
-    if kind != "bias":
+    if kind not in ("bias", "dropout"):
         np.testing.assert_allclose(an.sum(0), 1.0, atol=1e-2)
 
 
