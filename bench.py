@@ -621,7 +621,11 @@ def run_ours(args, w):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": config_of(args, w, world),
-            "notes": {"l2": "inputs (q,k,v = %.0f MB per GPU) larger than the 126 MB L2" % (h2d_bytes / 1e6),
+            # every step reads and writes the same arrays: what one step touches must not fit in L2
+            "notes": {"l2": ("arrays one step touches (q, k, v, x%s = %.0f MB per GPU) %s the 126 MB L2"
+                             % (", bias / mask / scores" if algorithmic_bytes(w, esz) > h2d_bytes + d2h_bytes else "",
+                                algorithmic_bytes(w, esz) / 1e6,
+                                "larger than" if algorithmic_bytes(w, esz) > 126e6 else "SMALLER than")),
                       "kernel_path": "tcgen05",
                       "mask": "make_causal_mask(q) built once before the timed region and passed as mask= "
                               "(recognised as unmodified, never read)" if w.get("causal") else None},
