@@ -143,7 +143,8 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int n_total = (a.Lkv + kBN - 1) / kBN;                 // <= kMaxTiles (the host checked)
   // A mask that does not depend on the query (key padding): one warp turns the mask bytes of the next item into
   // bits while the current item is in its passes, instead of every thread fetching the same bytes for its own row.
-  const bool rowinv = MASK_ONLY && a.mask != nullptr && a.mask_s[1] == 0;
+  // (A call without a mask array that runs this variant counts as one with an all-true mask.)
+  const bool rowinv = MASK_ONLY && (a.mask == nullptr || a.mask_s[1] == 0);
   struct Work { int h, b, q0, n_live; };
   auto work_of = [&](int w) {
     Work k;
@@ -315,7 +316,9 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const unsigned char* mrow = a.mask + (long long)wk.h * a.mask_s[2] + (long long)wk.b * a.mask_s[3];
           const int jj0 = lane * 32;
           unsigned int bits = 0u;
-          if (a.mask_s[0] == 1 && (reinterpret_cast<unsigned long long>(mrow) & 15ull) == 0 && jj0 + 32 <= a.Lkv) {
+          if (a.mask == nullptr) {
+            bits = 0xffffffffu;
+          } else if (a.mask_s[0] == 1 && (reinterpret_cast<unsigned long long>(mrow) & 15ull) == 0 && jj0 + 32 <= a.Lkv) {
             const uint4* p = reinterpret_cast<const uint4*>(mrow + jj0);
             bits = mask_word_bits(__ldg(p), __ldg(p + 1));
           } else {
@@ -693,7 +696,8 @@ cudaError_t short_attention(const AttnArgs& a, int dtype, cudaStream_t st) {
 #define NB_SH(DD, BF)                                                           \
   do {                                                                          \
     switch (xm) {                                                               \
-      case 0: return launch_short<DD, BF, 0>(mq, mk, mv, ma, a, st);            \
+      /* d = 64 without a mask array: the mask variant with an all-true mask (its passes are the lighter code) */ \
+      case 0: return launch_short<DD, BF, (DD == 64) ? 1 : 0>(mq, mk, mv, ma, a, st); \
       case 1: return launch_short<DD, BF, 1>(mq, mk, mv, ma, a, st);            \
       case 2: return launch_short<DD, BF, 2>(mq, mk, mv, ma, a, st);            \
       case 3: return launch_short<DD, BF, 3>(mq, mk, mv, ma, a, st);            \
