@@ -19,8 +19,8 @@
 //                epilogue x = O / l / (1-p), each half writing half of the features
 //   warp 10    ships every filled staging box with one cp.async.bulk.tensor store into the (Lkv, Lq, H, B) array
 //   warp 11    a mask array that does not depend on the query: its bytes -> keep bits, one item ahead
-// With d = 64 shared memory has room for the next work item's operands: one CTA per SM walks over the items and
-// the loads of the next one run under the passes of the current one.
+// Without bias and dropout one CTA per SM walks over the work items, and the loads of the next item run under the
+// passes of the current one (the bias / dropout variants have no registers to spare for the walk).
 // O lives in columns the packing freed (d = 64: the upper half of tile 0) or behind the scores (d = 128).
 // Bound by the HBM write of alpha.
 #include <cuda.h>
@@ -51,18 +51,21 @@ struct ShCfg {
   static constexpr int kVOff = kKOff + kMaxTiles * kTileBytes;
   static constexpr int kStOff = kVOff + kMaxTiles * kTileBytes;   // 2 halves x 2 staging boxes
   static constexpr int kBarOff = kStOff + 4 * kShStageBytes;
-  // d = 64 leaves room for a CTA that walks over several work items and loads the next item's Q, K, V while the
-  // current one is in its passes; nothing of one item may then share memory with the operands of the next.
-  // d = 128 fills shared memory: one work item per CTA, and the two small arrays below lie over memory that is
-  // idle when they are in use.
-  static constexpr bool kPersistent = (D == 64);
-  // row maxima and sums of the two halves.  One item per CTA: over K, which is done with by the time they are
-  // written (every score product has completed).
-  static constexpr int kXOff = kPersistent ? kBarOff + 512 : kKOff;
-  // keep bits of a mask array, [chunk of 32 keys][query row].  One item per CTA: in the staging boxes, which
-  // pass 3 is the first to fill — every thread is through pass 1 (the last reader of the bits) by then.
-  static constexpr int kKeepOff = kPersistent ? kXOff + 2048 : kStOff;
-  static constexpr int kSmemBytes = (kPersistent ? kKeepOff + kMaxTiles * 4 * 128 * 4 : kBarOff + 512) + 1024;
+  // A CTA may walk over several work items and load the next item's Q, K, V while the current one is in its
+  // passes; nothing of one item may then share memory with the operands of the next.
+  // Row maxima and sums of the two halves, [2 halves][128 rows] each.  d = 128 fills shared memory but for 1.5 KB:
+  // there the sums take the place of the maxima (a barrier of the softmax threads lies between the last read of
+  // one and the first write of the other).
+  static constexpr int kXOff = kBarOff + 512;
+  static constexpr int kXSum = (D == 64) ? 256 : 0;              // where the sums start, in floats
+  static constexpr int kXBytes = (D == 64) ? 2048 : 1024;
+  // Keep bits of a mask array that depends on the query, [chunk of 32 keys][query row].  d = 64: an area of their
+  // own.  d = 128: in the staging boxes, which pass 3 is the first to fill (every thread is through pass 1, the
+  // last reader of the bits, by then) — such a call is launched with one work item per CTA, since the boxes of
+  // one item are still being read when the bits of the next would be written.
+  static constexpr bool kKeepOwn = (D == 64);
+  static constexpr int kKeepOff = kKeepOwn ? kXOff + kXBytes : kStOff;
+  static constexpr int kSmemBytes = kXOff + kXBytes + (kKeepOwn ? kMaxTiles * 4 * 128 * 4 : 0) + 1024;
   static constexpr int kTmemCols = 512;
   static constexpr int kOCol = (D == 64) ? 64 : 256;
 };
@@ -128,7 +131,7 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   constexpr bool MASK_ONLY = EXTRAS && !XBIAS;
   // The walk over several items costs registers; the bias and dropout variants have none to spare and take one
   // item per CTA.
-  constexpr bool LOOP = C::kPersistent && XM < 2;
+  constexpr bool LOOP = XM < 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   ShBarriers* bars = reinterpret_cast<ShBarriers*>(smem + C::kBarOff);
@@ -501,9 +504,10 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (ok && lane == 0) mbar_arrive(&bars->p_ready);
-      xstat[256 + part * 128 + r] = l;
+      if (C::kXSum == 0) softmax_threads_sync();        // every thread has read the maxima the sums overwrite
+      xstat[C::kXSum + part * 128 + r] = l;
       if (softmax_threads_sync_any(!ok || *abort_flag != 0)) break;
-      l = xstat[256 + r] + xstat[256 + 128 + r];
+      l = xstat[C::kXSum + r] + xstat[C::kXSum + 128 + r];
 
       // ---- pass 3: alpha' = P / l / (1-p), box by box
       if (ok) {
@@ -663,8 +667,9 @@ cudaError_t launch_short(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
   const int n_qtiles = (a.Lq + kBM - 1) / kBM;
   const long long n_work = (long long)n_qtiles * a.H * a.B;
   if (n_work > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  // d = 64 without bias and dropout: one CTA per SM walks over the work items; otherwise one item per CTA
-  const bool loop = ShCfg<D>::kPersistent && XM < 2;   // as LOOP in the kernel
+  // without bias and dropout one CTA per SM walks over the work items (XM < 2, as LOOP in the kernel), unless the
+  // keep bits of a query-dependent mask have no area of their own; otherwise one item per CTA
+  const bool loop = XM < 2 && (ShCfg<D>::kKeepOwn || a.mask == nullptr || a.mask_s[1] == 0);
   const long long blocks = loop ? (n_work < sm_count() ? n_work : sm_count()) : n_work;
   kern<<<(unsigned)blocks, kShThreads, ShCfg<D>::kSmemBytes, st>>>(mq, mk, mv, ma, a, n_qtiles, (int)n_work);
   count_launch();
@@ -696,8 +701,8 @@ cudaError_t short_attention(const AttnArgs& a, int dtype, cudaStream_t st) {
 #define NB_SH(DD, BF)                                                           \
   do {                                                                          \
     switch (xm) {                                                               \
-      /* d = 64 without a mask array: the mask variant with an all-true mask (its passes are the lighter code) */ \
-      case 0: return launch_short<DD, BF, (DD == 64) ? 1 : 0>(mq, mk, mv, ma, a, st); \
+      /* no mask array: the mask variant with an all-true mask (its passes are the lighter code) */ \
+      case 0: return launch_short<DD, BF, 1>(mq, mk, mv, ma, a, st);            \
       case 1: return launch_short<DD, BF, 1>(mq, mk, mv, ma, a, st);            \
       case 2: return launch_short<DD, BF, 2>(mq, mk, mv, ma, a, st);            \
       case 3: return launch_short<DD, BF, 3>(mq, mk, mv, ma, a, st);            \
