@@ -160,7 +160,14 @@ def _check(rc: int, where: str):
     raise _lib.NNlibB200Error(rc, where)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream of the current device as a raw handle (the short way when torch offers it: building
+    a Stream object costs several microseconds per call, which a small problem notices)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
