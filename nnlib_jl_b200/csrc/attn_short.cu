@@ -72,7 +72,7 @@ struct ShCfg {
 static_assert(ShCfg<64>::kSmemBytes <= 232448 && ShCfg<128>::kSmemBytes <= 232448, "shared memory budget");
 
 struct ShBarriers {
-  uint64_t qk_full, v_full, s_full[2], p_ready, o_full, tmem_free;
+  uint64_t qk_full, v_full, s_full[2], p_ready, o_full, p_free, tmem_free;
   uint64_t stage_full[2][2], stage_free[2][2];
   uint64_t bits_full[2], bits_free[2];   // keep bits of a row-invariant mask: two slots, used by alternate items
   uint32_t maskbits[2][16];              // [slot][chunk of 32 keys]
@@ -166,6 +166,7 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->p_ready, 8);
     mbar_init(&bars->o_full, 1);
+    mbar_init(&bars->p_free, 8);
     mbar_init(&bars->tmem_free, 8);
     for (int p = 0; p < 2; ++p) {
       mbar_init(&bars->bits_full[p], 1);
@@ -199,8 +200,8 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       bool ok = true;
       for (int it = 0, w = blockIdx.x; (LOOP ? w < n_work : it < 1) && ok; w += gridDim.x, ++it) {
         const Work wk = work_of(w);
-        // Q and K of the previous item have been read by its last score product
-        if (it > 0) ok = mbar_wait(&bars->s_full[1], (it - 1) & 1, abort_flag);
+        // Q and K of the previous item have been read by its last score product (tile 0's: see the issuer)
+        if (it > 0) ok = mbar_wait(&bars->s_full[0], (it - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->qk_full, (1 + wk.n_live) * C::kTileBytes);
         for (int c = 0; c < C::kChunks; ++c)
@@ -238,11 +239,13 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int n_live = work_of(w).n_live;
         const uint32_t ph = it & 1;
         ok = mbar_wait(&bars->qk_full, ph, abort_flag);
-        // every softmax warp has read the previous item's probabilities and O out of tensor memory
-        if (ok && it > 0) ok = mbar_wait(&bars->tmem_free, (it - 1) & 1, abort_flag);
+        // Order of the score tiles: every tile but the first as soon as each softmax warp has fetched the previous
+        // item's probabilities (pass 3), the first — O shares or neighbours its columns — once the warps have read
+        // O as well.  The second half's scores are complete first.
+        if (ok && it > 0) ok = mbar_wait(&bars->p_free, (it - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        for (int t = 0; t < C::kMaxTiles; ++t) {
+        auto scores = [&](int t) {
           if (t < n_live) {
             const uint32_t ka = smem_u32(smem + C::kKOff + t * C::kTileBytes);
 #pragma unroll
@@ -252,8 +255,15 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                       idesc_qk, kk > 0 ? 1u : 0u);
             }
           }
-          if ((t + 1) % TPP == 0) umma_commit(&bars->s_full[t / TPP]);   // the scores of one half of the warps
-        }
+        };
+        for (int t = TPP; t < C::kMaxTiles; ++t) scores(t);
+        umma_commit(&bars->s_full[1]);                  // the scores of the second half of the warps
+        for (int t = 1; t < TPP; ++t) scores(t);
+        if (it > 0) ok = mbar_wait(&bars->tmem_free, (it - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        scores(0);
+        umma_commit(&bars->s_full[0]);                  // the scores of the first half: the last product of Q and K
         // every row's probabilities are packed (and every score column has been read): O may be written
         ok = mbar_wait(&bars->p_ready, ph, abort_flag);
         if (ok) ok = mbar_wait(&bars->v_full, ph, abort_flag);
@@ -442,7 +452,6 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->bits_free[it & 1]);
       }
-      if (part == 0) mbar_wait_warp(&bars->s_full[1], ph, abort_flag);   // the other half's products still read K until then
       xstat[part * 128 + r] = m * cs;                   // in scaled base-2 units from here on (scale > 0)
       softmax_threads_sync();
       m = fmaxf(xstat[r], xstat[128 + r]);              // fmaxf drops a NaN: a NaN logit shows up in the sum instead
@@ -583,6 +592,11 @@ attn_short_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (k + 2 < n_mine) fetch(n_first + k + 2, pk0);
           emit(k + 1, pk1);
         }
+
+        // this warp has fetched all its probabilities: the issuer may overwrite their columns with the next scores
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_free);
 
         // ---- epilogue: x = O / l / (1-p); each half of the warps handles half of the features.  A thread owns a
         // row, and rows lie far apart in x: the rows go through shared memory (V's, which the last P V product has
