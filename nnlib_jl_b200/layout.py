@@ -22,8 +22,11 @@ def _rev(n: int):
 def jl_empty(shape: Sequence[int], dtype=torch.float32, device="cpu") -> torch.Tensor:
     """Uninitialised column-major tensor of the given (Julia) shape."""
     shape = tuple(int(s) for s in shape)
-    t = torch.empty(shape[::-1], dtype=dtype, device=device)
-    return t.permute(_rev(len(shape))) if shape else t
+    strides, acc = [], 1
+    for n in shape:                      # first dimension fastest (an empty dimension counts as 1, as torch does)
+        strides.append(acc)
+        acc *= max(n, 1)
+    return torch.empty_strided(shape, strides, dtype=dtype, device=device)
 
 
 def jl_zeros(shape, dtype=torch.float32, device="cpu") -> torch.Tensor:
