@@ -264,7 +264,7 @@ class _Problem:
         self.p = p
 
     def alloc_lse(self):
-        self.lse = torch.empty((self.B, self.H, self.Lq), dtype=torch.float32, device=self.dev).permute(2, 1, 0)
+        self.lse = jl_empty((self.Lq, self.H, self.B), torch.float32, self.dev)
         self.p.lse = self.lse.data_ptr()
         return self.lse
 
