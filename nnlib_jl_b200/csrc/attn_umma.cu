@@ -91,7 +91,7 @@ template <int D, bool BF16, int XM, bool STATS, bool BSM>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
-                     const AttnArgs a, const int n_qblocks) {
+                     const AttnArgs a, const int n_qblocks, const int tail_units) {
   using C = Cfg<D>;
   constexpr bool EXTRAS = (XM % 3) != 0;
   constexpr bool XBIAS = (XM % 3) == 2;   // bias code compiled in
@@ -104,9 +104,23 @@ attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // block -> (unit, query block); within a unit the longest causal rows come first
-  const int unit = blockIdx.x / n_qblocks;
-  const int qb = n_qblocks - 1 - (blockIdx.x % n_qblocks);
+  // block -> (unit, query block).  Unit by unit, so that the CTAs running at one time share K and V in L2; within
+  // a unit the longest causal rows first.  The last `tail_units` units are dealt out together, all their longest
+  // blocks first: taken unit by unit, the long blocks of the last unit would start when the others are nearly
+  // done (3 - 4 % of a launch of 256 units, more of a shorter one).
+  int unit, qb;
+  {
+    const int n_units = gridDim.x / n_qblocks;
+    const int head = (n_units - tail_units) * n_qblocks;
+    if ((int)blockIdx.x < head) {
+      unit = blockIdx.x / n_qblocks;
+      qb = n_qblocks - 1 - (blockIdx.x % n_qblocks);
+    } else {
+      const int j = blockIdx.x - head;
+      unit = (n_units - tail_units) + j % tail_units;
+      qb = n_qblocks - 1 - j / tail_units;
+    }
+  }
   const int h = unit % a.H, b = unit / a.H;
   const int q0 = qb * (kQT * kBM);
 
@@ -1055,6 +1069,14 @@ attn_apply_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
 }
 
 // ------------------------------------------------------------------ host side
+int fwd_sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      n < 1)
+    n = 148;
+  return n;
+}
+
 template <int D, bool BF16, int XM, bool STATS, bool BSM>
 cudaError_t launch_fwd_impl(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mb,
                             const AttnArgs& a, cudaStream_t st) {
@@ -1065,7 +1087,11 @@ cudaError_t launch_fwd_impl(const CUtensorMap& mq, const CUtensorMap& mk, const 
   const int n_qblocks = (a.Lq + kQT * kBM - 1) / (kQT * kBM);
   const long long blocks = (long long)n_qblocks * a.H * a.B;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kThreads, smem, st>>>(mq, mk, mv, mb, a, n_qblocks);
+  // causal blocks differ in length: the units of the last two waves are dealt out longest blocks first
+  const long long n_units = (long long)a.H * a.B;
+  long long tail_units = a.causal ? 2 * ((fwd_sm_count() + n_qblocks - 1) / n_qblocks) : 0;
+  if (tail_units > n_units) tail_units = n_units;
+  kern<<<(unsigned)blocks, kThreads, smem, st>>>(mq, mk, mv, mb, a, n_qblocks, (int)tail_units);
   count_launch();
   return cudaGetLastError();
 }
