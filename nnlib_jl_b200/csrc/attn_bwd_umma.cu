@@ -154,7 +154,7 @@ template <int D, bool BF16, bool DKV, int FEAT>
 __global__ void __launch_bounds__(kBwThreads, 1)
 attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_constant__ CUtensorMap tm_fb,
                      const __grid_constant__ CUtensorMap tm_ra, const __grid_constant__ CUtensorMap tm_rb,
-                     const AttnArgs a, const BwdArgs g, const int n_tiles) {
+                     const AttnArgs a, const BwdArgs g, const int n_tiles, const int tail_units) {
   using C = BwCfg<D, DKV>;
   constexpr bool MASKED = (FEAT & 1) != 0, DROP = (FEAT & 2) != 0, BIAS = (FEAT & 4) != 0;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -170,9 +170,23 @@ attn_bwd_umma_kernel(const __grid_constant__ CUtensorMap tm_fa, const __grid_con
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // block -> (unit, resident tile); the tiles with the longest causal walk come first
-  const int unit = blockIdx.x / n_tiles;
-  const int tix = DKV ? (blockIdx.x % n_tiles) : (n_tiles - 1 - (blockIdx.x % n_tiles));
+  // block -> (unit, resident tile).  Unit by unit (the CTAs of one time share the unit's arrays in L2), the tiles
+  // with the longest causal walk first; the last `tail_units` units are dealt out together, all their longest
+  // walks first, so that the launch does not end on the long walks of the last unit.
+  int unit, rank;                       // rank: 0 = the longest walk of its unit
+  {
+    const int n_units = gridDim.x / n_tiles;
+    const int head = (n_units - tail_units) * n_tiles;
+    if ((int)blockIdx.x < head) {
+      unit = blockIdx.x / n_tiles;
+      rank = blockIdx.x % n_tiles;
+    } else {
+      const int j = blockIdx.x - head;
+      unit = (n_units - tail_units) + j % tail_units;
+      rank = j / tail_units;
+    }
+  }
+  const int tix = DKV ? rank : (n_tiles - 1 - rank);
   const int h = unit % a.H, b = unit / a.H;
   const int t0 = tix * 128;             // first row of the resident tile (query for dq, key for dk/dv)
 
@@ -789,7 +803,20 @@ cudaError_t launch_bwd_umma(const CUtensorMap& fa, const CUtensorMap& fb, const 
   const int n_tiles = ((DKV ? a.Lkv : a.Lq) + 127) / 128;
   const long long blocks = (long long)n_tiles * a.H * a.B;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kBwThreads, smem, st>>>(fa, fb, ra, rb, a, g, n_tiles);
+  // causal walks differ in length: the units of the last two waves are dealt out longest walks first
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      sms < 1)
+    sms = 148;
+  const long long n_units = (long long)a.H * a.B;
+  long long tail_units = a.causal ? 2 * ((sms + n_tiles - 1) / n_tiles) : 0;
+  if (tail_units > n_units) tail_units = n_units;
+  // ... as long as the arrays of those units (q, dx, k, v of each) stay well inside L2 together: with very long
+  // sequences the interleaved units evict each other and the launch gets slower instead (L = 32768: + 0.5 %)
+  const long long unit_bytes = 2ll * ((long long)a.Lq + a.Lkv) * a.d * 2;
+  if (tail_units * unit_bytes > (48ll << 20)) tail_units = (48ll << 20) / unit_bytes;
+  if (tail_units < 2) tail_units = 0;
+  kern<<<(unsigned)blocks, kBwThreads, smem, st>>>(fa, fb, ra, rb, a, g, n_tiles, (int)tail_units);
   count_launch();
   return cudaGetLastError();
 }
