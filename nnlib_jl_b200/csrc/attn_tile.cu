@@ -155,7 +155,8 @@ template <> struct Fmt<float> { static constexpr uint32_t v = 2; };
 template <typename T, int DQ, int DV, int MODE, bool SIDE>
 __global__ void __launch_bounds__(kTThreads, TCfg<T, DQ, DV>::kCtasPerSm)
 attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qtiles, const int n_splits) {
+                 const __grid_constant__ CUtensorMap tm_v, const AttnArgs a, const int n_qtiles, const int n_splits,
+                 const int tail_units) {
   using C = TCfg<T, DQ, DV>;
   constexpr bool TF32 = (sizeof(T) == 4);
   constexpr bool BF16 = std::is_same<T, __nv_bfloat16>::value;
@@ -166,11 +167,25 @@ attn_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // block -> (unit, query tile); within a unit the longest causal rows come first
-  // (TM_SPLIT: block -> (unit, split); there is one query tile)
-  const int unit = (MODE == TM_SPLIT) ? blockIdx.x / n_splits : blockIdx.x / n_qtiles;
-  const int split = (MODE == TM_SPLIT) ? blockIdx.x % n_splits : 0;
-  const int qt = (MODE == TM_SPLIT) ? 0 : n_qtiles - 1 - (blockIdx.x % n_qtiles);
+  // block -> (unit, query tile); within a unit the longest causal rows come first, and the last `tail_units` units
+  // are dealt out together, all their longest tiles first (the launch then does not end on the long tiles of the
+  // last unit).  (TM_SPLIT: block -> (unit, split); there is one query tile)
+  int unit, split = 0, qt = 0;
+  if (MODE == TM_SPLIT) {
+    unit = blockIdx.x / n_splits;
+    split = blockIdx.x % n_splits;
+  } else {
+    const int n_units = gridDim.x / n_qtiles;
+    const int head = (n_units - tail_units) * n_qtiles;
+    if ((int)blockIdx.x < head) {
+      unit = blockIdx.x / n_qtiles;
+      qt = n_qtiles - 1 - (blockIdx.x % n_qtiles);
+    } else {
+      const int j = blockIdx.x - head;
+      unit = (n_units - tail_units) + j % tail_units;
+      qt = n_qtiles - 1 - j / tail_units;
+    }
+  }
   const int h = unit % a.H, b = unit / a.H;
   const int q0 = qt * kTBM;
   const int n_total = (a.Lkv + kTBN - 1) / kTBN;
@@ -620,7 +635,18 @@ cudaError_t launch_tile_side(const CUtensorMap& mq, const CUtensorMap& mk, const
   const int n_qtiles = (a.Lq + kTBM - 1) / kTBM;
   const long long blocks = (long long)((MODE == TM_SPLIT) ? n_splits : n_qtiles) * a.H * a.B;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kTThreads, C::kSmemBytes, st>>>(mq, mk, mv, a, n_qtiles, n_splits);
+  // causal tiles differ in length: the units of the last two waves are dealt out longest tiles first
+  long long tail_units = 0;
+  if (MODE != TM_SPLIT && a.causal) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+      sms = 148;
+    const long long resident = (long long)sms * C::kCtasPerSm;
+    tail_units = 2 * ((resident + n_qtiles - 1) / n_qtiles);
+    if (tail_units > (long long)a.H * a.B) tail_units = (long long)a.H * a.B;
+  }
+  kern<<<(unsigned)blocks, kTThreads, C::kSmemBytes, st>>>(mq, mk, mv, a, n_qtiles, n_splits, (int)tail_units);
   count_launch();
   if (MODE == TM_SPLIT) {
     e = cudaGetLastError();
