@@ -684,7 +684,14 @@ cudaError_t launch_short(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
   // without bias and dropout one CTA per SM walks over the work items (XM < 2, as LOOP in the kernel), unless the
   // keep bits of a query-dependent mask have no area of their own; otherwise one item per CTA
   const bool loop = XM < 2 && (ShCfg<D>::kKeepOwn || a.mask == nullptr || a.mask_s[1] == 0);
-  const long long blocks = loop ? (n_work < sm_count() ? n_work : sm_count()) : n_work;
+  long long blocks = loop ? (n_work < sm_count() ? n_work : sm_count()) : n_work;
+  // Causal tiles of a unit differ in length, and a CTA takes items blockIdx.x, + gridDim.x, ...: with a grid that
+  // shares a factor with the tiles per unit it would meet the same tiles (always the long ones, or always the
+  // short ones) in every unit.  A grid coprime to the tiles per unit walks through all of them in turn.
+  if (loop && a.causal && blocks < n_work && n_qtiles > 1) {
+    auto gcd = [](long long x, long long y) { while (y) { const long long t = x % y; x = y; y = t; } return x; };
+    while (blocks > 1 && gcd(blocks, n_qtiles) != 1) --blocks;
+  }
   kern<<<(unsigned)blocks, kShThreads, ShCfg<D>::kSmemBytes, st>>>(mq, mk, mv, ma, a, n_qtiles, (int)n_work);
   count_launch();
   return cudaGetLastError();
